@@ -1,0 +1,373 @@
+#!/usr/bin/env python
+"""Benchmark of the GGUF block-quantized matmul hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Prints ONE JSON line.  A step is one pass over R distinct copies of the workload's weight (R chosen
+so R * weight bytes >= 2 x L2, so every launch streams its weight from HBM): R calls of the
+quantized matmul, each = activation quantizer + matvec kernel.
+
+  value      whole-job algorithmic GB/s with inputs resident in HBM (CUDA-graph replay of a step,
+             CUDA events on the launching stream, max over ranks)
+  roofline   the matvec kernel alone: algorithmic bytes per launch / its average event-timed
+             duration, against the measured HBM copy peak
+  e2e        the same metric through the host-buffer entry (QLinear::forward on host tensors):
+             pinned H2D of x and D2H of y inside the timed region, every call synchronized
+  cpu_baseline / --impl reference
+             xn's CPU path (AVX2-order restatement of the Rust kernels, all host threads)
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from xn_b200 import synth  # noqa: E402
+from xn_b200.dtypes import GgmlDType as D  # noqa: E402
+
+# name -> (dtype, n, k, m)
+WORKLOADS = {
+    "C1_q4_0_4096x4096_m1": (D.Q4_0, 4096, 4096, 1),
+    "C2_q8_0_11008x4096_m1": (D.Q8_0, 11008, 4096, 1),
+    "C2_q8_0_11008x4096_m16": (D.Q8_0, 11008, 4096, 16),
+    "C3_q4k_14336x4096_m1": (D.Q4K, 14336, 4096, 1),
+    "C3_q4k_14336x4096_m4": (D.Q4K, 14336, 4096, 4),
+    "C3_q4k_14336x4096_m16": (D.Q4K, 14336, 4096, 16),
+    "C4_q6k_128256x4096_m1": (D.Q6K, 128256, 4096, 1),
+}
+DEFAULT_WORKLOAD = "C3_q4k_14336x4096_m1"  # the matvec the metric's 75%-of-HBM target is quoted on
+METRIC = "quant matvec HBM GB/s"
+UNIT = "GB/s"
+
+
+def algorithmic_bytes(dt: D, n: int, k: int, m: int) -> int:
+    """GGUF weight bytes + f32 activations in + f32 outputs out, whatever the device layout."""
+    return n * dt.row_bytes(k) + 4 * m * k + 4 * m * n
+
+
+def measured_peaks() -> tuple[float, str]:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int, uuid: str | None = None):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            try:
+                self._h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if uuid and not uuid.startswith("GPU-") else uuid)
+            except Exception:
+                self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+            self._reasons_fn = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                getattr(pynvml, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        except Exception:
+            self._nv = None
+
+    def _loop(self):
+        nv = self._nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+                 "hw_power_brake": 0x80}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                r = self._reasons_fn(self._h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            self._stop.wait(0.02)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thr = threading.Thread(target=self._loop, daemon=True)
+            self._thr.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thr:
+            self._thr.join()
+
+    def summary(self) -> dict:
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def cpu_path(dt: D, n: int, k: int, m: int, weights: list, x: np.ndarray, calls: int, threads: int) -> float:
+    """Seconds per call of xn's CPU path (quantize_lhs + AVX2 dots, all threads), rotating weights."""
+    from oracle import oracle as O
+    O.build()
+    if not O.have_avx2():
+        raise RuntimeError("host CPU lacks AVX2/FMA/F16C: the reference's x86 path cannot be restated here")
+    O.matmul(int(dt), x, weights[0], n, threads=threads, order="avx2")  # warm the pool
+    t0 = time.perf_counter()
+    for i in range(calls):
+        O.matmul(int(dt), x, weights[i % len(weights)], n, threads=threads, order="avx2")
+    return (time.perf_counter() - t0) / calls
+
+
+def run_reference(args, name, dt, n, k, m):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    O.build()
+    threads = O.hw_threads()
+    ncopies = max(2, min(8, int(np.ceil(512e6 / (n * dt.row_bytes(k))))))  # rotate > L3
+    weights = [synth.make_weight(dt, n, k, seed=0, tensor_id=i) for i in range(ncopies)]
+    x = synth.make_activation(m, k, seed=0)
+    per_call0 = cpu_path(dt, n, k, m, weights, x, 4, threads)
+    # bounded sample: the whole run (warm-up included) stays near one minute of CPU time
+    calls_per_step = max(1, min(4 * ncopies, int(60.0 / ((args.steps + args.warmup) * max(per_call0, 1e-6)))))
+    for _ in range(args.warmup):
+        cpu_path(dt, n, k, m, weights, x, calls_per_step, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_path(dt, n, k, m, weights, x, calls_per_step, threads)
+    dt_s = time.perf_counter() - t0
+    per_call = dt_s / (args.steps * calls_per_step)
+    gbs = algorithmic_bytes(dt, n, k, m) / per_call / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt_s / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "i8 block dots, f32 accumulate", "data": "synthetic",
+        "config": {"workload": name, "ggml_dtype": dt.name, "n": n, "k": k, "m": m,
+                   "cpu_calls_per_step": calls_per_step, "weight_copies": ncopies},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"{args.steps} steps x {calls_per_step} matmul calls of the full workload, "
+                                   f"{ncopies} rotating weight copies; AVX2-order C restatement of xn's Rust CPU path "
+                                   "(the Rust original cannot be built offline)"},
+        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, name, dt, n, k, m):
+    import ctypes
+
+    import torch
+    import torch.distributed as dist
+
+    from xn_b200 import _lib, quantized as Q
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    Q.init(dev)
+    L = _lib.lib()
+
+    props = torch.cuda.get_device_properties(dev)
+    l2 = int(getattr(props, "L2_cache_size", 126 * 1024 * 1024))
+    w_bytes_full = n * dt.row_bytes(k)
+    n_local = n // world
+    if n % world:
+        raise SystemExit(f"n={n} does not divide over {world} GPUs")
+    w_bytes_local = n_local * dt.row_bytes(k)
+    ncopies = int(max(2, np.ceil(2 * l2 / w_bytes_local)))
+    ncopies = min(ncopies, 64)
+
+    # weights: rank r holds rows [r*n/G, (r+1)*n/G) of every copy (column-sharded along N)
+    weights = []
+    for i in range(ncopies):
+        rows = (rank * n_local, (rank + 1) * n_local)
+        blocks = synth.make_weight(dt, n, k, seed=0, tensor_id=i, rows=rows)
+        weights.append(Q.QCudaTensor.from_rows(dt, blocks, n, k, rows[0], n_local, dev))
+    x_np = synth.make_activation(m, k, seed=0)
+    x = torch.from_numpy(x_np).to(dev)
+    y_local = [torch.empty((m, n_local), dtype=torch.float32, device=dev) for _ in range(ncopies)]
+    y_full = [torch.empty((world, m, n_local), dtype=torch.float32, device=dev) for _ in range(ncopies)] if world > 1 else None
+    for w in weights:
+        w.workspace(m)
+
+    def step():
+        for i, w in enumerate(weights):
+            w.matmul_t(x, out=y_local[i])
+            if world > 1:
+                dist.all_gather_into_tensor(y_full[i], y_local[i])
+
+    def sync_all():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
+    launches_before = L.xnq_launch_count()
+    step()
+    launches_per_step = L.xnq_launch_count() - launches_before
+    for _ in range(max(args.warmup, 3) - 1):
+        step()
+    sync_all()
+
+    # one step as a CUDA graph: the decode loop of the reference is graph-captured too
+    graph = None
+    if world == 1:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream(dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side):
+                    step()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            graph.replay()
+            torch.cuda.synchronize(dev)
+        except Exception as e:  # a failed capture must not take the benchmark down
+            sys.stderr.write(f"[bench] CUDA graph capture failed ({e}); timing plain launches\n")
+            graph = None
+    run_step = graph.replay if graph is not None else step
+
+    sampler = ClockSampler(local, str(getattr(props, "uuid", "")) or None)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with sampler:
+        sync_all()
+        ev0.record()
+        for _ in range(args.steps):
+            run_step()
+        ev1.record()
+        sync_all()
+        elapsed_ms = ev0.elapsed_time(ev1)
+        # keep the load on while the sampler collects enough clock samples for a median
+        t_end = time.perf_counter() + 0.6
+        while len(sampler.samples) < 8 and time.perf_counter() < t_end:
+            for _ in range(50):
+                run_step()
+            torch.cuda.synchronize(dev)
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    ms_per_step = elapsed_ms / args.steps
+    step_bytes = ncopies * algorithmic_bytes(dt, n, k, m)  # whole job, all ranks
+    value = step_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- roofline: the matvec kernel alone, per-launch event pairs (separate pass, plain launches)
+    peak, peak_kind = measured_peaks()
+    prof_steps = max(1, min(args.steps, 64))
+    chunk_calls = 0
+    _lib.check(L.xnq_profile_begin(prof_steps * ncopies + 8))
+    for _ in range(prof_steps):
+        if chunk_calls == 0:
+            torch.cuda._sleep(40_000_000)  # let the host run ahead so no event waits for its kernel's enqueue
+        step()
+        chunk_calls = (chunk_calls + ncopies) % 256
+    tot = ctypes.c_double()
+    cnt = ctypes.c_int()
+    _lib.check(L.xnq_profile_end(ctypes.byref(tot), ctypes.byref(cnt)))
+    kern_ms = tot.value / max(cnt.value, 1)
+    kern_bytes = algorithmic_bytes(dt, n_local, k, m)
+    achieved = kern_bytes / (kern_ms * 1e-3) / 1e9 if kern_ms > 0 else None
+
+    # ---- e2e: host buffers through the QLinear::forward-on-host entry, every call synchronized
+    x_pin = torch.empty((m, k), dtype=torch.float32, pin_memory=True)
+    x_pin.copy_(torch.from_numpy(x_np))
+    x_host = x_pin.numpy()
+    e2e_steps = max(1, min(args.steps, 50))
+    for w in weights[:2]:
+        w.forward_host(x_host)
+    sync_all()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        for w in weights:
+            w.forward_host(x_host)
+    torch.cuda.synchronize(dev)
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_value = e2e_steps * step_bytes / e2e_s / 1e9
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- CPU baseline: bounded sample of the same workload on this box's host cores
+    cpu = None
+    try:
+        from oracle import oracle as O
+        threads = O.hw_threads()
+        ncpu = max(2, min(4, int(np.ceil(300e6 / w_bytes_full))))
+        cw = [synth.make_weight(dt, n, k, seed=0, tensor_id=i) for i in range(ncpu)]
+        per0 = cpu_path(dt, n, k, m, cw, x_np, 2, threads)
+        calls = int(max(4, min(400, 3.0 / max(per0, 1e-6))))
+        per = cpu_path(dt, n, k, m, cw, x_np, calls, threads)
+        cpu = {"value": algorithmic_bytes(dt, n, k, m) / per / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
+               "sample": f"{calls} matmul calls of the full workload ({per * 1e3:.3f} ms each), {ncpu} rotating weight copies; "
+                         "AVX2-order C restatement of xn's Rust CPU path"}
+    except Exception as e:
+        cpu = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": f"unavailable: {e}"}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "i8 block dots (dp4a), f32 accumulate", "data": "synthetic",
+        "config": {"workload": name, "ggml_dtype": dt.name, "n": n, "k": k, "m": m, "weight_copies_per_step": ncopies,
+                   "cache": f"cold: {ncopies} distinct weights per step = {ncopies * w_bytes_local / 1e6:.0f} MB per GPU, "
+                            f"L2 is {l2 / 1e6:.0f} MB",
+                   "parallelism": f"N-sharded x{world}" + (" + NCCL all-gather" if world > 1 else ""),
+                   "launch": "cuda graph replay" if graph is not None else "plain launches"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": (achieved / peak) if achieved else None, "traffic": None,
+                     "kernel": "matvec", "launch_us": kern_ms * 1e3, "launches_timed": cnt.value,
+                     "peak_kind": f"of {peak_kind}", "bytes_per_launch": kern_bytes,
+                     "timing": "CUDA event pair around each matvec launch, separate pass with plain launches"},
+        "cpu_baseline": cpu,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": ncopies * m * k * 4,
+                "d2h_bytes_per_step": ncopies * m * n_local * 4, "steps": e2e_steps,
+                "note": "QLinear::forward on pinned host tensors; one synchronize per call"},
+        "gpu_launches": int(launches_per_step * args.steps),
+        "clocks": sampler.summary(),
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    args = ap.parse_args()
+    dt, n, k, m = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, args.workload, dt, n, k, m)
+    else:
+        run_ours(args, args.workload, dt, n, k, m)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,144 @@
+/*
+ * xnq: B200-native (sm_100a) GGUF block-quantized matmul, C ABI.
+ *
+ * This is the boundary an xn-core build binds over FFI (the way xn-flash-attn binds `run_mha`,
+ * xn-flash-attn/src/ffi.rs:3-57) to put Q4_0 / Q8_0 / Q4_K / Q6_K linears on the GPU behind its
+ * existing `BackendQ` / `ModuleT` operator API (xn-core/src/lib.rs:123-156). Plain pointers and
+ * sizes only; no C++ or torch types. Every function returns XNQ_OK (0) or a negative xnq_status
+ * and never throws or aborts; xnq_last_error() gives the message for the calling thread.
+ * All shape / size / alignment validation happens before anything is enqueued.
+ *
+ * Streams: `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream). Compute
+ * entries only enqueue on it and return; they neither allocate nor synchronize, so they may be
+ * recorded into a CUDA graph once xnq_init() has run for the device.
+ *
+ * There is no CPU fallback anywhere behind this header.
+ */
+#ifndef XNQ_H
+#define XNQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define XNQ_VERSION 1
+
+typedef enum xnq_status {
+  XNQ_OK = 0,
+  XNQ_ERR_NULL = -1,        /* a required pointer is NULL */
+  XNQ_ERR_DTYPE = -2,       /* unsupported GGML / activation dtype */
+  XNQ_ERR_SHAPE = -3,       /* k not a multiple of the block, negative sizes, shard mismatch */
+  XNQ_ERR_ALIGN = -4,       /* pointer or leading dimension not aligned as documented */
+  XNQ_ERR_SIZE = -5,        /* byte count / workspace too small, or over a documented maximum */
+  XNQ_ERR_CUDA = -6,        /* a CUDA runtime call failed; message carries cudaGetErrorString */
+  XNQ_ERR_COMM = -7,        /* multi-GPU exchange failed or timed out */
+  XNQ_ERR_UNSUPPORTED = -8, /* valid request this build cannot serve (e.g. device is not sm_100) */
+} xnq_status;
+
+/* dtype codes are the GGML ids (GgmlDType::to_u32, xn-core/src/quantized/mod.rs:119-137) */
+enum {
+  XNQ_F32 = 0,
+  XNQ_F16 = 1,
+  XNQ_Q4_0 = 2,
+  XNQ_Q8_0 = 8,
+  XNQ_Q4K = 12,
+  XNQ_Q6K = 14,
+  XNQ_Q8K = 15,
+  XNQ_BF16 = 30,
+};
+
+/* An immutable quantized [n, k] weight (or an N-shard of one) resident in device memory.
+ * Replaces Q8Tensor (xn-core/src/cuda_backend/q8.rs:26-33) and the missing QStorage::Cuda variant
+ * (xn-core/src/quantized/mod.rs:32-34). Safe to use from several host threads at once. */
+typedef struct xnq_weight xnq_weight;
+
+/* Message of the last failure on the calling thread ("" if none). Replaces the xn::Error text a
+ * Rust caller builds with bail! (xn-core/src/error.rs:153-164). */
+const char *xnq_last_error(void);
+int xnq_version(void);
+
+/* Loads every kernel of the library on `device`, raises their shared-memory limits and checks the
+ * device is compute capability 10.x. Call once per device before the first stream capture.
+ * Stands in for the lazy PTX module load in Device::get_func (cuda_backend/mod.rs:311-403). */
+int xnq_init(int device);
+
+/* bytes per block / elements per block of a GGML dtype (GgmlDType::type_size / block_size,
+ * quantized/mod.rs:160-195); -1 for a dtype this library does not handle */
+int xnq_type_size(int ggml_dtype);
+int xnq_block_size(int ggml_dtype);
+
+/* Upload. `blocks` is the canonical GGUF byte image of the FULL [n, k] tensor in host memory
+ * (what QTensor::data() returns, quantized/mod.rs:330-332), nbytes = n * (k / block) * type_size.
+ * With shard_count G > 1 only rows [r*n/G, (r+1)*n/G) are uploaded (n must divide by G).
+ * The device layout may differ from GGUF (the reference's own Q8_0 upload re-lays out too,
+ * q8.rs:9-11,78-91); xnq_weight_canonical_bytes gives the canonical bytes back exactly.
+ * Synchronizes `stream` before returning. Replaces Q8Tensor::from_q8_0 (q8.rs:60-85). */
+int xnq_weight_upload(int ggml_dtype, const void *blocks, size_t nbytes, int64_t n, int64_t k,
+                      int shard_rank, int shard_count, void *stream, xnq_weight **out);
+/* Same, but `blocks` holds only rows [row0, row0 + n_rows) of an [n_total, k] tensor. */
+int xnq_weight_upload_rows(int ggml_dtype, const void *blocks, size_t nbytes, int64_t n_total,
+                           int64_t k, int64_t row0, int64_t n_rows, void *stream, xnq_weight **out);
+/* Replaces Drop of Q8Tensor's CudaSlices. NULL is accepted. */
+int xnq_weight_free(xnq_weight *w);
+/* Any out pointer may be NULL. n_local / row0 describe the shard held (QTensor::shape / dtype,
+ * quantized/mod.rs:305-315). */
+int xnq_weight_info(const xnq_weight *w, int *ggml_dtype, int64_t *n_total, int64_t *n_local,
+                    int64_t *row0, int64_t *k, size_t *device_bytes);
+
+/* Dense [n_local, k] row-major copy of the weight in out_dtype (XNQ_F32 / XNQ_F16 / XNQ_BF16);
+ * f32 output is bit-identical to GgmlType::to_float (k_quants.rs:213-233,618-634,1475-1503,
+ * 1874-1904). Replaces Q8Tensor::dequantize (q8.rs:94-113). dst is device memory. */
+int xnq_weight_dequantize(const xnq_weight *w, int out_dtype, void *dst, void *stream);
+/* Canonical GGUF bytes of the held rows into HOST memory (QTensor::data contract,
+ * quantized/mod.rs:206-214). Synchronizes `stream`. */
+int xnq_weight_canonical_bytes(const xnq_weight *w, void *host_dst, size_t nbytes, void *stream);
+
+/* Quantize activations x [m, k] (row stride ldx elements, x_dtype F32/F16/BF16, device memory) to
+ * canonical activation blocks in device memory: act_dtype XNQ_Q8_0 gives m*k/32 BlockQ8_0 (34 B),
+ * XNQ_Q8K gives m*k/256 BlockQ8K (292 B, bsums included). Byte-identical to
+ * BlockQ8_0::from_float / BlockQ8K::from_float (k_quants.rs:636-661, 1942-1979), which is what
+ * quantize_lhs runs per row (k_quants.rs:2015-2026). */
+int xnq_quantize_act(int act_dtype, const void *x, int x_dtype, int64_t m, int64_t k, int64_t ldx,
+                     void *dst_blocks, void *stream);
+
+/* Scratch bytes xnq_matmul_t needs for up to max_m activation rows against this weight. */
+size_t xnq_matmul_workspace_bytes(const xnq_weight *w, int64_t max_m);
+
+/* y[m, n_local] = x[m, k] . W^T, the quantized matmul of k_quants::matmul (k_quants.rs:1997-2011)
+ * = QTensor::matmul_t (quantized/mod.rs:334-339) = Q8Tensor::matmul_t (q8.rs:116-157):
+ * activations are quantized to the weight format's VecDotType exactly as the CPU path does, dots
+ * use exact integer block sums and f32 accumulation (m <= 16), or tensor-core MMA on the
+ * dequantized operands (m > 16).
+ *   x, y: device memory, x_dtype / y_dtype in {F32, F16, BF16}; ldx, ldy in elements;
+ *   x rows 16-byte aligned; workspace 256-byte aligned, ws_bytes >= xnq_matmul_workspace_bytes.
+ * Enqueues on `stream` only; allocates nothing. */
+int xnq_matmul_t(const xnq_weight *w, const void *x, int x_dtype, int64_t m, int64_t ldx, void *y,
+                 int y_dtype, int64_t ldy, void *workspace, size_t ws_bytes, void *stream);
+
+/* QLinear::forward on HOST tensors (quantized/mod.rs:352-384): copies x_host [m, k] f32 to the
+ * device, runs xnq_matmul_t, adds bias_host[n_local] if non-NULL, copies y back to y_host
+ * [m, n_local] and synchronizes. Device staging buffers are owned by the weight handle and grow on
+ * demand (first call at a given m allocates). Not for use from several threads on one handle. */
+int xnq_linear_forward_host(xnq_weight *w, const float *x_host, int64_t m, const float *bias_host,
+                            float *y_host, void *stream);
+
+/* ---- measurement hooks (no counterpart in the reference, which times with CudaEvent::elapsed_ms
+ * around whole operators, cuda_backend/mod.rs:76-100) ------------------------------------------ */
+
+/* Kernels this library has launched in this process so far (all threads, all devices). */
+uint64_t xnq_launch_count(void);
+/* Between xnq_profile_begin and xnq_profile_end every xnq_matmul_t call on the calling thread records
+ * a CUDA event pair around its dominant kernel (the matvec or prefill kernel, not the activation
+ * quantizer). xnq_profile_end synchronizes those events and returns the summed kernel time and the
+ * number of timed launches. At most max_launches pairs are kept; later launches are not timed.
+ * Do not use while the stream is being captured into a graph. */
+int xnq_profile_begin(int max_launches);
+int xnq_profile_end(double *total_ms, int *launches);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XNQ_H */

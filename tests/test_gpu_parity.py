@@ -1,0 +1,248 @@
+"""GPU parity tests: every call goes through the C ABI (via the ctypes host mirror) and is checked
+against the CPU oracle on the same seeded inputs.
+
+Bars: canonical bytes, dequantize and activation quantization are bit-exact; matmul with f32
+accumulation is within 2e-3 under the reference's own metric |g-w| <= tol*max(|w|,1)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_close_ref
+from xn_b200 import synth
+from xn_b200.dtypes import GgmlDType as D
+
+pytestmark = pytest.mark.gpu
+
+WEIGHT_TYPES = [D.Q4_0, D.Q8_0, D.Q4K, D.Q6K]
+TOL_F32 = 2e-3
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "known_answers.npz")
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def Q():
+    from xn_b200 import quantized
+    quantized.init(DEV)
+    return quantized
+
+
+def _upload(Q, dt, w, n, k, **kw):
+    return Q.QCudaTensor.from_qtensor(Q.QTensor(w, (n, k), dt), DEV, **kw)
+
+
+def test_library_is_loaded_and_device_is_b200(Q):
+    from xn_b200 import _lib
+    assert os.path.exists(_lib.LIB_PATH)
+    assert torch.cuda.get_device_capability(0)[0] == 10
+
+
+@pytest.mark.parametrize("dt", WEIGHT_TYPES)
+@pytest.mark.parametrize("n,kmul", [(1, 1), (7, 3), (33, 8), (130, 16)])
+def test_canonical_bytes_round_trip_and_dequantize_bit_exact(Q, O, dt, n, kmul):
+    k = dt.block_size * kmul
+    w = synth.make_weight(dt, n, k, seed=21)
+    t = _upload(Q, dt, w, n, k)
+    assert t.shape() == (n, k) and t.dtype() == dt
+    assert np.array_equal(t.data(), w), "device layout does not give the canonical GGUF bytes back"
+    want = O.to_float(int(dt), w, n * k).reshape(n, k)
+    got = t.dequantize(torch.float32).cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), "dequantize is not bit-identical to to_float"
+    for td in (torch.float16, torch.bfloat16):
+        got_h = t.dequantize(td).float().cpu().numpy()
+        assert np.array_equal(got_h, torch.from_numpy(want).to(td).float().numpy())
+
+
+def _tricky(m, k, seed):
+    x = synth.make_activation(m, k, seed=seed)
+    x[0, :32] = 0.0
+    if m > 1:
+        x[1, :] = 0.0
+        x[1, 5] = 1e-30
+    if m > 2:
+        x[2, :256] = np.clip(x[2, :256], -3.25, 3.25)
+        x[2, 7], x[2, 200] = 3.25, -3.25
+    if m > 3:
+        x[3] = np.round(x[3] * 4) / 8
+    return x
+
+
+@pytest.mark.parametrize("act", [D.Q8_0, D.Q8K])
+@pytest.mark.parametrize("m,k", [(1, 256), (5, 1024), (16, 4096), (3, 14336)])
+def test_activation_quantizer_bytes_identical(Q, O, act, m, k):
+    x = _tricky(m, k, 31 + m)
+    want = O.from_float(int(act), x)
+    got = Q.quantize_act(torch.from_numpy(x).to(DEV), act).cpu().numpy()
+    assert np.array_equal(got, want), f"{act.name} blocks differ at byte {np.flatnonzero(got != want)[:8]}"
+    for td in (torch.float16, torch.bfloat16):
+        xh = torch.from_numpy(x).to(td)
+        want_h = O.from_float(int(act), xh.float().numpy())
+        got_h = Q.quantize_act(xh.to(DEV), act).cpu().numpy()
+        assert np.array_equal(got_h, want_h), f"{act.name} from {td}"
+
+
+def test_activation_quantizer_strided_rows(Q, O):
+    big = synth.make_activation(4, 1024, seed=5)
+    x = torch.from_numpy(big).to(DEV)[:, :512]  # ldx = 1024
+    got = Q.quantize_act(x, D.Q8K).cpu().numpy()
+    assert np.array_equal(got, O.from_float(O.Q8K, np.ascontiguousarray(big[:, :512])))
+
+
+@pytest.mark.parametrize("dt", WEIGHT_TYPES)
+@pytest.mark.parametrize("m", list(range(1, 17)))
+def test_matmul_every_m_up_to_16(Q, O, dt, m):
+    n, k = 67, dt.block_size * 6
+    w = synth.make_weight(dt, n, k, seed=40)
+    x = _tricky(m, k, 40 + m)
+    want = O.matmul(int(dt), x, w, n)
+    got = _upload(Q, dt, w, n, k).matmul_t(torch.from_numpy(x).to(DEV)).cpu().numpy()
+    assert_close_ref(got, want, TOL_F32, f"{dt.name} m={m}")
+
+
+@pytest.mark.parametrize("dt", WEIGHT_TYPES)
+@pytest.mark.parametrize("n,kmul", [(1, 1), (15, 1), (17, 2), (129, 5), (8, 56)])
+def test_matmul_edge_shapes(Q, O, dt, n, kmul):
+    k = dt.block_size * kmul
+    w = synth.make_weight(dt, n, k, seed=50)
+    t = _upload(Q, dt, w, n, k)
+    for m in (1, 3, 16):
+        x = synth.make_activation(m, k, seed=50 + m)
+        got = t.matmul_t(torch.from_numpy(x).to(DEV)).cpu().numpy()
+        assert_close_ref(got, O.matmul(int(dt), x, w, n), TOL_F32, f"{dt.name} n={n} k={k} m={m}")
+    empty = t.matmul_t(torch.zeros((0, k), device=DEV))
+    assert tuple(empty.shape) == (0, n)
+
+
+def test_guard_words_after_output_are_untouched(Q, O):
+    dt, n, k, m = D.Q4K, 37, 512, 5
+    w = synth.make_weight(dt, n, k, seed=60)
+    x = synth.make_activation(m, k, seed=60)
+    buf = torch.full((m * n + 64,), 12345.0, device=DEV)
+    out = buf[:m * n].view(m, n)
+    _upload(Q, dt, w, n, k).matmul_t(torch.from_numpy(x).to(DEV), out=out)
+    assert torch.all(buf[m * n:] == 12345.0)
+    assert_close_ref(out.cpu().numpy(), O.matmul(int(dt), x, w, n), TOL_F32)
+
+
+@pytest.mark.parametrize("dt", WEIGHT_TYPES)
+def test_half_precision_io(Q, O, dt):
+    n, k, m = 96, 1024, 4
+    w = synth.make_weight(dt, n, k, seed=70)
+    t = _upload(Q, dt, w, n, k)
+    x = synth.make_activation(m, k, seed=70)
+    for td, tol in ((torch.float16, 2e-3), (torch.bfloat16, 1e-2)):
+        xh = torch.from_numpy(x).to(td)
+        want = O.matmul(int(dt), xh.float().numpy(), w, n)
+        got = t.matmul_t(xh.to(DEV))
+        assert got.dtype == td
+        # output rounding to the 16-bit type dominates: relative to |w|
+        err = np.abs(got.float().cpu().numpy() - want) / np.maximum(np.abs(want), 1.0)
+        assert err.max() <= tol, (dt.name, td, err.max())
+
+
+def test_three_d_input_and_bias(Q, O):
+    # qlinear_3d_input / qlinear_vs_linear_with_bias shapes: xn-core/tests/quantized_tests.rs:14-118
+    dt, n, k = D.Q8_0, 32, 64
+    w = synth.make_weight(dt, n, k, seed=80, dscale=0.05)
+    x = synth.make_activation(6, k, seed=80).reshape(2, 3, k)
+    bias = synth.make_activation(1, n, seed=81)[0]
+    lin = Q.QCudaLinear(_upload(Q, dt, w, n, k), torch.from_numpy(bias).to(DEV))
+    got = lin.forward(torch.from_numpy(x).to(DEV))
+    assert tuple(got.shape) == (2, 3, n)
+    want = O.matmul(int(dt), x.reshape(6, k), w, n) + bias
+    assert_close_ref(got.cpu().numpy().reshape(6, n), want, TOL_F32)
+    with pytest.raises(ValueError, match="only one dimension"):
+        lin.forward(torch.zeros(k, device=DEV))
+    with pytest.raises(ValueError, match="does not match weight"):
+        lin.forward(torch.zeros(2, k + 32, device=DEV))
+    host = lin.weight.forward_host(x, bias)
+    assert host.shape == (2, 3, n)
+    assert_close_ref(host.reshape(6, n), want, TOL_F32)
+
+
+def test_q8_0_reference_known_answer_recipe_on_gpu(Q, O):
+    # k_quants.rs:2155-2210: closed-form inputs, f64 dot of the quantized operands, 1e-4
+    for (m, k, n) in [(1, 256, 64), (4, 128, 32), (7, 96, 12), (13, 64, 4)]:
+        raw = ((np.arange(n * k) * 37 % 211).astype(np.float32) - np.float32(105.0)) / np.float32(64.0)
+        w = O.from_float(O.Q8_0, raw)
+        lhs = (((np.arange(m * k) * 53 % 173).astype(np.float32) - np.float32(86.0)) / np.float32(32.0)).reshape(m, k)
+        want = O.matmul(O.Q8_0, lhs, w, n, order="f64")
+        got = _upload(Q, D.Q8_0, w, n, k).matmul_t(torch.from_numpy(lhs).to(DEV)).cpu().numpy()
+        assert_close_ref(got, want, 1e-4, f"q8_0 {(m, k, n)}")
+
+
+def test_golden_vectors_without_oracle(Q):
+    g = np.load(GOLDEN)
+    x = torch.from_numpy(g["x"]).to(DEV)
+    assert np.array_equal(Q.quantize_act(x, D.Q8_0).cpu().numpy(), g["act_q8_0"])
+    assert np.array_equal(Q.quantize_act(x, D.Q8K).cpu().numpy(), g["act_q8k"])
+    n, k = 24, 512
+    for dt in WEIGHT_TYPES:
+        for key in (f"w_{dt.name}", f"wq_{dt.name}"):
+            t = _upload(Q, dt, g[key], n, k)
+            assert np.array_equal(t.data(), g[key])
+        t = _upload(Q, dt, g[f"w_{dt.name}"], n, k)
+        assert np.array_equal(t.dequantize().cpu().numpy().reshape(-1).view(np.uint32), g[f"deq_{dt.name}"].view(np.uint32))
+        assert_close_ref(t.matmul_t(x).cpu().numpy(), g[f"y_{dt.name}"], TOL_F32, dt.name)
+
+
+@pytest.mark.parametrize("dt", WEIGHT_TYPES)
+def test_sharded_upload_concatenates_to_unsharded(Q, O, dt):
+    n, k, m = 64, 1024, 3
+    w = synth.make_weight(dt, n, k, seed=90)
+    x = torch.from_numpy(synth.make_activation(m, k, seed=90)).to(DEV)
+    full = _upload(Q, dt, w, n, k).matmul_t(x)
+    for g in (2, 4, 8):
+        parts = [_upload(Q, dt, w, n, k, shard_rank=r, shard_count=g) for r in range(g)]
+        assert [p.row0 for p in parts] == [r * n // g for r in range(g)] and all(p.n_total == n for p in parts)
+        assert torch.equal(torch.cat([p.matmul_t(x) for p in parts], 1), full)
+        assert np.array_equal(np.concatenate([p.data() for p in parts]), w)
+
+
+# ---- the benchmark configurations at full size ---------------------------------------------------
+FULL = [
+    ("C1", D.Q4_0, 4096, 4096, (1,)),
+    ("C2", D.Q8_0, 11008, 4096, (1, 16)),
+    ("C3", D.Q4K, 14336, 4096, (1, 4, 16)),
+    ("C4", D.Q6K, 128256, 4096, (1,)),
+    ("down_proj", D.Q4K, 4096, 14336, (1, 16)),
+]
+
+
+@pytest.mark.parametrize("name,dt,n,k,ms", FULL)
+def test_full_size_configs_against_oracle(Q, O, name, dt, n, k, ms):
+    w = synth.make_weight(dt, n, k, seed=0)
+    t = _upload(Q, dt, w, n, k)
+    for m in ms:
+        x = synth.make_activation(m, k, seed=0)
+        got = t.matmul_t(torch.from_numpy(x).to(DEV)).cpu().numpy()
+        want = O.matmul(int(dt), x, w, n)
+        assert_close_ref(got, want, TOL_F32, f"{name} m={m}")
+        rms = float(np.sqrt((want.astype(np.float64) ** 2).mean()))
+        assert np.abs(got - want).max() / rms < TOL_F32, f"{name} m={m}: error relative to output rms"
+
+
+@pytest.mark.parametrize("dt", WEIGHT_TYPES)
+def test_full_size_properties_without_oracle(Q, dt):
+    """Size-independent properties at benchmark size: a one-hot-per-block activation quantizes
+    exactly (codes -128/127, scale |x|/127 or x/-128), so the product must equal the matching
+    columns of the dequantized weight summed in f32; and the rows of a stacked weight are
+    independent of the rows around them."""
+    n, k = 4096, 4096
+    w = synth.make_weight(dt, n, k, seed=3)
+    t = _upload(Q, dt, w, n, k)
+    dense = t.dequantize(torch.float32)
+    blk = dt.vec_dot_type.block_size
+    x = torch.zeros(2, k, device=DEV)
+    cols0 = torch.arange(0, k, blk, device=DEV) + 3
+    cols1 = torch.arange(0, k, blk, device=DEV) + (blk - 1)
+    x[0, cols0] = 1.0
+    x[1, cols1] = -2.0
+    got = t.matmul_t(x)
+    want = torch.stack([dense[:, cols0].double().sum(1), -2.0 * dense[:, cols1].double().sum(1)]).float()
+    err = (got - want).abs() / want.abs().clamp(min=1.0)
+    assert err.max().item() < 2e-3, err.max().item()
+    rb = dt.row_bytes(k)
+    sub = Q.QCudaTensor.from_rows(dt, w[1000 * rb:1512 * rb], n, k, 1000, 512, DEV)
+    assert torch.equal(sub.matmul_t(x), got[:, 1000:1512])

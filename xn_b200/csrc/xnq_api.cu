@@ -1,0 +1,400 @@
+// C ABI of the xnq library: argument validation, weight handles, dispatch. See include/xnq.h.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <atomic>
+#include <mutex>
+#include <new>
+#include <vector>
+
+#include "xnq_common.cuh"
+
+namespace xnq {
+
+static thread_local char g_err[512] = "";
+
+int fail(int code, const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+void clear_error() { g_err[0] = 0; }
+
+static std::atomic<uint64_t> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+struct Profile {
+  bool on = false;
+  std::vector<cudaEvent_t> ev; // start/stop pairs
+  size_t used = 0;
+};
+static thread_local Profile g_prof;
+void profile_mark(cudaStream_t s, bool start) {
+  Profile &p = g_prof;
+  if (!p.on) return;
+  if (start) {
+    if (p.used + 2 > p.ev.size()) return;
+    cudaEventRecord(p.ev[p.used], s);
+  } else {
+    if (p.used + 2 > p.ev.size()) return;
+    cudaEventRecord(p.ev[p.used + 1], s);
+    p.used += 2;
+  }
+}
+
+static inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+static inline size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+// Bytes of the device image of `n` rows, and the sub-buffer offsets inside it.
+struct Plan {
+  size_t qs, qh, sc, d, total;
+  int64_t dstride;
+};
+static Plan plan_for(int dtype, int64_t n, int64_t k) {
+  Plan p{};
+  const int64_t nblk = k / block_size(dtype);
+  p.dstride = (nblk + 7) & ~(int64_t)7;
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    size_t at = off;
+    off += up256(bytes);
+    return at;
+  };
+  switch (dtype) {
+    case XNQ_Q4_0:
+      p.qs = take((size_t)n * nblk * 16);
+      p.d = take((size_t)n * p.dstride * 2);
+      break;
+    case XNQ_Q8_0:
+      p.qs = take((size_t)n * k);
+      p.d = take((size_t)n * p.dstride * 2);
+      break;
+    case XNQ_Q4K:
+      p.qs = take((size_t)n * nblk * 144);
+      p.dstride = 0;
+      break;
+    case XNQ_Q6K:
+      p.qs = take((size_t)n * nblk * 128);
+      p.qh = take((size_t)n * nblk * 64);
+      p.sc = take((size_t)n * nblk * 16);
+      p.d = take((size_t)n * p.dstride * 2);
+      break;
+  }
+  p.total = off ? off : 256;
+  return p;
+}
+
+} // namespace xnq
+
+using namespace xnq;
+
+extern "C" {
+
+const char *xnq_last_error(void) { return g_err; }
+int xnq_version(void) { return XNQ_VERSION; }
+int xnq_type_size(int dt) { return (is_weight_dtype(dt) || dt == XNQ_Q8K || is_float_dtype(dt)) ? type_size(dt) : -1; }
+int xnq_block_size(int dt) { return (is_weight_dtype(dt) || dt == XNQ_Q8K || is_float_dtype(dt)) ? block_size(dt) : -1; }
+
+uint64_t xnq_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int xnq_profile_begin(int max_launches) {
+  clear_error();
+  if (max_launches <= 0 || max_launches > (1 << 20)) return fail(XNQ_ERR_SIZE, "profile_begin: max_launches = %d", max_launches);
+  Profile &p = g_prof;
+  for (cudaEvent_t e : p.ev) cudaEventDestroy(e);
+  p.ev.clear();
+  p.used = 0;
+  p.ev.resize((size_t)max_launches * 2);
+  for (auto &e : p.ev) XNQ_CUDA(cudaEventCreate(&e));
+  p.on = true;
+  return XNQ_OK;
+}
+
+int xnq_profile_end(double *total_ms, int *launches) {
+  clear_error();
+  Profile &p = g_prof;
+  if (!p.on) return fail(XNQ_ERR_SHAPE, "profile_end without profile_begin");
+  p.on = false;
+  double total = 0.0;
+  int rc = XNQ_OK;
+  for (size_t i = 0; i + 1 < p.used; i += 2) {
+    float ms = 0.f;
+    cudaError_t e = cudaEventSynchronize(p.ev[i + 1]);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, p.ev[i], p.ev[i + 1]);
+    if (e != cudaSuccess) {
+      rc = fail(XNQ_ERR_CUDA, "profile_end: %s", cudaGetErrorString(e));
+      break;
+    }
+    total += ms;
+  }
+  if (total_ms) *total_ms = total;
+  if (launches) *launches = (int)(p.used / 2);
+  for (cudaEvent_t e : p.ev) cudaEventDestroy(e);
+  p.ev.clear();
+  p.used = 0;
+  return rc;
+}
+
+int xnq_init(int device) {
+  clear_error();
+  int count = 0;
+  XNQ_CUDA(cudaGetDeviceCount(&count));
+  if (device < 0 || device >= count) return fail(XNQ_ERR_SHAPE, "xnq_init: device %d out of range (%d visible)", device, count);
+  cudaDeviceProp prop;
+  XNQ_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10)
+    return fail(XNQ_ERR_UNSUPPORTED, "xnq_init: device %d is sm_%d%d; this library is built for sm_100a only and has no fallback",
+                device, prop.major, prop.minor);
+  XNQ_CUDA(cudaSetDevice(device));
+  int rc;
+  if ((rc = layout_init(device)) != XNQ_OK) return rc;
+  if ((rc = quantize_init(device)) != XNQ_OK) return rc;
+  if ((rc = matvec_init(device)) != XNQ_OK) return rc;
+  return XNQ_OK;
+}
+
+int xnq_weight_upload_rows(int dtype, const void *blocks, size_t nbytes, int64_t n_total, int64_t k, int64_t row0, int64_t n_rows,
+                           void *stream, xnq_weight **out) {
+  clear_error();
+  if (!out) return fail(XNQ_ERR_NULL, "weight_upload: out is NULL");
+  *out = nullptr;
+  if (!is_weight_dtype(dtype)) return fail(XNQ_ERR_DTYPE, "weight_upload: ggml dtype %d is not one of Q4_0(2) Q8_0(8) Q4K(12) Q6K(14)", dtype);
+  if (n_total < 0 || k <= 0 || row0 < 0 || n_rows < 0 || row0 + n_rows > n_total)
+    return fail(XNQ_ERR_SHAPE, "weight_upload: bad shape n_total=%lld k=%lld rows [%lld, +%lld)", (long long)n_total, (long long)k,
+                (long long)row0, (long long)n_rows);
+  const int bs = block_size(dtype);
+  if (k % bs != 0) return fail(XNQ_ERR_SHAPE, "weight_upload: k = %lld is not a multiple of the %d-value block", (long long)k, bs);
+  if (n_total > INT32_MAX || k > INT32_MAX) return fail(XNQ_ERR_SHAPE, "weight_upload: n or k exceeds 2^31-1");
+  const size_t want = (size_t)n_rows * (k / bs) * type_size(dtype);
+  if (nbytes != want)
+    return fail(XNQ_ERR_SIZE, "weight_upload: [%lld, %lld] wants %zu bytes of blocks, got %zu", (long long)n_rows, (long long)k, want, nbytes);
+  if (!blocks && nbytes) return fail(XNQ_ERR_NULL, "weight_upload: blocks is NULL");
+
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  xnq_weight *w = new (std::nothrow) xnq_weight();
+  if (!w) return fail(XNQ_ERR_SIZE, "weight_upload: out of host memory");
+  std::memset(w, 0, sizeof(*w));
+  XNQ_CUDA(cudaGetDevice(&w->device));
+  w->n_total = n_total;
+  w->row0 = row0;
+  const Plan p = plan_for(dtype, n_rows, k);
+  cudaError_t e = cudaMalloc(&w->base, p.total);
+  if (e != cudaSuccess) {
+    delete w;
+    return fail(XNQ_ERR_CUDA, "weight_upload: cudaMalloc(%zu) failed: %s", p.total, cudaGetErrorString(e));
+  }
+  w->bytes = p.total;
+  char *b = static_cast<char *>(w->base);
+  w->v.dtype = dtype;
+  w->v.n = n_rows;
+  w->v.k = k;
+  w->v.dstride = p.dstride;
+  w->v.qs = reinterpret_cast<const uint8_t *>(b + p.qs);
+  w->v.qh = dtype == XNQ_Q6K ? reinterpret_cast<const uint8_t *>(b + p.qh) : nullptr;
+  w->v.sc = dtype == XNQ_Q6K ? reinterpret_cast<const int8_t *>(b + p.sc) : nullptr;
+  w->v.d = dtype == XNQ_Q4K ? nullptr : reinterpret_cast<const __half *>(b + p.d);
+
+  int rc = XNQ_OK;
+  void *staging = nullptr;
+  do {
+    if ((e = cudaMemsetAsync(w->base, 0, p.total, s)) != cudaSuccess) break;
+    if (nbytes == 0) break;
+    if (dtype == XNQ_Q4K) { // GGUF layout is the device layout
+      e = cudaMemcpyAsync(w->base, blocks, nbytes, cudaMemcpyHostToDevice, s);
+      break;
+    }
+    if ((e = cudaMalloc(&staging, nbytes)) != cudaSuccess) break;
+    if ((e = cudaMemcpyAsync(staging, blocks, nbytes, cudaMemcpyHostToDevice, s)) != cudaSuccess) break;
+    rc = launch_relayout(w->v, static_cast<const uint8_t *>(staging), s);
+  } while (0);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (staging) cudaFree(staging);
+  if (e != cudaSuccess || rc != XNQ_OK) {
+    cudaFree(w->base);
+    delete w;
+    if (rc != XNQ_OK) return rc;
+    return fail(XNQ_ERR_CUDA, "weight_upload: %s", cudaGetErrorString(e));
+  }
+  *out = w;
+  return XNQ_OK;
+}
+
+int xnq_weight_upload(int dtype, const void *blocks, size_t nbytes, int64_t n, int64_t k, int shard_rank, int shard_count, void *stream,
+                      xnq_weight **out) {
+  clear_error();
+  if (out) *out = nullptr;
+  if (!is_weight_dtype(dtype)) return fail(XNQ_ERR_DTYPE, "weight_upload: ggml dtype %d is not one of Q4_0(2) Q8_0(8) Q4K(12) Q6K(14)", dtype);
+  if (shard_count < 1 || shard_rank < 0 || shard_rank >= shard_count)
+    return fail(XNQ_ERR_SHAPE, "weight_upload: shard %d of %d", shard_rank, shard_count);
+  if (n < 0 || k <= 0 || k % block_size(dtype) != 0)
+    return fail(XNQ_ERR_SHAPE, "weight_upload: bad shape [%lld, %lld] for a %d-value block", (long long)n, (long long)k, block_size(dtype));
+  if (n % shard_count != 0) return fail(XNQ_ERR_SHAPE, "weight_upload: n = %lld does not divide over %d shards", (long long)n, shard_count);
+  const size_t row_bytes = (size_t)(k / block_size(dtype)) * type_size(dtype);
+  if (nbytes != (size_t)n * row_bytes)
+    return fail(XNQ_ERR_SIZE, "weight_upload: [%lld, %lld] wants %zu bytes of blocks, got %zu", (long long)n, (long long)k, (size_t)n * row_bytes,
+                nbytes);
+  if (!blocks && nbytes) return fail(XNQ_ERR_NULL, "weight_upload: blocks is NULL");
+  const int64_t rows = n / shard_count, row0 = rows * shard_rank;
+  return xnq_weight_upload_rows(dtype, static_cast<const char *>(blocks) + (size_t)row0 * row_bytes, (size_t)rows * row_bytes, n, k, row0, rows,
+                                stream, out);
+}
+
+int xnq_weight_free(xnq_weight *w) {
+  clear_error();
+  if (!w) return XNQ_OK;
+  if (w->base) cudaFree(w->base);
+  if (w->stage_dev) cudaFree(w->stage_dev);
+  if (w->stage_host) cudaFreeHost(w->stage_host);
+  delete w;
+  return XNQ_OK;
+}
+
+int xnq_weight_info(const xnq_weight *w, int *dtype, int64_t *n_total, int64_t *n_local, int64_t *row0, int64_t *k, size_t *device_bytes) {
+  clear_error();
+  if (!w) return fail(XNQ_ERR_NULL, "weight_info: weight is NULL");
+  if (dtype) *dtype = w->v.dtype;
+  if (n_total) *n_total = w->n_total;
+  if (n_local) *n_local = w->v.n;
+  if (row0) *row0 = w->row0;
+  if (k) *k = w->v.k;
+  if (device_bytes) *device_bytes = w->bytes;
+  return XNQ_OK;
+}
+
+int xnq_weight_dequantize(const xnq_weight *w, int out_dtype, void *dst, void *stream) {
+  clear_error();
+  if (!w) return fail(XNQ_ERR_NULL, "dequantize: weight is NULL");
+  if (!is_float_dtype(out_dtype)) return fail(XNQ_ERR_DTYPE, "dequantize: output dtype %d is not f32/f16/bf16", out_dtype);
+  if (w->v.n == 0) return XNQ_OK;
+  if (!dst) return fail(XNQ_ERR_NULL, "dequantize: dst is NULL");
+  return launch_dequantize(w->v, out_dtype, dst, static_cast<cudaStream_t>(stream));
+}
+
+int xnq_weight_canonical_bytes(const xnq_weight *w, void *host_dst, size_t nbytes, void *stream) {
+  clear_error();
+  if (!w) return fail(XNQ_ERR_NULL, "canonical_bytes: weight is NULL");
+  const size_t want = (size_t)w->v.n * (w->v.k / block_size(w->v.dtype)) * type_size(w->v.dtype);
+  if (nbytes != want) return fail(XNQ_ERR_SIZE, "canonical_bytes: the held rows are %zu bytes, buffer is %zu", want, nbytes);
+  if (want == 0) return XNQ_OK;
+  if (!host_dst) return fail(XNQ_ERR_NULL, "canonical_bytes: host_dst is NULL");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (w->v.dtype == XNQ_Q4K) {
+    XNQ_CUDA(cudaMemcpyAsync(host_dst, w->v.qs, want, cudaMemcpyDeviceToHost, s));
+    XNQ_CUDA(cudaStreamSynchronize(s));
+    return XNQ_OK;
+  }
+  void *staging = nullptr;
+  XNQ_CUDA(cudaMalloc(&staging, want));
+  int rc = launch_to_canonical(w->v, static_cast<uint8_t *>(staging), s);
+  cudaError_t e = cudaSuccess;
+  if (rc == XNQ_OK) e = cudaMemcpyAsync(host_dst, staging, want, cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  cudaFree(staging);
+  if (rc != XNQ_OK) return rc;
+  if (e != cudaSuccess) return fail(XNQ_ERR_CUDA, "canonical_bytes: %s", cudaGetErrorString(e));
+  return XNQ_OK;
+}
+
+static int check_x(const char *who, const void *x, int x_dtype, int64_t m, int64_t k, int64_t ldx) {
+  if (!is_float_dtype(x_dtype)) return fail(XNQ_ERR_DTYPE, "%s: activation dtype %d is not f32/f16/bf16", who, x_dtype);
+  if (m < 0) return fail(XNQ_ERR_SHAPE, "%s: m = %lld", who, (long long)m);
+  if (ldx < k) return fail(XNQ_ERR_SHAPE, "%s: ldx = %lld is smaller than k = %lld", who, (long long)ldx, (long long)k);
+  if (m > 0 && !x) return fail(XNQ_ERR_NULL, "%s: x is NULL", who);
+  const size_t es = type_size(x_dtype);
+  if (m > 0 && (!aligned(x, 16) || (m > 1 && (ldx * es) % 16 != 0)))
+    return fail(XNQ_ERR_ALIGN, "%s: activation rows must start 16-byte aligned (x=%p, ldx=%lld)", who, x, (long long)ldx);
+  return XNQ_OK;
+}
+
+int xnq_quantize_act(int act_dtype, const void *x, int x_dtype, int64_t m, int64_t k, int64_t ldx, void *dst, void *stream) {
+  clear_error();
+  if (act_dtype != XNQ_Q8_0 && act_dtype != XNQ_Q8K)
+    return fail(XNQ_ERR_DTYPE, "quantize_act: %d is not an activation block format (Q8_0=8, Q8K=15)", act_dtype);
+  const int bs = block_size(act_dtype);
+  if (k <= 0 || k % bs != 0) return fail(XNQ_ERR_SHAPE, "quantize_act: k = %lld is not a multiple of the %d-value block", (long long)k, bs);
+  int rc = check_x("quantize_act", x, x_dtype, m, k, ldx);
+  if (rc != XNQ_OK) return rc;
+  if (m == 0) return XNQ_OK;
+  if (!dst) return fail(XNQ_ERR_NULL, "quantize_act: dst_blocks is NULL");
+  if (!aligned(dst, 4)) return fail(XNQ_ERR_ALIGN, "quantize_act: dst_blocks must be 4-byte aligned");
+  return launch_quantize_act_blocks(act_dtype, x, x_dtype, m, k, ldx, dst, static_cast<cudaStream_t>(stream));
+}
+
+size_t xnq_matmul_workspace_bytes(const xnq_weight *w, int64_t max_m) {
+  if (!w || max_m <= 0) return 0;
+  const int64_t rows = max_m < MATVEC_MAX_M ? max_m : MATVEC_MAX_M; // larger m is processed in passes of <= 16 rows
+  return act_workspace_bytes(rows, w->v.k, act_dtype_for(w->v.dtype));
+}
+
+int xnq_matmul_t(const xnq_weight *w, const void *x, int x_dtype, int64_t m, int64_t ldx, void *y, int y_dtype, int64_t ldy, void *workspace,
+                 size_t ws_bytes, void *stream) {
+  clear_error();
+  if (!w) return fail(XNQ_ERR_NULL, "matmul_t: weight is NULL");
+  const int64_t k = w->v.k, n = w->v.n;
+  int rc = check_x("matmul_t", x, x_dtype, m, k, ldx);
+  if (rc != XNQ_OK) return rc;
+  if (!is_float_dtype(y_dtype)) return fail(XNQ_ERR_DTYPE, "matmul_t: output dtype %d is not f32/f16/bf16", y_dtype);
+  if (ldy < n) return fail(XNQ_ERR_SHAPE, "matmul_t: ldy = %lld is smaller than n = %lld", (long long)ldy, (long long)n);
+  if (m == 0 || n == 0) return XNQ_OK;
+  if (!y) return fail(XNQ_ERR_NULL, "matmul_t: y is NULL");
+  if (!aligned(y, type_size(y_dtype))) return fail(XNQ_ERR_ALIGN, "matmul_t: y is not aligned to its element size");
+  const size_t need = xnq_matmul_workspace_bytes(w, m);
+  if (!workspace) return fail(XNQ_ERR_NULL, "matmul_t: workspace is NULL (need %zu bytes)", need);
+  if (!aligned(workspace, 256)) return fail(XNQ_ERR_ALIGN, "matmul_t: workspace must be 256-byte aligned");
+  if (ws_bytes < need) return fail(XNQ_ERR_SIZE, "matmul_t: workspace has %zu bytes, m = %lld needs %zu", ws_bytes, (long long)m, need);
+  const int64_t pass = matvec_rows_per_pass(w->v.dtype, k);
+  if (pass == 0) return fail(XNQ_ERR_SIZE, "matmul_t: k = %lld is too large for the shared-memory staging of one activation row", (long long)k);
+
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int adt = act_dtype_for(w->v.dtype);
+  const size_t xes = type_size(x_dtype), yes = type_size(y_dtype);
+  for (int64_t r0 = 0; r0 < m; r0 += pass) {
+    const int64_t rows = (m - r0) < pass ? (m - r0) : pass;
+    ActView a = act_view(workspace, rows, k, adt);
+    const char *xp = static_cast<const char *>(x) + (size_t)r0 * ldx * xes;
+    char *yp = static_cast<char *>(y) + (size_t)r0 * ldy * yes;
+    if ((rc = launch_quantize_act_planar(a, xp, x_dtype, ldx, s)) != XNQ_OK) return rc;
+    profile_mark(s, true);
+    rc = launch_matvec(w->v, a, yp, y_dtype, ldy, s);
+    profile_mark(s, false);
+    if (rc != XNQ_OK) return rc;
+  }
+  return XNQ_OK;
+}
+
+int xnq_linear_forward_host(xnq_weight *w, const float *x_host, int64_t m, const float *bias_host, float *y_host, void *stream) {
+  clear_error();
+  if (!w) return fail(XNQ_ERR_NULL, "linear_forward_host: weight is NULL");
+  if (m < 0) return fail(XNQ_ERR_SHAPE, "linear_forward_host: m = %lld", (long long)m);
+  const int64_t k = w->v.k, n = w->v.n;
+  if (m == 0 || n == 0) return XNQ_OK;
+  if (!x_host || !y_host) return fail(XNQ_ERR_NULL, "linear_forward_host: x_host or y_host is NULL");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t xb = up256((size_t)m * k * 4), yb = up256((size_t)m * n * 4), bb = up256((size_t)n * 4);
+  const size_t wsb = up256(xnq_matmul_workspace_bytes(w, m));
+  const size_t need = xb + yb + bb + wsb;
+  if (w->stage_dev_bytes < need) {
+    if (w->stage_dev) cudaFree(w->stage_dev);
+    w->stage_dev = nullptr;
+    w->stage_dev_bytes = 0;
+    XNQ_CUDA(cudaMalloc(&w->stage_dev, need));
+    w->stage_dev_bytes = need;
+  }
+  char *base = static_cast<char *>(w->stage_dev);
+  float *xd = reinterpret_cast<float *>(base);
+  float *yd = reinterpret_cast<float *>(base + xb);
+  float *bd = reinterpret_cast<float *>(base + xb + yb);
+  void *ws = base + xb + yb + bb;
+  XNQ_CUDA(cudaMemcpyAsync(xd, x_host, (size_t)m * k * 4, cudaMemcpyHostToDevice, s));
+  if (bias_host) XNQ_CUDA(cudaMemcpyAsync(bd, bias_host, (size_t)n * 4, cudaMemcpyHostToDevice, s));
+  int rc = xnq_matmul_t(w, xd, XNQ_F32, m, k, yd, XNQ_F32, n, ws, wsb, s);
+  if (rc != XNQ_OK) return rc;
+  if (bias_host && (rc = launch_add_bias(yd, bd, m, n, n, s)) != XNQ_OK) return rc;
+  XNQ_CUDA(cudaMemcpyAsync(y_host, yd, (size_t)m * n * 4, cudaMemcpyDeviceToHost, s));
+  XNQ_CUDA(cudaStreamSynchronize(s));
+  return XNQ_OK;
+}
+
+} // extern "C"

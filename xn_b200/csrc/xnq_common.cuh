@@ -1,0 +1,146 @@
+// Shared declarations of the xnq library: device weight handle, activation workspace views,
+// error plumbing, launch entry points of each translation unit. sm_100a only.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+#include <string>
+
+#include "../../include/xnq.h"
+
+namespace xnq {
+
+constexpr int QK = 32;    // elements per Q4_0 / Q8_0 block (k_quants.rs:14-19)
+constexpr int QK_K = 256; // elements per K-quant super-block (k_quants.rs:11)
+
+// ------------------------------------------------------------------------------------------------
+// error plumbing: thread-local message + status code
+// ------------------------------------------------------------------------------------------------
+int fail(int code, const char *fmt, ...);
+void clear_error();
+#define XNQ_CUDA(expr)                                                                              \
+  do {                                                                                              \
+    cudaError_t e__ = (expr);                                                                       \
+    if (e__ != cudaSuccess)                                                                         \
+      return ::xnq::fail(XNQ_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__));            \
+  } while (0)
+
+inline int type_size(int dt) {
+  switch (dt) {
+    case XNQ_F32: return 4;
+    case XNQ_F16: return 2;
+    case XNQ_BF16: return 2;
+    case XNQ_Q4_0: return 18;
+    case XNQ_Q8_0: return 34;
+    case XNQ_Q4K: return 144;
+    case XNQ_Q6K: return 210;
+    case XNQ_Q8K: return 292;
+  }
+  return -1;
+}
+inline int block_size(int dt) {
+  switch (dt) {
+    case XNQ_F32:
+    case XNQ_F16:
+    case XNQ_BF16: return 1;
+    case XNQ_Q4_0:
+    case XNQ_Q8_0: return QK;
+    case XNQ_Q4K:
+    case XNQ_Q6K:
+    case XNQ_Q8K: return QK_K;
+  }
+  return -1;
+}
+inline bool is_weight_dtype(int dt) { return dt == XNQ_Q4_0 || dt == XNQ_Q8_0 || dt == XNQ_Q4K || dt == XNQ_Q6K; }
+inline bool is_float_dtype(int dt) { return dt == XNQ_F32 || dt == XNQ_F16 || dt == XNQ_BF16; }
+inline int act_dtype_for(int wdt) { return (wdt == XNQ_Q4_0 || wdt == XNQ_Q8_0) ? XNQ_Q8_0 : XNQ_Q8K; }
+
+// ------------------------------------------------------------------------------------------------
+// Device layout of a weight (or N-shard): what the kernels read.
+//
+//  Q4_0 : qs  [n][k/32][16]  nibble bytes exactly as in the GGUF block (16-byte chunks now aligned)
+//         d   [n][dstride]   f16 block scales
+//  Q8_0 : qs  [n][k]         int8 codes
+//         d   [n][dstride]   f16 block scales
+//  Q4_K : qs  = the canonical 144-byte super-blocks, untouched (144 = 9 x 16 B: already aligned)
+//  Q6_K : qs  [n][k/256][128] ql bytes,  qh [n][k/256][64],  sc [n][k/256][16] int8,
+//         d   [n][dstride]   f16 super-block scales
+// dstride (elements) is the scale count per row rounded up to 8, so every row of d starts 16-byte
+// aligned. Total bytes equal the GGUF bytes (plus that padding).
+// ------------------------------------------------------------------------------------------------
+struct WeightView {
+  int dtype;
+  int64_t n; // rows held
+  int64_t k;
+  int64_t dstride;
+  const uint8_t *qs;
+  const uint8_t *qh;
+  const int8_t *sc;
+  const __half *d;
+};
+
+// Planar device layout of quantized activations (the matmul scratch):
+//  q     [m][k]        int8 codes
+//  d     [m][k/blk]    f32 block scale (Q8_0: the f16-rounded scale widened, so dots use exactly
+//                      the value the reference reads back from the block; Q8_K: the f32 scale)
+//  bsum  [m][k/16]     int16 sums of 16 codes (BlockQ8K::bsums; for Q8_0 blocks the same sums, used
+//                      to fold Q4_0's -8 offset)
+struct ActView {
+  int act_dtype; // XNQ_Q8_0 or XNQ_Q8K
+  int64_t m, k;
+  int8_t *q;
+  float *d;
+  int16_t *bsum;
+};
+
+size_t act_workspace_bytes(int64_t m, int64_t k, int act_dtype);
+ActView act_view(void *workspace, int64_t m, int64_t k, int act_dtype);
+
+} // namespace xnq
+
+struct xnq_weight {
+  int device;
+  int64_t n_total, row0;
+  xnq::WeightView v;
+  void *base;    // single device allocation behind v
+  size_t bytes;  // its size
+  // host-call staging (xnq_linear_forward_host)
+  void *stage_dev;
+  size_t stage_dev_bytes;
+  void *stage_host;
+  size_t stage_host_bytes;
+};
+
+namespace xnq {
+
+// launch accounting + per-kernel event timing (xnq_api.cu)
+void count_launch(int n = 1);
+void profile_mark(cudaStream_t s, bool start);
+
+// xnq_layout.cu
+int launch_relayout(const WeightView &dst, const uint8_t *canonical_dev, cudaStream_t s);   // GGUF -> device layout
+int launch_to_canonical(const WeightView &src, uint8_t *canonical_dev, cudaStream_t s);     // device layout -> GGUF
+int launch_dequantize(const WeightView &w, int out_dtype, void *dst, cudaStream_t s);
+int layout_init(int device);
+
+// xnq_quantize_act.cu
+int launch_quantize_act_blocks(int act_dtype, const void *x, int x_dtype, int64_t m, int64_t k, int64_t ldx,
+                               void *dst_blocks, cudaStream_t s);
+int launch_quantize_act_planar(const ActView &a, const void *x, int x_dtype, int64_t ldx, cudaStream_t s);
+int quantize_init(int device);
+
+// xnq_matvec.cu  (m <= 16)
+constexpr int MATVEC_MAX_M = 16;
+int launch_matvec(const WeightView &w, const ActView &a, void *y, int y_dtype, int64_t ldy, cudaStream_t s);
+int matvec_init(int device);
+// activation rows one matvec launch can stage in shared memory for this k (0: k is too large)
+int64_t matvec_rows_per_pass(int wdtype, int64_t k);
+
+// xnq_bias.cu-ish helper in xnq_layout.cu: y[m, n] += bias[n]
+int launch_add_bias(float *y, const float *bias, int64_t m, int64_t n, int64_t ldy, cudaStream_t s);
+
+} // namespace xnq

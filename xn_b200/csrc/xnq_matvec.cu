@@ -1,0 +1,391 @@
+// Decode kernels (m <= 16): dequant-fused quantized matvec, HBM-bound.
+//
+//   y[r, n] = sum over blocks of  d_w * d_a * (integer dot of codes)          (+ min / offset terms)
+//
+// which is the arithmetic of the reference's CPU dots (xn-core/src/quantized/k_quants.rs:287-304
+// Q4_0, 677-691 Q8_0, 1337-1416 Q4_K, 1743-1799 Q6_K): exact integer sums per (sub-)block, scales
+// applied in f32, f32 accumulation. Only the f32 summation order differs (lanes, then a shuffle
+// tree), as it already does between the reference's scalar and AVX2 builds.
+//
+// Mapping. A warp owns R consecutive weight rows and walks k; every lane loads one 16-byte chunk
+// of each row per step with a streaming (no-L1-allocate) 128-bit load, unpacks the 4/6/8-bit codes
+// in registers, and runs dp4a against the int8 activations, which the CTA staged in shared memory
+// once. Activation registers are reused across the R rows, shared-memory traffic per weight byte
+// drops by R. Partial sums are reduced with warp shuffles; lane 0 stores.
+#include "xnq_common.cuh"
+#include "xnq_unpack.cuh"
+
+namespace xnq {
+
+namespace {
+
+constexpr int WARPS = 8;
+constexpr int THREADS = WARPS * 32;
+
+__device__ __forceinline__ uint4 ldg_stream(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint2 ldg_stream8(const void *p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ int dot16(const uint4 &w, const int4 &a, int acc) {
+  acc = __dp4a((int)w.x, a.x, acc);
+  acc = __dp4a((int)w.y, a.y, acc);
+  acc = __dp4a((int)w.z, a.z, acc);
+  acc = __dp4a((int)w.w, a.w, acc);
+  return acc;
+}
+__device__ __forceinline__ uint4 and4(const uint4 &v, uint32_t m) { return make_uint4(v.x & m, v.y & m, v.z & m, v.w & m); }
+__device__ __forceinline__ uint4 shr4(const uint4 &v, int s) { return make_uint4(v.x >> s, v.y >> s, v.z >> s, v.w >> s); }
+__device__ __forceinline__ uint4 shl4(const uint4 &v, int s) { return make_uint4(v.x << s, v.y << s, v.z << s, v.w << s); }
+__device__ __forceinline__ uint4 or4(const uint4 &a, const uint4 &b) { return make_uint4(a.x | b.x, a.y | b.y, a.z | b.z, a.w | b.w); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  return v;
+}
+
+__device__ __forceinline__ void store_y(void *y, int y_dtype, int64_t idx, float v) {
+  if (y_dtype == XNQ_F32) {
+    static_cast<float *>(y)[idx] = v;
+  } else if (y_dtype == XNQ_F16) {
+    static_cast<__half *>(y)[idx] = __float2half_rn(v);
+  } else {
+    static_cast<__nv_bfloat16 *>(y)[idx] = __float2bfloat16_rn(v);
+  }
+}
+
+// Shared-memory image of the quantized activations: q [m][k] int8 | d [m][nblk] f32 | bsum [m][k/16] i16
+struct SmemAct {
+  const int8_t *q;
+  const float *d;
+  const int16_t *bsum;
+};
+__host__ __device__ inline size_t smem_act_bytes(int64_t m, int64_t k, int blk, bool with_bsum) {
+  size_t b = (size_t)m * k;                                  // multiple of 32
+  b += (((size_t)m * (k / blk) * 4) + 15) & ~(size_t)15;
+  if (with_bsum) b += (((size_t)m * (k / 16) * 2) + 15) & ~(size_t)15;
+  return b;
+}
+
+__device__ __forceinline__ SmemAct stage_activations(unsigned char *smem, const ActView &a, int blk, bool with_bsum) {
+  const int64_t qbytes = a.m * a.k;
+  const int64_t dcount = a.m * (a.k / blk);
+  int8_t *sq = reinterpret_cast<int8_t *>(smem);
+  float *sd = reinterpret_cast<float *>(smem + qbytes);
+  int16_t *sb = reinterpret_cast<int16_t *>(smem + qbytes + ((dcount * 4 + 15) & ~(int64_t)15));
+  for (int64_t i = threadIdx.x; i < qbytes / 16; i += blockDim.x)
+    reinterpret_cast<uint4 *>(sq)[i] = reinterpret_cast<const uint4 *>(a.q)[i];
+  for (int64_t i = threadIdx.x; i < dcount; i += blockDim.x) sd[i] = a.d[i];
+  if (with_bsum) {
+    const int64_t bwords = a.m * (a.k / 16) / 2; // k/16 is even: pairs of int16
+    for (int64_t i = threadIdx.x; i < bwords; i += blockDim.x)
+      reinterpret_cast<uint32_t *>(sb)[i] = reinterpret_cast<const uint32_t *>(a.bsum)[i];
+  }
+  __syncthreads();
+  return SmemAct{sq, sd, sb};
+}
+
+template <int MT, int R>
+__device__ __forceinline__ void reduce_store(float (&acc)[R][MT], int lane, int64_t row0, int64_t n, int m, void *y, int y_dtype,
+                                             int64_t ldy) {
+#pragma unroll
+  for (int r = 0; r < R; r++) {
+#pragma unroll
+    for (int i = 0; i < MT; i++) {
+      const float v = warp_sum(acc[r][i]);
+      if (lane == 0 && i < m && row0 + r < n) store_y(y, y_dtype, (int64_t)i * ldy + row0 + r, v);
+    }
+  }
+}
+
+#define XNQ_MATVEC_BOUNDS __launch_bounds__(THREADS, (MT <= 2 ? 4 : (MT <= 4 ? 3 : 2)))
+
+// ---- Q4_0: one 16-byte chunk = one block (32 codes) ----------------------------------------------
+template <int MT, int R>
+__global__ void XNQ_MATVEC_BOUNDS matvec_q4_0(WeightView w, ActView a, void *y, int y_dtype, int64_t ldy) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  const SmemAct sa = stage_activations(smem, a, QK, true);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t row0 = ((int64_t)blockIdx.x * WARPS + warp) * R;
+  if (row0 >= w.n) return;
+  const int m = (int)a.m;
+  const int64_t k = w.k, nblk = k / QK;
+  float acc[R][MT];
+#pragma unroll
+  for (int r = 0; r < R; r++)
+#pragma unroll
+    for (int i = 0; i < MT; i++) acc[r][i] = 0.f;
+
+  for (int64_t b = lane; b < nblk; b += 32) {
+    uint4 q[R];
+    float dw[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+      const int64_t row = min(row0 + r, w.n - 1); // a duplicate row for the ragged tail; never stored
+      q[r] = ldg_stream(w.qs + (row * nblk + b) * 16);
+      dw[r] = __half2float(w.d[row * w.dstride + b]);
+    }
+#pragma unroll
+    for (int i = 0; i < MT; i++) {
+      if (i < m) {
+        const int4 alo = *reinterpret_cast<const int4 *>(sa.q + (int64_t)i * k + b * 32);
+        const int4 ahi = *reinterpret_cast<const int4 *>(sa.q + (int64_t)i * k + b * 32 + 16);
+        const float da = sa.d[(int64_t)i * nblk + b];
+        const uint32_t bs2 = *reinterpret_cast<const uint32_t *>(sa.bsum + (int64_t)i * (k / 16) + 2 * b);
+        const int bsum = (int)(int16_t)(bs2 & 0xffff) + (int)(int16_t)(bs2 >> 16);
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+          int s = dot16(and4(q[r], 0x0f0f0f0fu), alo, 0);
+          s = dot16(and4(shr4(q[r], 4), 0x0f0f0f0fu), ahi, s);
+          s -= 8 * bsum; // codes are stored +8
+          acc[r][i] += (float)s * dw[r] * da;
+        }
+      }
+    }
+  }
+  reduce_store<MT, R>(acc, lane, row0, w.n, m, y, y_dtype, ldy);
+}
+
+// ---- Q8_0: one 16-byte chunk = half a block -------------------------------------------------------
+template <int MT, int R>
+__global__ void XNQ_MATVEC_BOUNDS matvec_q8_0(WeightView w, ActView a, void *y, int y_dtype, int64_t ldy) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  const SmemAct sa = stage_activations(smem, a, QK, false);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t row0 = ((int64_t)blockIdx.x * WARPS + warp) * R;
+  if (row0 >= w.n) return;
+  const int m = (int)a.m;
+  const int64_t k = w.k, nblk = k / QK, nch = k / 16;
+  float acc[R][MT];
+#pragma unroll
+  for (int r = 0; r < R; r++)
+#pragma unroll
+    for (int i = 0; i < MT; i++) acc[r][i] = 0.f;
+
+  for (int64_t c = lane; c < nch; c += 32) {
+    uint4 q[R];
+    float dw[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+      const int64_t row = min(row0 + r, w.n - 1);
+      q[r] = ldg_stream(w.qs + row * k + c * 16);
+      dw[r] = __half2float(w.d[row * w.dstride + (c >> 1)]);
+    }
+#pragma unroll
+    for (int i = 0; i < MT; i++) {
+      if (i < m) {
+        const int4 av = *reinterpret_cast<const int4 *>(sa.q + (int64_t)i * k + c * 16);
+        const float da = sa.d[(int64_t)i * nblk + (c >> 1)];
+#pragma unroll
+        for (int r = 0; r < R; r++) acc[r][i] += (float)dot16(q[r], av, 0) * dw[r] * da;
+      }
+    }
+  }
+  reduce_store<MT, R>(acc, lane, row0, w.n, m, y, y_dtype, ldy);
+}
+
+// ---- Q4_K: 8 lanes per 144-byte super-block (header + 8 chunks of 16 nibble bytes) -----------------
+template <int MT, int R>
+__global__ void XNQ_MATVEC_BOUNDS matvec_q4k(WeightView w, ActView a, void *y, int y_dtype, int64_t ldy) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  const SmemAct sa = stage_activations(smem, a, QK_K, true);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t row0 = ((int64_t)blockIdx.x * WARPS + warp) * R;
+  if (row0 >= w.n) return;
+  const int m = (int)a.m;
+  const int64_t k = w.k, nsb = k / QK_K;
+  const int c = lane & 7;      // chunk of the super-block's qs
+  const int g = c >> 1;        // 64-element group: sub-blocks 2g (low nibbles) and 2g+1 (high nibbles)
+  const int eoff = (c & 1) * 16; // which 16 elements of those sub-blocks
+  float acc[R][MT];
+#pragma unroll
+  for (int r = 0; r < R; r++)
+#pragma unroll
+    for (int i = 0; i < MT; i++) acc[r][i] = 0.f;
+
+  for (int64_t sb = lane >> 3; sb < nsb; sb += 4) {
+    uint4 q[R];
+    float dd[R], dm[R];
+    int sc_lo[R], sc_hi[R], mn_lo[R], mn_hi[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+      const int64_t row = min(row0 + r, w.n - 1);
+      const uint8_t *blk = w.qs + (row * nsb + sb) * 144;
+      const uint4 hdr = ldg_stream(blk);
+      q[r] = ldg_stream(blk + 16 + 16 * c);
+      const __half2 h = *reinterpret_cast<const __half2 *>(&hdr.x);
+      dd[r] = __low2float(h);
+      dm[r] = __high2float(h);
+      const K4Scales ks = unpack_k4(hdr.y, hdr.z, hdr.w);
+      const uint32_t scw = (g < 2 ? ks.sc_lo : ks.sc_hi) >> (16 * (g & 1));
+      const uint32_t mnw = (g < 2 ? ks.mn_lo : ks.mn_hi) >> (16 * (g & 1));
+      sc_lo[r] = scw & 0xff;
+      sc_hi[r] = (scw >> 8) & 0xff;
+      mn_lo[r] = mnw & 0xff;
+      mn_hi[r] = (mnw >> 8) & 0xff;
+    }
+    const int64_t kbase = sb * QK_K + 64 * g + eoff;
+#pragma unroll
+    for (int i = 0; i < MT; i++) {
+      if (i < m) {
+        const int4 alo = *reinterpret_cast<const int4 *>(sa.q + (int64_t)i * k + kbase);
+        const int4 ahi = *reinterpret_cast<const int4 *>(sa.q + (int64_t)i * k + kbase + 32);
+        const float da = sa.d[(int64_t)i * nsb + sb];
+        const int16_t *bs = sa.bsum + (int64_t)i * (k / 16) + (kbase >> 4);
+        const int bs_lo = bs[0], bs_hi = bs[2];
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+          const int s_lo = dot16(and4(q[r], 0x0f0f0f0fu), alo, 0);
+          const int s_hi = dot16(and4(shr4(q[r], 4), 0x0f0f0f0fu), ahi, 0);
+          const int t1 = sc_lo[r] * s_lo + sc_hi[r] * s_hi;
+          const int t2 = mn_lo[r] * bs_lo + mn_hi[r] * bs_hi;
+          acc[r][i] += da * (dd[r] * (float)t1 - dm[r] * (float)t2);
+        }
+      }
+    }
+  }
+  reduce_store<MT, R>(acc, lane, row0, w.n, m, y, y_dtype, ldy);
+}
+
+// ---- Q6_K: 4 lanes per super-block; a lane takes 2 ql chunks + 1 qh chunk = 64 codes ---------------
+template <int MT, int R>
+__global__ void XNQ_MATVEC_BOUNDS matvec_q6k(WeightView w, ActView a, void *y, int y_dtype, int64_t ldy) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  const SmemAct sa = stage_activations(smem, a, QK_K, true);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t row0 = ((int64_t)blockIdx.x * WARPS + warp) * R;
+  if (row0 >= w.n) return;
+  const int m = (int)a.m;
+  const int64_t k = w.k, nsb = k / QK_K;
+  const int u = lane & 3, h = u >> 1, lh = u & 1; // half of the super-block, half of its 32 l-values
+  float acc[R][MT];
+#pragma unroll
+  for (int r = 0; r < R; r++)
+#pragma unroll
+    for (int i = 0; i < MT; i++) acc[r][i] = 0.f;
+
+  for (int64_t sb = lane >> 2; sb < nsb; sb += 8) {
+    const int64_t kbase = sb * QK_K + 128 * h + 16 * lh; // group gg adds 32*gg
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+      const int64_t row = min(row0 + r, w.n - 1);
+      const int64_t blk = row * nsb + sb;
+      const uint4 qa = ldg_stream(w.qs + blk * 128 + 64 * h + 16 * lh);
+      const uint4 qb = ldg_stream(w.qs + blk * 128 + 64 * h + 32 + 16 * lh);
+      const uint4 qh = ldg_stream(w.qh + blk * 64 + 32 * h + 16 * lh);
+      const uint2 scw = ldg_stream8(w.sc + blk * 16 + 8 * h);
+      const float dw = __half2float(w.d[row * w.dstride + sb]);
+      // 6-bit codes 0..63 of the four 16-element groups (k_quants.rs:1763-1770)
+      uint4 code[4];
+      code[0] = or4(and4(qa, 0x0f0f0f0fu), and4(shl4(qh, 4), 0x30303030u));
+      code[1] = or4(and4(qb, 0x0f0f0f0fu), and4(shl4(qh, 2), 0x30303030u));
+      code[2] = or4(and4(shr4(qa, 4), 0x0f0f0f0fu), and4(qh, 0x30303030u));
+      code[3] = or4(and4(shr4(qb, 4), 0x0f0f0f0fu), and4(shr4(qh, 2), 0x30303030u));
+      // int8 scales of groups gg: byte index lh + 2*gg of the half's 8 scale bytes
+      const uint64_t sc64 = ((uint64_t)scw.y << 32) | scw.x;
+      int sc[4];
+#pragma unroll
+      for (int gg = 0; gg < 4; gg++) sc[gg] = (int)(int8_t)((sc64 >> (8 * (lh + 2 * gg))) & 0xff);
+#pragma unroll
+      for (int i = 0; i < MT; i++) {
+        if (i < m) {
+          const int8_t *aq = sa.q + (int64_t)i * k + kbase;
+          const int16_t *bs = sa.bsum + (int64_t)i * (k / 16) + (kbase >> 4);
+          int t = 0;
+#pragma unroll
+          for (int gg = 0; gg < 4; gg++) {
+            const int4 av = *reinterpret_cast<const int4 *>(aq + 32 * gg);
+            const int s = dot16(code[gg], av, 0) - 32 * (int)bs[2 * gg]; // codes are stored +32
+            t += sc[gg] * s;
+          }
+          acc[r][i] += (dw * sa.d[(int64_t)i * nsb + sb]) * (float)t;
+        }
+      }
+    }
+  }
+  reduce_store<MT, R>(acc, lane, row0, w.n, m, y, y_dtype, ldy);
+}
+
+template <int MT, int R>
+int launch_mt(const WeightView &w, const ActView &a, void *y, int y_dtype, int64_t ldy, cudaStream_t s) {
+  const unsigned grid = (unsigned)((w.n + (int64_t)WARPS * R - 1) / ((int64_t)WARPS * R));
+  switch (w.dtype) {
+    case XNQ_Q4_0: {
+      const size_t sm = smem_act_bytes(a.m, a.k, QK, true);
+      matvec_q4_0<MT, R><<<grid, THREADS, sm, s>>>(w, a, y, y_dtype, ldy);
+      break;
+    }
+    case XNQ_Q8_0: {
+      const size_t sm = smem_act_bytes(a.m, a.k, QK, false);
+      matvec_q8_0<MT, R><<<grid, THREADS, sm, s>>>(w, a, y, y_dtype, ldy);
+      break;
+    }
+    case XNQ_Q4K: {
+      const size_t sm = smem_act_bytes(a.m, a.k, QK_K, true);
+      matvec_q4k<MT, R><<<grid, THREADS, sm, s>>>(w, a, y, y_dtype, ldy);
+      break;
+    }
+    case XNQ_Q6K: {
+      const size_t sm = smem_act_bytes(a.m, a.k, QK_K, true);
+      matvec_q6k<MT, R><<<grid, THREADS, sm, s>>>(w, a, y, y_dtype, ldy);
+      break;
+    }
+    default: return fail(XNQ_ERR_DTYPE, "matvec: dtype %d", w.dtype);
+  }
+  XNQ_CUDA(cudaGetLastError());
+  count_launch();
+  return XNQ_OK;
+}
+
+constexpr size_t MAX_DYN_SMEM = 200 * 1024;
+
+template <int MT, int R>
+int init_mt() {
+  XNQ_CUDA(cudaFuncSetAttribute(matvec_q4_0<MT, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM));
+  XNQ_CUDA(cudaFuncSetAttribute(matvec_q8_0<MT, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM));
+  XNQ_CUDA(cudaFuncSetAttribute(matvec_q4k<MT, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM));
+  XNQ_CUDA(cudaFuncSetAttribute(matvec_q6k<MT, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM));
+  return XNQ_OK;
+}
+
+} // namespace
+
+// Largest number of activation rows whose quantized image fits the shared-memory budget.
+int64_t matvec_rows_per_pass(int wdtype, int64_t k) {
+  const int blk = (wdtype == XNQ_Q4_0 || wdtype == XNQ_Q8_0) ? QK : QK_K;
+  const bool with_bsum = wdtype != XNQ_Q8_0;
+  int64_t rows = MATVEC_MAX_M;
+  while (rows > 1 && smem_act_bytes(rows, k, blk, with_bsum) > MAX_DYN_SMEM) rows >>= 1;
+  if (smem_act_bytes(rows, k, blk, with_bsum) > MAX_DYN_SMEM) return 0;
+  return rows;
+}
+
+int launch_matvec(const WeightView &w, const ActView &a, void *y, int y_dtype, int64_t ldy, cudaStream_t s) {
+  if (w.n == 0 || a.m == 0) return XNQ_OK;
+  if (a.m > MATVEC_MAX_M) return fail(XNQ_ERR_SHAPE, "matvec: m=%lld exceeds %d", (long long)a.m, MATVEC_MAX_M);
+  if (a.m == 1) return launch_mt<1, 2>(w, a, y, y_dtype, ldy, s);
+  if (a.m == 2) return launch_mt<2, 2>(w, a, y, y_dtype, ldy, s);
+  if (a.m <= 4) return launch_mt<4, 2>(w, a, y, y_dtype, ldy, s);
+  if (a.m <= 8) return launch_mt<8, 1>(w, a, y, y_dtype, ldy, s);
+  return launch_mt<16, 1>(w, a, y, y_dtype, ldy, s);
+}
+
+int matvec_init(int) {
+  int rc;
+  if ((rc = init_mt<1, 2>()) != XNQ_OK) return rc;
+  if ((rc = init_mt<2, 2>()) != XNQ_OK) return rc;
+  if ((rc = init_mt<4, 2>()) != XNQ_OK) return rc;
+  if ((rc = init_mt<8, 1>()) != XNQ_OK) return rc;
+  if ((rc = init_mt<16, 1>()) != XNQ_OK) return rc;
+  return XNQ_OK;
+}
+
+} // namespace xnq

@@ -1,0 +1,279 @@
+"""Host-side mirror of xn-core's quantized operator API, over the xnq C ABI.
+
+Names, argument meaning and error behaviour follow the reference so that its tests read the same
+here:
+
+=====================  ==========================================================================
+``QTensor``            xn-core/src/quantized/mod.rs:27-340 (host blocks + shape; canonical bytes)
+``QCudaTensor``        the device weight; API of ``Q8Tensor`` (cuda_backend/q8.rs:26-157)
+``QCudaLinear``        ``Q8Linear`` (q8.rs:160-185) / ``QLinear`` (mod.rs:342-406)
+``Q40 Q80 Q4K Q6K``    ``BackendQ`` implementations (lib.rs:141-156; q8.rs:187-224)
+=====================  ==========================================================================
+
+torch supplies device memory, streams and tensors; every computation happens in ``libxnq.so``.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import XnqError, check
+from .dtypes import GgmlDType
+
+_TORCH_TO_XNQ = {torch.float32: GgmlDType.F32, torch.float16: GgmlDType.F16, torch.bfloat16: GgmlDType.BF16}
+
+
+def _stream_ptr(device: torch.device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+_inited: set[int] = set()
+
+
+def init(device: torch.device | int | str = "cuda:0") -> None:
+    """``xnq_init`` for the device (idempotent). Call before capturing a CUDA graph."""
+    dev = torch.device(device) if not isinstance(device, int) else torch.device("cuda", device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    if idx in _inited:
+        return
+    torch.cuda.init()
+    with torch.cuda.device(idx):
+        torch.empty(1, device=f"cuda:{idx}")  # make the primary context current on this thread
+        check(_lib.lib().xnq_init(idx))
+    _inited.add(idx)
+
+
+class QTensor:
+    """Quantized blocks in host memory with a shape (mod.rs:27-340). ``data()`` is canonical GGUF bytes."""
+
+    def __init__(self, data: np.ndarray | bytes, shape: Sequence[int], dtype: GgmlDType):
+        dtype = GgmlDType(dtype)
+        shape = tuple(int(d) for d in shape)
+        if len(shape) == 0:
+            raise ValueError(f"scalar tensor cannot be quantized {shape}")  # mod.rs:264-266
+        if shape[-1] % dtype.block_size:
+            raise ValueError(
+                f"quantized tensor must have their last dim divisible by block size {shape} {dtype.block_size}")  # mod.rs:267-272
+        buf = np.frombuffer(data, np.uint8) if isinstance(data, (bytes, bytearray, memoryview)) else np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+        want = int(np.prod(shape)) // dtype.block_size * dtype.type_size
+        if buf.size != want:
+            raise ValueError(f"{dtype.name} {shape} wants {want} bytes of blocks, got {buf.size}")
+        self._data, self._shape, self._dtype = buf, shape, dtype
+
+    @classmethod
+    def new(cls, data, shape, dtype) -> "QTensor":
+        return cls(data, shape, dtype)
+
+    def dtype(self) -> GgmlDType:
+        return self._dtype
+
+    def rank(self) -> int:
+        return len(self._shape)
+
+    def shape(self) -> tuple[int, ...]:
+        return self._shape
+
+    def storage_size_in_bytes(self) -> int:
+        return int(self._data.size)
+
+    def data(self) -> np.ndarray:
+        """Canonical on-disk bytes (mod.rs:330-332)."""
+        return self._data
+
+
+class QCudaTensor:
+    """A ``(n, k)`` quantized weight (or an N-shard of one) resident on a CUDA device."""
+
+    def __init__(self, handle: int, device: torch.device):
+        self._h = ctypes.c_void_p(handle)
+        self.device = device
+        dt, nt, nl, r0, k, nb = ctypes.c_int(), ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64(), ctypes.c_size_t()
+        check(_lib.lib().xnq_weight_info(self._h, dt, nt, nl, r0, k, nb))
+        self._dtype = GgmlDType(dt.value)
+        self.n_total, self.n, self.row0, self.k, self.device_bytes = nt.value, nl.value, r0.value, k.value, nb.value
+        self._ws: Optional[torch.Tensor] = None
+
+    # -- construction ---------------------------------------------------------------------------
+    @classmethod
+    def from_qtensor(cls, qt: QTensor, device: torch.device | str = "cuda:0", shard_rank: int = 0,
+                     shard_count: int = 1) -> "QCudaTensor":
+        """Take GGUF blocks as they are (``Q8Tensor::from_q8_0``, q8.rs:60-85)."""
+        device = torch.device(device)
+        if qt.dtype() not in (GgmlDType.Q4_0, GgmlDType.Q8_0, GgmlDType.Q4K, GgmlDType.Q6K):
+            raise ValueError(f"cuda quantized: expected a Q4_0/Q8_0/Q4K/Q6K tensor, got {qt.dtype().name}")
+        if qt.rank() != 2:
+            raise ValueError(f"cuda quantized: expected a 2-d weight, got shape {qt.shape()}")
+        n, k = qt.shape()
+        init(device)
+        out = ctypes.c_void_p()
+        buf = qt.data()
+        with torch.cuda.device(device):
+            check(_lib.lib().xnq_weight_upload(int(qt.dtype()), ctypes.c_void_p(buf.ctypes.data), buf.size, n, k,
+                                               shard_rank, shard_count, _stream_ptr(device), ctypes.byref(out)))
+        return cls(out.value, device)
+
+    @classmethod
+    def from_rows(cls, dtype: GgmlDType, blocks: np.ndarray, n_total: int, k: int, row0: int, n_rows: int,
+                  device: torch.device | str = "cuda:0") -> "QCudaTensor":
+        """Upload rows ``[row0, row0 + n_rows)`` of an ``[n_total, k]`` weight from their own bytes."""
+        device = torch.device(device)
+        init(device)
+        out = ctypes.c_void_p()
+        buf = np.ascontiguousarray(blocks).view(np.uint8).reshape(-1)
+        with torch.cuda.device(device):
+            check(_lib.lib().xnq_weight_upload_rows(int(dtype), ctypes.c_void_p(buf.ctypes.data), buf.size, n_total, k, row0,
+                                                    n_rows, _stream_ptr(device), ctypes.byref(out)))
+        return cls(out.value, device)
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            try:
+                _lib.lib().xnq_weight_free(h)
+            except Exception:
+                pass
+
+    # -- queries --------------------------------------------------------------------------------
+    def dtype(self) -> GgmlDType:
+        return self._dtype
+
+    def shape(self) -> tuple[int, int]:
+        """Shape of the rows held on this device."""
+        return (self.n, self.k)
+
+    def data(self) -> np.ndarray:
+        """Canonical GGUF bytes of the held rows, back on the host."""
+        out = np.empty(self.n * self._dtype.row_bytes(self.k), np.uint8)
+        with torch.cuda.device(self.device):
+            check(_lib.lib().xnq_weight_canonical_bytes(self._h, ctypes.c_void_p(out.ctypes.data), out.size, _stream_ptr(self.device)))
+        return out
+
+    def dequantize(self, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        """The weight as a dense ``(n, k)`` matrix (q8.rs:94-113)."""
+        out = torch.empty((self.n, self.k), dtype=dtype, device=self.device)
+        with torch.cuda.device(self.device):
+            check(_lib.lib().xnq_weight_dequantize(self._h, int(_TORCH_TO_XNQ[dtype]), ctypes.c_void_p(out.data_ptr()), _stream_ptr(self.device)))
+        return out
+
+    # -- compute --------------------------------------------------------------------------------
+    def workspace(self, m: int) -> torch.Tensor:
+        need = _lib.lib().xnq_matmul_workspace_bytes(self._h, m)
+        if self._ws is None or self._ws.numel() < need:
+            self._ws = torch.empty(max(need, 256), dtype=torch.uint8, device=self.device)
+        return self._ws
+
+    def matmul_t(self, lhs: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``lhs @ self^T`` with ``lhs`` of shape ``(.., k)``; the result is ``(.., n)`` (q8.rs:116-157)."""
+        if lhs.shape[-1] != self.k:
+            raise ValueError(f"cuda quantized matmul: input {tuple(lhs.shape)} does not match weight (n={self.n}, k={self.k})")
+        if lhs.dtype not in _TORCH_TO_XNQ:
+            raise ValueError(f"cuda quantized matmul: unsupported activation dtype {lhs.dtype}")
+        if lhs.device != self.device:
+            raise ValueError(f"cuda quantized matmul: input on {lhs.device}, weight on {self.device}")
+        x = lhs.reshape(-1, self.k)
+        if x.stride(-1) != 1 or (x.shape[0] > 1 and x.stride(0) < self.k):
+            x = x.contiguous()
+        m = x.shape[0]
+        ldx = x.stride(0) if m > 1 else self.k
+        if out is None:
+            out = torch.empty(lhs.shape[:-1] + (self.n,), dtype=lhs.dtype, device=self.device)
+        y = out.view(-1, self.n)
+        ws = self.workspace(m)
+        with torch.cuda.device(self.device):
+            check(_lib.lib().xnq_matmul_t(self._h, ctypes.c_void_p(x.data_ptr()), int(_TORCH_TO_XNQ[x.dtype]), m, ldx,
+                                          ctypes.c_void_p(y.data_ptr()), int(_TORCH_TO_XNQ[y.dtype]), y.stride(0) if m > 1 else self.n,
+                                          ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(self.device)))
+        return out
+
+    def forward_host(self, x: np.ndarray, bias: Optional[np.ndarray] = None) -> np.ndarray:
+        """``QLinear::forward`` on host arrays (mod.rs:352-384): H2D copy, matmul, optional bias, D2H copy, sync."""
+        x = np.ascontiguousarray(x, np.float32)
+        if x.ndim < 2:
+            raise ValueError(f"input tensor has only one dimension {x.shape}")  # mod.rs:363-365
+        if x.shape[-1] != self.k:
+            raise ValueError(f"input tensor {x.shape} incompatible with {(self.n, self.k)}")  # mod.rs:368-370
+        m = int(np.prod(x.shape[:-1]))
+        y = np.empty(x.shape[:-1] + (self.n,), np.float32)
+        b = None if bias is None else np.ascontiguousarray(bias, np.float32)
+        if b is not None and b.shape != (self.n,):
+            raise ValueError(f"bias shape {b.shape} does not match n={self.n}")
+        with torch.cuda.device(self.device):
+            check(_lib.lib().xnq_linear_forward_host(self._h, ctypes.c_void_p(x.ctypes.data), m,
+                                                     ctypes.c_void_p(b.ctypes.data) if b is not None else None,
+                                                     ctypes.c_void_p(y.ctypes.data), _stream_ptr(self.device)))
+        return y
+
+
+class QCudaLinear:
+    """A linear layer with GGUF-quantized weights on the device (``Q8Linear``, q8.rs:160-185)."""
+
+    def __init__(self, weight: QCudaTensor, bias: Optional[torch.Tensor] = None):
+        if bias is not None and tuple(bias.shape) != (weight.n,):
+            raise ValueError(f"bias shape {tuple(bias.shape)} does not match out_features {weight.n}")
+        self.weight, self.bias = weight, bias
+
+    @classmethod
+    def new(cls, weight: QCudaTensor, bias: Optional[torch.Tensor] = None) -> "QCudaLinear":
+        return cls(weight, bias)
+
+    def forward(self, xs: torch.Tensor) -> torch.Tensor:
+        if xs.dim() < 2:
+            raise ValueError(f"input tensor has only one dimension {tuple(xs.shape)}")  # mod.rs:363-365
+        out = self.weight.matmul_t(xs)
+        return out if self.bias is None else out + self.bias.to(out.dtype)  # broadcast_add, q8.rs:172-175
+
+    __call__ = forward
+
+
+def quantize_act(x: torch.Tensor, act_dtype: GgmlDType) -> torch.Tensor:
+    """Canonical Q8_0 / Q8_K activation blocks of ``x`` ``[m, k]`` as a uint8 device tensor."""
+    act_dtype = GgmlDType(act_dtype)
+    if x.dim() != 2 or x.stride(-1) != 1:
+        raise ValueError("quantize_act wants a 2-d tensor with contiguous rows")
+    m, k = x.shape
+    init(x.device)
+    nbytes = m * (k // act_dtype.block_size) * act_dtype.type_size if k % act_dtype.block_size == 0 else 0
+    out = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        check(_lib.lib().xnq_quantize_act(int(act_dtype), ctypes.c_void_p(x.data_ptr()), int(_TORCH_TO_XNQ[x.dtype]), m, k,
+                                          x.stride(0) if m > 1 else k, ctypes.c_void_p(out.data_ptr()), _stream_ptr(x.device)))
+    return out[:nbytes]
+
+
+class _BackendQ:
+    """``BackendQ`` for the CUDA device with one GGML weight format (lib.rs:141-156)."""
+    DTYPE: GgmlDType
+
+    @classmethod
+    def linear_from_qtensor(cls, qt: QTensor, in_features: int, out_features: int, device="cuda:0", shard_rank: int = 0,
+                            shard_count: int = 1) -> QCudaLinear:
+        """The ``linear_load`` branch that takes a file's blocks as they are (q8.rs:203-213): dtype and
+        shape must match; weight only, no bias."""
+        if qt.dtype() != cls.DTYPE:
+            raise ValueError(f"cuda {cls.DTYPE.name}: expected a {cls.DTYPE.name} tensor, got {qt.dtype().name}")
+        if tuple(qt.shape()) != (out_features, in_features):
+            raise ValueError(f"cuda {cls.DTYPE.name}: weight is {list(qt.shape())}, expected [{out_features}, {in_features}]")
+        return QCudaLinear(QCudaTensor.from_qtensor(qt, device, shard_rank, shard_count), None)
+
+
+class Q40(_BackendQ):
+    DTYPE = GgmlDType.Q4_0
+
+
+class Q80(_BackendQ):
+    DTYPE = GgmlDType.Q8_0
+
+
+class Q4K(_BackendQ):
+    DTYPE = GgmlDType.Q4K
+
+
+class Q6K(_BackendQ):
+    DTYPE = GgmlDType.Q6K
+
+
+__all__ = ["QTensor", "QCudaTensor", "QCudaLinear", "Q40", "Q80", "Q4K", "Q6K", "GgmlDType", "XnqError", "init", "quantize_act"]
