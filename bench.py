@@ -185,6 +185,9 @@ def run_ours(args, name, dt, n, k, m):
         dist.init_process_group("nccl", device_id=dev)
     Q.init(dev)
     L = _lib.lib()
+    for opt in args.option:
+        name, val = opt.split("=")
+        _lib.check(L.xnq_set_option(name.encode(), int(val)))
 
     props = torch.cuda.get_device_properties(dev)
     l2 = int(getattr(props, "L2_cache_size", 126 * 1024 * 1024))
@@ -336,7 +339,8 @@ def run_ours(args, name, dt, n, k, m):
                    "cache": f"cold: {ncopies} distinct weights per step = {ncopies * w_bytes_local / 1e6:.0f} MB per GPU, "
                             f"L2 is {l2 / 1e6:.0f} MB",
                    "parallelism": f"N-sharded x{world}" + (" + NCCL all-gather" if world > 1 else ""),
-                   "launch": "cuda graph replay" if graph is not None else "plain launches"},
+                   "launch": "cuda graph replay" if graph is not None else "plain launches",
+                   "options": args.option},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": (achieved / peak) if achieved else None, "traffic": None,
                      "kernel": "matvec", "launch_us": kern_ms * 1e3, "launches_timed": cnt.value,
@@ -361,6 +365,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--option", action="append", default=[], help="library switch NAME=INT (A/B measurements), e.g. matvec_tma=0")
     args = ap.parse_args()
     dt, n, k, m = WORKLOADS[args.workload]
     if args.impl == "reference":

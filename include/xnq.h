@@ -125,6 +125,20 @@ int xnq_matmul_t(const xnq_weight *w, const void *x, int x_dtype, int64_t m, int
 int xnq_linear_forward_host(xnq_weight *w, const float *x_host, int64_t m, const float *bias_host,
                             float *y_host, void *stream);
 
+/* Sticky device-side status bits of this library's kernels on the current device (0 = healthy):
+ * bit 0 a consumer's bounded mbarrier wait expired, bit 1 a producer's, bit 2 a self-check refused an
+ * access. Synchronizes the device.
+ * No counterpart in the reference (its kernels never wait on anything). */
+int xnq_device_status(unsigned int *bits);
+/* When bit 2 of the status is set, a kernel's self-check refused an out-of-range copy or store
+ * instead of performing it; this returns what it recorded first: code, block, iteration, offset,
+ * bytes, limit (two spare words). Synchronizes the device. No counterpart in the reference. */
+int xnq_device_check_record(unsigned long long out[8]);
+/* Tuning switches, for A/B measurements: "matvec_tma" (default 1) selects the persistent TMA-ring
+ * decode kernel for m == 1, k <= 4096; 0 forces the plain streaming-load kernel. No counterpart in
+ * the reference. */
+int xnq_set_option(const char *name, int value);
+
 /* ---- measurement hooks (no counterpart in the reference, which times with CudaEvent::elapsed_ms
  * around whole operators, cuda_backend/mod.rs:76-100) ------------------------------------------ */
 

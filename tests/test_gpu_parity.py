@@ -62,7 +62,7 @@ def _tricky(m, k, seed):
         x[1, 5] = 1e-30
     if m > 2:
         x[2, :256] = np.clip(x[2, :256], -3.25, 3.25)
-        x[2, 7], x[2, 200] = 3.25, -3.25
+        x[2, 7], x[2, min(200, k - 1)] = 3.25, -3.25
     if m > 3:
         x[3] = np.round(x[3] * 4) / 8
     return x
@@ -246,3 +246,42 @@ def test_full_size_properties_without_oracle(Q, dt):
     rb = dt.row_bytes(k)
     sub = Q.QCudaTensor.from_rows(dt, w[1000 * rb:1512 * rb], n, k, 1000, 512, DEV)
     assert torch.equal(sub.matmul_t(x), got[:, 1000:1512])
+
+
+@pytest.mark.parametrize("dt", WEIGHT_TYPES)
+@pytest.mark.parametrize("n,k", [(1, 256), (15, 512), (16, 1024), (17, 2048), (1000, 4096), (4096, 4096)])
+def test_tma_ring_decode_kernel_matches_oracle_and_plain_kernel(Q, O, dt, n, k):
+    """m == 1, k <= 4096 takes the persistent TMA-ring kernel; forcing the plain kernel must give
+    results within f32 summation order of it, and both must match the oracle."""
+    from xn_b200 import _lib
+    L = _lib.lib()
+    w = synth.make_weight(dt, n, k, seed=100)
+    t = _upload(Q, dt, w, n, k)
+    x = _tricky(1, k, 100)
+    xd = torch.from_numpy(x).to(DEV)
+    want = O.matmul(int(dt), x, w, n)
+    try:
+        _lib.check(L.xnq_set_option(b"matvec_tma", 1))
+        got_tma = t.matmul_t(xd).cpu().numpy()
+        _lib.check(L.xnq_set_option(b"matvec_tma", 0))
+        got_plain = t.matmul_t(xd).cpu().numpy()
+    finally:
+        _lib.check(L.xnq_set_option(b"matvec_tma", 1))
+    assert_close_ref(got_tma, want, TOL_F32, f"tma {dt.name} n={n} k={k}")
+    assert_close_ref(got_plain, want, TOL_F32, f"plain {dt.name} n={n} k={k}")
+    assert_close_ref(got_tma, got_plain, 1e-4, "tma vs plain")
+    for td in (torch.float16, torch.bfloat16):
+        xh = torch.from_numpy(x).to(td)
+        want_h = O.matmul(int(dt), xh.float().numpy(), w, n)
+        got_h = t.matmul_t(xh.to(DEV)).float().cpu().numpy()
+        err = np.abs(got_h - want_h) / np.maximum(np.abs(want_h), 1.0)
+        assert err.max() <= (2e-3 if td == torch.float16 else 1e-2)
+
+
+def test_zz_device_status_is_clean(Q):
+    """No bounded wait inside any kernel of this session expired."""
+    import ctypes
+    from xn_b200 import _lib
+    bits = ctypes.c_uint(123)
+    _lib.check(_lib.lib().xnq_device_status(ctypes.byref(bits)))
+    assert bits.value == 0, f"device status bits {bits.value:#x}"

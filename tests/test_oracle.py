@@ -102,7 +102,7 @@ def _tricky_activations(m, k, seed):
         x[1, :] = 0.0
         x[1, 5] = 1e-30
     if m > 2:
-        x[2, 7], x[2, 200] = 3.25, -3.25          # |x| tie: the first one sets the Q8_K scale's sign
+        x[2, 7], x[2, min(200, k - 1)] = 3.25, -3.25   # |x| tie: the first one sets the Q8_K scale's sign
         x[2, :256] = np.clip(x[2, :256], -3.25, 3.25)
     if m > 3:
         x[3] = np.round(x[3] * 4) / 8             # many exact .5 products: round half away from zero

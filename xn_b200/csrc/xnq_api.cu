@@ -23,6 +23,7 @@ int fail(int code, const char *fmt, ...) {
 void clear_error() { g_err[0] = 0; }
 
 static std::atomic<uint64_t> g_launches{0};
+static std::atomic<bool> g_opt_matvec_tma{true};
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 
 struct Profile {
@@ -152,7 +153,40 @@ int xnq_init(int device) {
   if ((rc = layout_init(device)) != XNQ_OK) return rc;
   if ((rc = quantize_init(device)) != XNQ_OK) return rc;
   if ((rc = matvec_init(device)) != XNQ_OK) return rc;
+  if ((rc = matvec_tma_init(device)) != XNQ_OK) return rc;
   return XNQ_OK;
+}
+
+int xnq_device_status(unsigned int *bits) {
+  clear_error();
+  if (!bits) return fail(XNQ_ERR_NULL, "device_status: bits is NULL");
+  return matvec_status(bits);
+}
+
+int xnq_device_check_record(unsigned long long out[8]) {
+  clear_error();
+  if (!out) return fail(XNQ_ERR_NULL, "device_check_record: out is NULL");
+  return matvec_check_record(out);
+}
+
+int xnq_debug_trace(unsigned long long *out, unsigned int *n) {
+  clear_error();
+  if (!out || !n) return fail(XNQ_ERR_NULL, "debug_trace: NULL");
+  return matvec_trace(out, n);
+}
+
+int xnq_set_option(const char *name, int value) {
+  clear_error();
+  if (!name) return fail(XNQ_ERR_NULL, "set_option: name is NULL");
+  if (std::strcmp(name, "matvec_tma") == 0) {
+    g_opt_matvec_tma.store(value != 0);
+    return XNQ_OK;
+  }
+  if (std::strcmp(name, "matvec_tma_dbg") == 0) {
+    matvec_tma_set_dbg(value);
+    return XNQ_OK;
+  }
+  return fail(XNQ_ERR_UNSUPPORTED, "set_option: unknown option '%s'", name);
 }
 
 int xnq_weight_upload_rows(int dtype, const void *blocks, size_t nbytes, int64_t n_total, int64_t k, int64_t row0, int64_t n_rows,
@@ -201,10 +235,6 @@ int xnq_weight_upload_rows(int dtype, const void *blocks, size_t nbytes, int64_t
   do {
     if ((e = cudaMemsetAsync(w->base, 0, p.total, s)) != cudaSuccess) break;
     if (nbytes == 0) break;
-    if (dtype == XNQ_Q4K) { // GGUF layout is the device layout
-      e = cudaMemcpyAsync(w->base, blocks, nbytes, cudaMemcpyHostToDevice, s);
-      break;
-    }
     if ((e = cudaMalloc(&staging, nbytes)) != cudaSuccess) break;
     if ((e = cudaMemcpyAsync(staging, blocks, nbytes, cudaMemcpyHostToDevice, s)) != cudaSuccess) break;
     rc = launch_relayout(w->v, static_cast<const uint8_t *>(staging), s);
@@ -280,11 +310,6 @@ int xnq_weight_canonical_bytes(const xnq_weight *w, void *host_dst, size_t nbyte
   if (want == 0) return XNQ_OK;
   if (!host_dst) return fail(XNQ_ERR_NULL, "canonical_bytes: host_dst is NULL");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (w->v.dtype == XNQ_Q4K) {
-    XNQ_CUDA(cudaMemcpyAsync(host_dst, w->v.qs, want, cudaMemcpyDeviceToHost, s));
-    XNQ_CUDA(cudaStreamSynchronize(s));
-    return XNQ_OK;
-  }
   void *staging = nullptr;
   XNQ_CUDA(cudaMalloc(&staging, want));
   int rc = launch_to_canonical(w->v, static_cast<uint8_t *>(staging), s);
@@ -348,6 +373,13 @@ int xnq_matmul_t(const xnq_weight *w, const void *x, int x_dtype, int64_t m, int
   if (pass == 0) return fail(XNQ_ERR_SIZE, "matmul_t: k = %lld is too large for the shared-memory staging of one activation row", (long long)k);
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (g_opt_matvec_tma.load(std::memory_order_relaxed) && matvec_tma_supported(w->v, m)) {
+    // decode fast path: one kernel, activations quantized in its prologue, no scratch
+    profile_mark(s, true);
+    rc = launch_matvec_tma(w->v, x, x_dtype, y, y_dtype, s);
+    profile_mark(s, false);
+    return rc;
+  }
   const int adt = act_dtype_for(w->v.dtype);
   const size_t xes = type_size(x_dtype), yes = type_size(y_dtype);
   for (int64_t r0 = 0; r0 < m; r0 += pass) {

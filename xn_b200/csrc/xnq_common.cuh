@@ -66,7 +66,8 @@ inline int act_dtype_for(int wdt) { return (wdt == XNQ_Q4_0 || wdt == XNQ_Q8_0) 
 //         d   [n][dstride]   f16 block scales
 //  Q8_0 : qs  [n][k]         int8 codes
 //         d   [n][dstride]   f16 block scales
-//  Q4_K : qs  = the canonical 144-byte super-blocks, untouched (144 = 9 x 16 B: already aligned)
+//  Q4_K : qs  = the 144-byte super-blocks in GGUF order (144 = 9 x 16 B: already aligned); only the
+//               12 scale bytes are re-packed into four 24-bit per-group fields (xnq_unpack.cuh)
 //  Q6_K : qs  [n][k/256][128] ql bytes,  qh [n][k/256][64],  sc [n][k/256][16] int8,
 //         d   [n][dstride]   f16 super-block scales
 // dstride (elements) is the scale count per row rounded up to 8, so every row of d starts 16-byte
@@ -139,6 +140,15 @@ int launch_matvec(const WeightView &w, const ActView &a, void *y, int y_dtype, i
 int matvec_init(int device);
 // activation rows one matvec launch can stage in shared memory for this k (0: k is too large)
 int64_t matvec_rows_per_pass(int wdtype, int64_t k);
+
+// xnq_matvec_tma.cu  (m == 1, k <= 4096: persistent TMA-ring kernel that quantizes x in its prologue)
+bool matvec_tma_supported(const WeightView &w, int64_t m);
+int launch_matvec_tma(const WeightView &w, const void *x, int x_dtype, void *y, int y_dtype, cudaStream_t s);
+int matvec_tma_init(int device);
+int matvec_status(unsigned int *bits);
+void matvec_tma_set_dbg(int v);
+int matvec_check_record(unsigned long long out[8]);
+int matvec_trace(unsigned long long *out, unsigned int *n);
 
 // xnq_bias.cu-ish helper in xnq_layout.cu: y[m, n] += bias[n]
 int launch_add_bias(float *y, const float *bias, int64_t m, int64_t n, int64_t ldy, cudaStream_t s);

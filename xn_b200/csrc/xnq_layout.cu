@@ -58,6 +58,26 @@ __global__ void relayout_q6k(const uint8_t *__restrict__ src, uint8_t *__restric
   }
 }
 
+// Q4_K: blocks stay where they are; one thread per super-block re-packs the 12 scale bytes
+template <bool TO_DEVICE>
+__global__ void repack_q4k(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, int64_t nblocks) {
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i >= nblocks) return;
+  const uint4 *s = reinterpret_cast<const uint4 *>(src + i * 144);
+  uint4 *o = reinterpret_cast<uint4 *>(dst + i * 144);
+  uint4 hdr = s[0];
+  const uint32_t in[3] = {hdr.y, hdr.z, hdr.w};
+  uint32_t out[3];
+  if (TO_DEVICE) k4_fields_from_gguf(in, out);
+  else k4_fields_to_gguf(in, out);
+  hdr.y = out[0];
+  hdr.z = out[1];
+  hdr.w = out[2];
+  o[0] = hdr;
+#pragma unroll
+  for (int j = 1; j < 9; j++) o[j] = s[j];
+}
+
 // ---- device layout -> GGUF blocks ----------------------------------------------------------------
 __global__ void canonical_q4_0(uint8_t *__restrict__ dst, const uint8_t *__restrict__ qs, const __half *__restrict__ d,
                                int64_t n, int64_t nblk, int64_t dstride) {
@@ -155,7 +175,8 @@ int launch_relayout(const WeightView &v, const uint8_t *src, cudaStream_t s) {
       relayout_q6k<<<grid_for(v.n * nblk * 105), TPB, 0, s>>>(src, const_cast<uint8_t *>(v.qs), const_cast<uint8_t *>(v.qh),
                                                               const_cast<int8_t *>(v.sc), const_cast<__half *>(v.d), v.n, nblk, v.dstride);
       break;
-    default: return fail(XNQ_ERR_DTYPE, "relayout: dtype %d keeps its GGUF layout", v.dtype);
+    case XNQ_Q4K: repack_q4k<true><<<grid_for(v.n * nblk), TPB, 0, s>>>(src, const_cast<uint8_t *>(v.qs), v.n * nblk); break;
+    default: return fail(XNQ_ERR_DTYPE, "relayout: dtype %d", v.dtype);
   }
   XNQ_CUDA(cudaGetLastError());
   count_launch();
@@ -169,7 +190,8 @@ int launch_to_canonical(const WeightView &v, uint8_t *dst, cudaStream_t s) {
     case XNQ_Q4_0: canonical_q4_0<<<grid_for(v.n * nblk), TPB, 0, s>>>(dst, v.qs, v.d, v.n, nblk, v.dstride); break;
     case XNQ_Q8_0: canonical_q8_0<<<grid_for(v.n * nblk), TPB, 0, s>>>(dst, v.qs, v.d, v.n, nblk, v.dstride); break;
     case XNQ_Q6K: canonical_q6k<<<grid_for(v.n * nblk * 105), TPB, 0, s>>>(dst, v.qs, v.qh, v.sc, v.d, v.n, nblk, v.dstride); break;
-    default: return fail(XNQ_ERR_DTYPE, "to_canonical: dtype %d keeps its GGUF layout", v.dtype);
+    case XNQ_Q4K: repack_q4k<false><<<grid_for(v.n * nblk), TPB, 0, s>>>(v.qs, dst, v.n * nblk); break;
+    default: return fail(XNQ_ERR_DTYPE, "to_canonical: dtype %d", v.dtype);
   }
   XNQ_CUDA(cudaGetLastError());
   count_launch();
@@ -206,6 +228,8 @@ int layout_init(int) {
   XNQ_CUDA(cudaFuncGetAttributes(&fa, canonical_q4_0));
   XNQ_CUDA(cudaFuncGetAttributes(&fa, canonical_q8_0));
   XNQ_CUDA(cudaFuncGetAttributes(&fa, canonical_q6k));
+  XNQ_CUDA(cudaFuncGetAttributes(&fa, repack_q4k<true>));
+  XNQ_CUDA(cudaFuncGetAttributes(&fa, repack_q4k<false>));
   XNQ_CUDA(cudaFuncGetAttributes(&fa, dequantize_kernel<float>));
   XNQ_CUDA(cudaFuncGetAttributes(&fa, dequantize_kernel<__half>));
   XNQ_CUDA(cudaFuncGetAttributes(&fa, dequantize_kernel<__nv_bfloat16>));

@@ -224,13 +224,11 @@ __global__ void XNQ_MATVEC_BOUNDS matvec_q4k(WeightView w, ActView a, void *y, i
       const __half2 h = *reinterpret_cast<const __half2 *>(&hdr.x);
       dd[r] = __low2float(h);
       dm[r] = __high2float(h);
-      const K4Scales ks = unpack_k4(hdr.y, hdr.z, hdr.w);
-      const uint32_t scw = (g < 2 ? ks.sc_lo : ks.sc_hi) >> (16 * (g & 1));
-      const uint32_t mnw = (g < 2 ? ks.mn_lo : ks.mn_hi) >> (16 * (g & 1));
-      sc_lo[r] = scw & 0xff;
-      sc_hi[r] = (scw >> 8) & 0xff;
-      mn_lo[r] = mnw & 0xff;
-      mn_hi[r] = (mnw >> 8) & 0xff;
+      const uint32_t f = k4_field(hdr.y, hdr.z, hdr.w, g);
+      sc_lo[r] = f & 63;
+      sc_hi[r] = (f >> 6) & 63;
+      mn_lo[r] = (f >> 12) & 63;
+      mn_hi[r] = f >> 18;
     }
     const int64_t kbase = sb * QK_K + 64 * g + eoff;
 #pragma unroll

@@ -1,0 +1,717 @@
+// Decode matvec, m == 1, k <= 4096: persistent TMA-ring kernel.
+//
+// Two CTAs per SM each own a contiguous band of weight rows. A producer thread streams the band
+// through a ring of shared-memory stages with 1-D bulk-async copies (cp.async.bulk, the non-tensor
+// form of TMA; never multicast) that complete on mbarriers, so tens of KB per SM are in flight from
+// the first cycle without holding registers. Eight consumer warps take R rows of a stage each.
+//
+// The activation row is quantized in the kernel's prologue (same device function, same bytes as the
+// stand-alone quantizer; the reference's quantize_lhs, k_quants.rs:2015-2026) and every lane then
+// keeps ITS slices of the int8 activations, block scales and block sums in registers for the whole
+// kernel: a lane always works on the same k positions of every row, so the main loop reads shared
+// memory only for weights, and the R rows of a warp share those registers.
+//
+// Launch overlap. A CTA uses at most half an SM (shared memory, registers, threads) and the kernel is
+// launched with programmatic stream serialization: the next launch in the stream may start while
+// this one drains. Its producer begins prefetching weights at once (weights are immutable after
+// upload); only its consumers execute griddepcontrol.wait before they read x or write y, so results
+// are ordered exactly as without the overlap.
+//
+// The dot arithmetic is that of xnq_matvec.cu (exact integer block sums, f32 scales, f32
+// accumulate; k_quants.rs:287-304, 677-691, 1337-1416, 1743-1799).
+//
+// Every mbarrier wait is bounded: on expiry the thread records a status bit, stops consuming and
+// leaves; the producer still waits (bounded) for the copies it has in flight before it returns.
+// Every bulk copy and every store is range-checked first; a refused access is recorded, not made.
+// Every stage is always consumed by the same warps in order, so a parity wait never refers to a
+// phase its waiter has not seen the predecessor of.
+#include <algorithm>
+#include <cstring>
+
+#include "xnq_common.cuh"
+#include "xnq_quantize_act.cuh"
+#include "xnq_unpack.cuh"
+
+namespace xnq {
+
+__device__ unsigned int g_matvec_status; // sticky bits: 1 = consumer wait expired, 2 = producer wait expired,
+                                         // 4 = a self-check refused an out-of-range copy or store
+__device__ unsigned long long g_matvec_check[8]; // first refused access: code, block, iteration, offset, bytes, limit
+
+// experiment trace (dbg bit 4): per launch, %globaltimer at a few points of block 0 and of the last block
+__device__ unsigned long long g_matvec_trace[64][16];
+__device__ unsigned int g_matvec_trace_n;
+
+namespace {
+
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+constexpr int CW = 8;                    // consumer warps per CTA
+constexpr int NTHREADS = (CW + 1) * 32;  // + one producer warp
+constexpr int CTAS_PER_SM = 2;           // so that two consecutive launches can share an SM
+constexpr int MAX_STAGES = 8;
+constexpr uint32_t WAIT_LIMIT = 1u << 20; // tries of about a microsecond each
+constexpr size_t SMEM_BUDGET = 112 * 1024; // per CTA: two CTAs fit the 227 KB of an SM
+
+struct Ring {
+  int nstreams;
+  uint32_t row_bytes[4];   // bytes of one weight row in stream s (multiple of 16)
+  const uint8_t *src[4];   // stream base in global memory (256-byte aligned)
+  uint32_t stream_off[4];  // offset of stream s inside a stage
+  uint32_t stage_bytes;    // rps * sum(row_bytes), multiple of 128
+  uint32_t row_bytes_total;
+  int rps;                 // rows per stage = CW * R
+  int nstages;
+  uint32_t act_off, ring_off; // byte offsets in dynamic shared memory
+  uint32_t smem_bytes;        // dynamic shared memory of the launch
+  int dbg;                    // experiment knobs (0 in production): 1 = skip the dots, 2 = skip the copies
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// try_wait with a suspend-time hint: the thread sleeps in hardware until the phase completes or about
+// `hint_ns` elapse, instead of polling at full issue rate and starving the warps that compute.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+// bounded wait of one thread: false (and a sticky status bit) if the phase never completes
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int bit) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+    if (mbar_try_wait(bar, parity, 1000u)) return true;
+  atomicOr(&g_matvec_status, bit);
+  return false;
+}
+// bounded wait of a whole warp: lane 0 polls, the other lanes park on the warp barrier
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, unsigned int bit, int lane) {
+  int ok = 1;
+  if (lane == 0) ok = mbar_wait(bar, parity, bit) ? 1 : 0;
+  __syncwarp();
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+// Self-check: record the first out-of-range access instead of performing it.
+__device__ __noinline__ void record_violation(unsigned long long code, unsigned long long a, unsigned long long b, unsigned long long c,
+                                              unsigned long long d) {
+  if ((atomicOr(&g_matvec_status, 4u) & 4u) == 0) {
+    g_matvec_check[0] = code;
+    g_matvec_check[1] = blockIdx.x;
+    g_matvec_check[2] = a;
+    g_matvec_check[3] = b;
+    g_matvec_check[4] = c;
+    g_matvec_check[5] = d;
+  }
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+               "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ float lds_half(uint32_t a) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+  return __half2float(__ushort_as_half(v));
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+__device__ __forceinline__ int dot16(const uint4 &w, const int4 &a, int acc) {
+  acc = __dp4a((int)w.x, a.x, acc);
+  acc = __dp4a((int)w.y, a.y, acc);
+  acc = __dp4a((int)w.z, a.z, acc);
+  acc = __dp4a((int)w.w, a.w, acc);
+  return acc;
+}
+// unsigned weight bytes x signed activation bytes
+__device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ int dot16_us(const uint4 &w, const int4 &a, int acc) {
+  acc = dp4a_us(w.x, a.x, acc);
+  acc = dp4a_us(w.y, a.y, acc);
+  acc = dp4a_us(w.z, a.z, acc);
+  acc = dp4a_us(w.w, a.w, acc);
+  return acc;
+}
+__device__ __forceinline__ uint4 and4(const uint4 &v, uint32_t m) { return make_uint4(v.x & m, v.y & m, v.z & m, v.w & m); }
+__device__ __forceinline__ uint4 shr4(const uint4 &v, int s) { return make_uint4(v.x >> s, v.y >> s, v.z >> s, v.w >> s); }
+__device__ __forceinline__ uint4 shl4(const uint4 &v, int s) { return make_uint4(v.x << s, v.y << s, v.z << s, v.w << s); }
+__device__ __forceinline__ uint4 or4(const uint4 &a, const uint4 &b) { return make_uint4(a.x | b.x, a.y | b.y, a.z | b.z, a.w | b.w); }
+
+// ---- per-format lane state (activations in registers) and row dots ----------------------------------
+// sq / sd / sb: the CTA's quantized activation row in shared memory (codes, block scales, 16-sums).
+// row[r][s]: shared-memory address of the warp's r-th row inside stream s of the current stage.
+// dot<R> returns this lane's partial sum for each of the R rows.
+
+struct Q4_0Lane { // lane owns blocks lane, lane+32, ...  (k <= 4096: 4 of them)
+  static constexpr int NIT = 4;
+  int4 alo[NIT], ahi[NIT];
+  float da[NIT];
+  int bsum8[NIT]; // 8 * sum of the block's 32 activation codes (weights are stored +8)
+  __device__ __forceinline__ void load(const int8_t *sq, const float *sd, const int16_t *sb, int lane, int64_t k) {
+    const int nblk = (int)(k / QK);
+#pragma unroll
+    for (int it = 0; it < NIT; it++) {
+      const int b = lane + 32 * it;
+      if (b < nblk) {
+        alo[it] = *reinterpret_cast<const int4 *>(sq + b * 32);
+        ahi[it] = *reinterpret_cast<const int4 *>(sq + b * 32 + 16);
+        da[it] = sd[b];
+        bsum8[it] = 8 * ((int)sb[2 * b] + (int)sb[2 * b + 1]);
+      } else {
+        alo[it] = ahi[it] = make_int4(0, 0, 0, 0);
+        da[it] = 0.f;
+        bsum8[it] = 0;
+      }
+    }
+  }
+  template <int R>
+  __device__ __forceinline__ void dot(const uint32_t (&row)[R][4], int lane, int64_t k, float (&acc)[R]) const {
+    const int nblk = (int)(k / QK);
+#pragma unroll
+    for (int r = 0; r < R; r++) acc[r] = 0.f;
+#pragma unroll
+    for (int it = 0; it < NIT; it++) {
+      const int b = lane + 32 * it;
+      if (b < nblk) {
+        uint4 q[R];
+        float dw[R];
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+          q[r] = lds128(row[r][0] + b * 16);
+          dw[r] = lds_half(row[r][1] + b * 2);
+        }
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+          const int s_lo = dot16(and4(q[r], 0x0f0f0f0fu), alo[it], -bsum8[it]);
+          const int s_hi = dot16_us(and4(q[r], 0xf0f0f0f0u), ahi[it], 0); // 16 x the high-nibble sum
+          acc[r] += (float)(s_lo + (s_hi >> 4)) * dw[r] * da[it];
+        }
+      }
+    }
+  }
+};
+
+struct Q8_0Lane { // lane owns 16-byte chunks lane, lane+32, ...  (k <= 4096: 8 of them)
+  static constexpr int NIT = 8;
+  int4 a[NIT];
+  float da[NIT];
+  __device__ __forceinline__ void load(const int8_t *sq, const float *sd, const int16_t *, int lane, int64_t k) {
+    const int nch = (int)(k / 16);
+#pragma unroll
+    for (int it = 0; it < NIT; it++) {
+      const int c = lane + 32 * it;
+      if (c < nch) {
+        a[it] = *reinterpret_cast<const int4 *>(sq + c * 16);
+        da[it] = sd[c >> 1];
+      } else {
+        a[it] = make_int4(0, 0, 0, 0);
+        da[it] = 0.f;
+      }
+    }
+  }
+  template <int R>
+  __device__ __forceinline__ void dot(const uint32_t (&row)[R][4], int lane, int64_t k, float (&acc)[R]) const {
+    const int nch = (int)(k / 16);
+#pragma unroll
+    for (int r = 0; r < R; r++) acc[r] = 0.f;
+#pragma unroll
+    for (int it = 0; it < NIT; it++) {
+      const int c = lane + 32 * it;
+      if (c < nch) {
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+          const uint4 q = lds128(row[r][0] + c * 16);
+          const float dw = lds_half(row[r][1] + (c >> 1) * 2);
+          acc[r] += (float)dot16(q, a[it], 0) * dw * da[it];
+        }
+      }
+    }
+  }
+};
+
+struct Q4KLane { // 2 lanes per super-block: lane = 2*sb + h; half h owns sub-blocks 4h..4h+3 (qs bytes 64h..64h+63)
+  static constexpr int NIT = 1;
+  int4 alo[2][2], ahi[2][2]; // [group g' of the half][16-element half of the sub-block]
+  int bs_lo[2], bs_hi[2];    // sums of the 32 activation codes under sub-blocks 2g (low nibbles) and 2g+1 (high)
+  float da;
+  __device__ __forceinline__ void load(const int8_t *sq, const float *sd, const int16_t *sb, int lane, int64_t k) {
+    const int nsb = (int)(k / QK_K);
+    const int s = lane >> 1, h = lane & 1;
+    if (s < nsb) {
+      const int kbase = s * QK_K + 128 * h;
+#pragma unroll
+      for (int g = 0; g < 2; g++) {
+        alo[g][0] = *reinterpret_cast<const int4 *>(sq + kbase + 64 * g);
+        alo[g][1] = *reinterpret_cast<const int4 *>(sq + kbase + 64 * g + 16);
+        ahi[g][0] = *reinterpret_cast<const int4 *>(sq + kbase + 64 * g + 32);
+        ahi[g][1] = *reinterpret_cast<const int4 *>(sq + kbase + 64 * g + 48);
+        const int16_t *b = sb + ((kbase + 64 * g) >> 4);
+        bs_lo[g] = (int)b[0] + (int)b[1];
+        bs_hi[g] = (int)b[2] + (int)b[3];
+      }
+      da = sd[s];
+    } else {
+#pragma unroll
+      for (int g = 0; g < 2; g++) {
+        alo[g][0] = alo[g][1] = ahi[g][0] = ahi[g][1] = make_int4(0, 0, 0, 0);
+        bs_lo[g] = bs_hi[g] = 0;
+      }
+      da = 0.f;
+    }
+  }
+  template <int R>
+  __device__ __forceinline__ void dot(const uint32_t (&row)[R][4], int lane, int64_t k, float (&acc)[R]) const {
+    const int nsb = (int)(k / QK_K);
+    const int s = lane >> 1, h = lane & 1;
+#pragma unroll
+    for (int r = 0; r < R; r++) acc[r] = 0.f;
+    if (s >= nsb) return;
+    uint4 hdr[R], q[R][4];
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+      const uint32_t blk = row[r][0] + s * 144;
+      hdr[r] = lds128(blk);
+#pragma unroll
+      for (int c = 0; c < 4; c++) q[r][c] = lds128(blk + 16 + 64 * h + 16 * c);
+    }
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+      const __half2 dm = *reinterpret_cast<const __half2 *>(&hdr[r].x);
+      // the half's two 24-bit scale fields: bits [48h, 48h+48) of the 96-bit field array
+      const uint32_t lo32 = h ? __funnelshift_r(hdr[r].z, hdr[r].w, 16) : hdr[r].y;
+      const uint32_t hi16 = h ? (hdr[r].w >> 16) : (hdr[r].z & 0xffffu);
+      const uint32_t f[2] = {lo32 & 0xffffffu, __funnelshift_r(lo32, hi16, 24) & 0xffffffu};
+      int t1 = 0, t2 = 0;
+#pragma unroll
+      for (int g = 0; g < 2; g++) {
+        int s_lo = dot16(and4(q[r][2 * g], 0x0f0f0f0fu), alo[g][0], 0);
+        s_lo = dot16(and4(q[r][2 * g + 1], 0x0f0f0f0fu), alo[g][1], s_lo);
+        // high nibbles stay in place (value * 16, unsigned bytes): one shift per sub-block instead of one per word
+        int s_hi = dot16_us(and4(q[r][2 * g], 0xf0f0f0f0u), ahi[g][0], 0);
+        s_hi = dot16_us(and4(q[r][2 * g + 1], 0xf0f0f0f0u), ahi[g][1], s_hi);
+        t1 += (int)(f[g] & 63) * s_lo + (int)((f[g] >> 6) & 63) * (s_hi >> 4);
+        t2 += (int)((f[g] >> 12) & 63) * bs_lo[g] + (int)(f[g] >> 18) * bs_hi[g];
+      }
+      acc[r] = da * (__low2float(dm) * (float)t1 - __high2float(dm) * (float)t2);
+    }
+  }
+};
+
+struct Q6KLane { // 4 lanes per super-block; lane owns (half h, l-half lh) of super-blocks lane/4, lane/4+8
+  static constexpr int NIT = 2;
+  int4 a[NIT][4];
+  int bs32[NIT][4]; // 32 * sum of the group's 16 activation codes (weights are stored +32)
+  float da[NIT];
+  __device__ __forceinline__ void load(const int8_t *sq, const float *sd, const int16_t *sb, int lane, int64_t k) {
+    const int nsb = (int)(k / QK_K);
+    const int u = lane & 3, h = u >> 1, lh = u & 1;
+#pragma unroll
+    for (int it = 0; it < NIT; it++) {
+      const int s = (lane >> 2) + 8 * it;
+      if (s < nsb) {
+        const int kbase = s * QK_K + 128 * h + 16 * lh;
+#pragma unroll
+        for (int gg = 0; gg < 4; gg++) {
+          a[it][gg] = *reinterpret_cast<const int4 *>(sq + kbase + 32 * gg);
+          bs32[it][gg] = 32 * (int)sb[(kbase >> 4) + 2 * gg];
+        }
+        da[it] = sd[s];
+      } else {
+#pragma unroll
+        for (int gg = 0; gg < 4; gg++) {
+          a[it][gg] = make_int4(0, 0, 0, 0);
+          bs32[it][gg] = 0;
+        }
+        da[it] = 0.f;
+      }
+    }
+  }
+  template <int R>
+  __device__ __forceinline__ void dot(const uint32_t (&row)[R][4], int lane, int64_t k, float (&acc)[R]) const {
+    const int nsb = (int)(k / QK_K);
+    const int u = lane & 3, h = u >> 1, lh = u & 1;
+#pragma unroll
+    for (int r = 0; r < R; r++) acc[r] = 0.f;
+#pragma unroll
+    for (int it = 0; it < NIT; it++) {
+      const int s = (lane >> 2) + 8 * it;
+      if (s < nsb) {
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+          const uint4 qa = lds128(row[r][0] + s * 128 + 64 * h + 16 * lh);
+          const uint4 qb = lds128(row[r][0] + s * 128 + 64 * h + 32 + 16 * lh);
+          const uint4 qh = lds128(row[r][1] + s * 64 + 32 * h + 16 * lh);
+          const uint2 scw = lds64(row[r][2] + s * 16 + 8 * h);
+          const float dw = lds_half(row[r][3] + s * 2);
+          uint4 code[4]; // 6-bit codes 0..63 of the four 16-element groups (k_quants.rs:1763-1770)
+          code[0] = or4(and4(qa, 0x0f0f0f0fu), and4(shl4(qh, 4), 0x30303030u));
+          code[1] = or4(and4(qb, 0x0f0f0f0fu), and4(shl4(qh, 2), 0x30303030u));
+          code[2] = or4(and4(shr4(qa, 4), 0x0f0f0f0fu), and4(qh, 0x30303030u));
+          code[3] = or4(and4(shr4(qb, 4), 0x0f0f0f0fu), and4(shr4(qh, 2), 0x30303030u));
+          const uint64_t sc64 = (((uint64_t)scw.y << 32) | scw.x) >> (8 * lh); // scale of group gg now at byte 2*gg
+          int t = 0;
+#pragma unroll
+          for (int gg = 0; gg < 4; gg++) {
+            const int sc = (int)(int8_t)((sc64 >> (16 * gg)) & 0xff);
+            t += sc * dot16(code[gg], a[it][gg], -bs32[it][gg]);
+          }
+          acc[r] += (dw * da[it]) * (float)t;
+        }
+      }
+    }
+  }
+};
+
+template <int ACT>
+__device__ __forceinline__ void quantize_row_to_smem(const void *x, int x_dtype, int64_t k, int8_t *sq, float *sd, int16_t *sb,
+                                                     bool signal_producer) {
+  // consumer threads only (CW*32 of them, whole warps), 8 elements per thread per pass. All global
+  // loads are issued before any arithmetic: the loads queue behind the weight copies already in
+  // flight, and two dependent round trips would double that wait.
+  constexpr int PASSES = 4096 / 8 / (CW * 32); // k <= 4096
+  const int lane = threadIdx.x & 31;
+  const int64_t per_row = k / 8;
+  float v[PASSES][8];
+#pragma unroll
+  for (int p = 0; p < PASSES; p++) {
+    const int64_t t = (int64_t)p * CW * 32 + threadIdx.x;
+    if (t < per_row) {
+      if (x_dtype == XNQ_F32) load8(static_cast<const float *>(x) + t * 8, v[p]);
+      else if (x_dtype == XNQ_F16) load8(static_cast<const __half *>(x) + t * 8, v[p]);
+      else load8(static_cast<const __nv_bfloat16 *>(x) + t * 8, v[p]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; i++) v[p][i] = 0.f;
+    }
+  }
+  // the activation loads are now queued ahead of the weight copies the producer is about to issue
+  if (signal_producer) asm volatile("bar.arrive 2, %0;" ::"n"(NTHREADS) : "memory");
+#pragma unroll
+  for (int p = 0; p < PASSES; p++) {
+    const int64_t t = (int64_t)p * CW * 32 + threadIdx.x;
+    if ((int64_t)p * CW * 32 >= per_row) break; // whole warps leave together
+    const Quant8 q = ACT == XNQ_Q8_0 ? quantize8_q8_0(v[p], lane) : quantize8_q8k(v[p], lane);
+    if (t < per_row) {
+      *reinterpret_cast<uint2 *>(sq + t * 8) = make_uint2(q.lo, q.hi);
+      if (ACT == XNQ_Q8_0) {
+        if ((lane & 3) == 0) sd[t / 4] = q.d;
+      } else {
+        if (lane == 0) sd[t / 32] = q.d;
+      }
+      if ((lane & 1) == 0) sb[t / 2] = (int16_t)q.sum16;
+    }
+  }
+}
+
+template <typename LaneT, int ACT, int R>
+__global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM)
+matvec_tma_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtype, Ring ring) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem); // full[MAX_STAGES], empty[MAX_STAGES]
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + MAX_STAGES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t k = w.k;
+  const int64_t row_begin = w.n * (int64_t)blockIdx.x / gridDim.x;
+  const int64_t row_end = w.n * ((int64_t)blockIdx.x + 1) / gridDim.x;
+  const int nrows = (int)(row_end - row_begin);
+  constexpr int RPS = CW * R;
+  const int S = ring.nstages;
+  const int niter = (nrows + RPS - 1) / RPS;
+  const uint32_t ring0 = smem_u32(smem + ring.ring_off);
+
+  __shared__ unsigned int trace_slot;
+  const bool tr = (ring.dbg & 4) && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1);
+  const int tb = blockIdx.x == 0 ? 0 : 8;
+  if (tr && threadIdx.x == 0) {
+    if (blockIdx.x == 0) trace_slot = atomicAdd(&g_matvec_trace_n, 1u) & 63;
+    else trace_slot = g_matvec_trace_n & 63; // approximate pairing; block 0 normally starts first
+    g_matvec_trace[trace_slot][tb + 0] = gtime();
+  }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; s++) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, CW); // one arrival per consumer warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  pdl_launch_dependents(); // the next launch may begin its own weight prefetch
+
+  const bool late_prefetch = (ring.dbg & 16) != 0;
+  if (warp == CW) { // ---- producer: weights are immutable after upload, no dependency on earlier kernels ----
+    if (late_prefetch) {
+      pdl_wait();
+      asm volatile("bar.sync 2, %0;" ::"n"(NTHREADS) : "memory"); // consumers have issued their loads of x
+    }
+    if (lane == 0) {
+      int issued = 0;
+      for (int it = 0; it < niter; it++) {
+        const int s = it % S;
+        if (it >= S && !mbar_wait(empty0 + 8 * s, ((it / S) - 1) & 1, 2u)) break;
+        const int rows = min(RPS, nrows - it * RPS);
+        issued = it + 1;
+        if (ring.dbg & 2) {
+          mbar_arrive(full0 + 8 * s);
+          continue;
+        }
+        mbar_expect_tx(full0 + 8 * s, (uint32_t)rows * ring.row_bytes_total);
+#pragma unroll
+        for (int st = 0; st < 4; st++) {
+          if (st < ring.nstreams) {
+            const unsigned long long off = (unsigned long long)(row_begin + (int64_t)it * RPS) * ring.row_bytes[st];
+            const unsigned long long bytes = (unsigned long long)rows * ring.row_bytes[st];
+            const unsigned long long limit = (unsigned long long)w.n * ring.row_bytes[st];
+            const uint32_t dst_off = ring.ring_off + s * ring.stage_bytes + ring.stream_off[st];
+            if (off + bytes > limit || (bytes & 15) || (off & 15) || (dst_off & 15) || dst_off + bytes > ring.smem_bytes ||
+                ((unsigned long long)ring.src[st] & 15)) {
+              record_violation(0x100 + st, it, off, bytes, limit);
+              continue; // the stage never completes; consumers give up on their bounded wait
+            }
+            bulk_g2s(ring0 + s * ring.stage_bytes + ring.stream_off[st], ring.src[st] + off, (uint32_t)bytes, full0 + 8 * s);
+          }
+        }
+      }
+      // nothing may be in flight into this CTA's shared memory when it exits
+      for (int it = max(0, issued - S); it < issued; it++) mbar_wait(full0 + 8 * (it % S), (it / S) & 1, 2u);
+    }
+    return;
+  }
+
+  // ---- consumers ----
+  pdl_wait(); // x may be the previous kernel's output; y may still be read by it
+  if (tr && threadIdx.x == 0) g_matvec_trace[trace_slot][tb + 1] = gtime();
+  int8_t *sq = reinterpret_cast<int8_t *>(smem + ring.act_off);
+  float *sd = reinterpret_cast<float *>(sq + k);
+  int16_t *sb = reinterpret_cast<int16_t *>(reinterpret_cast<unsigned char *>(sd) + ((k / (ACT == XNQ_Q8_0 ? QK : QK_K) * 4 + 15) & ~15));
+  quantize_row_to_smem<ACT>(x, x_dtype, k, sq, sd, sb, late_prefetch);
+  consumer_sync();
+  LaneT st;
+  st.load(sq, sd, sb, lane, k);
+  if (tr && threadIdx.x == 0) g_matvec_trace[trace_slot][tb + 2] = gtime();
+
+  for (int it = 0; it < niter; it++) {
+    const int s = it % S;
+    if (!mbar_wait_warp(full0 + 8 * s, (it / S) & 1, 1u, lane)) return;
+    if (tr && threadIdx.x == 0 && it == 0) g_matvec_trace[trace_slot][tb + 3] = gtime();
+    const int rows = min(RPS, nrows - it * RPS);
+    const int slot0 = warp * R;
+    if (slot0 < rows) {
+      uint32_t row[R][4];
+#pragma unroll
+      for (int r = 0; r < R; r++) {
+        const int slot = min(slot0 + r, rows - 1); // a duplicate of the last row past the ragged end; never stored
+#pragma unroll
+        for (int q = 0; q < 4; q++) row[r][q] = ring0 + s * ring.stage_bytes + ring.stream_off[q] + slot * ring.row_bytes[q];
+      }
+      float acc[R];
+      if (ring.dbg & 1) {
+#pragma unroll
+        for (int r = 0; r < R; r++) acc[r] = 0.f;
+      } else {
+        st.template dot<R>(row, lane, k, acc);
+      }
+#pragma unroll
+      for (int off = 16; off >= 1; off >>= 1) {
+#pragma unroll
+        for (int r = 0; r < R; r++) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], off);
+      }
+      if (lane < R && slot0 + lane < rows) {
+        float v = acc[0];
+#pragma unroll
+        for (int r = 1; r < R; r++) v = lane == r ? acc[r] : v;
+        const int64_t idx = row_begin + (int64_t)it * RPS + slot0 + lane;
+        if (idx < 0 || idx >= w.n) {
+          record_violation(0x200, it, (unsigned long long)idx, slot0, w.n);
+        } else if (y_dtype == XNQ_F32) {
+          static_cast<float *>(y)[idx] = v;
+        } else if (y_dtype == XNQ_F16) {
+          static_cast<__half *>(y)[idx] = __float2half_rn(v);
+        } else {
+          static_cast<__nv_bfloat16 *>(y)[idx] = __float2bfloat16_rn(v);
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty0 + 8 * s);
+  }
+  if (tr && threadIdx.x == 0) g_matvec_trace[trace_slot][tb + 4] = gtime();
+}
+
+int g_num_sms = 0;
+int g_dbg = 0;
+
+// Rows per consumer warp per stage. One row per warp keeps stages small, so the ring holds many of
+// them and (almost) the whole band of a CTA is requested before the first row is consumed.
+int plan_ring(const WeightView &w, Ring &r) {
+  const int64_t k = w.k;
+  std::memset(&r, 0, sizeof(r));
+  switch (w.dtype) {
+    case XNQ_Q4_0:
+      r.nstreams = 2;
+      r.row_bytes[0] = (uint32_t)(k / 2); r.src[0] = w.qs;
+      r.row_bytes[1] = (uint32_t)(w.dstride * 2); r.src[1] = reinterpret_cast<const uint8_t *>(w.d);
+      break;
+    case XNQ_Q8_0:
+      r.nstreams = 2;
+      r.row_bytes[0] = (uint32_t)k; r.src[0] = w.qs;
+      r.row_bytes[1] = (uint32_t)(w.dstride * 2); r.src[1] = reinterpret_cast<const uint8_t *>(w.d);
+      break;
+    case XNQ_Q4K:
+      r.nstreams = 1;
+      r.row_bytes[0] = (uint32_t)(k / QK_K * 144); r.src[0] = w.qs;
+      break;
+    case XNQ_Q6K:
+      r.nstreams = 4;
+      r.row_bytes[0] = (uint32_t)(k / 2); r.src[0] = w.qs;
+      r.row_bytes[1] = (uint32_t)(k / 4); r.src[1] = w.qh;
+      r.row_bytes[2] = (uint32_t)(k / 16); r.src[2] = reinterpret_cast<const uint8_t *>(w.sc);
+      r.row_bytes[3] = (uint32_t)(w.dstride * 2); r.src[3] = reinterpret_cast<const uint8_t *>(w.d);
+      break;
+    default: return 0;
+  }
+  for (int s = 0; s < r.nstreams; s++) r.row_bytes_total += r.row_bytes[s];
+  const int act_blk = (w.dtype == XNQ_Q4_0 || w.dtype == XNQ_Q8_0) ? QK : QK_K;
+  const uint32_t act_bytes = (uint32_t)(k + ((k / act_blk * 4 + 15) & ~15) + ((k / 16 * 2 + 15) & ~15));
+  r.act_off = 2 * MAX_STAGES * 8;
+  r.ring_off = (r.act_off + act_bytes + 127) & ~127u;
+  const size_t avail = SMEM_BUDGET - r.ring_off;
+  int rows_per_warp = 0;
+  for (int R = 2; R >= 1 && !rows_per_warp; R--) {
+    const size_t stage = ((size_t)CW * R * r.row_bytes_total + 127) & ~(size_t)127;
+    if ((R == 2 ? 3 : 2) * stage <= avail) rows_per_warp = R;
+  }
+  if (g_dbg & 32) rows_per_warp = 1;
+  if (!rows_per_warp) return 0;
+  r.rps = CW * rows_per_warp;
+  uint32_t off = 0;
+  for (int s = 0; s < r.nstreams; s++) {
+    r.stream_off[s] = off;
+    off += r.rps * r.row_bytes[s];
+  }
+  r.stage_bytes = (off + 127) & ~127u;
+  r.nstages = (int)std::min<size_t>(MAX_STAGES, avail / r.stage_bytes);
+  r.smem_bytes = r.ring_off + (uint32_t)r.nstages * r.stage_bytes;
+  r.dbg = g_dbg;
+  return rows_per_warp;
+}
+
+template <typename LaneT, int ACT, int R>
+int launch_fmt(const WeightView &w, const void *x, int x_dtype, void *y, int y_dtype, const Ring &r, cudaStream_t s) {
+  const int64_t max_ctas = (w.n + r.rps - 1) / r.rps; // at least one stage of rows per CTA
+  const int per_sm = (r.dbg & 8) ? 1 : CTAS_PER_SM;
+  const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>((int64_t)g_num_sms * per_sm, max_ctas));
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(NTHREADS);
+  cfg.dynamicSmemBytes = r.smem_bytes;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  XNQ_CUDA(cudaLaunchKernelEx(&cfg, matvec_tma_kernel<LaneT, ACT, R>, w, x, x_dtype, y, y_dtype, r));
+  count_launch();
+  return XNQ_OK;
+}
+
+template <typename LaneT, int ACT>
+int launch_r(int R, const WeightView &w, const void *x, int x_dtype, void *y, int y_dtype, const Ring &r, cudaStream_t s) {
+  if (R == 2) return launch_fmt<LaneT, ACT, 2>(w, x, x_dtype, y, y_dtype, r, s);
+  return launch_fmt<LaneT, ACT, 1>(w, x, x_dtype, y, y_dtype, r, s);
+}
+
+template <typename LaneT, int ACT>
+int init_fmt() {
+  XNQ_CUDA(cudaFuncSetAttribute(matvec_tma_kernel<LaneT, ACT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET));
+  XNQ_CUDA(cudaFuncSetAttribute(matvec_tma_kernel<LaneT, ACT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET));
+  return XNQ_OK;
+}
+
+} // namespace
+
+bool matvec_tma_supported(const WeightView &w, int64_t m) {
+  if (m != 1 || g_num_sms <= 0 || w.n < 1) return false;
+  if (w.k > 4096) return false; // lane-resident activations are sized for k <= 4096
+  Ring r;
+  return plan_ring(w, r) > 0;
+}
+
+int launch_matvec_tma(const WeightView &w, const void *x, int x_dtype, void *y, int y_dtype, cudaStream_t s) {
+  Ring r;
+  const int R = plan_ring(w, r);
+  if (!R) return fail(XNQ_ERR_SIZE, "matvec_tma: no ring fits k = %lld", (long long)w.k);
+  switch (w.dtype) {
+    case XNQ_Q4_0: return launch_r<Q4_0Lane, XNQ_Q8_0>(R, w, x, x_dtype, y, y_dtype, r, s);
+    case XNQ_Q8_0: return launch_r<Q8_0Lane, XNQ_Q8_0>(R, w, x, x_dtype, y, y_dtype, r, s);
+    case XNQ_Q4K: return launch_r<Q4KLane, XNQ_Q8K>(R, w, x, x_dtype, y, y_dtype, r, s);
+    case XNQ_Q6K: return launch_r<Q6KLane, XNQ_Q8K>(R, w, x, x_dtype, y, y_dtype, r, s);
+  }
+  return fail(XNQ_ERR_DTYPE, "matvec_tma: dtype %d", w.dtype);
+}
+
+int matvec_tma_init(int device) {
+  cudaDeviceProp prop;
+  XNQ_CUDA(cudaGetDeviceProperties(&prop, device));
+  g_num_sms = prop.multiProcessorCount;
+  int rc;
+  if ((rc = init_fmt<Q4_0Lane, XNQ_Q8_0>()) != XNQ_OK) return rc;
+  if ((rc = init_fmt<Q8_0Lane, XNQ_Q8_0>()) != XNQ_OK) return rc;
+  if ((rc = init_fmt<Q4KLane, XNQ_Q8K>()) != XNQ_OK) return rc;
+  if ((rc = init_fmt<Q6KLane, XNQ_Q8K>()) != XNQ_OK) return rc;
+  unsigned int zero = 0;
+  XNQ_CUDA(cudaMemcpyToSymbol(g_matvec_status, &zero, sizeof(zero)));
+  return XNQ_OK;
+}
+
+void matvec_tma_set_dbg(int v) { g_dbg = v; }
+
+int matvec_status(unsigned int *bits) {
+  XNQ_CUDA(cudaMemcpyFromSymbol(bits, g_matvec_status, sizeof(*bits)));
+  return XNQ_OK;
+}
+
+int matvec_trace(unsigned long long *out, unsigned int *n) {
+  XNQ_CUDA(cudaMemcpyFromSymbol(out, g_matvec_trace, sizeof(unsigned long long) * 64 * 16));
+  XNQ_CUDA(cudaMemcpyFromSymbol(n, g_matvec_trace_n, sizeof(unsigned int)));
+  return XNQ_OK;
+}
+
+int matvec_check_record(unsigned long long out[8]) {
+  XNQ_CUDA(cudaMemcpyFromSymbol(out, g_matvec_check, sizeof(unsigned long long) * 8));
+  return XNQ_OK;
+}
+
+} // namespace xnq

@@ -28,6 +28,48 @@ __device__ __forceinline__ uint32_t k4_byte(uint32_t lo, uint32_t hi, int j) { /
   return ((j < 4 ? lo : hi) >> (8 * (j & 3))) & 0xffu;
 }
 
+// Device form of a Q4_K header (same 16 bytes as in GGUF): f16 d, f16 dmin, then the sixteen 6-bit
+// values re-packed as four 24-bit little-endian fields, one per 64-element group g:
+//   field g = sc[2g] | sc[2g+1] << 6 | mn[2g] << 12 | mn[2g+1] << 18
+// so a lane that works on group g gets its two scales and two mins with one shift and four masks.
+// The GGUF packing (utils.rs:53-63) is restored exactly on read-back.
+__device__ __forceinline__ uint32_t k4_field(uint32_t w0, uint32_t w1, uint32_t w2, int g) {
+  const uint32_t lo = g < 2 ? w0 : w1, hi = g < 2 ? w1 : w2;
+  const int sh = g < 2 ? 24 * g : 24 * g - 32; // 0, 24, 16, 40
+  return (uint32_t)((((uint64_t)hi << 32) | lo) >> sh) & 0xffffffu;
+}
+__device__ __forceinline__ void k4_fields_from_gguf(const uint32_t u[3], uint32_t out[3]) {
+  const K4Scales ks = unpack_k4(u[0], u[1], u[2]);
+  uint64_t f[4];
+#pragma unroll
+  for (int g = 0; g < 4; g++) {
+    const uint32_t sc0 = k4_byte(ks.sc_lo, ks.sc_hi, 2 * g), sc1 = k4_byte(ks.sc_lo, ks.sc_hi, 2 * g + 1);
+    const uint32_t mn0 = k4_byte(ks.mn_lo, ks.mn_hi, 2 * g), mn1 = k4_byte(ks.mn_lo, ks.mn_hi, 2 * g + 1);
+    f[g] = sc0 | (sc1 << 6) | (mn0 << 12) | (mn1 << 18);
+  }
+  out[0] = (uint32_t)(f[0] | (f[1] << 24));
+  out[1] = (uint32_t)((f[1] >> 8) | (f[2] << 16));
+  out[2] = (uint32_t)((f[2] >> 16) | (f[3] << 8));
+}
+__device__ __forceinline__ void k4_fields_to_gguf(const uint32_t w[3], uint32_t out[3]) {
+  uint32_t sc[8], mn[8];
+#pragma unroll
+  for (int g = 0; g < 4; g++) {
+    const uint32_t f = k4_field(w[0], w[1], w[2], g);
+    sc[2 * g] = f & 63;
+    sc[2 * g + 1] = (f >> 6) & 63;
+    mn[2 * g] = (f >> 12) & 63;
+    mn[2 * g + 1] = (f >> 18) & 63;
+  }
+  out[0] = out[1] = out[2] = 0;
+#pragma unroll
+  for (int j = 0; j < 4; j++) { // k_quants.rs:1437-1444
+    out[0] |= (sc[j] | ((sc[j + 4] >> 4) << 6)) << (8 * j);
+    out[1] |= (mn[j] | ((mn[j + 4] >> 4) << 6)) << (8 * j);
+    out[2] |= ((sc[j + 4] & 0xF) | ((mn[j + 4] & 0xF) << 4)) << (8 * j);
+  }
+}
+
 __device__ __forceinline__ float deq_q4_0(const WeightView &w, int64_t row, int col) {
   const int64_t nblk = w.k / QK;
   const int b = col / QK, j = col % QK;
@@ -47,9 +89,9 @@ __device__ __forceinline__ float deq_q4k(const WeightView &w, int64_t row, int c
   const int e = col % QK_K, sub = e / 32, l = e % 32;
   const __half2 dm = *reinterpret_cast<const __half2 *>(blk);
   const uint32_t *u = reinterpret_cast<const uint32_t *>(blk + 4);
-  const K4Scales ks = unpack_k4(u[0], u[1], u[2]);
-  const float sc = (float)k4_byte(ks.sc_lo, ks.sc_hi, sub);
-  const float mn = (float)k4_byte(ks.mn_lo, ks.mn_hi, sub);
+  const uint32_t f = k4_field(u[0], u[1], u[2], sub >> 1);
+  const float sc = (float)((f >> (6 * (sub & 1))) & 63);
+  const float mn = (float)((f >> (12 + 6 * (sub & 1))) & 63);
   const uint8_t byte = blk[16 + 32 * (sub >> 1) + l];
   const float code = (float)((sub & 1) ? (byte >> 4) : (byte & 0xF));
   const float d1 = __fmul_rn(__low2float(dm), sc);
