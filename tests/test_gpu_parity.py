@@ -285,3 +285,32 @@ def test_zz_device_status_is_clean(Q):
     bits = ctypes.c_uint(123)
     _lib.check(_lib.lib().xnq_device_status(ctypes.byref(bits)))
     assert bits.value == 0, f"device status bits {bits.value:#x}"
+
+
+def test_activation_quantizer_rounding_ties_and_near_ties(Q, O):
+    """Rust's f32::round is half away from zero. With a block maximum of 127 (Q8_0: scale 1) or a
+    first-largest element of -128 (Q8_K: iscale 1) the products equal the inputs, so exact .5 ties,
+    the floats just below .5 and the saturating 127.5 -> 127 case reach the rounding step as written."""
+    below_half = np.nextafter(np.float32(0.5), np.float32(0))
+    vals = np.array([0.5, 1.5, 2.5, 3.5, -0.5, -1.5, -2.5, 126.5, -126.5, below_half, -below_half, 0.25, -0.75,
+                     np.nextafter(np.float32(1.5), np.float32(0)), np.nextafter(np.float32(2.5), np.float32(3)), 63.5, -63.5,
+                     100.49999, -100.5, 7.5000005, 1e-8, -1e-8, 0.0, 126.49999, 125.5, -0.0, 31.5, -31.5, 15.5, 8.5, -8.5],
+                    np.float32)
+    x8 = np.zeros((2, 256), np.float32)
+    for r in range(2):
+        for b in range(8):
+            blk = np.roll(vals, 3 * b + r)[:31]
+            x8[r, 32 * b] = 127.0 if (b + r) % 2 == 0 else -127.0
+            x8[r, 32 * b + 1:32 * b + 32] = blk
+    got = Q.quantize_act(torch.from_numpy(x8).to(DEV), D.Q8_0).cpu().numpy()
+    assert np.array_equal(got, O.from_float(O.Q8_0, x8))
+    xk = np.zeros((2, 512), np.float32)
+    for r in range(2):
+        for b in range(2):
+            xk[r, 256 * b:256 * b + 256] = np.resize(np.roll(vals, b + 5 * r), 256)
+            xk[r, 256 * b + 17] = -128.0
+            xk[r, 256 * b + 40] = 127.5      # rounds to 128, clipped to 127
+            xk[r, 256 * b + 90] = 128.0      # same magnitude as the maximum but later: must not win
+    got = Q.quantize_act(torch.from_numpy(xk).to(DEV), D.Q8K).cpu().numpy()
+    want = O.from_float(O.Q8K, xk)
+    assert np.array_equal(got, want), np.flatnonzero(got != want)[:10]

@@ -5,7 +5,7 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libxnq.so")
+LIB_PATH = os.path.join(HERE, os.environ.get("XNQ_LIB_NAME", "libxnq.so"))
 
 XNQ_OK = 0
 STATUS_NAMES = {0: "XNQ_OK", -1: "XNQ_ERR_NULL", -2: "XNQ_ERR_DTYPE", -3: "XNQ_ERR_SHAPE", -4: "XNQ_ERR_ALIGN",

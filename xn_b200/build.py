@@ -15,9 +15,14 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libxnq.so")
 
+EXTRA = os.environ.get("XNQ_EXTRA_NVCC_FLAGS", "").split()
+if os.environ.get("XNQ_LIB_NAME"):
+    LIB = os.path.join(HERE, os.environ["XNQ_LIB_NAME"])
+    OBJ = os.path.join(HERE, "build_" + os.environ["XNQ_LIB_NAME"].replace(".", "_"))
+
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "-Xcompiler", "-fPIC",
+    "-Xcompiler", "-fPIC", *EXTRA,
 ]
 
 

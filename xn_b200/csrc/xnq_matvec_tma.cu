@@ -50,12 +50,15 @@ __device__ __forceinline__ unsigned long long gtime() {
   return t;
 }
 
-constexpr int CW = 8;                    // consumer warps per CTA
+#ifndef XNQ_MV_CW
+#define XNQ_MV_CW 16
+#endif
+constexpr int CW = XNQ_MV_CW;            // consumer warps per CTA
 constexpr int NTHREADS = (CW + 1) * 32;  // + one producer warp
-constexpr int CTAS_PER_SM = 2;           // so that two consecutive launches can share an SM
+constexpr int CTAS_PER_SM = CW <= 8 ? 2 : 1; // 8 warps: two consecutive launches can share an SM
 constexpr int MAX_STAGES = 8;
-constexpr uint32_t WAIT_LIMIT = 1u << 20; // tries of about a microsecond each
-constexpr size_t SMEM_BUDGET = 112 * 1024; // per CTA: two CTAs fit the 227 KB of an SM
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr size_t SMEM_BUDGET = (CW <= 8 ? 112 : 225) * 1024; // per CTA: CTAS_PER_SM of them fit the 227 KB of an SM
 
 struct Ring {
   int nstreams;
@@ -81,17 +84,18 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// try_wait with a suspend-time hint: the thread sleeps in hardware until the phase completes or about
-// `hint_ns` elapse, instead of polling at full issue rate and starving the warps that compute.
+// try_wait without a suspend-time hint: a hint of 1 us was measured to delay every wake-up by about
+// that much. Only one lane per warp polls (mbar_wait_warp), so polling costs few issue slots.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "r"(bar), "r"(parity)
       : "memory");
+  (void)hint_ns;
   return ok != 0;
 }
 // bounded wait of one thread: false (and a sticky status bit) if the phase never completes
@@ -396,7 +400,7 @@ struct Q6KLane { // 4 lanes per super-block; lane owns (half h, l-half lh) of su
 
 template <int ACT>
 __device__ __forceinline__ void quantize_row_to_smem(const void *x, int x_dtype, int64_t k, int8_t *sq, float *sd, int16_t *sb,
-                                                     bool signal_producer) {
+                                                     bool signal_producer, unsigned long long *trace) {
   // consumer threads only (CW*32 of them, whole warps), 8 elements per thread per pass. All global
   // loads are issued before any arithmetic: the loads queue behind the weight copies already in
   // flight, and two dependent round trips would double that wait.
@@ -418,6 +422,9 @@ __device__ __forceinline__ void quantize_row_to_smem(const void *x, int x_dtype,
   }
   // the activation loads are now queued ahead of the weight copies the producer is about to issue
   if (signal_producer) asm volatile("bar.arrive 2, %0;" ::"n"(NTHREADS) : "memory");
+  if (trace && threadIdx.x == 0) {
+    if (v[0][0] != 123456.75f) trace[5] = gtime(); // after the first load has landed
+  }
 #pragma unroll
   for (int p = 0; p < PASSES; p++) {
     const int64_t t = (int64_t)p * CW * 32 + threadIdx.x;
@@ -515,8 +522,10 @@ matvec_tma_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtype
   int8_t *sq = reinterpret_cast<int8_t *>(smem + ring.act_off);
   float *sd = reinterpret_cast<float *>(sq + k);
   int16_t *sb = reinterpret_cast<int16_t *>(reinterpret_cast<unsigned char *>(sd) + ((k / (ACT == XNQ_Q8_0 ? QK : QK_K) * 4 + 15) & ~15));
-  quantize_row_to_smem<ACT>(x, x_dtype, k, sq, sd, sb, late_prefetch);
+  quantize_row_to_smem<ACT>(x, x_dtype, k, sq, sd, sb, late_prefetch, tr ? &g_matvec_trace[trace_slot][tb] : nullptr);
+  if (tr && threadIdx.x == 0) g_matvec_trace[trace_slot][tb + 6] = gtime();
   consumer_sync();
+  if (tr && threadIdx.x == 0) g_matvec_trace[trace_slot][tb + 7] = gtime();
   LaneT st;
   st.load(sq, sd, sb, lane, k);
   if (tr && threadIdx.x == 0) g_matvec_trace[trace_slot][tb + 2] = gtime();

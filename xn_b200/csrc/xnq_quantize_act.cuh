@@ -43,10 +43,14 @@ __device__ __forceinline__ void load8(const __nv_bfloat16 *p, float v[8]) {
   }
 }
 
-// Rust `as i8` on an already rounded float: saturate, NaN -> 0 (cvt.rzi of NaN is 0).
-__device__ __forceinline__ int sat_i8(float r) {
-  int q = (int)r;
-  return max(-128, min(127, q));
+// Rust `f32::round` (half away from zero) followed by `as i8` (saturating, NaN -> 0), for the
+// products a quantizer forms (|v| far below 2^22). trunc(v + copysign(0.5, v)) is exact there: v and
+// v + 0.5 share a binade whose ulp divides 0.5, or the sum lands just ABOVE a power of two, so the
+// addition never rounds up across an integer; the one exception, |v| just under 0.5 (the sum would
+// round to 1), is caught by the guard. cvt.rzi of NaN is 0 and of +-inf saturates, as `as` does.
+__device__ __forceinline__ int round_away_sat_i8(float v) {
+  const int r = __float2int_rz(v + copysignf(0.5f, v));
+  return fabsf(v) < 0.5f ? 0 : max(-128, min(127, r));
 }
 
 __device__ __forceinline__ void pack8(const int q[8], Quant8 &o) {
@@ -68,7 +72,7 @@ __device__ __forceinline__ Quant8 quantize8_q8_0(const float v[8], int /*lane*/)
   const float id = d != 0.f ? __fdiv_rn(1.0f, d) : 0.f;
   int q[8];
 #pragma unroll
-  for (int i = 0; i < 8; i++) q[i] = sat_i8(roundf(__fmul_rn(v[i], id)));
+  for (int i = 0; i < 8; i++) q[i] = round_away_sat_i8(__fmul_rn(v[i], id));
   Quant8 o;
   pack8(q, o);
   o.d_unrounded = d;
@@ -93,14 +97,13 @@ __device__ __forceinline__ Quant8 quantize8_q8k(const float v[8], int lane) {
 #pragma unroll
   for (int off = 16; off >= 1; off >>= 1) {
     const float oa = __shfl_xor_sync(0xffffffffu, amax, off);
-    const float om = __shfl_xor_sync(0xffffffffu, mx, off);
     const int oi = __shfl_xor_sync(0xffffffffu, idx, off);
     if (oa > amax || (oa == amax && oi < idx)) {
       amax = oa;
-      mx = om;
       idx = oi;
     }
   }
+  mx = __shfl_sync(0xffffffffu, mx, idx >> 3); // the winning lane's own first-largest element is element idx
   Quant8 o;
   int q[8];
   if (amax == 0.f) {
@@ -112,7 +115,7 @@ __device__ __forceinline__ Quant8 quantize8_q8k(const float v[8], int lane) {
   }
   const float iscale = __fdiv_rn(-128.f, mx);
 #pragma unroll
-  for (int i = 0; i < 8; i++) q[i] = sat_i8(fminf(roundf(__fmul_rn(iscale, v[i])), 127.f));
+  for (int i = 0; i < 8; i++) q[i] = min(127, round_away_sat_i8(__fmul_rn(iscale, v[i])));
   pack8(q, o);
   o.d = o.d_unrounded = __fdiv_rn(1.0f, iscale);
   return o;
