@@ -154,13 +154,18 @@ int xnq_init(int device) {
   if ((rc = quantize_init(device)) != XNQ_OK) return rc;
   if ((rc = matvec_init(device)) != XNQ_OK) return rc;
   if ((rc = matvec_tma_init(device)) != XNQ_OK) return rc;
+  if ((rc = prefill_init(device)) != XNQ_OK) return rc;
   return XNQ_OK;
 }
 
 int xnq_device_status(unsigned int *bits) {
   clear_error();
   if (!bits) return fail(XNQ_ERR_NULL, "device_status: bits is NULL");
-  return matvec_status(bits);
+  unsigned int mv = 0, pf = 0;
+  int rc = matvec_status(&mv);
+  if (rc == XNQ_OK) rc = prefill_status(&pf);
+  *bits = mv | (pf << 8);
+  return rc;
 }
 
 int xnq_device_check_record(unsigned long long out[8]) {
@@ -213,6 +218,7 @@ int xnq_weight_upload_rows(int dtype, const void *blocks, size_t nbytes, int64_t
   XNQ_CUDA(cudaGetDevice(&w->device));
   w->n_total = n_total;
   w->row0 = row0;
+  w->wscale = 1.0f;
   const Plan p = plan_for(dtype, n_rows, k);
   cudaError_t e = cudaMalloc(&w->base, p.total);
   if (e != cudaSuccess) {
@@ -238,6 +244,19 @@ int xnq_weight_upload_rows(int dtype, const void *blocks, size_t nbytes, int64_t
     if ((e = cudaMalloc(&staging, nbytes)) != cudaSuccess) break;
     if ((e = cudaMemcpyAsync(staging, blocks, nbytes, cudaMemcpyHostToDevice, s)) != cudaSuccess) break;
     rc = launch_relayout(w->v, static_cast<const uint8_t *>(staging), s);
+    if (rc != XNQ_OK) break;
+    // largest |weight| -> the power-of-two scale of the fp16 prefill path (the staging buffer's first word is free now)
+    if ((e = cudaStreamSynchronize(s)) != cudaSuccess) break;
+    rc = launch_max_abs(w->v, static_cast<float *>(staging), s);
+    if (rc != XNQ_OK) break;
+    float maxabs = 0.f;
+    if ((e = cudaMemcpyAsync(&maxabs, staging, sizeof(float), cudaMemcpyDeviceToHost, s)) != cudaSuccess) break;
+    if ((e = cudaStreamSynchronize(s)) != cudaSuccess) break;
+    if (maxabs > 0.f) {
+      int ex = 0;
+      (void)std::frexp(maxabs, &ex); // maxabs = f * 2^ex, f in [0.5, 1)
+      w->wscale = std::ldexp(1.0f, 10 - ex);
+    }
   } while (0);
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   if (staging) cudaFree(staging);
@@ -349,8 +368,11 @@ int xnq_quantize_act(int act_dtype, const void *x, int x_dtype, int64_t m, int64
 
 size_t xnq_matmul_workspace_bytes(const xnq_weight *w, int64_t max_m) {
   if (!w || max_m <= 0) return 0;
-  const int64_t rows = max_m < MATVEC_MAX_M ? max_m : MATVEC_MAX_M; // larger m is processed in passes of <= 16 rows
-  return act_workspace_bytes(rows, w->v.k, act_dtype_for(w->v.dtype));
+  const int64_t rows = max_m < MATVEC_MAX_M ? max_m : MATVEC_MAX_M;
+  const size_t decode = act_workspace_bytes(rows, w->v.k, act_dtype_for(w->v.dtype));
+  if (max_m <= MATVEC_MAX_M) return decode;
+  const size_t prefill = prefill_workspace_bytes(max_m, w->v.k); // m > 16 runs on the tensor cores
+  return prefill > decode ? prefill : decode;
 }
 
 int xnq_matmul_t(const xnq_weight *w, const void *x, int x_dtype, int64_t m, int64_t ldx, void *y, int y_dtype, int64_t ldy, void *workspace,
@@ -380,6 +402,7 @@ int xnq_matmul_t(const xnq_weight *w, const void *x, int x_dtype, int64_t m, int
     profile_mark(s, false);
     return rc;
   }
+  if (m > MATVEC_MAX_M) return launch_prefill(w->v, w->wscale, x, x_dtype, m, ldx, y, y_dtype, ldy, workspace, s);
   const int adt = act_dtype_for(w->v.dtype);
   const size_t xes = type_size(x_dtype), yes = type_size(y_dtype);
   for (int64_t r0 = 0; r0 < m; r0 += pass) {

@@ -109,6 +109,7 @@ struct xnq_weight {
   xnq::WeightView v;
   void *base;    // single device allocation behind v
   size_t bytes;  // its size
+  float wscale;  // power of two that brings the largest |weight| into (2^9, 2^10] for the fp16 prefill path
   // host-call staging (xnq_linear_forward_host)
   void *stage_dev;
   size_t stage_dev_bytes;
@@ -149,6 +150,16 @@ int matvec_status(unsigned int *bits);
 void matvec_tma_set_dbg(int v);
 int matvec_check_record(unsigned long long out[8]);
 int matvec_trace(unsigned long long *out, unsigned int *n);
+
+// xnq_prefill.cu  (m > 16: tcgen05 / TMEM contraction on fp16 operands)
+size_t prefill_workspace_bytes(int64_t m, int64_t k);
+int launch_prefill(const WeightView &w, float wscale, const void *x, int x_dtype, int64_t m, int64_t ldx, void *y, int y_dtype, int64_t ldy,
+                   void *workspace, cudaStream_t s);
+int prefill_init(int device);
+int prefill_status(unsigned int *bits);
+
+// largest |dequantized weight| of the tensor, written to *dev_out (a float in device memory)
+int launch_max_abs(const WeightView &w, float *dev_out, cudaStream_t s);
 
 // xnq_bias.cu-ish helper in xnq_layout.cu: y[m, n] += bias[n]
 int launch_add_bias(float *y, const float *bias, int64_t m, int64_t n, int64_t ldy, cudaStream_t s);

@@ -4,6 +4,8 @@
 // the API's counterpart of Q8Tensor::dequantize (xn-core/src/cuda_backend/q8.rs:94-113). What
 // matters here is exactness: dequantize is bit-identical to GgmlType::to_float, so every float
 // operation is an explicit round-to-nearest intrinsic the compiler may not contract into an FMA.
+#include <algorithm>
+
 #include "xnq_common.cuh"
 #include "xnq_unpack.cuh"
 
@@ -150,6 +152,27 @@ __global__ void dequantize_kernel(WeightView w, T *__restrict__ out) {
   out[i] = cast_out<T>(v);
 }
 
+__global__ void max_abs_kernel(WeightView w, unsigned int *out) {
+  float m = 0.f;
+  const int64_t total = w.n * w.k;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / w.k;
+    const int col = (int)(i % w.k);
+    float v;
+    switch (w.dtype) {
+      case XNQ_Q4_0: v = deq_q4_0(w, row, col); break;
+      case XNQ_Q8_0: v = deq_q8_0(w, row, col); break;
+      case XNQ_Q4K: v = deq_q4k(w, row, col); break;
+      default: v = deq_q6k(w, row, col); break;
+    }
+    v = fabsf(v);
+    if (v < 3.0e38f) m = fmaxf(m, v); // ignore inf / nan scales
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+  if ((threadIdx.x & 31) == 0) atomicMax(out, __float_as_uint(m)); // non-negative floats order like their bit patterns
+}
+
 __global__ void add_bias_kernel(float *__restrict__ y, const float *__restrict__ bias, int64_t m, int64_t n, int64_t ldy) {
   const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (i >= m * n) return;
@@ -212,6 +235,17 @@ int launch_dequantize(const WeightView &w, int out_dtype, void *dst, cudaStream_
   return XNQ_OK;
 }
 
+int launch_max_abs(const WeightView &w, float *dev_out, cudaStream_t s) {
+  XNQ_CUDA(cudaMemsetAsync(dev_out, 0, sizeof(float), s));
+  if (w.n == 0) return XNQ_OK;
+  const int64_t total = w.n * w.k;
+  const unsigned grid = (unsigned)std::min<int64_t>((total + TPB - 1) / TPB, 148 * 16);
+  max_abs_kernel<<<grid, TPB, 0, s>>>(w, reinterpret_cast<unsigned int *>(dev_out));
+  XNQ_CUDA(cudaGetLastError());
+  count_launch();
+  return XNQ_OK;
+}
+
 int launch_add_bias(float *y, const float *bias, int64_t m, int64_t n, int64_t ldy, cudaStream_t s) {
   if (m == 0 || n == 0) return XNQ_OK;
   add_bias_kernel<<<grid_for(m * n), TPB, 0, s>>>(y, bias, m, n, ldy);
@@ -234,6 +268,7 @@ int layout_init(int) {
   XNQ_CUDA(cudaFuncGetAttributes(&fa, dequantize_kernel<__half>));
   XNQ_CUDA(cudaFuncGetAttributes(&fa, dequantize_kernel<__nv_bfloat16>));
   XNQ_CUDA(cudaFuncGetAttributes(&fa, add_bias_kernel));
+  XNQ_CUDA(cudaFuncGetAttributes(&fa, max_abs_kernel));
   return XNQ_OK;
 }
 

@@ -1,0 +1,455 @@
+// Prefill (m > 16): quantized weights x activations as a dense contraction on the 5th-generation
+// tensor cores (tcgen05.mma, accumulators in TMEM).
+//
+//   D[128 weight rows, mt activation rows] += A[128, 64] . B[mt, 64]^T      per k-step of 64
+//
+//   A  weights of the tile, dequantized by four producer warps (one thread per weight row) from the
+//      quantized blocks straight into the 128-byte-swizzled K-major shared-memory image the MMA reads.
+//      Every weight is dequantized once per m-tile (mt up to 256 rows).
+//   B  activations, prepared once per call by prefill_prepare_acts: quantized to Q8_0 / Q8_K exactly
+//      as the reference's quantize_lhs does (k_quants.rs:2015-2026), dequantized, scaled by a power of
+//      two per row and stored as fp16 in the same swizzled image, so that one 1-D bulk-async copy
+//      (cp.async.bulk, non-multicast) brings a whole stage.
+//   D  f32 in tensor memory; four epilogue warps read it back with tcgen05.ld, undo the power-of-two
+//      scales and store y.
+//
+// Operand type. The contraction runs in fp16 (kind::f16 with f16 inputs), not bf16: both have the
+// same tensor throughput, and fp16's 11-bit significand keeps the operand rounding 8x smaller, which
+// is what lets the result stay within 1e-2 of the reference's integer-exact CPU result element by
+// element. Range is handled exactly: every activation row and the whole weight tensor are multiplied
+// by powers of two that put their maxima near 2^11 / 2^10, and the epilogue divides them out.
+//
+// k order. A dot product does not care in which order k is visited as long as both operands agree,
+// so within a k-step the 64 elements are stored in the order the nibble unpack produces them
+// (xnq_prefill.cuh: kperm) and the activation image uses the same order; no shuffles are needed.
+//
+// Synchronisation. Per stage: a_full (128 producer arrivals), b_full (bulk-copy transaction bytes),
+// empty (tcgen05.commit by the MMA thread). Every wait is bounded; on expiry a status bit is set and
+// every role falls through to the common exit, where tensor memory is released.
+#include <algorithm>
+#include <cstring>
+
+#include "xnq_common.cuh"
+#include "xnq_quantize_act.cuh"
+#include "xnq_prefill_rows.cuh"
+#include "xnq_unpack.cuh"
+
+namespace xnq {
+
+__device__ unsigned int g_prefill_status; // sticky: 1 producer wait, 2 loader wait, 4 mma wait, 8 epilogue wait expired
+
+namespace {
+
+constexpr int BK = 64;             // k-step (elements) = one 128-byte swizzle row of fp16
+constexpr int TILE_N = 128;        // weight rows per CTA = UMMA M
+constexpr int MAX_MT = 256;        // activation rows per CTA = UMMA N
+constexpr int PRODUCERS = 256;     // two threads per weight row
+constexpr int NTHREADS = PRODUCERS + 64; // warps 0-7 producers/epilogue, warp 8 loader, warp 9 MMA
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr int A_STAGE_BYTES = TILE_N * BK * 2; // 16 KB
+constexpr int NSTAGES = 3;         // operand stages (A 16 KB + B up to 32 KB each)
+constexpr int RAW_DEPTH = 4;       // k-steps of raw weight bytes each producer thread keeps in flight
+constexpr int RAW_SLOT_MAX = 80;   // largest per-thread slot (Q6_K)
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int bit) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  atomicOr(&g_prefill_status, bit);
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+               "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+// ---- tcgen05 wrappers --------------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrives on the mbarrier once every MMA issued so far by this thread has finished reading smem / writing tmem
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, 128-byte-swizzled operand tile: rows of 128 bytes, 8-row groups 1024 bytes apart.
+// Fields: start address >> 4 [0,14), leading byte offset >> 4 [16,30) (unused for swizzled K-major),
+// stride byte offset >> 4 [32,46), descriptor version 1 [46,48), swizzle mode 2 = 128 B [61,64).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3ffffu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// kind::f16 instruction descriptor: D f32 (bit 4), A/B format (0 = f16) at [7,10) / [10,13), both K-major,
+// N >> 3 at [17,23), M >> 4 at [24,29).
+__device__ __forceinline__ uint32_t idesc_f16(int umma_n) { return (1u << 4) | ((uint32_t)(umma_n >> 3) << 17) | ((uint32_t)(TILE_N >> 4) << 24); }
+
+struct PrefillArgs {
+  WeightView w;
+  const uint8_t *xh;      // activation image: [k-steps][m_pad][64] fp16, swizzled rows, k-step-permuted
+  const float *row_unscale; // [m_pad]: 1 / (activation row scale * weight scale)
+  void *y;
+  int y_dtype;
+  int64_t ldy;
+  int64_t m, m_pad;
+  int ksteps;
+  int nstages;
+  float wscale;           // power of two applied to every dequantized weight
+};
+
+// Dequantize the 64 weights of k-step `kt` of row `row` and store them as 8 swizzled 16-byte chunks.
+// All arithmetic is fp16 on exactly representable integers times an fp16 scale.
+using namespace prefill_rows;
+
+__device__ __forceinline__ void zero_half_row(uint32_t dst_row, int hf) { // chunks 4hf..4hf+3, whatever the swizzle
+  const int sw = (dst_row >> 7) & 7;
+#pragma unroll
+  for (int c = 0; c < 4; c++) sts128(dst_row + (((hf * 4 + c) ^ sw) << 4), 0, 0, 0, 0);
+}
+
+template <typename RowT>
+__global__ void __launch_bounds__(NTHREADS, 1) prefill_kernel(PrefillArgs p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // dynamic shared memory is only guaranteed 16-byte aligned: align the operand stages to 1024 by hand
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  __shared__ __align__(8) uint64_t bars[3 * 8 + 1];
+  __shared__ uint32_t tmem_slot;
+  const int S = p.nstages;
+  const uint32_t a_full = smem_u32(bars), b_full = a_full + 64, empty = a_full + 128, acc_full = a_full + 192;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t n0 = (int64_t)blockIdx.x * TILE_N;
+  const int64_t m0 = (int64_t)blockIdx.y * MAX_MT;
+  const int mt = (int)min((int64_t)MAX_MT, p.m_pad - m0); // multiple of 16
+  const uint32_t b_stage_bytes = (uint32_t)mt * 128;
+  const uint32_t stage_bytes = A_STAGE_BYTES + MAX_MT * 128;
+  const int KT = p.ksteps;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; s++) {
+      mbar_init(a_full + 8 * s, PRODUCERS);
+      mbar_init(b_full + 8 * s, 1);
+      mbar_init(empty + 8 * s, 1);
+    }
+    mbar_init(acc_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 8) { // one warp owns the tensor-memory allocation
+    tmem_alloc(smem_u32(&tmem_slot), MAX_MT);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_d = tmem_slot;
+
+  if (warp < 8) {
+    // ---- producers: two threads per weight row, each converts half of the k-step ----
+    const int r = threadIdx.x & (TILE_N - 1), hf = threadIdx.x >> 7;
+    const int64_t row = n0 + r;
+    const bool row_ok = row < p.w.n;
+    const int sw = r & 7;
+    bool alive = true;
+    const int64_t lrow = row_ok ? row : p.w.n - 1; // rows past the end copy a valid row and store zeros
+    // private ring of raw bytes: slot j of this thread at raw_base + (j * PRODUCERS + tid) * SLOT
+    const uint32_t raw_base = smem_base + S * stage_bytes;
+#pragma unroll
+    for (int j = 0; j < RAW_DEPTH; j++) {
+      if (j < KT) RowT::issue(p.w, lrow, j, hf, raw_base + (j * PRODUCERS + threadIdx.x) * RowT::SLOT);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (int kt = 0; kt < KT && alive; kt++) {
+      const int s = kt % S;
+      const uint32_t slot = raw_base + ((kt % RAW_DEPTH) * PRODUCERS + threadIdx.x) * RowT::SLOT;
+      asm volatile("cp.async.wait_group %0;" ::"n"(RAW_DEPTH - 1) : "memory"); // this k-step's bytes have landed
+      if (kt >= S) alive = mbar_wait(empty + 8 * s, ((kt / S) - 1) & 1, 1u);
+      if (!alive) break;
+      const uint32_t dst_row = smem_base + s * stage_bytes + r * 128;
+      if (row_ok) RowT::store(p.w, slot, kt, hf, p.wscale, dst_row, sw);
+      else zero_half_row(dst_row, hf);
+      if (kt + RAW_DEPTH < KT) RowT::issue(p.w, lrow, kt + RAW_DEPTH, hf, slot); // refill the slot just consumed
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic-proxy stores -> visible to the tensor core
+      mbar_arrive(a_full + 8 * s);
+    }
+    // ---- epilogue: accumulator lane r = weight row n0 + r; a warp may only read the 32 lanes of its
+    // quarter (warp % 4), so warps w and w + 4 share a quarter and split the column chunks ----
+    if (alive) alive = mbar_wait(acc_full, 0, 8u);
+    if (alive) {
+      tc_fence_after();
+      const uint32_t lane_addr = tmem_d + ((uint32_t)(32 * (warp & 3)) << 16);
+      for (int c0 = 32 * hf; c0 < mt; c0 += 64) {
+        uint32_t v[32];
+        tmem_ld32(lane_addr + c0, v);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; j++) {
+            const int64_t mm = m0 + c0 + j;
+            if (mm < p.m) {
+              const float val = __uint_as_float(v[j]) * p.row_unscale[mm];
+              const int64_t idx = mm * p.ldy + row;
+              if (p.y_dtype == XNQ_F32) static_cast<float *>(p.y)[idx] = val;
+              else if (p.y_dtype == XNQ_F16) static_cast<__half *>(p.y)[idx] = __float2half_rn(val);
+              else static_cast<__nv_bfloat16 *>(p.y)[idx] = __float2bfloat16_rn(val);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 8) {
+    // ---- activation loader: one bulk copy per stage ----
+    if (lane == 0) {
+      int issued = 0;
+      for (int kt = 0; kt < KT; kt++) {
+        const int s = kt % S;
+        if (kt >= S && !mbar_wait(empty + 8 * s, ((kt / S) - 1) & 1, 2u)) break;
+        mbar_expect_tx(b_full + 8 * s, b_stage_bytes);
+        bulk_g2s(smem_base + s * stage_bytes + A_STAGE_BYTES, p.xh + ((size_t)kt * p.m_pad + m0) * 128, b_stage_bytes, b_full + 8 * s);
+        issued = kt + 1;
+      }
+      for (int kt = max(0, issued - S); kt < issued; kt++) mbar_wait(b_full + 8 * (kt % S), (kt / S) & 1, 2u); // nothing in flight at exit
+    }
+  } else {
+    // ---- MMA issuer ----
+    if (lane == 0) {
+      const uint32_t idesc = idesc_f16(mt);
+      bool alive = true;
+      for (int kt = 0; kt < KT && alive; kt++) {
+        const int s = kt % S;
+        alive = mbar_wait(a_full + 8 * s, (kt / S) & 1, 4u) && mbar_wait(b_full + 8 * s, (kt / S) & 1, 4u);
+        if (!alive) break;
+        tc_fence_after();
+        const uint64_t adesc = smem_desc_sw128(smem_base + s * stage_bytes);
+        const uint64_t bdesc = smem_desc_sw128(smem_base + s * stage_bytes + A_STAGE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < BK / 16; ks++) // K = 16 per instruction: advance 32 bytes inside the swizzle row
+          umma_f16(tmem_d, adesc + (uint64_t)(ks * 2), bdesc + (uint64_t)(ks * 2), idesc, (kt | ks) ? 1u : 0u);
+        umma_commit(empty + 8 * s); // frees the stage when these MMAs have read it
+      }
+      if (alive) umma_commit(acc_full);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) tmem_dealloc(tmem_d, MAX_MT);
+}
+
+// ---- activation image -----------------------------------------------------------------------------------
+// position of source element e (0..63) of a k-step inside the stored k-step, per weight format
+__device__ __forceinline__ int kpos_q4_0(int e) { // stored chunk (b*4 + wi) holds [j, j+2, j+16, j+18, j+1, j+3, j+17, j+19] + 32b, j = 4wi
+  const int b = e >> 5, x = e & 31, hi = x >> 4, y = x & 15, wi = y >> 2, t = y & 3;
+  const int slot = (t & 1) * 4 + hi * 2 + (t >> 1);
+  return (b * 4 + wi) * 8 + slot;
+}
+__device__ __forceinline__ int kpos_q4k(int e) { // stored chunk wi holds [l, l+2, 32+l, 32+l+2, l+1, l+3, 32+l+1, 32+l+3], l = 4wi
+  const int hi = e >> 5, y = e & 31, wi = y >> 2, t = y & 3;
+  const int slot = (t & 1) * 4 + hi * 2 + (t >> 1);
+  return wi * 8 + slot;
+}
+
+// One CTA per activation row: Q8 quantize (the reference's activation blocks), dequantize, scale the row
+// by a power of two so its largest magnitude lands in [2^11, 2^12), store fp16 into the swizzled image.
+template <int ACT, typename XT>
+__global__ void __launch_bounds__(256) prefill_prepare_acts(const XT *__restrict__ x, int64_t m, int64_t k, int64_t ldx, int64_t m_pad, int ksteps,
+                                                            int wdtype, float wscale, uint8_t *__restrict__ xh, float *__restrict__ row_unscale) {
+  __shared__ float red[8];
+  const int64_t row = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t per_row = (int64_t)ksteps * 8; // 8-element groups in the padded row
+  __half *img = reinterpret_cast<__half *>(xh);
+  if (row >= m) { // padding rows: zeros
+    for (int64_t t = threadIdx.x; t < per_row; t += blockDim.x) {
+      const int64_t kt = t >> 3;
+      *reinterpret_cast<uint4 *>(img + (kt * m_pad + row) * 64 + (t & 7) * 8) = make_uint4(0, 0, 0, 0);
+    }
+    if (threadIdx.x == 0) row_unscale[row] = 0.f;
+    return;
+  }
+  const XT *xr = x + row * ldx;
+  // pass 1: row maximum of the QUANTIZED-then-dequantized values is bounded by the raw maximum (codes <= 128/127 of it)
+  float amax = 0.f;
+  for (int64_t t = threadIdx.x; t < k / 8; t += blockDim.x) {
+    float v[8];
+    load8(xr + t * 8, v);
+#pragma unroll
+    for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  if (lane == 0) red[warp] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; i++) amax = fmaxf(amax, red[i]);
+  // power of two s with amax * s in [2^10, 2^11): room for the 128/127 growth of the Q8_K codes
+  int e = 0;
+  if (amax > 0.f && amax < 3.0e38f) {
+    (void)frexpf(amax, &e); // amax = f * 2^e, f in [0.5, 1)
+  }
+  const float rscale = amax > 0.f ? ldexpf(1.f, 11 - e) : 1.f;
+  if (threadIdx.x == 0) row_unscale[row] = 1.f / (rscale * wscale); // exact: powers of two
+  // pass 2: quantize per block, dequantize, scale, store. Whole warps stay together for the shuffles.
+  const int64_t groups = k / 8;
+  for (int64_t base = 0; base < per_row; base += blockDim.x) {
+    const int64_t t = base + threadIdx.x;
+    const bool valid = t < groups;
+    float v[8];
+    if (valid) load8(xr + t * 8, v);
+    else {
+#pragma unroll
+      for (int i = 0; i < 8; i++) v[i] = 0.f;
+    }
+    const Quant8 q = ACT == XNQ_Q8_0 ? quantize8_q8_0(v, lane) : quantize8_q8k(v, lane);
+    if (t >= per_row) continue;
+    const float ds = q.d * rscale; // exact unless it leaves the normal range
+    const int64_t kt = t >> 3;
+    __half *dst = img + (kt * m_pad + row) * 64;
+    const int sw = (int)(row & 7);
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const int code = (int)(int8_t)(((i < 4 ? q.lo : q.hi) >> (8 * (i & 3))) & 0xff);
+      const int esrc = (int)((t & 7) * 8 + i);
+      const int pos = wdtype == XNQ_Q4_0 ? kpos_q4_0(esrc) : (wdtype == XNQ_Q4K ? kpos_q4k(esrc) : esrc);
+      const int chunk = pos >> 3;
+      dst[((chunk ^ sw) << 3) + (pos & 7)] = __float2half_rn(valid ? (float)code * ds : 0.f);
+    }
+  }
+}
+
+int g_num_sms = 0;
+
+template <typename RowT>
+int launch_prefill_fmt(const PrefillArgs &a, dim3 grid, size_t smem, cudaStream_t s) {
+  prefill_kernel<RowT><<<grid, NTHREADS, smem, s>>>(a);
+  XNQ_CUDA(cudaGetLastError());
+  count_launch();
+  return XNQ_OK;
+}
+
+// operand stages + the producers' raw-byte rings + alignment slack: 215 KB of the 227 KB an SM offers
+constexpr size_t PREFILL_SMEM = NSTAGES * (A_STAGE_BYTES + MAX_MT * 128) + (size_t)RAW_DEPTH * PRODUCERS * RAW_SLOT_MAX + 1024;
+
+} // namespace
+
+size_t prefill_workspace_bytes(int64_t m, int64_t k) {
+  const int64_t m_pad = (m + 15) / 16 * 16;
+  const int64_t ksteps = (k + BK - 1) / BK;
+  return (size_t)ksteps * m_pad * 128 + (((size_t)m_pad * 4 + 255) & ~(size_t)255) + 256;
+}
+
+int launch_prefill(const WeightView &w, float wscale, const void *x, int x_dtype, int64_t m, int64_t ldx, void *y, int y_dtype, int64_t ldy,
+                   void *workspace, cudaStream_t s) {
+  const int64_t k = w.k;
+  const int64_t m_pad = (m + 15) / 16 * 16;
+  const int ksteps = (int)((k + BK - 1) / BK);
+  float *row_unscale = static_cast<float *>(workspace);
+  uint8_t *xh = static_cast<uint8_t *>(workspace) + ((((size_t)m_pad * 4 + 255) & ~(size_t)255));
+  const int act = act_dtype_for(w.dtype);
+#define XNQ_PREP(ACT, XT)                                                                                                   \
+  prefill_prepare_acts<ACT, XT><<<(unsigned)m_pad, 256, 0, s>>>(static_cast<const XT *>(x), m, k, ldx, m_pad, ksteps, w.dtype, wscale, xh, \
+                                                                row_unscale)
+  if (act == XNQ_Q8_0) {
+    if (x_dtype == XNQ_F32) XNQ_PREP(XNQ_Q8_0, float);
+    else if (x_dtype == XNQ_F16) XNQ_PREP(XNQ_Q8_0, __half);
+    else XNQ_PREP(XNQ_Q8_0, __nv_bfloat16);
+  } else {
+    if (x_dtype == XNQ_F32) XNQ_PREP(XNQ_Q8K, float);
+    else if (x_dtype == XNQ_F16) XNQ_PREP(XNQ_Q8K, __half);
+    else XNQ_PREP(XNQ_Q8K, __nv_bfloat16);
+  }
+#undef XNQ_PREP
+  XNQ_CUDA(cudaGetLastError());
+  count_launch();
+
+  PrefillArgs a{};
+  a.w = w;
+  a.xh = xh;
+  a.row_unscale = row_unscale;
+  a.y = y;
+  a.y_dtype = y_dtype;
+  a.ldy = ldy;
+  a.m = m;
+  a.m_pad = m_pad;
+  a.ksteps = ksteps;
+  a.nstages = NSTAGES;
+  a.wscale = wscale;
+  const dim3 grid((unsigned)((w.n + TILE_N - 1) / TILE_N), (unsigned)((m_pad + MAX_MT - 1) / MAX_MT));
+  profile_mark(s, true);
+  int rc;
+  switch (w.dtype) {
+    case XNQ_Q4_0: rc = launch_prefill_fmt<RowQ4_0>(a, grid, PREFILL_SMEM, s); break;
+    case XNQ_Q8_0: rc = launch_prefill_fmt<RowQ8_0>(a, grid, PREFILL_SMEM, s); break;
+    case XNQ_Q4K: rc = launch_prefill_fmt<RowQ4K>(a, grid, PREFILL_SMEM, s); break;
+    case XNQ_Q6K: rc = launch_prefill_fmt<RowQ6K>(a, grid, PREFILL_SMEM, s); break;
+    default: rc = fail(XNQ_ERR_DTYPE, "prefill: dtype %d", w.dtype);
+  }
+  profile_mark(s, false);
+  return rc;
+}
+
+int prefill_init(int device) {
+  cudaDeviceProp prop;
+  XNQ_CUDA(cudaGetDeviceProperties(&prop, device));
+  g_num_sms = prop.multiProcessorCount;
+  XNQ_CUDA(cudaFuncSetAttribute(prefill_kernel<RowQ4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PREFILL_SMEM));
+  XNQ_CUDA(cudaFuncSetAttribute(prefill_kernel<RowQ8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PREFILL_SMEM));
+  XNQ_CUDA(cudaFuncSetAttribute(prefill_kernel<RowQ4K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PREFILL_SMEM));
+  XNQ_CUDA(cudaFuncSetAttribute(prefill_kernel<RowQ6K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PREFILL_SMEM));
+  unsigned int zero = 0;
+  XNQ_CUDA(cudaMemcpyToSymbol(g_prefill_status, &zero, sizeof(zero)));
+  return XNQ_OK;
+}
+
+int prefill_status(unsigned int *bits) {
+  XNQ_CUDA(cudaMemcpyFromSymbol(bits, g_prefill_status, sizeof(*bits)));
+  return XNQ_OK;
+}
+
+} // namespace xnq
