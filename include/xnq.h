@@ -118,6 +118,22 @@ size_t xnq_matmul_workspace_bytes(const xnq_weight *w, int64_t max_m);
 int xnq_matmul_t(const xnq_weight *w, const void *x, int x_dtype, int64_t m, int64_t ldx, void *y,
                  int y_dtype, int64_t ldy, void *workspace, size_t ws_bytes, void *stream);
 
+/* xnq_matmul_t for callers that can neither supply a workspace nor let the library allocate one:
+ * hosts whose allocator owns all device memory, steps being recorded into a CUDA graph, plugins under
+ * a fixed memory budget. Same arithmetic and results as xnq_matmul_t's small-batch path, for
+ * 0 <= m <= 16; the quantized-activation scratch is a 128 KiB array built into the library (each GPU
+ * that loads the library holds it until the process exits). Rows are taken in passes that fit the
+ * array (1.25 bytes per activation element); a request fails with XNQ_ERR_SIZE only when a single
+ * row does not fit, i.e. k above about 104,000, or m > 16. It calls no cudaMalloc / cudaFree and no
+ * allocating library routine.
+ * The first call on a device looks up the array's device address; make that call (or any call of this
+ * entry) once per device before starting a stream capture. All calls share the one array: it keeps
+ * the previous call's contents (nothing needs clearing, each call rewrites what it reads), and two
+ * calls that overlap on the GPU - different streams, or different threads - race on it; callers must
+ * order them. This entry has no counterpart in the reference. */
+int xnq_matmul_t_static(const xnq_weight *w, const void *x, int x_dtype, int64_t m, int64_t ldx, void *y,
+                        int y_dtype, int64_t ldy, void *stream);
+
 /* QLinear::forward on HOST tensors (quantized/mod.rs:352-384): copies x_host [m, k] f32 to the
  * device, runs xnq_matmul_t, adds bias_host[n_local] if non-NULL, copies y back to y_host
  * [m, n_local] and synchronizes. Device staging buffers are owned by the weight handle and grow on

@@ -51,6 +51,7 @@ def lib() -> ctypes.CDLL:
     L.xnq_matmul_workspace_bytes.restype = sz
     L.xnq_matmul_t.argtypes = [vp, vp, ci, i64, i64, vp, ci, i64, vp, sz, vp]
     L.xnq_linear_forward_host.argtypes = [vp, vp, i64, vp, vp, vp]
+    L.xnq_matmul_t_static.argtypes = [vp, vp, ci, i64, i64, vp, ci, i64, vp]
     L.xnq_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint)]
     L.xnq_device_check_record.argtypes = [ctypes.POINTER(ctypes.c_ulonglong)]
     L.xnq_set_option.argtypes = [ctypes.c_char_p, ci]
