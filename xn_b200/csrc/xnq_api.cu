@@ -174,6 +174,8 @@ int xnq_device_check_record(unsigned long long out[8]) {
   return matvec_check_record(out);
 }
 
+int xnq_debug_prefill_trace(unsigned long long out[16]) { return prefill_trace(out); }
+
 int xnq_debug_trace(unsigned long long *out, unsigned int *n) {
   clear_error();
   if (!out || !n) return fail(XNQ_ERR_NULL, "debug_trace: NULL");
@@ -185,6 +187,10 @@ int xnq_set_option(const char *name, int value) {
   if (!name) return fail(XNQ_ERR_NULL, "set_option: name is NULL");
   if (std::strcmp(name, "matvec_tma") == 0) {
     g_opt_matvec_tma.store(value != 0);
+    return XNQ_OK;
+  }
+  if (std::strcmp(name, "prefill_dbg") == 0) {
+    prefill_set_dbg(value);
     return XNQ_OK;
   }
   if (std::strcmp(name, "matvec_tma_dbg") == 0) {

@@ -157,6 +157,8 @@ int launch_prefill(const WeightView &w, float wscale, const void *x, int x_dtype
                    void *workspace, cudaStream_t s);
 int prefill_init(int device);
 int prefill_status(unsigned int *bits);
+void prefill_set_dbg(int v);
+int prefill_trace(unsigned long long out[16]);
 
 // largest |dequantized weight| of the tensor, written to *dev_out (a float in device memory)
 int launch_max_abs(const WeightView &w, float *dev_out, cudaStream_t s);

@@ -57,7 +57,7 @@ constexpr int CW = XNQ_MV_CW;            // consumer warps per CTA
 constexpr int NTHREADS = (CW + 1) * 32;  // + one producer warp
 constexpr int CTAS_PER_SM = CW <= 8 ? 2 : 1; // 8 warps: two consecutive launches can share an SM
 constexpr int MAX_STAGES = 8;
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr uint32_t WAIT_LIMIT = 1u << 26; // non-blocking polls (a few ns each): about a second
 constexpr size_t SMEM_BUDGET = (CW <= 8 ? 112 : 225) * 1024; // per CTA: CTAS_PER_SM of them fit the 227 KB of an SM
 
 struct Ring {
@@ -90,7 +90,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uin
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)

@@ -36,6 +36,7 @@
 
 namespace xnq {
 
+__device__ unsigned long long g_prefill_trace[16]; // experiment (dbg bit 32): cycles per segment of producer warp 0 of block 0
 __device__ unsigned int g_prefill_status; // sticky: 1 producer wait, 2 loader wait, 4 mma wait, 8 epilogue wait expired
 
 namespace {
@@ -43,12 +44,15 @@ namespace {
 constexpr int BK = 64;             // k-step (elements) = one 128-byte swizzle row of fp16
 constexpr int TILE_N = 128;        // weight rows per CTA = UMMA M
 constexpr int MAX_MT = 256;        // activation rows per CTA = UMMA N
-constexpr int PRODUCERS = 256;     // two threads per weight row
-constexpr int NTHREADS = PRODUCERS + 64; // warps 0-7 producers/epilogue, warp 8 loader, warp 9 MMA
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr int GROUP = 256;         // one producer group: two threads per weight row
+constexpr int PRODUCERS = 2 * GROUP; // two groups take alternate k-steps, so a warp's per-k-step latency chain is halved
+constexpr int LOADER_WARP = PRODUCERS / 32, MMA_WARP = LOADER_WARP + 1;
+constexpr int NTHREADS = PRODUCERS + 64; // warps 0-15 producers/epilogue, then the loader warp and the MMA warp
+constexpr uint32_t WAIT_LIMIT = 1u << 26; // non-blocking polls (a few ns each): about a second
 constexpr int A_STAGE_BYTES = TILE_N * BK * 2; // 16 KB
-constexpr int NSTAGES = 3;         // operand stages (A 16 KB + B up to 32 KB each)
-constexpr int RAW_DEPTH = 4;       // k-steps of raw weight bytes each producer thread keeps in flight
+constexpr int NSTAGES = 4;         // even: each producer group owns every other A stage
+        // A stages (16 KB each)
+constexpr int RAW_DEPTH = 2;       // own k-steps (every other one) of raw weight bytes a producer thread keeps in flight
 constexpr int RAW_SLOT_MAX = 80;   // largest per-thread slot (Q6_K)
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -65,7 +69,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
@@ -139,8 +143,12 @@ struct PrefillArgs {
   int64_t ldy;
   int64_t m, m_pad;
   int ksteps;
-  int nstages;
+  int nstages;            // A (weight) stages
+  int b_stages;           // B (activation) stages: deeper, the bulk copy's L2 latency has to be covered
+  uint32_t b_stride;      // bytes between B stages (largest mt of the grid x 128, multiple of 1024)
+  uint32_t b_off, raw_off; // offsets of the B ring and of the producers' raw rings from the aligned base
   float wscale;           // power of two applied to every dequantized weight
+  int dbg;                // experiment knobs (0 in production): 1 skip the conversion, 2 skip the raw copies, 4 skip the proxy fence
 };
 
 // Dequantize the 64 weights of k-step `kt` of row `row` and store them as 8 swizzled 16-byte chunks.
@@ -158,28 +166,32 @@ __global__ void __launch_bounds__(NTHREADS, 1) prefill_kernel(PrefillArgs p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // dynamic shared memory is only guaranteed 16-byte aligned: align the operand stages to 1024 by hand
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  __shared__ __align__(8) uint64_t bars[3 * 8 + 1];
+  __shared__ __align__(8) uint64_t bars[4 * 8 + 1]; // a_full, a_empty, b_full, b_empty (8 each), acc_full
   __shared__ uint32_t tmem_slot;
   const int S = p.nstages;
-  const uint32_t a_full = smem_u32(bars), b_full = a_full + 64, empty = a_full + 128, acc_full = a_full + 192;
+  const int SB = p.b_stages;
+  const uint32_t a_full = smem_u32(bars), a_empty = a_full + 64, b_full = a_full + 128, b_empty = a_full + 192, acc_full = a_full + 256;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t n0 = (int64_t)blockIdx.x * TILE_N;
   const int64_t m0 = (int64_t)blockIdx.y * MAX_MT;
   const int mt = (int)min((int64_t)MAX_MT, p.m_pad - m0); // multiple of 16
   const uint32_t b_stage_bytes = (uint32_t)mt * 128;
-  const uint32_t stage_bytes = A_STAGE_BYTES + MAX_MT * 128;
+  const uint32_t a_ring = smem_base, b_ring = smem_base + p.b_off;
   const int KT = p.ksteps;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; s++) {
-      mbar_init(a_full + 8 * s, PRODUCERS);
+      mbar_init(a_full + 8 * s, GROUP / 32); // one arrival per warp of the group that owns the stage
+      mbar_init(a_empty + 8 * s, 1);
+    }
+    for (int s = 0; s < SB; s++) {
       mbar_init(b_full + 8 * s, 1);
-      mbar_init(empty + 8 * s, 1);
+      mbar_init(b_empty + 8 * s, 1);
     }
     mbar_init(acc_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 8) { // one warp owns the tensor-memory allocation
+  if (warp == LOADER_WARP) { // one warp owns the tensor-memory allocation
     tmem_alloc(smem_u32(&tmem_slot), MAX_MT);
     tmem_relinquish();
   }
@@ -188,42 +200,68 @@ __global__ void __launch_bounds__(NTHREADS, 1) prefill_kernel(PrefillArgs p) {
   tc_fence_after();
   const uint32_t tmem_d = tmem_slot;
 
-  if (warp < 8) {
-    // ---- producers: two threads per weight row, each converts half of the k-step ----
-    const int r = threadIdx.x & (TILE_N - 1), hf = threadIdx.x >> 7;
+  if (warp < PRODUCERS / 32) {
+    // ---- producers: group g takes k-steps g, g+2, ...; inside a group two threads share a weight row ----
+    const int grp = threadIdx.x / GROUP, tg = threadIdx.x % GROUP;
+    const int r = tg & (TILE_N - 1), hf = tg >> 7;
     const int64_t row = n0 + r;
     const bool row_ok = row < p.w.n;
     const int sw = r & 7;
     bool alive = true;
     const int64_t lrow = row_ok ? row : p.w.n - 1; // rows past the end copy a valid row and store zeros
     // private ring of raw bytes: slot j of this thread at raw_base + (j * PRODUCERS + tid) * SLOT
-    const uint32_t raw_base = smem_base + S * stage_bytes;
+    const uint32_t raw_base = smem_base + p.raw_off;
 #pragma unroll
     for (int j = 0; j < RAW_DEPTH; j++) {
-      if (j < KT) RowT::issue(p.w, lrow, j, hf, raw_base + (j * PRODUCERS + threadIdx.x) * RowT::SLOT);
+      if (grp + 2 * j < KT) RowT::issue(p.w, lrow, grp + 2 * j, hf, raw_base + (j * PRODUCERS + threadIdx.x) * RowT::SLOT);
       asm volatile("cp.async.commit_group;" ::: "memory");
     }
-    for (int kt = 0; kt < KT && alive; kt++) {
-      const int s = kt % S;
-      const uint32_t slot = raw_base + ((kt % RAW_DEPTH) * PRODUCERS + threadIdx.x) * RowT::SLOT;
+    const bool tr = (p.dbg & 32) && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0;
+    long long tacc[6] = {0, 0, 0, 0, 0, 0}, tprev = clock64();
+#define XNQ_TR(i) if (tr) { const long long tn = clock64(); tacc[i] += tn - tprev; tprev = tn; }
+    int s = grp, rs = 0;        // operand stage and raw-ring slot of this k-step
+    uint32_t round = 0;         // kt / S
+    for (int kt = grp; kt < KT && alive; kt += 2) {
+      const uint32_t slot = raw_base + (rs * PRODUCERS + threadIdx.x) * RowT::SLOT;
+      XNQ_TR(5)
       asm volatile("cp.async.wait_group %0;" ::"n"(RAW_DEPTH - 1) : "memory"); // this k-step's bytes have landed
-      if (kt >= S) alive = mbar_wait(empty + 8 * s, ((kt / S) - 1) & 1, 1u);
+      XNQ_TR(0)
+      if (kt >= S) { // one lane polls, the warp parks on the reconvergence barrier
+        int ok = 1;
+        if (lane == 0) ok = mbar_wait(a_empty + 8 * s, (round - 1) & 1, 1u) ? 1 : 0;
+        __syncwarp();
+        alive = __shfl_sync(0xffffffffu, ok, 0) != 0;
+      }
       if (!alive) break;
-      const uint32_t dst_row = smem_base + s * stage_bytes + r * 128;
-      if (row_ok) RowT::store(p.w, slot, kt, hf, p.wscale, dst_row, sw);
-      else zero_half_row(dst_row, hf);
-      if (kt + RAW_DEPTH < KT) RowT::issue(p.w, lrow, kt + RAW_DEPTH, hf, slot); // refill the slot just consumed
+      XNQ_TR(1)
+      const uint32_t dst_row = a_ring + s * A_STAGE_BYTES + r * 128;
+      if (!(p.dbg & 1)) {
+        if (row_ok) RowT::store(p.w, slot, kt, hf, p.wscale, dst_row, sw);
+        else zero_half_row(dst_row, hf);
+      }
+      XNQ_TR(2)
+      if (kt + 2 * RAW_DEPTH < KT && !(p.dbg & 2)) RowT::issue(p.w, lrow, kt + 2 * RAW_DEPTH, hf, slot); // refill the slot just consumed
       asm volatile("cp.async.commit_group;" ::: "memory");
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic-proxy stores -> visible to the tensor core
-      mbar_arrive(a_full + 8 * s);
+      XNQ_TR(3)
+      if (!(p.dbg & 4)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic-proxy stores -> visible to the tensor core
+      __syncwarp();
+      if (lane == 0) mbar_arrive(a_full + 8 * s); // 256 separate arrivals on one barrier word serialize; 8 do not
+      XNQ_TR(4)
+      rs = (rs + 1 == RAW_DEPTH) ? 0 : rs + 1;
+      s += 2;
+      if (s >= S) {
+        s -= S;
+        round++;
+      }
     }
+    if (tr) for (int i = 0; i < 6; i++) g_prefill_trace[i] = (unsigned long long)tacc[i];
     // ---- epilogue: accumulator lane r = weight row n0 + r; a warp may only read the 32 lanes of its
-    // quarter (warp % 4), so warps w and w + 4 share a quarter and split the column chunks ----
+    // quarter (warp % 4), so the four warps of a quarter split the 32-column chunks ----
     if (alive) alive = mbar_wait(acc_full, 0, 8u);
     if (alive) {
       tc_fence_after();
       const uint32_t lane_addr = tmem_d + ((uint32_t)(32 * (warp & 3)) << 16);
-      for (int c0 = 32 * hf; c0 < mt; c0 += 64) {
+      for (int c0 = 32 * (warp >> 2); c0 < mt; c0 += 32 * (PRODUCERS / 128)) {
         uint32_t v[32];
         tmem_ld32(lane_addr + c0, v);
         tmem_ld_wait();
@@ -242,43 +280,77 @@ __global__ void __launch_bounds__(NTHREADS, 1) prefill_kernel(PrefillArgs p) {
         }
       }
     }
-  } else if (warp == 8) {
+  } else if (warp == LOADER_WARP) {
     // ---- activation loader: one bulk copy per stage ----
     if (lane == 0) {
-      int issued = 0;
+      int issued = 0, s = 0;
+      uint32_t round = 0;
       for (int kt = 0; kt < KT; kt++) {
-        const int s = kt % S;
-        if (kt >= S && !mbar_wait(empty + 8 * s, ((kt / S) - 1) & 1, 2u)) break;
-        mbar_expect_tx(b_full + 8 * s, b_stage_bytes);
-        bulk_g2s(smem_base + s * stage_bytes + A_STAGE_BYTES, p.xh + ((size_t)kt * p.m_pad + m0) * 128, b_stage_bytes, b_full + 8 * s);
+        if (round > 0 && !mbar_wait(b_empty + 8 * s, (round - 1) & 1, 2u)) break;
+        if (p.dbg & 16) {
+          mbar_arrive(b_full + 8 * s);
+        } else {
+          mbar_expect_tx(b_full + 8 * s, b_stage_bytes);
+          bulk_g2s(b_ring + s * p.b_stride, p.xh + ((size_t)kt * p.m_pad + m0) * 128, b_stage_bytes, b_full + 8 * s);
+        }
         issued = kt + 1;
+        if (++s == SB) {
+          s = 0;
+          round++;
+        }
       }
-      for (int kt = max(0, issued - S); kt < issued; kt++) mbar_wait(b_full + 8 * (kt % S), (kt / S) & 1, 2u); // nothing in flight at exit
+      for (int kt = max(0, issued - SB); kt < issued; kt++) mbar_wait(b_full + 8 * (kt % SB), (kt / SB) & 1, 2u); // nothing in flight at exit
     }
   } else {
     // ---- MMA issuer ----
     if (lane == 0) {
       const uint32_t idesc = idesc_f16(mt);
       bool alive = true;
+      int s = 0, sb = 0;
+      uint32_t round = 0, bround = 0;
+      const bool trm = (p.dbg & 32) && blockIdx.x == 0 && blockIdx.y == 0;
+      long long macc[4] = {0, 0, 0, 0}, mprev = clock64();
+#define XNQ_TRM(i) if (trm) { const long long tn = clock64(); macc[i] += tn - mprev; mprev = tn; }
+      // The readiness of the NEXT k-step is probed before this k-step's MMAs are issued, so the probe's
+      // latency (a couple of hundred cycles per mbarrier test) hides behind the issue of four MMAs.
+      bool a_ready = false, b_ready = false;
       for (int kt = 0; kt < KT && alive; kt++) {
-        const int s = kt % S;
-        alive = mbar_wait(a_full + 8 * s, (kt / S) & 1, 4u) && mbar_wait(b_full + 8 * s, (kt / S) & 1, 4u);
+        if (!a_ready) alive = mbar_wait(a_full + 8 * s, round & 1, 4u);
+        XNQ_TRM(0)
+        if (alive && !b_ready) alive = mbar_wait(b_full + 8 * sb, bround & 1, 4u);
+        XNQ_TRM(1)
         if (!alive) break;
         tc_fence_after();
-        const uint64_t adesc = smem_desc_sw128(smem_base + s * stage_bytes);
-        const uint64_t bdesc = smem_desc_sw128(smem_base + s * stage_bytes + A_STAGE_BYTES);
+        const uint64_t adesc = smem_desc_sw128(a_ring + s * A_STAGE_BYTES);
+        const uint64_t bdesc = smem_desc_sw128(b_ring + sb * p.b_stride);
+        const int cs = s, csb = sb;
+        if (++s == S) {
+          s = 0;
+          round++;
+        }
+        if (++sb == SB) {
+          sb = 0;
+          bround++;
+        }
+        a_ready = kt + 1 < KT && mbar_try_wait(a_full + 8 * s, round & 1);
+        b_ready = kt + 1 < KT && mbar_try_wait(b_full + 8 * sb, bround & 1);
+        if (!(p.dbg & 8))
 #pragma unroll
         for (int ks = 0; ks < BK / 16; ks++) // K = 16 per instruction: advance 32 bytes inside the swizzle row
           umma_f16(tmem_d, adesc + (uint64_t)(ks * 2), bdesc + (uint64_t)(ks * 2), idesc, (kt | ks) ? 1u : 0u);
-        umma_commit(empty + 8 * s); // frees the stage when these MMAs have read it
+        XNQ_TRM(2)
+        umma_commit(a_empty + 8 * cs); // each commit fires when every MMA issued so far has read its operands
+        umma_commit(b_empty + 8 * csb);
+        XNQ_TRM(3)
       }
       if (alive) umma_commit(acc_full);
+      if (trm) for (int i = 0; i < 4; i++) g_prefill_trace[8 + i] = (unsigned long long)macc[i];
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) tmem_dealloc(tmem_d, MAX_MT);
+  if (warp == LOADER_WARP) tmem_dealloc(tmem_d, MAX_MT);
 }
 
 // ---- activation image -----------------------------------------------------------------------------------
@@ -364,6 +436,7 @@ __global__ void __launch_bounds__(256) prefill_prepare_acts(const XT *__restrict
 }
 
 int g_num_sms = 0;
+int g_prefill_dbg = 0;
 
 template <typename RowT>
 int launch_prefill_fmt(const PrefillArgs &a, dim3 grid, size_t smem, cudaStream_t s) {
@@ -373,8 +446,7 @@ int launch_prefill_fmt(const PrefillArgs &a, dim3 grid, size_t smem, cudaStream_
   return XNQ_OK;
 }
 
-// operand stages + the producers' raw-byte rings + alignment slack: 215 KB of the 227 KB an SM offers
-constexpr size_t PREFILL_SMEM = NSTAGES * (A_STAGE_BYTES + MAX_MT * 128) + (size_t)RAW_DEPTH * PRODUCERS * RAW_SLOT_MAX + 1024;
+constexpr size_t PREFILL_SMEM = 226 * 1024; // everything an SM offers minus the static barriers and a reserve
 
 } // namespace
 
@@ -419,7 +491,18 @@ int launch_prefill(const WeightView &w, float wscale, const void *x, int x_dtype
   a.m_pad = m_pad;
   a.ksteps = ksteps;
   a.nstages = NSTAGES;
+  // shared-memory plan: A ring | B ring (as deep as fits, at most 8) | raw rings
+  const int slot = w.dtype == XNQ_Q6K ? 80 : 48;
+  const uint32_t mt_max = (uint32_t)std::min<int64_t>(MAX_MT, m_pad);
+  a.b_stride = (mt_max * 128 + 1023) & ~1023u;
+  const size_t raw_bytes = (size_t)RAW_DEPTH * PRODUCERS * slot;
+  const size_t fixed = (size_t)NSTAGES * A_STAGE_BYTES + raw_bytes + 1024; // + alignment slack
+  a.b_stages = (int)std::min<size_t>(8, (PREFILL_SMEM - fixed) / a.b_stride);
+  if (a.b_stages < 2) return fail(XNQ_ERR_SIZE, "prefill: shared-memory plan does not fit");
+  a.b_off = NSTAGES * A_STAGE_BYTES;
+  a.raw_off = a.b_off + a.b_stages * a.b_stride;
   a.wscale = wscale;
+  a.dbg = g_prefill_dbg;
   const dim3 grid((unsigned)((w.n + TILE_N - 1) / TILE_N), (unsigned)((m_pad + MAX_MT - 1) / MAX_MT));
   profile_mark(s, true);
   int rc;
@@ -444,6 +527,12 @@ int prefill_init(int device) {
   XNQ_CUDA(cudaFuncSetAttribute(prefill_kernel<RowQ6K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PREFILL_SMEM));
   unsigned int zero = 0;
   XNQ_CUDA(cudaMemcpyToSymbol(g_prefill_status, &zero, sizeof(zero)));
+  return XNQ_OK;
+}
+
+void prefill_set_dbg(int v) { g_prefill_dbg = v; }
+int prefill_trace(unsigned long long out[16]) {
+  XNQ_CUDA(cudaMemcpyFromSymbol(out, g_prefill_trace, sizeof(unsigned long long) * 16));
   return XNQ_OK;
 }
 
