@@ -216,15 +216,28 @@ def run_ours(args, name, dt, n, k, m):
     x_np = synth.make_activation(m, k, seed=0)
     x = torch.from_numpy(x_np).to(dev)
     y_local = [torch.empty((m, n_local), dtype=torch.float32, device=dev) for _ in range(ncopies)]
-    y_full = [torch.empty((world, m, n_local), dtype=torch.float32, device=dev) for _ in range(ncopies)] if world > 1 else None
+    fused = world > 1 and args.gather == "peer-stores"
+    y_full = [torch.empty((world, m, n_local), dtype=torch.float32, device=dev) for _ in range(ncopies)] if world > 1 and not fused else None
+    pg = None
+    if fused:
+        # every weight copy gathers into its own slot, so a replayed step never ends on the slot it starts with
+        from xn_b200.parallel import PeerGather
+        pg = PeerGather(dev, rank, world, slot_elems=m * n, nslots=ncopies)
     for w in weights:
         w.workspace(m)
 
-    def step():
+    def local_step():
         for i, w in enumerate(weights):
             w.matmul_t(x, out=y_local[i])
-            if world > 1:
-                dist.all_gather_into_tensor(y_full[i], y_local[i])
+
+    def step():
+        for i, w in enumerate(weights):
+            if fused:
+                pg.matmul_t(w, x, slot=i)       # the kernel stores its columns into every rank's slot i
+            else:
+                w.matmul_t(x, out=y_local[i])
+                if world > 1:
+                    dist.all_gather_into_tensor(y_full[i], y_local[i])
 
     def sync_all():
         torch.cuda.synchronize(dev)
@@ -241,7 +254,7 @@ def run_ours(args, name, dt, n, k, m):
 
     # one step as a CUDA graph: the decode loop of the reference is graph-captured too
     graph = None
-    if world == 1:
+    if world == 1 or fused:   # NCCL calls stay outside graphs here: a capture that fails on one rank only would strand the others
         try:
             graph = torch.cuda.CUDAGraph()
             side = torch.cuda.Stream(dev)
@@ -253,6 +266,8 @@ def run_ours(args, name, dt, n, k, m):
             graph.replay()
             torch.cuda.synchronize(dev)
         except Exception as e:  # a failed capture must not take the benchmark down
+            if world > 1:
+                raise           # ranks must not diverge on how they launch
             sys.stderr.write(f"[bench] CUDA graph capture failed ({e}); timing plain launches\n")
             graph = None
     run_step = graph.replay if graph is not None else step
@@ -269,10 +284,12 @@ def run_ours(args, name, dt, n, k, m):
         elapsed_ms = ev0.elapsed_time(ev1)
         # keep the load on while the sampler collects enough clock samples for a median
         t_end = time.perf_counter() + 0.6
-        while len(sampler.samples) < 8 and time.perf_counter() < t_end:
-            for _ in range(50):
+        extra = 0
+        while (extra < 4) if world > 1 else (len(sampler.samples) < 8 and time.perf_counter() < t_end):
+            for _ in range(50):   # N > 1: the same count on every rank, since every gather needs all of them
                 run_step()
             torch.cuda.synchronize(dev)
+            extra += 1
     if world > 1:
         t = torch.tensor([elapsed_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -289,7 +306,7 @@ def run_ours(args, name, dt, n, k, m):
     for _ in range(prof_steps):
         if chunk_calls == 0:
             torch.cuda._sleep(40_000_000)  # let the host run ahead so no event waits for its kernel's enqueue
-        step()
+        local_step()                       # this rank's kernel on its own rows; no rank waits for another here
         chunk_calls = (chunk_calls + ncopies) % 256
     tot = ctypes.c_double()
     cnt = ctypes.c_int()
@@ -330,6 +347,12 @@ def run_ours(args, name, dt, n, k, m):
         e2e_s = float(t.item())
     e2e_value = e2e_steps * step_bytes / e2e_s / 1e9
 
+    late = pg.late_peers() if pg is not None else 0
+    if pg is not None:
+        dist.barrier()
+        pg.close()
+    if late:
+        raise SystemExit(f"rank {rank}: gathers gave up waiting for peers {late:#x}; the numbers are void")
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -358,7 +381,7 @@ def run_ours(args, name, dt, n, k, m):
         "config": {"workload": name, "ggml_dtype": dt.name, "n": n, "k": k, "m": m, "weight_copies_per_step": ncopies,
                    "cache": f"cold: {ncopies} distinct weights per step = {ncopies * w_bytes_local / 1e6:.0f} MB per GPU, "
                             f"L2 is {l2 / 1e6:.0f} MB",
-                   "parallelism": f"N-sharded x{world}" + (" + NCCL all-gather" if world > 1 else ""),
+                   "parallelism": f"N-sharded x{world}" + ((" + output gather by peer stores from the matmul kernel" if fused else " + NCCL all-gather") if world > 1 else ""),
                    "launch": "cuda graph replay" if graph is not None else "plain launches",
                    "options": args.option},
         "roofline": roofline,
@@ -381,6 +404,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--gather", default="peer-stores", choices=["peer-stores", "nccl"], help="N > 1: how output slices are gathered")
     ap.add_argument("--option", action="append", default=[], help="library switch NAME=INT (A/B measurements), e.g. matvec_tma=0")
     args = ap.parse_args()
     dt, n, k, m = WORKLOADS[args.workload]

@@ -141,6 +141,40 @@ int xnq_matmul_t_static(const xnq_weight *w, const void *x, int x_dtype, int64_t
 int xnq_linear_forward_host(xnq_weight *w, const float *x_host, int64_t m, const float *bias_host,
                             float *y_host, void *stream);
 
+/* ---- N-sharded matmul with the output gather done by the kernels (no counterpart in the
+ * reference, which runs on one device: cuda_backend/mod.rs:141-167). One process per GPU; rank r of
+ * `world` holds weight rows [r*n/G, (r+1)*n/G) (xnq_weight_upload's shard arguments). Each rank owns
+ * one device allocation of `nslots` output slots plus a row of epoch words, maps its peers'
+ * allocations through CUDA IPC, and the matmul kernel stores its output columns into the same slot
+ * of every rank; a one-warp kernel then waits (bounded) until every peer's columns have arrived.
+ * Every rank must issue the same sequence of gathers. Works inside a captured CUDA graph. --------- */
+typedef struct xnq_comm xnq_comm;
+#define XNQ_IPC_HANDLE_BYTES 64
+/* Allocates this rank's slots on the current device: nslots (2..64) buffers of slot_bytes each. */
+int xnq_comm_create(int rank, int world, size_t slot_bytes, int nslots, xnq_comm **out);
+/* The XNQ_IPC_HANDLE_BYTES-byte handle of this rank's allocation, to be sent to every peer process
+ * by whatever transport the host has (torch.distributed, MPI, a socket). */
+int xnq_comm_ipc_handle(const xnq_comm *c, void *handle64);
+/* handles: world * XNQ_IPC_HANDLE_BYTES bytes, rank p's handle at p * XNQ_IPC_HANDLE_BYTES (the own
+ * entry is ignored). Maps every peer's allocation. The host must put a barrier between the last
+ * rank's connect and the first gather. */
+int xnq_comm_connect(xnq_comm *c, const void *handles);
+/* Local device address and size of a slot. */
+int xnq_comm_slot(const xnq_comm *c, int slot, void **ptr, size_t *bytes);
+/* y[m, n_total] = x[m, k] @ W^T gathered on every rank, in slot `slot` (row stride n_total elements
+ * of y_dtype); *y_out receives the slot's local address. m == 1, k <= 4096: the decode kernel itself
+ * stores to every rank; otherwise the local result is pushed by a copy kernel. workspace as for
+ * xnq_matmul_t. A slot may be named again once another gather has been issued in between; two
+ * consecutive calls on one slot are refused, and a replayed graph must not end on the slot it
+ * starts with. */
+int xnq_matmul_t_gather(const xnq_weight *w, xnq_comm *c, int slot, const void *x, int x_dtype, int64_t m,
+                        int64_t ldx, int y_dtype, void *workspace, size_t ws_bytes, void *stream, void **y_out);
+/* Bit p set: a wait for rank p's columns gave up after 4 s (the results of that gather are not
+ * complete). Synchronizes the device. */
+int xnq_comm_status(const xnq_comm *c, unsigned int *late_peers);
+/* Unmaps the peers and frees the slots. All ranks must have finished their gathers. */
+int xnq_comm_free(xnq_comm *c);
+
 /* Sticky device-side status bits of this library's kernels on the current device (0 = healthy):
  * bit 0 a consumer's bounded mbarrier wait expired, bit 1 a producer's, bit 2 a self-check refused an
  * access. Synchronizes the device.

@@ -52,6 +52,13 @@ def lib() -> ctypes.CDLL:
     L.xnq_matmul_t.argtypes = [vp, vp, ci, i64, i64, vp, ci, i64, vp, sz, vp]
     L.xnq_linear_forward_host.argtypes = [vp, vp, i64, vp, vp, vp]
     L.xnq_matmul_t_static.argtypes = [vp, vp, ci, i64, i64, vp, ci, i64, vp]
+    L.xnq_comm_create.argtypes = [ci, ci, sz, ci, pvp]
+    L.xnq_comm_ipc_handle.argtypes = [vp, vp]
+    L.xnq_comm_connect.argtypes = [vp, vp]
+    L.xnq_comm_slot.argtypes = [vp, ci, pvp, ctypes.POINTER(sz)]
+    L.xnq_matmul_t_gather.argtypes = [vp, vp, ci, vp, ci, i64, i64, ci, vp, sz, vp, pvp]
+    L.xnq_comm_status.argtypes = [vp, ctypes.POINTER(ctypes.c_uint)]
+    L.xnq_comm_free.argtypes = [vp]
     L.xnq_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint)]
     L.xnq_device_check_record.argtypes = [ctypes.POINTER(ctypes.c_ulonglong)]
     L.xnq_set_option.argtypes = [ctypes.c_char_p, ci]

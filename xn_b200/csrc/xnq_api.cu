@@ -24,6 +24,7 @@ void clear_error() { g_err[0] = 0; }
 
 static std::atomic<uint64_t> g_launches{0};
 static std::atomic<bool> g_opt_matvec_tma{true};
+bool matvec_tma_enabled() { return g_opt_matvec_tma.load(std::memory_order_relaxed); }
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 
 struct Profile {
@@ -85,6 +86,17 @@ static Plan plan_for(int dtype, int64_t n, int64_t k) {
   }
   p.total = off ? off : 256;
   return p;
+}
+
+int check_activations(const char *who, const void *x, int x_dtype, int64_t m, int64_t k, int64_t ldx) {
+  if (!is_float_dtype(x_dtype)) return fail(XNQ_ERR_DTYPE, "%s: activation dtype %d is not f32/f16/bf16", who, x_dtype);
+  if (m < 0) return fail(XNQ_ERR_SHAPE, "%s: m = %lld", who, (long long)m);
+  if (ldx < k) return fail(XNQ_ERR_SHAPE, "%s: ldx = %lld is smaller than k = %lld", who, (long long)ldx, (long long)k);
+  if (m > 0 && !x) return fail(XNQ_ERR_NULL, "%s: x is NULL", who);
+  const size_t es = type_size(x_dtype);
+  if (m > 0 && (!aligned(x, 16) || (m > 1 && (ldx * es) % 16 != 0)))
+    return fail(XNQ_ERR_ALIGN, "%s: activation rows must start 16-byte aligned (x=%p, ldx=%lld)", who, x, (long long)ldx);
+  return XNQ_OK;
 }
 
 } // namespace xnq
@@ -347,24 +359,13 @@ int xnq_weight_canonical_bytes(const xnq_weight *w, void *host_dst, size_t nbyte
   return XNQ_OK;
 }
 
-static int check_x(const char *who, const void *x, int x_dtype, int64_t m, int64_t k, int64_t ldx) {
-  if (!is_float_dtype(x_dtype)) return fail(XNQ_ERR_DTYPE, "%s: activation dtype %d is not f32/f16/bf16", who, x_dtype);
-  if (m < 0) return fail(XNQ_ERR_SHAPE, "%s: m = %lld", who, (long long)m);
-  if (ldx < k) return fail(XNQ_ERR_SHAPE, "%s: ldx = %lld is smaller than k = %lld", who, (long long)ldx, (long long)k);
-  if (m > 0 && !x) return fail(XNQ_ERR_NULL, "%s: x is NULL", who);
-  const size_t es = type_size(x_dtype);
-  if (m > 0 && (!aligned(x, 16) || (m > 1 && (ldx * es) % 16 != 0)))
-    return fail(XNQ_ERR_ALIGN, "%s: activation rows must start 16-byte aligned (x=%p, ldx=%lld)", who, x, (long long)ldx);
-  return XNQ_OK;
-}
-
 int xnq_quantize_act(int act_dtype, const void *x, int x_dtype, int64_t m, int64_t k, int64_t ldx, void *dst, void *stream) {
   clear_error();
   if (act_dtype != XNQ_Q8_0 && act_dtype != XNQ_Q8K)
     return fail(XNQ_ERR_DTYPE, "quantize_act: %d is not an activation block format (Q8_0=8, Q8K=15)", act_dtype);
   const int bs = block_size(act_dtype);
   if (k <= 0 || k % bs != 0) return fail(XNQ_ERR_SHAPE, "quantize_act: k = %lld is not a multiple of the %d-value block", (long long)k, bs);
-  int rc = check_x("quantize_act", x, x_dtype, m, k, ldx);
+  int rc = check_activations("quantize_act", x, x_dtype, m, k, ldx);
   if (rc != XNQ_OK) return rc;
   if (m == 0) return XNQ_OK;
   if (!dst) return fail(XNQ_ERR_NULL, "quantize_act: dst_blocks is NULL");
@@ -386,7 +387,7 @@ int xnq_matmul_t(const xnq_weight *w, const void *x, int x_dtype, int64_t m, int
   clear_error();
   if (!w) return fail(XNQ_ERR_NULL, "matmul_t: weight is NULL");
   const int64_t k = w->v.k, n = w->v.n;
-  int rc = check_x("matmul_t", x, x_dtype, m, k, ldx);
+  int rc = check_activations("matmul_t", x, x_dtype, m, k, ldx);
   if (rc != XNQ_OK) return rc;
   if (!is_float_dtype(y_dtype)) return fail(XNQ_ERR_DTYPE, "matmul_t: output dtype %d is not f32/f16/bf16", y_dtype);
   if (ldy < n) return fail(XNQ_ERR_SHAPE, "matmul_t: ldy = %lld is smaller than n = %lld", (long long)ldy, (long long)n);

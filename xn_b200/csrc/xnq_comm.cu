@@ -1,0 +1,234 @@
+// N-sharded matmul with the output gather done by the kernels themselves.
+//
+// The reference runs on one device (xn-core/src/cuda_backend/mod.rs:141-167) and has no collective;
+// the quantized matmul shards along N without any exchange except the gather of the [m, n/G] output
+// slices (every output column is an independent dot product, k_quants.rs:72-75). Here that gather is
+// not a separate collective: every rank owns one device allocation ("region": a row of epoch words
+// followed by `nslots` output slots), maps the regions of the other ranks through CUDA IPC, and the
+// matmul kernel of rank r stores its columns into the same slot of EVERY rank through those
+// mappings (NVLink stores, no loads from a peer). The last CTA of the launch then publishes rank r's
+// next epoch into each peer's epoch row, and a one-warp kernel on each rank waits - bounded - until
+// every peer's epoch has reached its own count.
+//
+// Epoch counters live in device memory and are advanced by the kernels, so a captured CUDA graph can
+// be replayed: nothing about the protocol is baked into kernel arguments.
+//
+// Slot reuse. Rank r reaches the stores of its gather number e only after its wait for gather e-1
+// returned, i.e. after every peer has LAUNCHED gather e-1, which in stream order follows everything
+// that peer did with the results of gathers <= e-2. So a slot may be written again as soon as one
+// other gather lies in between: callers alternate between at least two slots (checked here for
+// consecutive calls; a replayed graph must also end on a different slot than it starts with).
+#include <cstring>
+
+#include "xnq_common.cuh"
+
+struct xnq_comm {
+  int device, rank, world, nslots;
+  size_t slot_bytes;   // rounded up to 256
+  void *region;        // local: [XNQ_MAX_RANKS epoch words, padded to 256 B][slot 0][slot 1]...
+  void *peer[xnq::XNQ_MAX_RANKS]; // peer[rank] == region; the others are IPC mappings
+  unsigned int *ctl;   // local, not shared: {epochs sent, epochs awaited, CTAs done, status bits}
+  bool connected;
+  int last_slot;
+};
+
+namespace xnq {
+namespace {
+
+constexpr size_t FLAG_BYTES = 256;
+constexpr unsigned long long WAIT_LIMIT_NS = 4000000000ull; // a peer that has not published within 4 s is reported, not awaited
+
+__device__ __forceinline__ unsigned long long gtime_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Copies this rank's [m, n] column block from its own slot into the same place of every peer's slot,
+// then publishes the epoch. Used when the producing kernel could not store remotely itself.
+__global__ void __launch_bounds__(256) gather_push_kernel(GatherArgs g, int64_t m, int64_t n, int es) {
+  const int64_t row_bytes = n * es;
+  const char *src = static_cast<const char *>(g.dst[g.rank]);
+  const bool vec = ((g.col0 * es) % 16 == 0) && ((g.ld * es) % 16 == 0) && (row_bytes % 16 == 0);
+  const int64_t unit = vec ? 16 : es;
+  const int64_t per_row = row_bytes / unit, total = m * per_row;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / per_row, c = i - r * per_row;
+    const int64_t off = (r * g.ld + g.col0) * es + c * unit;
+    if (vec) {
+      const uint4 v = *reinterpret_cast<const uint4 *>(src + off);
+      for (int p = 0; p < g.world; p++)
+        if (p != g.rank) *reinterpret_cast<uint4 *>(static_cast<char *>(g.dst[p]) + off) = v;
+    } else if (es == 4) {
+      const uint32_t v = *reinterpret_cast<const uint32_t *>(src + off);
+      for (int p = 0; p < g.world; p++)
+        if (p != g.rank) *reinterpret_cast<uint32_t *>(static_cast<char *>(g.dst[p]) + off) = v;
+    } else {
+      const uint16_t v = *reinterpret_cast<const uint16_t *>(src + off);
+      for (int p = 0; p < g.world; p++)
+        if (p != g.rank) *reinterpret_cast<uint16_t *>(static_cast<char *>(g.dst[p]) + off) = v;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) gather_publish(g);
+}
+
+// One warp; lane p waits for rank p. Gives up after WAIT_LIMIT_NS and records which peer was late.
+__global__ void gather_wait_kernel(const unsigned int *flags, unsigned int *ctl, int world, int rank) {
+  __shared__ unsigned int want;
+  if (threadIdx.x == 0) {
+    want = ctl[1] + 1;
+    ctl[1] = want;
+  }
+  __syncthreads();
+  const int p = threadIdx.x;
+  if (p < world && p != rank) {
+    const unsigned long long t0 = gtime_ns();
+    for (;;) {
+      unsigned int v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + p) : "memory");
+      if ((int)(v - want) >= 0) break;
+      if (gtime_ns() - t0 > WAIT_LIMIT_NS) {
+        atomicOr(ctl + 3, 1u << p);
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+}
+
+inline char *slot_ptr(const xnq_comm *c, int r, int slot) { return static_cast<char *>(c->peer[r]) + FLAG_BYTES + (size_t)slot * c->slot_bytes; }
+
+} // namespace
+} // namespace xnq
+
+using namespace xnq;
+
+extern "C" {
+
+int xnq_comm_create(int rank, int world, size_t slot_bytes, int nslots, xnq_comm **out) {
+  clear_error();
+  if (!out) return fail(XNQ_ERR_NULL, "comm_create: out is NULL");
+  *out = nullptr;
+  if (world < 1 || world > XNQ_MAX_RANKS || rank < 0 || rank >= world) return fail(XNQ_ERR_SHAPE, "comm_create: rank %d of %d (at most %d ranks)", rank, world, XNQ_MAX_RANKS);
+  if (nslots < 2 || nslots > 64) return fail(XNQ_ERR_SIZE, "comm_create: %d slots; consecutive gathers must alternate between at least 2 (at most 64)", nslots);
+  if (slot_bytes == 0) return fail(XNQ_ERR_SIZE, "comm_create: slot_bytes is 0");
+  xnq_comm *c = new xnq_comm();
+  std::memset(c, 0, sizeof(*c));
+  c->rank = rank, c->world = world, c->nslots = nslots, c->last_slot = -1;
+  c->slot_bytes = (slot_bytes + 255) & ~(size_t)255;
+  cudaError_t e = cudaGetDevice(&c->device);
+  if (e == cudaSuccess) e = cudaMalloc(&c->region, FLAG_BYTES + c->slot_bytes * nslots);
+  if (e == cudaSuccess) e = cudaMemset(c->region, 0, FLAG_BYTES + c->slot_bytes * nslots);
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&c->ctl), 64);
+  if (e == cudaSuccess) e = cudaMemset(c->ctl, 0, 64);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    if (c->region) cudaFree(c->region);
+    if (c->ctl) cudaFree(c->ctl);
+    delete c;
+    return fail(XNQ_ERR_CUDA, "comm_create: %s", cudaGetErrorString(e));
+  }
+  c->peer[rank] = c->region;
+  c->connected = world == 1;
+  *out = c;
+  return XNQ_OK;
+}
+
+int xnq_comm_ipc_handle(const xnq_comm *c, void *handle64) {
+  clear_error();
+  if (!c || !handle64) return fail(XNQ_ERR_NULL, "comm_ipc_handle: NULL argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == XNQ_IPC_HANDLE_BYTES, "handle size");
+  cudaIpcMemHandle_t h;
+  XNQ_CUDA(cudaIpcGetMemHandle(&h, c->region));
+  std::memcpy(handle64, &h, sizeof(h));
+  return XNQ_OK;
+}
+
+int xnq_comm_connect(xnq_comm *c, const void *handles) {
+  clear_error();
+  if (!c || !handles) return fail(XNQ_ERR_NULL, "comm_connect: NULL argument");
+  if (c->connected) return c->world == 1 ? XNQ_OK : fail(XNQ_ERR_UNSUPPORTED, "comm_connect: already connected");
+  for (int p = 0; p < c->world; p++) {
+    if (p == c->rank) continue;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, static_cast<const char *>(handles) + (size_t)p * XNQ_IPC_HANDLE_BYTES, sizeof(h));
+    XNQ_CUDA(cudaIpcOpenMemHandle(&c->peer[p], h, cudaIpcMemLazyEnablePeerAccess));
+  }
+  c->connected = true;
+  return XNQ_OK;
+}
+
+int xnq_comm_slot(const xnq_comm *c, int slot, void **ptr, size_t *bytes) {
+  clear_error();
+  if (!c || !ptr) return fail(XNQ_ERR_NULL, "comm_slot: NULL argument");
+  if (slot < 0 || slot >= c->nslots) return fail(XNQ_ERR_SIZE, "comm_slot: slot %d of %d", slot, c->nslots);
+  *ptr = slot_ptr(c, c->rank, slot);
+  if (bytes) *bytes = c->slot_bytes;
+  return XNQ_OK;
+}
+
+int xnq_comm_status(const xnq_comm *c, unsigned int *late_peers) {
+  clear_error();
+  if (!c || !late_peers) return fail(XNQ_ERR_NULL, "comm_status: NULL argument");
+  XNQ_CUDA(cudaMemcpy(late_peers, c->ctl + 3, sizeof(unsigned int), cudaMemcpyDeviceToHost));
+  return XNQ_OK;
+}
+
+int xnq_comm_free(xnq_comm *c) {
+  clear_error();
+  if (!c) return XNQ_OK;
+  for (int p = 0; p < c->world; p++)
+    if (p != c->rank && c->peer[p]) cudaIpcCloseMemHandle(c->peer[p]);
+  cudaFree(c->region);
+  cudaFree(c->ctl);
+  delete c;
+  return XNQ_OK;
+}
+
+int xnq_matmul_t_gather(const xnq_weight *w, xnq_comm *c, int slot, const void *x, int x_dtype, int64_t m, int64_t ldx, int y_dtype, void *workspace,
+                        size_t ws_bytes, void *stream, void **y_out) {
+  clear_error();
+  if (!w || !c) return fail(XNQ_ERR_NULL, "matmul_t_gather: weight or comm is NULL");
+  if (!c->connected) return fail(XNQ_ERR_UNSUPPORTED, "matmul_t_gather: comm is not connected to its peers");
+  if (slot < 0 || slot >= c->nslots) return fail(XNQ_ERR_SIZE, "matmul_t_gather: slot %d of %d", slot, c->nslots);
+  if (slot == c->last_slot) return fail(XNQ_ERR_UNSUPPORTED, "matmul_t_gather: slot %d was written by the previous gather; alternate slots", slot);
+  if (!is_float_dtype(y_dtype)) return fail(XNQ_ERR_DTYPE, "matmul_t_gather: output dtype %d is not f32/f16/bf16", y_dtype);
+  if (m < 1) return fail(XNQ_ERR_SHAPE, "matmul_t_gather: m = %lld (every rank must take part in every gather)", (long long)m);
+  const int64_t n = w->v.n, nt = w->n_total;
+  const size_t es = type_size(y_dtype);
+  if ((size_t)m * (size_t)nt * es > c->slot_bytes)
+    return fail(XNQ_ERR_SIZE, "matmul_t_gather: [%lld, %lld] output needs %zu bytes, slots have %zu", (long long)m, (long long)nt, (size_t)m * nt * es, c->slot_bytes);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  GatherArgs g{};
+  for (int p = 0; p < c->world; p++) {
+    g.dst[p] = slot_ptr(c, p, slot);
+    g.flag[p] = reinterpret_cast<unsigned int *>(c->peer[p]) + c->rank;
+  }
+  g.ctl = c->ctl, g.world = c->world, g.rank = c->rank, g.col0 = w->row0, g.ld = nt;
+  char *local = slot_ptr(c, c->rank, slot);
+  int rc;
+  if (m == 1 && matvec_tma_enabled() && matvec_tma_supported(w->v, 1)) {
+    if ((rc = check_activations("matmul_t_gather", x, x_dtype, m, w->v.k, ldx)) != XNQ_OK) return rc;
+    rc = launch_matvec_tma(w->v, x, x_dtype, nullptr, y_dtype, s, &g); // stores go to every rank's slot from inside the kernel
+    if (rc != XNQ_OK) return rc;
+  } else {
+    rc = xnq_matmul_t(w, x, x_dtype, m, ldx, local + (size_t)w->row0 * es, y_dtype, nt, workspace, ws_bytes, s);
+    if (rc != XNQ_OK) return rc;
+    const int64_t units = m * n;
+    const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(296, (units + 1023) / 1024));
+    gather_push_kernel<<<grid, 256, 0, s>>>(g, m, n, (int)es);
+    XNQ_CUDA(cudaGetLastError());
+    count_launch();
+  }
+  if (c->world > 1) {
+    gather_wait_kernel<<<1, 32, 0, s>>>(reinterpret_cast<const unsigned int *>(c->region), c->ctl, c->world, c->rank);
+    XNQ_CUDA(cudaGetLastError());
+    count_launch();
+  }
+  c->last_slot = slot;
+  if (y_out) *y_out = local;
+  return XNQ_OK;
+}
+
+} // extern "C"

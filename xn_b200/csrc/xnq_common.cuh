@@ -98,6 +98,37 @@ struct ActView {
   int16_t *bsum;
 };
 
+// Destination of an N-sharded matmul whose output slices are gathered on every rank by peer stores.
+// dst[r] is rank r's gathered-output buffer for this call (dst[rank] is local, the others are peer
+// mappings of the same allocation on the other GPUs); this rank writes columns [col0, col0 + n) of
+// every row into all of them. flag[r] is the address, inside rank r's mapping, of the word that
+// carries THIS rank's epoch; ctl is local: {epochs sent, epochs awaited, CTAs done, status bits}.
+constexpr int XNQ_MAX_RANKS = 8;
+struct GatherArgs {
+  void *dst[XNQ_MAX_RANKS];
+  unsigned int *flag[XNQ_MAX_RANKS];
+  unsigned int *ctl;
+  int world, rank;
+  int64_t col0, ld; // first column this rank produces; row stride of the gathered buffer (elements)
+};
+
+#ifdef __CUDACC__
+// Called by ONE thread of each CTA after a CTA-wide barrier that follows the CTA's stores into the
+// gathered buffers. The last CTA of the launch advances this rank's epoch and stores it, with
+// release semantics at system scope, into every peer's epoch row.
+__device__ __forceinline__ void gather_publish(const GatherArgs &g) {
+  __threadfence_system();
+  if (atomicAdd(g.ctl + 2, 1u) == gridDim.x - 1) {
+    g.ctl[2] = 0;
+    const unsigned int epoch = g.ctl[0] + 1;
+    g.ctl[0] = epoch;
+    __threadfence_system();
+    for (int p = 0; p < g.world; p++)
+      if (p != g.rank) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(g.flag[p]), "r"(epoch) : "memory");
+  }
+}
+#endif
+
 size_t act_workspace_bytes(int64_t m, int64_t k, int act_dtype);
 ActView act_view(void *workspace, int64_t m, int64_t k, int act_dtype);
 
@@ -144,7 +175,11 @@ int64_t matvec_rows_per_pass(int wdtype, int64_t k);
 
 // xnq_matvec_tma.cu  (m == 1, k <= 4096: persistent TMA-ring kernel that quantizes x in its prologue)
 bool matvec_tma_supported(const WeightView &w, int64_t m);
-int launch_matvec_tma(const WeightView &w, const void *x, int x_dtype, void *y, int y_dtype, cudaStream_t s);
+// g != nullptr: results go to column col0 + row of every rank's gathered buffer (y is ignored)
+int launch_matvec_tma(const WeightView &w, const void *x, int x_dtype, void *y, int y_dtype, cudaStream_t s, const GatherArgs *g = nullptr);
+bool matvec_tma_enabled(); // the "matvec_tma" library option
+// shared argument checks of the matmul entries (dtype, leading dimension, 16-byte row alignment)
+int check_activations(const char *who, const void *x, int x_dtype, int64_t m, int64_t k, int64_t ldx);
 int matvec_tma_init(int device);
 int matvec_status(unsigned int *bits);
 void matvec_tma_set_dbg(int v);

@@ -442,9 +442,18 @@ __device__ __forceinline__ void quantize_row_to_smem(const void *x, int x_dtype,
   }
 }
 
-template <typename LaneT, int ACT, int R>
+__device__ __forceinline__ void store_out(void *y, int y_dtype, int64_t idx, float v) {
+  if (y_dtype == XNQ_F32) static_cast<float *>(y)[idx] = v;
+  else if (y_dtype == XNQ_F16) static_cast<__half *>(y)[idx] = __float2half_rn(v);
+  else static_cast<__nv_bfloat16 *>(y)[idx] = __float2bfloat16_rn(v);
+}
+
+// GATHER: this rank holds rows [col0, col0 + n) of an N-sharded weight; every result goes straight
+// into the gathered output of every rank (plain stores through peer mappings), and the last CTA to
+// finish publishes this rank's next epoch to every peer. The waiting side is gather_wait_kernel.
+template <typename LaneT, int ACT, int R, bool GATHER>
 __global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM)
-matvec_tma_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtype, Ring ring) {
+matvec_tma_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtype, Ring ring, GatherArgs g) {
   extern __shared__ __align__(128) unsigned char smem[];
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem); // full[MAX_STAGES], empty[MAX_STAGES]
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + MAX_STAGES);
@@ -532,7 +541,7 @@ matvec_tma_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtype
 
   for (int it = 0; it < niter; it++) {
     const int s = it % S;
-    if (!mbar_wait_warp(full0 + 8 * s, (it / S) & 1, 1u, lane)) return;
+    if (!mbar_wait_warp(full0 + 8 * s, (it / S) & 1, 1u, lane)) break; // status bit is set; still take part in the epilogue
     if (tr && threadIdx.x == 0 && it == 0) g_matvec_trace[trace_slot][tb + 3] = gtime();
     const int rows = min(RPS, nrows - it * RPS);
     const int slot0 = warp * R;
@@ -563,12 +572,10 @@ matvec_tma_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtype
         const int64_t idx = row_begin + (int64_t)it * RPS + slot0 + lane;
         if (idx < 0 || idx >= w.n) {
           record_violation(0x200, it, (unsigned long long)idx, slot0, w.n);
-        } else if (y_dtype == XNQ_F32) {
-          static_cast<float *>(y)[idx] = v;
-        } else if (y_dtype == XNQ_F16) {
-          static_cast<__half *>(y)[idx] = __float2half_rn(v);
+        } else if (!GATHER) {
+          store_out(y, y_dtype, idx, v);
         } else {
-          static_cast<__nv_bfloat16 *>(y)[idx] = __float2bfloat16_rn(v);
+          for (int p = 0; p < g.world; p++) store_out(g.dst[p], y_dtype, g.col0 + idx, v);
         }
       }
     }
@@ -576,6 +583,10 @@ matvec_tma_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtype
     if (lane == 0) mbar_arrive(empty0 + 8 * s);
   }
   if (tr && threadIdx.x == 0) g_matvec_trace[trace_slot][tb + 4] = gtime();
+  if (GATHER) {
+    consumer_sync(); // every store of this CTA has been issued
+    if (threadIdx.x == 0) gather_publish(g);
+  }
 }
 
 int g_num_sms = 0;
@@ -637,7 +648,7 @@ int plan_ring(const WeightView &w, Ring &r) {
 }
 
 template <typename LaneT, int ACT, int R>
-int launch_fmt(const WeightView &w, const void *x, int x_dtype, void *y, int y_dtype, const Ring &r, cudaStream_t s) {
+int launch_fmt(const WeightView &w, const void *x, int x_dtype, void *y, int y_dtype, const Ring &r, cudaStream_t s, const GatherArgs *g) {
   const int64_t max_ctas = (w.n + r.rps - 1) / r.rps; // at least one stage of rows per CTA
   const int per_sm = (r.dbg & 8) ? 1 : CTAS_PER_SM;
   const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>((int64_t)g_num_sms * per_sm, max_ctas));
@@ -651,21 +662,24 @@ int launch_fmt(const WeightView &w, const void *x, int x_dtype, void *y, int y_d
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  XNQ_CUDA(cudaLaunchKernelEx(&cfg, matvec_tma_kernel<LaneT, ACT, R>, w, x, x_dtype, y, y_dtype, r));
+  if (g) XNQ_CUDA(cudaLaunchKernelEx(&cfg, matvec_tma_kernel<LaneT, ACT, R, true>, w, x, x_dtype, y, y_dtype, r, *g));
+  else XNQ_CUDA(cudaLaunchKernelEx(&cfg, matvec_tma_kernel<LaneT, ACT, R, false>, w, x, x_dtype, y, y_dtype, r, GatherArgs{}));
   count_launch();
   return XNQ_OK;
 }
 
 template <typename LaneT, int ACT>
-int launch_r(int R, const WeightView &w, const void *x, int x_dtype, void *y, int y_dtype, const Ring &r, cudaStream_t s) {
-  if (R == 2) return launch_fmt<LaneT, ACT, 2>(w, x, x_dtype, y, y_dtype, r, s);
-  return launch_fmt<LaneT, ACT, 1>(w, x, x_dtype, y, y_dtype, r, s);
+int launch_r(int R, const WeightView &w, const void *x, int x_dtype, void *y, int y_dtype, const Ring &r, cudaStream_t s, const GatherArgs *g) {
+  if (R == 2) return launch_fmt<LaneT, ACT, 2>(w, x, x_dtype, y, y_dtype, r, s, g);
+  return launch_fmt<LaneT, ACT, 1>(w, x, x_dtype, y, y_dtype, r, s, g);
 }
 
 template <typename LaneT, int ACT>
 int init_fmt() {
-  XNQ_CUDA(cudaFuncSetAttribute(matvec_tma_kernel<LaneT, ACT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET));
-  XNQ_CUDA(cudaFuncSetAttribute(matvec_tma_kernel<LaneT, ACT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET));
+  XNQ_CUDA(cudaFuncSetAttribute(matvec_tma_kernel<LaneT, ACT, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET));
+  XNQ_CUDA(cudaFuncSetAttribute(matvec_tma_kernel<LaneT, ACT, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET));
+  XNQ_CUDA(cudaFuncSetAttribute(matvec_tma_kernel<LaneT, ACT, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET));
+  XNQ_CUDA(cudaFuncSetAttribute(matvec_tma_kernel<LaneT, ACT, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET));
   return XNQ_OK;
 }
 
@@ -678,15 +692,15 @@ bool matvec_tma_supported(const WeightView &w, int64_t m) {
   return plan_ring(w, r) > 0;
 }
 
-int launch_matvec_tma(const WeightView &w, const void *x, int x_dtype, void *y, int y_dtype, cudaStream_t s) {
+int launch_matvec_tma(const WeightView &w, const void *x, int x_dtype, void *y, int y_dtype, cudaStream_t s, const GatherArgs *g) {
   Ring r;
   const int R = plan_ring(w, r);
   if (!R) return fail(XNQ_ERR_SIZE, "matvec_tma: no ring fits k = %lld", (long long)w.k);
   switch (w.dtype) {
-    case XNQ_Q4_0: return launch_r<Q4_0Lane, XNQ_Q8_0>(R, w, x, x_dtype, y, y_dtype, r, s);
-    case XNQ_Q8_0: return launch_r<Q8_0Lane, XNQ_Q8_0>(R, w, x, x_dtype, y, y_dtype, r, s);
-    case XNQ_Q4K: return launch_r<Q4KLane, XNQ_Q8K>(R, w, x, x_dtype, y, y_dtype, r, s);
-    case XNQ_Q6K: return launch_r<Q6KLane, XNQ_Q8K>(R, w, x, x_dtype, y, y_dtype, r, s);
+    case XNQ_Q4_0: return launch_r<Q4_0Lane, XNQ_Q8_0>(R, w, x, x_dtype, y, y_dtype, r, s, g);
+    case XNQ_Q8_0: return launch_r<Q8_0Lane, XNQ_Q8_0>(R, w, x, x_dtype, y, y_dtype, r, s, g);
+    case XNQ_Q4K: return launch_r<Q4KLane, XNQ_Q8K>(R, w, x, x_dtype, y, y_dtype, r, s, g);
+    case XNQ_Q6K: return launch_r<Q6KLane, XNQ_Q8K>(R, w, x, x_dtype, y, y_dtype, r, s, g);
   }
   return fail(XNQ_ERR_DTYPE, "matvec_tma: dtype %d", w.dtype);
 }
