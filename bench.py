@@ -50,6 +50,9 @@ WORKLOADS = {
     "C3_q4k_14336x4096_m64": (D.Q4K, 14336, 4096, 64),
     "C3_q4k_14336x4096_m512": (D.Q4K, 14336, 4096, 512),
 }
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
+# summarized under profiles/ (bytes; workloads without a capture report null)
+NCU_TRAFFIC = {"C3_q4k_14336x4096_m1": 33086464, "C3_q4k_14336x4096_m512": 38877952}
 DEFAULT_WORKLOAD = "C3_q4k_14336x4096_m1"  # the matvec the metric's 75%-of-HBM target is quoted on
 METRIC = "quant matvec HBM GB/s"
 UNIT = "GB/s"
@@ -321,7 +324,8 @@ def run_ours(args, name, dt, n, k, m):
     roofline = {"bound": "tensor" if tensor_bound else "hbm",
                 "achieved": tflops if tensor_bound else achieved, "peak": peak_tf if tensor_bound else peak,
                 "unit": "TFLOP/s" if tensor_bound else "GB/s",
-                "frac": ((tflops / peak_tf) if tensor_bound else (achieved / peak)) if achieved else None, "traffic": None,
+                "frac": ((tflops / peak_tf) if tensor_bound else (achieved / peak)) if achieved else None,
+                "traffic": NCU_TRAFFIC.get(name) if world == 1 else None,
                 "kernel": "prefill_kernel (tcgen05)" if m > 16 else ("matvec_tma_kernel" if (m == 1 and k <= 4096) else "matvec"),
                 "launch_us": kern_ms * 1e3, "launches_timed": cnt.value, "peak_kind": f"of {peak_kind}",
                 "bytes_per_launch": kern_bytes, "flops_per_launch": flops, "hbm_gbs": achieved, "tflops": tflops,

@@ -7,14 +7,14 @@
 // followed by `nslots` output slots), maps the regions of the other ranks through CUDA IPC, and the
 // matmul kernel of rank r stores its columns into the same slot of EVERY rank through those
 // mappings (NVLink stores, no loads from a peer). The last CTA of the launch then publishes rank r's
-// next epoch into each peer's epoch row, and a one-warp kernel on each rank waits - bounded - until
-// every peer's epoch has reached its own count.
+// next epoch into each peer's epoch row and waits - bounded - until every peer's epoch in the local
+// row has reached the same count, so a launch that has retired has a complete gathered buffer.
 //
 // Epoch counters live in device memory and are advanced by the kernels, so a captured CUDA graph can
 // be replayed: nothing about the protocol is baked into kernel arguments.
 //
-// Slot reuse. Rank r reaches the stores of its gather number e only after its wait for gather e-1
-// returned, i.e. after every peer has LAUNCHED gather e-1, which in stream order follows everything
+// Slot reuse. Rank r reaches the stores of its gather number e only after its gather e-1 retired,
+// i.e. after every peer has LAUNCHED gather e-1, which in stream order follows everything
 // that peer did with the results of gathers <= e-2. So a slot may be written again as soon as one
 // other gather lies in between: callers alternate between at least two slots (checked here for
 // consecutive calls; a replayed graph must also end on a different slot than it starts with).
@@ -27,7 +27,7 @@ struct xnq_comm {
   size_t slot_bytes;   // rounded up to 256
   void *region;        // local: [XNQ_MAX_RANKS epoch words, padded to 256 B][slot 0][slot 1]...
   void *peer[xnq::XNQ_MAX_RANKS]; // peer[rank] == region; the others are IPC mappings
-  unsigned int *ctl;   // local, not shared: {epochs sent, epochs awaited, CTAs done, status bits}
+  unsigned int *ctl;   // local, not shared: {epochs sent, unused, CTAs done, late-peer bits}
   bool connected;
   int last_slot;
 };
@@ -36,13 +36,6 @@ namespace xnq {
 namespace {
 
 constexpr size_t FLAG_BYTES = 256;
-constexpr unsigned long long WAIT_LIMIT_NS = 4000000000ull; // a peer that has not published within 4 s is reported, not awaited
-
-__device__ __forceinline__ unsigned long long gtime_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
 
 // Copies this rank's [m, n] column block from its own slot into the same place of every peer's slot,
 // then publishes the epoch. Used when the producing kernel could not store remotely itself.
@@ -70,31 +63,7 @@ __global__ void __launch_bounds__(256) gather_push_kernel(GatherArgs g, int64_t 
     }
   }
   __syncthreads();
-  if (threadIdx.x == 0) gather_publish(g);
-}
-
-// One warp; lane p waits for rank p. Gives up after WAIT_LIMIT_NS and records which peer was late.
-__global__ void gather_wait_kernel(const unsigned int *flags, unsigned int *ctl, int world, int rank) {
-  __shared__ unsigned int want;
-  if (threadIdx.x == 0) {
-    want = ctl[1] + 1;
-    ctl[1] = want;
-  }
-  __syncthreads();
-  const int p = threadIdx.x;
-  if (p < world && p != rank) {
-    const unsigned long long t0 = gtime_ns();
-    for (;;) {
-      unsigned int v;
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + p) : "memory");
-      if ((int)(v - want) >= 0) break;
-      if (gtime_ns() - t0 > WAIT_LIMIT_NS) {
-        atomicOr(ctl + 3, 1u << p);
-        break;
-      }
-      __nanosleep(64);
-    }
-  }
+  if (threadIdx.x == 0) gather_publish_and_wait(g);
 }
 
 inline char *slot_ptr(const xnq_comm *c, int r, int slot) { return static_cast<char *>(c->peer[r]) + FLAG_BYTES + (size_t)slot * c->slot_bytes; }
@@ -218,11 +187,6 @@ int xnq_matmul_t_gather(const xnq_weight *w, xnq_comm *c, int slot, const void *
     const int64_t units = m * n;
     const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(296, (units + 1023) / 1024));
     gather_push_kernel<<<grid, 256, 0, s>>>(g, m, n, (int)es);
-    XNQ_CUDA(cudaGetLastError());
-    count_launch();
-  }
-  if (c->world > 1) {
-    gather_wait_kernel<<<1, 32, 0, s>>>(reinterpret_cast<const unsigned int *>(c->region), c->ctl, c->world, c->rank);
     XNQ_CUDA(cudaGetLastError());
     count_launch();
   }

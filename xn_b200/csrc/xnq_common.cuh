@@ -102,7 +102,7 @@ struct ActView {
 // dst[r] is rank r's gathered-output buffer for this call (dst[rank] is local, the others are peer
 // mappings of the same allocation on the other GPUs); this rank writes columns [col0, col0 + n) of
 // every row into all of them. flag[r] is the address, inside rank r's mapping, of the word that
-// carries THIS rank's epoch; ctl is local: {epochs sent, epochs awaited, CTAs done, status bits}.
+// carries THIS rank's epoch (flag[rank] is the local word); ctl is local: {epochs sent, unused, CTAs done, late-peer bits}.
 constexpr int XNQ_MAX_RANKS = 8;
 struct GatherArgs {
   void *dst[XNQ_MAX_RANKS];
@@ -113,10 +113,14 @@ struct GatherArgs {
 };
 
 #ifdef __CUDACC__
+constexpr unsigned long long GATHER_WAIT_LIMIT_NS = 4000000000ull; // a peer that has not published within 4 s is reported, not awaited
+
 // Called by ONE thread of each CTA after a CTA-wide barrier that follows the CTA's stores into the
-// gathered buffers. The last CTA of the launch advances this rank's epoch and stores it, with
-// release semantics at system scope, into every peer's epoch row.
-__device__ __forceinline__ void gather_publish(const GatherArgs &g) {
+// gathered buffers. The last CTA of the launch advances this rank's epoch, stores it with release
+// semantics at system scope into every peer's epoch row, and then waits until every peer's epoch in
+// the local row has reached the same count: when the launch retires, the gathered buffer of this
+// rank is complete. The wait is bounded; a late peer sets its bit in ctl[3] and the kernel returns.
+__device__ __forceinline__ void gather_publish_and_wait(const GatherArgs &g) {
   __threadfence_system();
   if (atomicAdd(g.ctl + 2, 1u) == gridDim.x - 1) {
     g.ctl[2] = 0;
@@ -125,6 +129,23 @@ __device__ __forceinline__ void gather_publish(const GatherArgs &g) {
     __threadfence_system();
     for (int p = 0; p < g.world; p++)
       if (p != g.rank) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(g.flag[p]), "r"(epoch) : "memory");
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+    const unsigned int *mine = g.flag[g.rank] - g.rank; // the local epoch row
+    for (int p = 0; p < g.world; p++) {
+      if (p == g.rank) continue;
+      for (;;) {
+        unsigned int v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine + p) : "memory");
+        if ((int)(v - epoch) >= 0) break;
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        if (t - t0 > GATHER_WAIT_LIMIT_NS) {
+          atomicOr(g.ctl + 3, 1u << p);
+          break;
+        }
+      }
+    }
   }
 }
 #endif

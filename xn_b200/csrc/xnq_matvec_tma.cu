@@ -450,7 +450,7 @@ __device__ __forceinline__ void store_out(void *y, int y_dtype, int64_t idx, flo
 
 // GATHER: this rank holds rows [col0, col0 + n) of an N-sharded weight; every result goes straight
 // into the gathered output of every rank (plain stores through peer mappings), and the last CTA to
-// finish publishes this rank's next epoch to every peer. The waiting side is gather_wait_kernel.
+// finish publishes this rank's next epoch to every peer and waits (bounded) for theirs.
 template <typename LaneT, int ACT, int R, bool GATHER>
 __global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM)
 matvec_tma_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtype, Ring ring, GatherArgs g) {
@@ -585,7 +585,7 @@ matvec_tma_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtype
   if (tr && threadIdx.x == 0) g_matvec_trace[trace_slot][tb + 4] = gtime();
   if (GATHER) {
     consumer_sync(); // every store of this CTA has been issued
-    if (threadIdx.x == 0) gather_publish(g);
+    if (threadIdx.x == 0) gather_publish_and_wait(g);
   }
 }
 
