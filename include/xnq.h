@@ -70,7 +70,7 @@ int xnq_init(int device);
 int xnq_type_size(int ggml_dtype);
 int xnq_block_size(int ggml_dtype);
 
-/* Upload. `blocks` is the canonical GGUF byte image of the FULL [n, k] tensor in host memory
+/* Upload. `blocks` is the canonical GGUF byte image of the FULL [n, k] tensor, in host or device memory
  * (what QTensor::data() returns, quantized/mod.rs:330-332), nbytes = n * (k / block) * type_size.
  * With shard_count G > 1 only rows [r*n/G, (r+1)*n/G) are uploaded (n must divide by G).
  * The device layout may differ from GGUF (the reference's own Q8_0 upload re-lays out too,
@@ -95,6 +95,14 @@ int xnq_weight_dequantize(const xnq_weight *w, int out_dtype, void *dst, void *s
 /* Canonical GGUF bytes of the held rows into HOST memory (QTensor::data contract,
  * quantized/mod.rs:206-214). Synchronizes `stream`. */
 int xnq_weight_canonical_bytes(const xnq_weight *w, void *host_dst, size_t nbytes, void *stream);
+
+/* QTensor::quantize_f32 / QLinear::from_linear for a weight that already lives on the device
+ * (quantized/mod.rs:290-297, 398-405): x_dev is a dense f32 [n, k] matrix, blocks_dev receives
+ * n * k / block GGUF blocks in canonical byte order, bit-identical to the reference's host
+ * quantizers (BlockQ4_0 / BlockQ8_0 / BlockQ4K / BlockQ6K ::from_float, k_quants.rs:235-270,
+ * 636-661, 1418-1473, 1801-1871 with utils.rs:65-254). Both pointers 16-byte aligned. Feed the
+ * result to xnq_weight_upload, which accepts host or device memory for `blocks`. */
+int xnq_quantize_weight(int ggml_dtype, const float *x_dev, int64_t n, int64_t k, void *blocks_dev, void *stream);
 
 /* Quantize activations x [m, k] (row stride ldx elements, x_dtype F32/F16/BF16, device memory) to
  * canonical activation blocks in device memory: act_dtype XNQ_Q8_0 gives m*k/32 BlockQ8_0 (34 B),

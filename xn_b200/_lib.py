@@ -47,6 +47,7 @@ def lib() -> ctypes.CDLL:
     L.xnq_weight_dequantize.argtypes = [vp, ci, vp, vp]
     L.xnq_weight_canonical_bytes.argtypes = [vp, vp, sz, vp]
     L.xnq_quantize_act.argtypes = [ci, vp, ci, i64, i64, i64, vp, vp]
+    L.xnq_quantize_weight.argtypes = [ci, vp, i64, i64, vp, vp]
     L.xnq_matmul_workspace_bytes.argtypes = [vp, i64]
     L.xnq_matmul_workspace_bytes.restype = sz
     L.xnq_matmul_t.argtypes = [vp, vp, ci, i64, i64, vp, ci, i64, vp, sz, vp]

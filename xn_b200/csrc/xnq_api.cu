@@ -260,7 +260,7 @@ int xnq_weight_upload_rows(int dtype, const void *blocks, size_t nbytes, int64_t
     if ((e = cudaMemsetAsync(w->base, 0, p.total, s)) != cudaSuccess) break;
     if (nbytes == 0) break;
     if ((e = cudaMalloc(&staging, nbytes)) != cudaSuccess) break;
-    if ((e = cudaMemcpyAsync(staging, blocks, nbytes, cudaMemcpyHostToDevice, s)) != cudaSuccess) break;
+    if ((e = cudaMemcpyAsync(staging, blocks, nbytes, cudaMemcpyDefault, s)) != cudaSuccess) break;
     rc = launch_relayout(w->v, static_cast<const uint8_t *>(staging), s);
     if (rc != XNQ_OK) break;
     // largest |weight| -> the power-of-two scale of the fp16 prefill path (the staging buffer's first word is free now)
@@ -371,6 +371,18 @@ int xnq_quantize_act(int act_dtype, const void *x, int x_dtype, int64_t m, int64
   if (!dst) return fail(XNQ_ERR_NULL, "quantize_act: dst_blocks is NULL");
   if (!aligned(dst, 4)) return fail(XNQ_ERR_ALIGN, "quantize_act: dst_blocks must be 4-byte aligned");
   return launch_quantize_act_blocks(act_dtype, x, x_dtype, m, k, ldx, dst, static_cast<cudaStream_t>(stream));
+}
+
+int xnq_quantize_weight(int ggml_dtype, const float *x_dev, int64_t n, int64_t k, void *blocks_dev, void *stream) {
+  clear_error();
+  if (!is_weight_dtype(ggml_dtype)) return fail(XNQ_ERR_DTYPE, "quantize_weight: dtype %d is not Q4_0/Q8_0/Q4K/Q6K", ggml_dtype);
+  const int bs = block_size(ggml_dtype);
+  if (n < 0 || k <= 0 || k % bs != 0)
+    return fail(XNQ_ERR_SHAPE, "quantize_weight: quantized tensor must have their last dim divisible by block size [%lld, %lld] %d", (long long)n, (long long)k, bs);
+  if (n == 0) return XNQ_OK;
+  if (!x_dev || !blocks_dev) return fail(XNQ_ERR_NULL, "quantize_weight: x_dev or blocks_dev is NULL");
+  if (!aligned(x_dev, 16) || !aligned(blocks_dev, 16)) return fail(XNQ_ERR_ALIGN, "quantize_weight: x_dev and blocks_dev must be 16-byte aligned");
+  return launch_quantize_weight(ggml_dtype, x_dev, n, k, blocks_dev, static_cast<cudaStream_t>(stream));
 }
 
 size_t xnq_matmul_workspace_bytes(const xnq_weight *w, int64_t max_m) {

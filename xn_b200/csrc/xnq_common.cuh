@@ -187,6 +187,9 @@ int launch_quantize_act_blocks(int act_dtype, const void *x, int x_dtype, int64_
 int launch_quantize_act_planar(const ActView &a, const void *x, int x_dtype, int64_t ldx, cudaStream_t s);
 int quantize_init(int device);
 
+// xnq_quantize_weight.cu: dense f32 [n, k] on the device -> canonical GGUF blocks on the device
+int launch_quantize_weight(int dtype, const float *x, int64_t n, int64_t k, void *blocks, cudaStream_t s);
+
 // xnq_matvec.cu  (m <= 16)
 constexpr int MATVEC_MAX_M = 16;
 int launch_matvec(const WeightView &w, const ActView &a, void *y, int y_dtype, int64_t ldy, cudaStream_t s);

@@ -117,6 +117,22 @@ class QCudaTensor:
         return cls(out.value, device)
 
     @classmethod
+    def from_dense(cls, weight: torch.Tensor, dtype: GgmlDType, shard_rank: int = 0, shard_count: int = 1) -> "QCudaTensor":
+        """Quantize a dense ``[n, k]`` device tensor with the reference's quantizer for ``dtype`` (run on the
+        GPU, same bits) and keep the blocks on the device: ``QTensor::quantize_f32`` + ``from_qtensor``
+        (mod.rs:290-297, q8.rs:218-223) without the trip through host memory."""
+        dtype = GgmlDType(dtype)
+        if weight.dim() != 2:
+            raise ValueError(f"cuda quantized: expected a 2-d weight, got shape {tuple(weight.shape)}")
+        n, k = weight.shape
+        blocks = quantize_weight(weight, dtype)
+        out = ctypes.c_void_p()
+        with torch.cuda.device(weight.device):
+            check(_lib.lib().xnq_weight_upload(int(dtype), ctypes.c_void_p(blocks.data_ptr()), blocks.numel(), n, k,
+                                               shard_rank, shard_count, _stream_ptr(weight.device), ctypes.byref(out)))
+        return cls(out.value, weight.device)
+
+    @classmethod
     def from_rows(cls, dtype: GgmlDType, blocks: np.ndarray, n_total: int, k: int, row0: int, n_rows: int,
                   device: torch.device | str = "cuda:0") -> "QCudaTensor":
         """Upload rows ``[row0, row0 + n_rows)`` of an ``[n_total, k]`` weight from their own bytes."""
@@ -220,6 +236,11 @@ class QCudaLinear:
     def new(cls, weight: QCudaTensor, bias: Optional[torch.Tensor] = None) -> "QCudaLinear":
         return cls(weight, bias)
 
+    @classmethod
+    def from_linear(cls, weight: torch.Tensor, dtype: GgmlDType, bias: Optional[torch.Tensor] = None) -> "QCudaLinear":
+        """``QLinear::from_linear`` (mod.rs:398-405): quantize a dense linear's ``[out, in]`` weight."""
+        return cls(QCudaTensor.from_dense(weight, dtype), bias)
+
     def forward(self, xs: torch.Tensor) -> torch.Tensor:
         if xs.dim() < 2:
             raise ValueError(f"input tensor has only one dimension {tuple(xs.shape)}")  # mod.rs:363-365
@@ -227,6 +248,24 @@ class QCudaLinear:
         return out if self.bias is None else out + self.bias.to(out.dtype)  # broadcast_add, q8.rs:172-175
 
     __call__ = forward
+
+
+def quantize_weight(weight: torch.Tensor, dtype: GgmlDType) -> torch.Tensor:
+    """Canonical GGUF blocks of a dense ``[n, k]`` device tensor as a uint8 device tensor, bit-identical
+    to the reference's host quantizers (``GgmlType::from_float``, k_quants.rs:235-270, 636-661, 1418-1473,
+    1801-1871)."""
+    dtype = GgmlDType(dtype)
+    if weight.dim() != 2:
+        raise ValueError(f"quantize_weight wants a 2-d tensor, got {tuple(weight.shape)}")
+    n, k = weight.shape
+    if k % dtype.block_size:
+        raise ValueError(f"quantized tensor must have their last dim divisible by block size {tuple(weight.shape)} {dtype.block_size}")  # mod.rs:267-272
+    init(weight.device)
+    w = weight.to(torch.float32).contiguous()
+    out = torch.empty(max(n * dtype.row_bytes(k), 16), dtype=torch.uint8, device=weight.device)
+    with torch.cuda.device(weight.device):
+        check(_lib.lib().xnq_quantize_weight(int(dtype), ctypes.c_void_p(w.data_ptr()), n, k, ctypes.c_void_p(out.data_ptr()), _stream_ptr(weight.device)))
+    return out[: n * dtype.row_bytes(k)]
 
 
 def quantize_act(x: torch.Tensor, act_dtype: GgmlDType) -> torch.Tensor:
