@@ -53,6 +53,7 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
 # summarized under profiles/ (bytes; workloads without a capture report null)
 NCU_TRAFFIC = {"C3_q4k_14336x4096_m1": 33086464, "C3_q4k_14336x4096_m512": 38877952}
+DECODER_WORKLOADS = {"C5_llama7b_q4k_decode_b1": 1, "C5_llama7b_q4k_decode_b16": 16}  # batch
 DEFAULT_WORKLOAD = "C3_q4k_14336x4096_m1"  # the matvec the metric's 75%-of-HBM target is quoted on
 METRIC = "quant matvec HBM GB/s"
 UNIT = "GB/s"
@@ -401,16 +402,121 @@ def run_ours(args, name, dt, n, k, m):
         dist.destroy_process_group()
 
 
+def run_decoder(args, name, batch):
+    """Config 5: the 32-layer Q4_K decoder (Q6_K LM head). Prefill 512 random tokens, then args.steps greedy
+    decode steps replayed from one captured CUDA graph; a step is one token for each of `batch` sequences."""
+    import torch
+    import torch.distributed as dist
+
+    from xn_b200 import _lib, quantized as Q
+    from xn_b200.llama import LlamaConfig, QLlama
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    Q.init(dev)
+    L = _lib.lib()
+    cfg = LlamaConfig.llama_7b()
+    prompt_len = 512
+    steps = min(args.steps, 256)
+    t0 = time.perf_counter()
+    model = QLlama(cfg, dev, batch=batch, max_seq=prompt_len + steps + 8, rank=rank, world=world, max_prefill_rows=batch * prompt_len)
+    torch.cuda.synchronize(dev)
+    build_s = time.perf_counter() - t0
+    g = torch.Generator(device="cpu"); g.manual_seed(0)
+    prompt_host = torch.randint(0, cfg.vocab, (batch, prompt_len), generator=g).pin_memory()
+
+    def sync_all():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    model.prefill(prompt_host.to(dev))          # warm-up of the prefill path
+    sync_all()
+    ev[0].record()
+    model.prefill(prompt_host.to(dev, non_blocking=True))
+    ev[1].record()
+    sync_all()
+    prefill_ms = ev[0].elapsed_time(ev[1])
+    model.capture_decode()
+    for _ in range(max(args.warmup, 3)):
+        model._graph.replay()
+    model.prefill(prompt_host.to(dev))          # back to the end of the prompt
+    sync_all()
+    props = torch.cuda.get_device_properties(dev)
+    sampler = ClockSampler(local, str(getattr(props, "uuid", "")) or None)
+    launches_before = L.xnq_launch_count()
+    with sampler:
+        sync_all()
+        t0 = time.perf_counter()
+        ev[2].record()
+        toks = model.decode(steps)
+        ev[3].record()
+        toks_host = toks.cpu()                  # the generated ids come back to the host
+        e2e_s = time.perf_counter() - t0
+        sync_all()
+    launches = model.launches_per_step * steps   # replayed from the graph: counted once, at capture
+    decode_ms = ev[2].elapsed_time(ev[3])
+    if world > 1:
+        t = torch.tensor([decode_ms, prefill_ms, e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        decode_ms, prefill_ms, e2e_s = (float(v) for v in t.tolist())
+    late = model.pg.late_peers() if model.pg is not None else 0
+    if world > 1:
+        dist.barrier()
+    model.close()
+    if late:
+        raise SystemExit(f"rank {rank}: exchanges gave up waiting for peers {late:#x}; the numbers are void")
+    if rank == 0:
+        peak, peak_tf, peak_kind = measured_peaks()
+        wbytes = cfg.weight_bytes_per_step()
+        ms_per_step = decode_ms / steps
+        line = {
+            "metric": "7B Q4_K decode tok/s", "value": batch * steps / (decode_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "i8 block dots (dp4a), f32 accumulate; bf16 attention", "data": "synthetic",
+            "config": {"workload": name, "layers": cfg.n_layers, "d_model": cfg.d_model, "heads": f"{cfg.n_heads}q/{cfg.n_kv_heads}kv x {cfg.head_dim}",
+                       "ffn": cfg.ffn, "vocab": cfg.vocab, "linears": cfg.linear_dtype.name, "lm_head": cfg.head_dtype.name, "batch": batch,
+                       "prompt": prompt_len, "decode_steps": steps,
+                       "cache": f"{wbytes / 1e6:.0f} MB of weights per step, far above L2",
+                       "parallelism": f"tensor parallel x{world}: head-sharded attention, N-sharded linears, 4 peer-store exchanges per layer" if world > 1 else "one GPU",
+                       "launch": "one CUDA graph per decode step"},
+            "roofline": {"bound": "hbm", "achieved": wbytes / (ms_per_step * 1e-3) / 1e9 / world, "peak": peak, "unit": "GB/s",
+                         "frac": wbytes / (ms_per_step * 1e-3) / 1e9 / world / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                         "kernel": "whole decode step: weight bytes of all linears per GPU / step time", "bytes_per_step": wbytes},
+            "cpu_baseline": None,
+            "e2e": {"value": batch * steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": batch * 8,
+                    "note": "decode loop timed on the host including the copy of the generated ids back to host memory"},
+            "prefill": {"tokens": batch * prompt_len, "ms": prefill_ms, "tok_s": batch * prompt_len / (prefill_ms * 1e-3)},
+            "build_s": build_s, "gpu_launches": int(launches), "clocks": sampler.summary(),
+            "generated_head": toks_host[0, :8].tolist(),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + sorted(DECODER_WORKLOADS))
     ap.add_argument("--gather", default="peer-stores", choices=["peer-stores", "nccl"], help="N > 1: how output slices are gathered")
     ap.add_argument("--option", action="append", default=[], help="library switch NAME=INT (A/B measurements), e.g. matvec_tma=0")
     args = ap.parse_args()
+    if args.workload in DECODER_WORKLOADS:
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the decoder workloads have no CPU arm; the matmul workloads do"}), flush=True)
+            return
+        return run_decoder(args, args.workload, DECODER_WORKLOADS[args.workload])
     dt, n, k, m = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args, args.workload, dt, n, k, m)

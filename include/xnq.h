@@ -177,11 +177,39 @@ int xnq_comm_slot(const xnq_comm *c, int slot, void **ptr, size_t *bytes);
  * starts with. */
 int xnq_matmul_t_gather(const xnq_weight *w, xnq_comm *c, int slot, const void *x, int x_dtype, int64_t m,
                         int64_t ldx, int y_dtype, void *workspace, size_t ws_bytes, void *stream, void **y_out);
+/* All-gather of a tensor this rank already holds: src is [m, n_local] (row stride ld_src elements of
+ * elem_dtype) in local device memory; slot `slot` of every rank receives [m, world * n_local] with
+ * rank r's block in columns [r * n_local, (r + 1) * n_local). Same slot rule as above. */
+int xnq_comm_gather(xnq_comm *c, int slot, const void *src, int elem_dtype, int64_t m, int64_t n_local,
+                    int64_t ld_src, void *stream, void **y_out);
 /* Bit p set: a wait for rank p's columns gave up after 4 s (the results of that gather are not
  * complete). Synchronizes the device. */
 int xnq_comm_status(const xnq_comm *c, unsigned int *late_peers);
 /* Unmaps the peers and frees the slots. All ranks must have finished their gathers. */
 int xnq_comm_free(xnq_comm *c);
+
+/* ---- the operators between the quantized linears of a Llama-style decode step, fused (the callers of
+ * the path in xn-core/src/models/llama.rs:145-216, 258-265, 300-320; reference kernels rmsnorm / rope /
+ * sdpa in cuda-kernels/reduce.cu). All pointers are device memory, f32 unless stated. ------------- */
+/* x[rows, d] += delta[rows, d] (delta may be NULL), out = x * rsqrt(mean(x^2) + eps) * weight[d]. */
+int xnq_add_rmsnorm(float *x, const float *delta, const float *weight, float eps, float *out, int64_t rows,
+                    int64_t d, void *stream);
+/* out[rows, f] = silu(gate_up[rows, 0:f]) * gate_up[rows, f:2f]. */
+int xnq_swiglu(const float *gate_up, float *out, int64_t rows, int64_t f, void *stream);
+/* One new token per sequence: qkv[batch, (heads + 2 kv_heads) * head_dim] -> rotate-half RoPE at
+ * position *pos_dev (cos/sin tables [max_seq, head_dim / 2]); q_out[batch, heads, head_dim]; rotated k
+ * and plain v are stored as bf16 into k_cache / v_cache [batch, kv_heads, max_seq, head_dim]. */
+int xnq_rope_kv_store(const float *qkv, const float *cos_table, const float *sin_table, const long long *pos_dev,
+                      float *q_out, void *k_cache, void *v_cache, int64_t batch, int heads, int kv_heads,
+                      int head_dim, int64_t max_seq, void *stream);
+/* Single-query attention over cache positions 0..*pos_dev: out[batch, heads, head_dim] =
+ * softmax(q k^T / sqrt(head_dim)) v with heads / kv_heads query heads per KV head. head_dim 128. The
+ * sequence is split over several CTAs per head; `workspace` (xnq_attn_decode_workspace_bytes, zeroed
+ * once after allocation, reusable by every later call on the same stream) holds their partial sums. */
+size_t xnq_attn_decode_workspace_bytes(int64_t batch, int heads);
+int xnq_attn_decode(const float *q, const void *k_cache, const void *v_cache, const long long *pos_dev, float *out,
+                    int64_t batch, int heads, int kv_heads, int head_dim, int64_t max_seq, void *workspace,
+                    size_t ws_bytes, void *stream);
 
 /* Sticky device-side status bits of this library's kernels on the current device (0 = healthy):
  * bit 0 a consumer's bounded mbarrier wait expired, bit 1 a producer's, bit 2 a self-check refused an

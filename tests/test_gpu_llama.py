@@ -1,0 +1,108 @@
+"""The decoder harness on a tiny configuration: quantized path vs dense math on the dequantized weights,
+KV-cache consistency, graph replay, and tensor parallelism over two GPUs when present."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return float((a - b).norm() / b.norm())
+
+
+def test_tiny_decoder_matches_dense_math_and_its_own_cache():
+    from xn_b200.llama import LlamaConfig, QLlama, dense_reference_logits
+    dev = torch.device("cuda", 0)
+    m = QLlama(LlamaConfig.tiny(), dev, batch=2, max_seq=64, max_prefill_rows=64)
+    g = torch.Generator(device="cpu"); g.manual_seed(5)
+    prompt = torch.randint(0, m.cfg.vocab, (2, 12), generator=g).to(dev)
+    logits = m.prefill(prompt)
+    ref = dense_reference_logits(m, prompt)
+    assert logits.shape == (2, m.cfg.vocab)
+    assert _rel(logits, ref) < 3e-2, _rel(logits, ref)      # Q8 activation blocks + bf16 attention vs f32 dense
+    # one decode step through the cache == prefill of the extended prompt
+    nxt = m.tokens.clone()
+    m._decode_step()
+    step_logits = m.last_logits.clone()
+    m2 = QLlama(LlamaConfig.tiny(), dev, batch=2, max_seq=64, max_prefill_rows=64)
+    full = m2.prefill(torch.cat([prompt, nxt[:, None]], dim=1))
+    assert _rel(step_logits, full) < 2e-2, _rel(step_logits, full)
+
+
+def test_graph_replay_generates_what_eager_decode_generates():
+    from xn_b200.llama import LlamaConfig, QLlama
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device="cpu"); g.manual_seed(6)
+    prompt = torch.randint(0, 512, (1, 9), generator=g).to(dev)
+    a = QLlama(LlamaConfig.tiny(), dev, batch=1, max_seq=64, max_prefill_rows=64)
+    a.prefill(prompt)
+    eager = a.decode(10)
+    b = QLlama(LlamaConfig.tiny(), dev, batch=1, max_seq=64, max_prefill_rows=64)
+    b.prefill(prompt)
+    b.capture_decode()
+    replayed = b.decode(10)
+    assert torch.equal(eager, replayed)
+    assert int(b.pos.item()) == 19
+
+
+def test_fused_decode_step_agrees_with_the_torch_op_decode_step():
+    from xn_b200.llama import LlamaConfig, QLlama
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device="cpu"); g.manual_seed(8)
+    prompt = torch.randint(0, 512, (3, 11), generator=g).to(dev)
+    logits = []
+    for fused in (True, False):
+        m = QLlama(LlamaConfig.tiny(), dev, batch=3, max_seq=64, max_prefill_rows=64, fused_decode=fused)
+        m.prefill(prompt)
+        for _ in range(3):
+            m._decode_step()
+        logits.append(m.last_logits.clone())
+    # torch's attention runs on bf16 q and rounds its output to bf16; the fused one keeps f32
+    assert _rel(logits[0], logits[1]) < 3e-2, _rel(logits[0], logits[1])
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _tp_rank(rank, world, port, ret):
+    import torch.distributed as dist
+    from xn_b200.llama import LlamaConfig, QLlama
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator(device="cpu"); g.manual_seed(7)
+        prompt = torch.randint(0, 512, (2, 20), generator=g).to(dev)
+        tp = QLlama(LlamaConfig.tiny(), dev, batch=2, max_seq=64, rank=rank, world=world, max_prefill_rows=64)
+        lt = tp.prefill(prompt)
+        tp.capture_decode()
+        dist.barrier()
+        toks = tp.decode(6)
+        torch.cuda.synchronize(dev)
+        late = tp.pg.late_peers()
+        single = QLlama(LlamaConfig.tiny(), dev, batch=2, max_seq=64, max_prefill_rows=64)
+        ls = single.prefill(prompt)
+        single.capture_decode()
+        ts = single.decode(6)
+        ret[rank] = {"rel": _rel(lt, ls), "same_tokens": bool(torch.equal(toks, ts)), "late": late}
+        dist.barrier()
+        tp.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_tensor_parallel_decoder_equals_one_rank():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    ret = mp.get_context("spawn").Manager().dict()
+    mp.spawn(_tp_rank, args=(2, _free_port(), ret), nprocs=2, join=True)
+    for r in range(2):
+        assert ret[r]["late"] == 0 and ret[r]["rel"] < 1e-3 and ret[r]["same_tokens"], dict(ret)

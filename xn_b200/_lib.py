@@ -58,8 +58,16 @@ def lib() -> ctypes.CDLL:
     L.xnq_comm_connect.argtypes = [vp, vp]
     L.xnq_comm_slot.argtypes = [vp, ci, pvp, ctypes.POINTER(sz)]
     L.xnq_matmul_t_gather.argtypes = [vp, vp, ci, vp, ci, i64, i64, ci, vp, sz, vp, pvp]
+    L.xnq_comm_gather.argtypes = [vp, ci, vp, ci, i64, i64, i64, vp, pvp]
     L.xnq_comm_status.argtypes = [vp, ctypes.POINTER(ctypes.c_uint)]
     L.xnq_comm_free.argtypes = [vp]
+    fp = ctypes.c_float
+    L.xnq_add_rmsnorm.argtypes = [vp, vp, vp, fp, vp, i64, i64, vp]
+    L.xnq_swiglu.argtypes = [vp, vp, i64, i64, vp]
+    L.xnq_rope_kv_store.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, ci, ci, ci, i64, vp]
+    L.xnq_attn_decode_workspace_bytes.argtypes = [i64, ci]
+    L.xnq_attn_decode_workspace_bytes.restype = sz
+    L.xnq_attn_decode.argtypes = [vp, vp, vp, vp, vp, i64, ci, ci, ci, i64, vp, sz, vp]
     L.xnq_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint)]
     L.xnq_device_check_record.argtypes = [ctypes.POINTER(ctypes.c_ulonglong)]
     L.xnq_set_option.argtypes = [ctypes.c_char_p, ci]

@@ -37,35 +37,39 @@ namespace {
 
 constexpr size_t FLAG_BYTES = 256;
 
-// Copies this rank's [m, n] column block from its own slot into the same place of every peer's slot,
-// then publishes the epoch. Used when the producing kernel could not store remotely itself.
-__global__ void __launch_bounds__(256) gather_push_kernel(GatherArgs g, int64_t m, int64_t n, int es) {
+// Copies this rank's [m, n] column block from `src` (row stride ld_src elements; may be the rank's own
+// slot) into columns [col0, col0 + n) of the slot of every rank except `skip`, then publishes the
+// epoch and waits for the peers'. Used when the producing kernel could not store remotely itself.
+__global__ void __launch_bounds__(256) gather_push_kernel(GatherArgs g, const void *src_v, int64_t ld_src, int64_t m, int64_t n, int es, int skip) {
   const int64_t row_bytes = n * es;
-  const char *src = static_cast<const char *>(g.dst[g.rank]);
-  const bool vec = ((g.col0 * es) % 16 == 0) && ((g.ld * es) % 16 == 0) && (row_bytes % 16 == 0);
+  const char *src = static_cast<const char *>(src_v);
+  const bool vec = ((g.col0 * es) % 16 == 0) && ((g.ld * es) % 16 == 0) && (row_bytes % 16 == 0) && ((ld_src * es) % 16 == 0) &&
+                   ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
   const int64_t unit = vec ? 16 : es;
   const int64_t per_row = row_bytes / unit, total = m * per_row;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = i / per_row, c = i - r * per_row;
+    const int64_t soff = r * ld_src * es + c * unit;
     const int64_t off = (r * g.ld + g.col0) * es + c * unit;
     if (vec) {
-      const uint4 v = *reinterpret_cast<const uint4 *>(src + off);
+      const uint4 v = *reinterpret_cast<const uint4 *>(src + soff);
       for (int p = 0; p < g.world; p++)
-        if (p != g.rank) *reinterpret_cast<uint4 *>(static_cast<char *>(g.dst[p]) + off) = v;
+        if (p != skip) *reinterpret_cast<uint4 *>(static_cast<char *>(g.dst[p]) + off) = v;
     } else if (es == 4) {
-      const uint32_t v = *reinterpret_cast<const uint32_t *>(src + off);
+      const uint32_t v = *reinterpret_cast<const uint32_t *>(src + soff);
       for (int p = 0; p < g.world; p++)
-        if (p != g.rank) *reinterpret_cast<uint32_t *>(static_cast<char *>(g.dst[p]) + off) = v;
+        if (p != skip) *reinterpret_cast<uint32_t *>(static_cast<char *>(g.dst[p]) + off) = v;
     } else {
-      const uint16_t v = *reinterpret_cast<const uint16_t *>(src + off);
+      const uint16_t v = *reinterpret_cast<const uint16_t *>(src + soff);
       for (int p = 0; p < g.world; p++)
-        if (p != g.rank) *reinterpret_cast<uint16_t *>(static_cast<char *>(g.dst[p]) + off) = v;
+        if (p != skip) *reinterpret_cast<uint16_t *>(static_cast<char *>(g.dst[p]) + off) = v;
     }
   }
   __syncthreads();
   if (threadIdx.x == 0) gather_publish_and_wait(g);
 }
 
+inline bool aligned_to(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 inline char *slot_ptr(const xnq_comm *c, int r, int slot) { return static_cast<char *>(c->peer[r]) + FLAG_BYTES + (size_t)slot * c->slot_bytes; }
 
 } // namespace
@@ -155,6 +159,36 @@ int xnq_comm_free(xnq_comm *c) {
   return XNQ_OK;
 }
 
+int xnq_comm_gather(xnq_comm *c, int slot, const void *src, int elem_dtype, int64_t m, int64_t n_local, int64_t ld_src, void *stream, void **y_out) {
+  clear_error();
+  if (!c) return fail(XNQ_ERR_NULL, "comm_gather: comm is NULL");
+  if (!c->connected) return fail(XNQ_ERR_UNSUPPORTED, "comm_gather: comm is not connected to its peers");
+  if (slot < 0 || slot >= c->nslots) return fail(XNQ_ERR_SIZE, "comm_gather: slot %d of %d", slot, c->nslots);
+  if (slot == c->last_slot) return fail(XNQ_ERR_UNSUPPORTED, "comm_gather: slot %d was written by the previous gather; alternate slots", slot);
+  if (!is_float_dtype(elem_dtype)) return fail(XNQ_ERR_DTYPE, "comm_gather: element dtype %d is not f32/f16/bf16", elem_dtype);
+  if (m < 1 || n_local < 1 || ld_src < n_local) return fail(XNQ_ERR_SHAPE, "comm_gather: m = %lld, n_local = %lld, ld_src = %lld", (long long)m, (long long)n_local, (long long)ld_src);
+  if (!src) return fail(XNQ_ERR_NULL, "comm_gather: src is NULL");
+  const size_t es = type_size(elem_dtype);
+  if (!aligned_to(src, es)) return fail(XNQ_ERR_ALIGN, "comm_gather: src is not aligned to its element size");
+  const int64_t nt = n_local * c->world;
+  if ((size_t)m * (size_t)nt * es > c->slot_bytes)
+    return fail(XNQ_ERR_SIZE, "comm_gather: [%lld, %lld] output needs %zu bytes, slots have %zu", (long long)m, (long long)nt, (size_t)m * nt * es, c->slot_bytes);
+  GatherArgs g{};
+  for (int p = 0; p < c->world; p++) {
+    g.dst[p] = slot_ptr(c, p, slot);
+    g.flag[p] = reinterpret_cast<unsigned int *>(c->peer[p]) + c->rank;
+  }
+  g.ctl = c->ctl, g.world = c->world, g.rank = c->rank, g.col0 = n_local * c->rank, g.ld = nt;
+  const int64_t units = m * n_local;
+  const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(296, (units + 1023) / 1024));
+  gather_push_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(g, src, ld_src, m, n_local, (int)es, -1);
+  XNQ_CUDA(cudaGetLastError());
+  count_launch();
+  c->last_slot = slot;
+  if (y_out) *y_out = slot_ptr(c, c->rank, slot);
+  return XNQ_OK;
+}
+
 int xnq_matmul_t_gather(const xnq_weight *w, xnq_comm *c, int slot, const void *x, int x_dtype, int64_t m, int64_t ldx, int y_dtype, void *workspace,
                         size_t ws_bytes, void *stream, void **y_out) {
   clear_error();
@@ -186,7 +220,7 @@ int xnq_matmul_t_gather(const xnq_weight *w, xnq_comm *c, int slot, const void *
     if (rc != XNQ_OK) return rc;
     const int64_t units = m * n;
     const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(296, (units + 1023) / 1024));
-    gather_push_kernel<<<grid, 256, 0, s>>>(g, m, n, (int)es);
+    gather_push_kernel<<<grid, 256, 0, s>>>(g, local + (size_t)w->row0 * es, nt, m, n, (int)es, c->rank);
     XNQ_CUDA(cudaGetLastError());
     count_launch();
   }

@@ -1,0 +1,261 @@
+// The small operators that sit between the quantized linears of a Llama-style decode step, fused so a
+// step is a handful of launches per layer instead of dozens: residual-add + RMSNorm, RoPE + KV-cache
+// store, single-query attention over the cache, SwiGLU. They are the callers of the quantized matmul
+// path in the reference's model (xn-core/src/models/llama.rs:145-216, 258-265, 300-320) and follow
+// its arithmetic: RMSNorm as x * rsqrt(mean(x^2) + eps) * w, rotate-half RoPE, softmax(q k^T / sqrt(d)) v
+// with grouped-query heads, silu(gate) * up. All f32 math; the KV cache is bf16.
+#include "xnq_common.cuh"
+
+namespace xnq {
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// x[row] += delta[row] (if delta), out[row] = x[row] * rsqrt(mean(x^2) + eps) * w.  One CTA per row.
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(float *x, const float *delta, const float *w, float eps, float *out, int d) {
+  __shared__ float part[8];
+  const int64_t row = blockIdx.x;
+  float *xr = x + row * d;
+  const float *dr = delta ? delta + row * d : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+    float4 v = *reinterpret_cast<const float4 *>(xr + i);
+    if (dr) {
+      const float4 a = *reinterpret_cast<const float4 *>(dr + i);
+      v.x += a.x, v.y += a.y, v.z += a.z, v.w += a.w;
+      *reinterpret_cast<float4 *>(xr + i) = v;
+    }
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; i++) tot += part[i];
+  const float r = rsqrtf(tot / (float)d + eps);
+  for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+    const float4 v = *reinterpret_cast<const float4 *>(xr + i), g = *reinterpret_cast<const float4 *>(w + i);
+    *reinterpret_cast<float4 *>(out + row * d + i) = make_float4(v.x * r * g.x, v.y * r * g.y, v.z * r * g.z, v.w * r * g.w);
+  }
+}
+
+// out[row, j] = silu(gu[row, j]) * gu[row, f + j]
+__global__ void __launch_bounds__(256) swiglu_kernel(const float *gu, float *out, int64_t rows, int f) {
+  const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= rows * f) return;
+  const int64_t r = i / f, j = i - r * f;
+  const float4 g = *reinterpret_cast<const float4 *>(gu + r * 2 * f + j), u = *reinterpret_cast<const float4 *>(gu + r * 2 * f + f + j);
+  auto silu = [](float v) { return v / (1.f + __expf(-v)); };
+  *reinterpret_cast<float4 *>(out + i) = make_float4(silu(g.x) * u.x, silu(g.y) * u.y, silu(g.z) * u.z, silu(g.w) * u.w);
+}
+
+// One token per sequence. qkv [B, (H + 2 KV) * hd] f32 -> q_out [B, H, hd] f32 (rotated), and the rotated k
+// and plain v of every KV head go to the caches [B, KV, max_seq, hd] (bf16) at position *pos.
+// grid (H + 2 KV, B), block hd / 2.
+__global__ void rope_store_kernel(const float *qkv, const float *cos_t, const float *sin_t, const long long *pos_p, float *q_out,
+                                  __nv_bfloat16 *k_cache, __nv_bfloat16 *v_cache, int H, int KV, int hd, int max_seq) {
+  const int head = blockIdx.x, b = blockIdx.y, i = threadIdx.x, half = hd / 2;
+  const long long pos = *pos_p;
+  if (pos < 0 || pos >= max_seq) return;
+  const float *src = qkv + ((int64_t)b * (H + 2 * KV) + head) * hd;
+  const float x1 = src[i], x2 = src[i + half];
+  if (head < H + KV) {
+    const float c = cos_t[pos * half + i], s = sin_t[pos * half + i];
+    const float r1 = x1 * c - x2 * s, r2 = x2 * c + x1 * s;
+    if (head < H) {
+      float *q = q_out + ((int64_t)b * H + head) * hd;
+      q[i] = r1, q[i + half] = r2;
+    } else {
+      __nv_bfloat16 *k = k_cache + (((int64_t)b * KV + (head - H)) * max_seq + pos) * hd;
+      k[i] = __float2bfloat16_rn(r1), k[i + half] = __float2bfloat16_rn(r2);
+    }
+  } else {
+    __nv_bfloat16 *v = v_cache + (((int64_t)b * KV + (head - H - KV)) * max_seq + pos) * hd;
+    v[i] = __float2bfloat16_rn(x1), v[i + half] = __float2bfloat16_rn(x2);
+  }
+}
+
+// Single-query attention over positions 0..*pos of the cache, split over the sequence so that even one
+// sequence fills the machine: grid (heads, batch, splits), 4 warps per CTA. A warp takes 32 positions
+// at a time: lane j computes the whole q.k of position base + j (16 independent 16-byte loads of its
+// k row), the warp turns the 32 scores into softmax weights against its running maximum, and then
+// every lane accumulates its own 4 output dimensions over the 32 v rows (coalesced 256-byte rows).
+// Each CTA leaves (max, sum, acc[128]) in the workspace; the last CTA of a (head, sequence) to finish
+// merges the splits. The arrival counters wrap to zero by themselves (atomicInc), so the workspace
+// only has to be zeroed once, when it is allocated.
+constexpr int ATT_WARPS = 4, ATT_HD = 128, ATT_MAX_SPLITS = 16, ATT_REC = ATT_HD + 2;
+
+__device__ __forceinline__ void online_merge(float &m, float &l, float4 &acc, float m2, float l2, const float4 &a2) {
+  const float mn = fmaxf(m, m2);
+  const float f1 = m == -INFINITY ? 0.f : __expf(m - mn), f2 = m2 == -INFINITY ? 0.f : __expf(m2 - mn);
+  acc = make_float4(acc.x * f1 + a2.x * f2, acc.y * f1 + a2.y * f2, acc.z * f1 + a2.z * f2, acc.w * f1 + a2.w * f2);
+  l = l * f1 + l2 * f2;
+  m = mn;
+}
+
+__global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const float *q, const __nv_bfloat16 *k_cache, const __nv_bfloat16 *v_cache,
+                                                                      const long long *pos_p, float *out, float *part, unsigned int *arrivals, int H, int KV,
+                                                                      int max_seq, float scale) {
+  __shared__ __align__(16) float s_q[ATT_HD];
+  __shared__ float s_m[ATT_WARPS], s_l[ATT_WARPS];
+  __shared__ __align__(16) float s_acc[ATT_WARPS][ATT_HD];
+  __shared__ bool s_last;
+  const int head = blockIdx.x, b = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvh = head / (H / KV);
+  long long last = *pos_p;
+  if (last >= max_seq) last = max_seq - 1;
+  const long long npos = last + 1, per = (npos + nsplit - 1) / nsplit;
+  const long long c0 = split * per, c1 = min(npos, c0 + per);
+  if (threadIdx.x < ATT_HD) s_q[threadIdx.x] = q[((int64_t)b * H + head) * ATT_HD + threadIdx.x] * scale;
+  __syncthreads();
+  const __nv_bfloat16 *kb = k_cache + ((int64_t)b * KV + kvh) * max_seq * ATT_HD, *vb = v_cache + ((int64_t)b * KV + kvh) * max_seq * ATT_HD;
+  float m = -INFINITY, l = 0.f;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (long long base = c0 + warp * 32; base < c1; base += ATT_WARPS * 32) {
+    const long long p = base + lane;
+    float s = -INFINITY;
+    if (p < c1) {
+      uint4 kr[16];
+#pragma unroll
+      for (int c = 0; c < 16; c++) kr[c] = *reinterpret_cast<const uint4 *>(kb + p * ATT_HD + c * 8);
+      float d = 0.f;
+#pragma unroll
+      for (int c = 0; c < 16; c++) {
+        const float4 qa = *reinterpret_cast<const float4 *>(&s_q[c * 8]), qb = *reinterpret_cast<const float4 *>(&s_q[c * 8 + 4]);
+        const float2 k0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&kr[c].x)), k1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&kr[c].y));
+        const float2 k2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&kr[c].z)), k3 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&kr[c].w));
+        d += qa.x * k0.x + qa.y * k0.y + qa.z * k1.x + qa.w * k1.y + qb.x * k2.x + qb.y * k2.y + qb.z * k3.x + qb.w * k3.y;
+      }
+      s = d;
+    }
+    const float mn = fmaxf(m, warp_max(s));
+    const float pw = s == -INFINITY ? 0.f : __expf(s - mn), corr = m == -INFINITY ? 0.f : __expf(m - mn);
+    l = l * corr + warp_sum(pw);
+    acc = make_float4(acc.x * corr, acc.y * corr, acc.z * corr, acc.w * corr);
+    const int cnt = (int)min((long long)32, c1 - base);
+#pragma unroll 8
+    for (int j = 0; j < cnt; j++) {
+      const float w = __shfl_sync(0xffffffffu, pw, j);
+      const uint2 vr = *reinterpret_cast<const uint2 *>(vb + (base + j) * ATT_HD + lane * 4);
+      const float2 v01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&vr.x)), v23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&vr.y));
+      acc.x += w * v01.x, acc.y += w * v01.y, acc.z += w * v23.x, acc.w += w * v23.y;
+    }
+    m = mn;
+  }
+  if (lane == 0) s_m[warp] = m, s_l[warp] = l;
+  *reinterpret_cast<float4 *>(&s_acc[warp][lane * 4]) = acc;
+  __syncthreads();
+  float *rec = part + (((int64_t)b * H + head) * ATT_MAX_SPLITS + split) * ATT_REC;
+  if (warp == 0) { // merge the CTA's warps; lane owns dims 4*lane..
+    float gm = s_m[0], gl = s_l[0];
+    float4 ga = *reinterpret_cast<const float4 *>(&s_acc[0][lane * 4]);
+#pragma unroll
+    for (int w = 1; w < ATT_WARPS; w++) online_merge(gm, gl, ga, s_m[w], s_l[w], *reinterpret_cast<const float4 *>(&s_acc[w][lane * 4]));
+    if (nsplit == 1) {
+      *reinterpret_cast<float4 *>(out + ((int64_t)b * H + head) * ATT_HD + lane * 4) = make_float4(ga.x / gl, ga.y / gl, ga.z / gl, ga.w / gl);
+      return;
+    }
+    if (lane == 0) rec[0] = gm, rec[1] = gl;
+    rec[2 + lane * 4 + 0] = ga.x, rec[2 + lane * 4 + 1] = ga.y, rec[2 + lane * 4 + 2] = ga.z, rec[2 + lane * 4 + 3] = ga.w;
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) s_last = atomicInc(arrivals + b * H + head, nsplit - 1) == (unsigned)(nsplit - 1);
+    __syncwarp();
+    if (!s_last) return;
+    __threadfence();
+    const float *r0 = part + ((int64_t)b * H + head) * ATT_MAX_SPLITS * ATT_REC;
+    gm = -INFINITY, gl = 0.f, ga = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int sidx = 0; sidx < nsplit; sidx++) {
+      const volatile float *r = r0 + sidx * ATT_REC;
+      online_merge(gm, gl, ga, r[0], r[1], make_float4(r[2 + lane * 4], r[3 + lane * 4], r[4 + lane * 4], r[5 + lane * 4]));
+    }
+    *reinterpret_cast<float4 *>(out + ((int64_t)b * H + head) * ATT_HD + lane * 4) = make_float4(ga.x / gl, ga.y / gl, ga.z / gl, ga.w / gl);
+  }
+}
+
+} // namespace
+} // namespace xnq
+
+using namespace xnq;
+
+extern "C" {
+
+int xnq_add_rmsnorm(float *x, const float *delta, const float *weight, float eps, float *out, int64_t rows, int64_t d, void *stream) {
+  clear_error();
+  if (!x || !weight || !out) return fail(XNQ_ERR_NULL, "add_rmsnorm: NULL argument");
+  if (rows < 0 || d <= 0 || d % 4) return fail(XNQ_ERR_SHAPE, "add_rmsnorm: rows = %lld, d = %lld (d must be a multiple of 4)", (long long)rows, (long long)d);
+  if (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) return fail(XNQ_ERR_ALIGN, "add_rmsnorm: pointers must be 16-byte aligned");
+  if (rows == 0) return XNQ_OK;
+  add_rmsnorm_kernel<<<(unsigned)rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, delta, weight, eps, out, (int)d);
+  XNQ_CUDA(cudaGetLastError());
+  count_launch();
+  return XNQ_OK;
+}
+
+int xnq_swiglu(const float *gate_up, float *out, int64_t rows, int64_t f, void *stream) {
+  clear_error();
+  if (!gate_up || !out) return fail(XNQ_ERR_NULL, "swiglu: NULL argument");
+  if (rows < 0 || f <= 0 || f % 4) return fail(XNQ_ERR_SHAPE, "swiglu: rows = %lld, f = %lld (f must be a multiple of 4)", (long long)rows, (long long)f);
+  if (((uintptr_t)gate_up | (uintptr_t)out) & 15) return fail(XNQ_ERR_ALIGN, "swiglu: pointers must be 16-byte aligned");
+  if (rows == 0) return XNQ_OK;
+  const int64_t quads = rows * f / 4;
+  swiglu_kernel<<<(unsigned)((quads + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(gate_up, out, rows, (int)f);
+  XNQ_CUDA(cudaGetLastError());
+  count_launch();
+  return XNQ_OK;
+}
+
+int xnq_rope_kv_store(const float *qkv, const float *cos_table, const float *sin_table, const long long *pos_dev, float *q_out, void *k_cache,
+                      void *v_cache, int64_t batch, int heads, int kv_heads, int head_dim, int64_t max_seq, void *stream) {
+  clear_error();
+  if (!qkv || !cos_table || !sin_table || !pos_dev || !q_out || !k_cache || !v_cache) return fail(XNQ_ERR_NULL, "rope_kv_store: NULL argument");
+  if (batch < 0 || heads < 1 || kv_heads < 1 || head_dim < 2 || head_dim % 2 || head_dim > 2048 || max_seq < 1)
+    return fail(XNQ_ERR_SHAPE, "rope_kv_store: batch %lld heads %d kv_heads %d head_dim %d max_seq %lld", (long long)batch, heads, kv_heads, head_dim, (long long)max_seq);
+  if (batch == 0) return XNQ_OK;
+  rope_store_kernel<<<dim3(heads + 2 * kv_heads, (unsigned)batch), head_dim / 2, 0, static_cast<cudaStream_t>(stream)>>>(
+      qkv, cos_table, sin_table, pos_dev, q_out, static_cast<__nv_bfloat16 *>(k_cache), static_cast<__nv_bfloat16 *>(v_cache), heads, kv_heads, head_dim, (int)max_seq);
+  XNQ_CUDA(cudaGetLastError());
+  count_launch();
+  return XNQ_OK;
+}
+
+size_t xnq_attn_decode_workspace_bytes(int64_t batch, int heads) {
+  if (batch <= 0 || heads <= 0) return 0;
+  return (size_t)batch * heads * (ATT_MAX_SPLITS * ATT_REC * sizeof(float) + sizeof(unsigned int));
+}
+
+int xnq_attn_decode(const float *q, const void *k_cache, const void *v_cache, const long long *pos_dev, float *out, int64_t batch, int heads,
+                    int kv_heads, int head_dim, int64_t max_seq, void *workspace, size_t ws_bytes, void *stream) {
+  clear_error();
+  if (!q || !k_cache || !v_cache || !pos_dev || !out) return fail(XNQ_ERR_NULL, "attn_decode: NULL argument");
+  if (head_dim != ATT_HD) return fail(XNQ_ERR_UNSUPPORTED, "attn_decode: head_dim %d (this kernel is written for %d)", head_dim, ATT_HD);
+  if (batch < 0 || heads < 1 || kv_heads < 1 || heads % kv_heads || max_seq < 1)
+    return fail(XNQ_ERR_SHAPE, "attn_decode: batch %lld heads %d kv_heads %d max_seq %lld", (long long)batch, heads, kv_heads, (long long)max_seq);
+  if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out | (uintptr_t)workspace) & 15) return fail(XNQ_ERR_ALIGN, "attn_decode: pointers must be 16-byte aligned");
+  if (batch == 0) return XNQ_OK;
+  const size_t need = xnq_attn_decode_workspace_bytes(batch, heads);
+  if (!workspace || ws_bytes < need) return fail(XNQ_ERR_SIZE, "attn_decode: workspace has %zu bytes, needs %zu (zero it once after allocating)", ws_bytes, need);
+  int splits = (int)(296 / (batch * heads));
+  splits = splits < 1 ? 1 : (splits > ATT_MAX_SPLITS ? ATT_MAX_SPLITS : splits);
+  float *part = static_cast<float *>(workspace);
+  unsigned int *arrivals = reinterpret_cast<unsigned int *>(part + (size_t)batch * heads * ATT_MAX_SPLITS * ATT_REC);
+  attn_decode_kernel<<<dim3(heads, (unsigned)batch, splits), ATT_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      q, static_cast<const __nv_bfloat16 *>(k_cache), static_cast<const __nv_bfloat16 *>(v_cache), pos_dev, out, part, arrivals, heads, kv_heads, (int)max_seq,
+      1.0f / sqrtf((float)head_dim));
+  XNQ_CUDA(cudaGetLastError());
+  count_launch();
+  return XNQ_OK;
+}
+
+} // extern "C"

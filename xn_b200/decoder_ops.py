@@ -1,0 +1,71 @@
+"""Torch-tensor wrappers of the fused decode-step operators (``xnq_add_rmsnorm``, ``xnq_swiglu``,
+``xnq_rope_kv_store``, ``xnq_attn_decode``): the pieces of the reference's Llama block between its
+linears (xn-core/src/models/llama.rs:145-216, 258-265, 300-320)."""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .quantized import _stream_ptr
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _f32c(*ts):
+    for t in ts:
+        if t is not None and (t.dtype is not torch.float32 or not t.is_contiguous()):
+            raise ValueError("expected contiguous float32 tensors")
+
+
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """In place ``x += delta`` (skipped when ``delta`` is None), then ``out = rmsnorm(x) * weight``; ``x`` is ``[rows, d]``."""
+    _f32c(x, delta, weight, out)
+    rows, d = x.shape
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().xnq_add_rmsnorm(_p(x), _p(delta), _p(weight), eps, _p(out), rows, d, _stream_ptr(x.device)))
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[rows, f] = silu(gate_up[:, :f]) * gate_up[:, f:]``."""
+    _f32c(gate_up, out)
+    rows, f2 = gate_up.shape
+    with torch.cuda.device(out.device):
+        _lib.check(_lib.lib().xnq_swiglu(_p(gate_up), _p(out), rows, f2 // 2, _stream_ptr(out.device)))
+    return out
+
+
+def rope_kv_store(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor,
+                  v_cache: torch.Tensor, heads: int, kv_heads: int) -> None:
+    """One token per sequence: rotate q and k at ``pos`` (int64 device scalar), write q to ``q_out [B, heads, hd]``
+    and k, v (bf16) into the caches ``[B, kv_heads, max_seq, hd]`` at that position."""
+    _f32c(qkv, cos, sin, q_out)
+    B, _, max_seq, hd = k_cache.shape
+    if k_cache.dtype is not torch.bfloat16 or not k_cache.is_contiguous() or not v_cache.is_contiguous() or pos.dtype is not torch.int64:
+        raise ValueError("caches must be contiguous bfloat16 and pos int64")
+    with torch.cuda.device(qkv.device):
+        _lib.check(_lib.lib().xnq_rope_kv_store(_p(qkv), _p(cos), _p(sin), _p(pos), _p(q_out), _p(k_cache), _p(v_cache), B, heads, kv_heads, hd,
+                                                max_seq, _stream_ptr(qkv.device)))
+
+
+_attn_ws: dict[tuple[int, int, int], torch.Tensor] = {}
+
+
+def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int) -> torch.Tensor:
+    """Single-query attention over cache positions ``0..pos``; ``q`` and ``out`` are ``[B, heads, hd]``."""
+    _f32c(q, out)
+    B, _, max_seq, hd = k_cache.shape
+    L = _lib.lib()
+    key = (q.device.index or 0, B, heads)
+    ws = _attn_ws.get(key)
+    if ws is None:   # zeroed once; the kernel leaves its arrival counters at zero
+        ws = _attn_ws[key] = torch.zeros(max(int(L.xnq_attn_decode_workspace_bytes(B, heads)), 16), dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        _lib.check(L.xnq_attn_decode(_p(q), _p(k_cache), _p(v_cache), _p(pos), _p(out), B, heads, kv_heads, hd, max_seq, _p(ws), ws.numel(),
+                                     _stream_ptr(q.device)))
+    return out

@@ -128,6 +128,29 @@ class PeerGather:
             y = y.view(torch.bfloat16)
         return y.view(*lhs.shape[:-1], w.n_total)
 
+    def gather(self, y_local: torch.Tensor, slot: Optional[int] = None) -> torch.Tensor:
+        """All-gather ``(.., n_local)`` blocks that each rank already holds into ``(.., world * n_local)``."""
+        import ctypes
+
+        from . import _lib
+        from .quantized import _TORCH_TO_XNQ, _stream_ptr
+        if self.world == 1:
+            return y_local
+        nl = y_local.shape[-1]
+        src = y_local.reshape(-1, nl)
+        if src.stride(-1) != 1:
+            src = src.contiguous()
+        m = src.shape[0]
+        slot = self.next_slot() if slot is None else slot
+        out = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            _lib.check(self._L.xnq_comm_gather(self._h, slot, ctypes.c_void_p(src.data_ptr()), int(_TORCH_TO_XNQ[src.dtype]), m, nl,
+                                               src.stride(0) if m > 1 else nl, _stream_ptr(self.device), ctypes.byref(out)))
+        y = torch.as_tensor(_DeviceBuffer(out.value, (m, nl * self.world), _TYPESTR[src.dtype]), device=self.device)
+        if src.dtype is torch.bfloat16:
+            y = y.view(torch.bfloat16)
+        return y.view(*y_local.shape[:-1], nl * self.world)
+
     def late_peers(self) -> int:
         import ctypes
 

@@ -32,6 +32,7 @@ def _stream_ptr(device: torch.device) -> ctypes.c_void_p:
 
 
 _inited: set[int] = set()
+_workspaces: dict[int, list[torch.Tensor]] = {}
 
 
 def init(device: torch.device | int | str = "cuda:0") -> None:
@@ -145,6 +146,17 @@ class QCudaTensor:
                                                     n_rows, _stream_ptr(device), ctypes.byref(out)))
         return cls(out.value, device)
 
+    @classmethod
+    def from_device_rows(cls, dtype: GgmlDType, blocks: torch.Tensor, n_total: int, k: int, row0: int, n_rows: int) -> "QCudaTensor":
+        """``from_rows`` for canonical blocks that already sit in device memory (a uint8 tensor)."""
+        init(blocks.device)
+        out = ctypes.c_void_p()
+        buf = blocks.contiguous().view(torch.uint8).reshape(-1)
+        with torch.cuda.device(blocks.device):
+            check(_lib.lib().xnq_weight_upload_rows(int(dtype), ctypes.c_void_p(buf.data_ptr()), buf.numel(), n_total, k, row0,
+                                                    n_rows, _stream_ptr(blocks.device), ctypes.byref(out)))
+        return cls(out.value, blocks.device)
+
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
         if h:
@@ -177,10 +189,14 @@ class QCudaTensor:
 
     # -- compute --------------------------------------------------------------------------------
     def workspace(self, m: int) -> torch.Tensor:
+        """Scratch for ``m`` activation rows. All weights of a device share one buffer (the reference's device
+        has a single stream, cuda_backend/mod.rs:141-167, so calls never overlap); it only ever grows, and
+        outgrown buffers stay alive because a captured graph may still point at them."""
         need = _lib.lib().xnq_matmul_workspace_bytes(self._h, m)
-        if self._ws is None or self._ws.numel() < need:
-            self._ws = torch.empty(max(need, 256), dtype=torch.uint8, device=self.device)
-        return self._ws
+        pool = _workspaces.setdefault(self.device.index or 0, [])
+        if not pool or pool[-1].numel() < need:
+            pool.append(torch.empty(max(need, 256), dtype=torch.uint8, device=self.device))
+        return pool[-1]
 
     def matmul_t(self, lhs: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``lhs @ self^T`` with ``lhs`` of shape ``(.., k)``; the result is ``(.., n)`` (q8.rs:116-157)."""
