@@ -485,7 +485,7 @@ def run_decoder(args, name, batch):
                        "ffn": cfg.ffn, "vocab": cfg.vocab, "linears": cfg.linear_dtype.name, "lm_head": cfg.head_dtype.name, "batch": batch,
                        "prompt": prompt_len, "decode_steps": steps,
                        "cache": f"{wbytes / 1e6:.0f} MB of weights per step, far above L2",
-                       "parallelism": f"tensor parallel x{world}: head-sharded attention, N-sharded linears, 4 peer-store exchanges per layer" if world > 1 else "one GPU",
+                       "parallelism": f"tensor parallel x{world}: head-sharded attention, N-sharded qkv / gate-up / LM head, K-sharded o / down whose kernels store their summands into every rank (2 exchanges per layer)" if world > 1 else "one GPU",
                        "launch": "one CUDA graph per decode step"},
             "roofline": {"bound": "hbm", "achieved": wbytes / (ms_per_step * 1e-3) / 1e9 / world, "peak": peak, "unit": "GB/s",
                          "frac": wbytes / (ms_per_step * 1e-3) / 1e9 / world / peak, "traffic": None, "peak_kind": f"of {peak_kind}",

@@ -174,9 +174,16 @@ int xnq_comm_slot(const xnq_comm *c, int slot, void **ptr, size_t *bytes);
  * stores to every rank; otherwise the local result is pushed by a copy kernel. workspace as for
  * xnq_matmul_t. A slot may be named again once another gather has been issued in between; two
  * consecutive calls on one slot are refused, and a replayed graph must not end on the slot it
- * starts with. */
-int xnq_matmul_t_gather(const xnq_weight *w, xnq_comm *c, int slot, const void *x, int x_dtype, int64_t m,
-                        int64_t ldx, int y_dtype, void *workspace, size_t ws_bytes, void *stream, void **y_out);
+ * starts with.
+ * layout XNQ_GATHER_COLUMNS: w is this rank's rows of an N-sharded weight; the slot receives [m, n_total].
+ * layout XNQ_GATHER_PARTS: every rank holds a whole-N weight (for instance its K-shard of a row-parallel
+ * linear, fed with its own slice of the input); the slot receives [m, world * n] with rank r's result in
+ * columns [r * n, (r + 1) * n) - the summands of an all-reduce, to be added by the consumer. */
+#define XNQ_GATHER_COLUMNS 0
+#define XNQ_GATHER_PARTS 1
+int xnq_matmul_t_gather(const xnq_weight *w, xnq_comm *c, int slot, int layout, const void *x, int x_dtype,
+                        int64_t m, int64_t ldx, int y_dtype, void *workspace, size_t ws_bytes, void *stream,
+                        void **y_out);
 /* All-gather of a tensor this rank already holds: src is [m, n_local] (row stride ld_src elements of
  * elem_dtype) in local device memory; slot `slot` of every rank receives [m, world * n_local] with
  * rank r's block in columns [r * n_local, (r + 1) * n_local). Same slot rule as above. */
@@ -191,9 +198,10 @@ int xnq_comm_free(xnq_comm *c);
 /* ---- the operators between the quantized linears of a Llama-style decode step, fused (the callers of
  * the path in xn-core/src/models/llama.rs:145-216, 258-265, 300-320; reference kernels rmsnorm / rope /
  * sdpa in cuda-kernels/reduce.cu). All pointers are device memory, f32 unless stated. ------------- */
-/* x[rows, d] += delta[rows, d] (delta may be NULL), out = x * rsqrt(mean(x^2) + eps) * weight[d]. */
-int xnq_add_rmsnorm(float *x, const float *delta, const float *weight, float eps, float *out, int64_t rows,
-                    int64_t d, void *stream);
+/* x[rows, d] += sum over p of delta[rows, p, d] (delta may be NULL; delta_parts >= 1 summands per row,
+ * e.g. the per-rank partial results of a row-parallel linear), out = x * rsqrt(mean(x^2) + eps) * weight[d]. */
+int xnq_add_rmsnorm(float *x, const float *delta, int delta_parts, const float *weight, float eps, float *out,
+                    int64_t rows, int64_t d, void *stream);
 /* out[rows, f] = silu(gate_up[rows, 0:f]) * gate_up[rows, f:2f]. */
 int xnq_swiglu(const float *gate_up, float *out, int64_t rows, int64_t f, void *stream);
 /* One new token per sequence: qkv[batch, (heads + 2 kv_heads) * head_dim] -> rotate-half RoPE at
@@ -221,8 +229,9 @@ int xnq_device_status(unsigned int *bits);
  * bytes, limit (two spare words). Synchronizes the device. No counterpart in the reference. */
 int xnq_device_check_record(unsigned long long out[8]);
 /* Tuning switches, for A/B measurements: "matvec_tma" (default 1) selects the persistent TMA-ring
- * decode kernel for m == 1, k <= 4096; 0 forces the plain streaming-load kernel. No counterpart in
- * the reference. */
+ * decode kernel for m == 1, k <= 4096; 0 forces the plain streaming-load kernel. "gather_cta_fence"
+ * (default 1): scope of the per-CTA fence before the arrival count of a kernel-side gather, 1 = gpu,
+ * 0 = system. No counterpart in the reference. */
 int xnq_set_option(const char *name, int value);
 
 /* ---- measurement hooks (no counterpart in the reference, which times with CudaEvent::elapsed_ms

@@ -27,6 +27,12 @@ def test_add_rmsnorm():
             ref = xs * torch.rsqrt(xs.pow(2).mean(-1, keepdim=True) + 1e-5) * w
             assert torch.equal(xin, xs)                      # the residual stream is updated in place, exactly
             torch.testing.assert_close(out, ref, rtol=2e-5, atol=2e-6)
+        parts = torch.randn(rows, 3 * d, device=DEV)                 # three summands per row, side by side
+        xin = x.clone(); out = torch.empty_like(x)
+        ops.add_rmsnorm(xin, parts, w, 1e-5, out)
+        xs = x + parts.view(rows, 3, d)[:, 0] + parts.view(rows, 3, d)[:, 1] + parts.view(rows, 3, d)[:, 2]
+        torch.testing.assert_close(xin, xs, rtol=1e-6, atol=1e-6)
+        torch.testing.assert_close(out, xs * torch.rsqrt(xs.pow(2).mean(-1, keepdim=True) + 1e-5) * w, rtol=2e-5, atol=2e-6)
 
 
 def test_swiglu():

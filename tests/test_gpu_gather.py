@@ -50,6 +50,21 @@ def _run_rank(rank, world, port, ret):
                 if y.shape != (m, n) or not err <= tol:
                     bad.append((dt.name, n, k, m, rep, err, tol))
             dist.barrier()  # a weight is freed only after every rank has finished with its gathers
+        # row-parallel: each rank holds a K-shard (whole-N weight over its own input slice); the slot receives the summands
+        dt, n, k, m = D.Q4K, 256, 1024 * world, 1
+        full = synth.make_weight(dt, n, k, seed=903)
+        x = synth.make_activation(m, k, seed=904)
+        ref = O.matmul(int(dt), x, full, n, threads=4)
+        kl = k // world
+        rb = dt.row_bytes(k) // world
+        shard = np.ascontiguousarray(full.reshape(n, dt.row_bytes(k))[:, rank * rb:(rank + 1) * rb])
+        w = Q.QCudaTensor.from_rows(dt, shard, n, kl, 0, n, dev)
+        xd = torch.from_numpy(np.ascontiguousarray(x[:, rank * kl:(rank + 1) * kl])).to(dev)
+        y = pg.matmul_t(w, xd, parts=True)
+        got = y.view(m, world, n).sum(1).cpu().numpy()
+        if y.shape != (m, world * n) or not float(np.abs(got - ref).max()) <= 2e-3 * max(1.0, float(np.sqrt((ref ** 2).mean()))):
+            bad.append(("parts", float(np.abs(got - ref).max())))
+        dist.barrier()
         # graph replay: epochs are device-side, so a captured pair of gathers can be replayed
         dt, n, k = D.Q4K, 512, 1024
         r0, r1 = shard_rows(n, rank, world)
@@ -57,7 +72,7 @@ def _run_rank(rank, world, port, ret):
         x = synth.make_activation(1, k, seed=902)
         ref = O.matmul(int(dt), x, synth.make_weight(dt, n, k, seed=900), n, threads=4)
         xd = torch.from_numpy(x).to(dev)
-        pg.matmul_t(w, xd, slot=0); pg.matmul_t(w, xd, slot=1)
+        pg.matmul_t(w, xd, slot=1); pg.matmul_t(w, xd, slot=2)
         torch.cuda.synchronize(dev)
         dist.barrier()
         g = torch.cuda.CUDAGraph()

@@ -57,12 +57,12 @@ def lib() -> ctypes.CDLL:
     L.xnq_comm_ipc_handle.argtypes = [vp, vp]
     L.xnq_comm_connect.argtypes = [vp, vp]
     L.xnq_comm_slot.argtypes = [vp, ci, pvp, ctypes.POINTER(sz)]
-    L.xnq_matmul_t_gather.argtypes = [vp, vp, ci, vp, ci, i64, i64, ci, vp, sz, vp, pvp]
+    L.xnq_matmul_t_gather.argtypes = [vp, vp, ci, ci, vp, ci, i64, i64, ci, vp, sz, vp, pvp]
     L.xnq_comm_gather.argtypes = [vp, ci, vp, ci, i64, i64, i64, vp, pvp]
     L.xnq_comm_status.argtypes = [vp, ctypes.POINTER(ctypes.c_uint)]
     L.xnq_comm_free.argtypes = [vp]
     fp = ctypes.c_float
-    L.xnq_add_rmsnorm.argtypes = [vp, vp, vp, fp, vp, i64, i64, vp]
+    L.xnq_add_rmsnorm.argtypes = [vp, vp, ci, vp, fp, vp, i64, i64, vp]
     L.xnq_swiglu.argtypes = [vp, vp, i64, i64, vp]
     L.xnq_rope_kv_store.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, ci, ci, ci, i64, vp]
     L.xnq_attn_decode_workspace_bytes.argtypes = [i64, ci]

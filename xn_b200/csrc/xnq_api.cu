@@ -24,6 +24,8 @@ void clear_error() { g_err[0] = 0; }
 
 static std::atomic<uint64_t> g_launches{0};
 static std::atomic<bool> g_opt_matvec_tma{true};
+static std::atomic<int> g_opt_gather_cta_fence{1};
+int gather_cta_fence_scope() { return g_opt_gather_cta_fence.load(std::memory_order_relaxed); }
 bool matvec_tma_enabled() { return g_opt_matvec_tma.load(std::memory_order_relaxed); }
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 
@@ -199,6 +201,10 @@ int xnq_set_option(const char *name, int value) {
   if (!name) return fail(XNQ_ERR_NULL, "set_option: name is NULL");
   if (std::strcmp(name, "matvec_tma") == 0) {
     g_opt_matvec_tma.store(value != 0);
+    return XNQ_OK;
+  }
+  if (std::strcmp(name, "gather_cta_fence") == 0) {
+    g_opt_gather_cta_fence.store(value);
     return XNQ_OK;
   }
   if (std::strcmp(name, "prefill_dbg") == 0) {

@@ -178,7 +178,7 @@ int xnq_comm_gather(xnq_comm *c, int slot, const void *src, int elem_dtype, int6
     g.dst[p] = slot_ptr(c, p, slot);
     g.flag[p] = reinterpret_cast<unsigned int *>(c->peer[p]) + c->rank;
   }
-  g.ctl = c->ctl, g.world = c->world, g.rank = c->rank, g.col0 = n_local * c->rank, g.ld = nt;
+  g.ctl = c->ctl, g.world = c->world, g.rank = c->rank, g.col0 = n_local * c->rank, g.ld = nt, g.cta_fence_gpu = gather_cta_fence_scope();
   const int64_t units = m * n_local;
   const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(296, (units + 1023) / 1024));
   gather_push_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(g, src, ld_src, m, n_local, (int)es, -1);
@@ -189,8 +189,8 @@ int xnq_comm_gather(xnq_comm *c, int slot, const void *src, int elem_dtype, int6
   return XNQ_OK;
 }
 
-int xnq_matmul_t_gather(const xnq_weight *w, xnq_comm *c, int slot, const void *x, int x_dtype, int64_t m, int64_t ldx, int y_dtype, void *workspace,
-                        size_t ws_bytes, void *stream, void **y_out) {
+int xnq_matmul_t_gather(const xnq_weight *w, xnq_comm *c, int slot, int layout, const void *x, int x_dtype, int64_t m, int64_t ldx, int y_dtype,
+                        void *workspace, size_t ws_bytes, void *stream, void **y_out) {
   clear_error();
   if (!w || !c) return fail(XNQ_ERR_NULL, "matmul_t_gather: weight or comm is NULL");
   if (!c->connected) return fail(XNQ_ERR_UNSUPPORTED, "matmul_t_gather: comm is not connected to its peers");
@@ -198,7 +198,11 @@ int xnq_matmul_t_gather(const xnq_weight *w, xnq_comm *c, int slot, const void *
   if (slot == c->last_slot) return fail(XNQ_ERR_UNSUPPORTED, "matmul_t_gather: slot %d was written by the previous gather; alternate slots", slot);
   if (!is_float_dtype(y_dtype)) return fail(XNQ_ERR_DTYPE, "matmul_t_gather: output dtype %d is not f32/f16/bf16", y_dtype);
   if (m < 1) return fail(XNQ_ERR_SHAPE, "matmul_t_gather: m = %lld (every rank must take part in every gather)", (long long)m);
-  const int64_t n = w->v.n, nt = w->n_total;
+  if (layout != XNQ_GATHER_COLUMNS && layout != XNQ_GATHER_PARTS) return fail(XNQ_ERR_UNSUPPORTED, "matmul_t_gather: layout %d", layout);
+  // columns: this rank's rows of an N-sharded weight land at their place in [m, n_total];
+  // parts:   every rank holds a whole-N weight (its K-shard) and its [m, n] result becomes block `rank` of [m, world * n]
+  const int64_t n = w->v.n, nt = layout == XNQ_GATHER_COLUMNS ? w->n_total : n * c->world;
+  const int64_t col0 = layout == XNQ_GATHER_COLUMNS ? w->row0 : n * c->rank;
   const size_t es = type_size(y_dtype);
   if ((size_t)m * (size_t)nt * es > c->slot_bytes)
     return fail(XNQ_ERR_SIZE, "matmul_t_gather: [%lld, %lld] output needs %zu bytes, slots have %zu", (long long)m, (long long)nt, (size_t)m * nt * es, c->slot_bytes);
@@ -208,7 +212,7 @@ int xnq_matmul_t_gather(const xnq_weight *w, xnq_comm *c, int slot, const void *
     g.dst[p] = slot_ptr(c, p, slot);
     g.flag[p] = reinterpret_cast<unsigned int *>(c->peer[p]) + c->rank;
   }
-  g.ctl = c->ctl, g.world = c->world, g.rank = c->rank, g.col0 = w->row0, g.ld = nt;
+  g.ctl = c->ctl, g.world = c->world, g.rank = c->rank, g.col0 = col0, g.ld = nt, g.cta_fence_gpu = gather_cta_fence_scope();
   char *local = slot_ptr(c, c->rank, slot);
   int rc;
   if (m == 1 && matvec_tma_enabled() && matvec_tma_supported(w->v, 1)) {
@@ -216,11 +220,11 @@ int xnq_matmul_t_gather(const xnq_weight *w, xnq_comm *c, int slot, const void *
     rc = launch_matvec_tma(w->v, x, x_dtype, nullptr, y_dtype, s, &g); // stores go to every rank's slot from inside the kernel
     if (rc != XNQ_OK) return rc;
   } else {
-    rc = xnq_matmul_t(w, x, x_dtype, m, ldx, local + (size_t)w->row0 * es, y_dtype, nt, workspace, ws_bytes, s);
+    rc = xnq_matmul_t(w, x, x_dtype, m, ldx, local + (size_t)col0 * es, y_dtype, nt, workspace, ws_bytes, s);
     if (rc != XNQ_OK) return rc;
     const int64_t units = m * n;
     const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(296, (units + 1023) / 1024));
-    gather_push_kernel<<<grid, 256, 0, s>>>(g, local + (size_t)w->row0 * es, nt, m, n, (int)es, c->rank);
+    gather_push_kernel<<<grid, 256, 0, s>>>(g, local + (size_t)col0 * es, nt, m, n, (int)es, c->rank);
     XNQ_CUDA(cudaGetLastError());
     count_launch();
   }

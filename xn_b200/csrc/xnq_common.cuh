@@ -109,6 +109,7 @@ struct GatherArgs {
   unsigned int *flag[XNQ_MAX_RANKS];
   unsigned int *ctl;
   int world, rank;
+  int cta_fence_gpu; // 1: CTAs order their stores before the arrival count with a gpu-scope fence; the last CTA's system-scope release carries them on
   int64_t col0, ld; // first column this rank produces; row stride of the gathered buffer (elements)
 };
 
@@ -120,8 +121,14 @@ constexpr unsigned long long GATHER_WAIT_LIMIT_NS = 4000000000ull; // a peer tha
 // semantics at system scope into every peer's epoch row, and then waits until every peer's epoch in
 // the local row has reached the same count: when the launch retires, the gathered buffer of this
 // rank is complete. The wait is bounded; a late peer sets its bit in ctl[3] and the kernel returns.
+// Ordering: the CTA's stores precede its barrier; the calling thread then fences at gpu scope and counts
+// its arrival (a release pattern the last CTA's atomic + system-scope fence acquires), and the last
+// CTA's release store at system scope carries every CTA's stores with it (causality order is
+// cumulative across scopes). A system-scope fence in every CTA is not needed and costs about 3 us per
+// launch; the "gather_cta_fence" option (0) brings it back for comparison.
 __device__ __forceinline__ void gather_publish_and_wait(const GatherArgs &g) {
-  __threadfence_system();
+  if (g.cta_fence_gpu) __threadfence();
+  else __threadfence_system();
   if (atomicAdd(g.ctl + 2, 1u) == gridDim.x - 1) {
     g.ctl[2] = 0;
     const unsigned int epoch = g.ctl[0] + 1;
@@ -202,6 +209,7 @@ bool matvec_tma_supported(const WeightView &w, int64_t m);
 // g != nullptr: results go to column col0 + row of every rank's gathered buffer (y is ignored)
 int launch_matvec_tma(const WeightView &w, const void *x, int x_dtype, void *y, int y_dtype, cudaStream_t s, const GatherArgs *g = nullptr);
 bool matvec_tma_enabled(); // the "matvec_tma" library option
+int gather_cta_fence_scope(); // the "gather_cta_fence" library option
 // shared argument checks of the matmul entries (dtype, leading dimension, 16-byte row alignment)
 int check_activations(const char *who, const void *x, int x_dtype, int64_t m, int64_t k, int64_t ldx);
 int matvec_tma_init(int device);

@@ -20,18 +20,20 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
-// x[row] += delta[row] (if delta), out[row] = x[row] * rsqrt(mean(x^2) + eps) * w.  One CTA per row.
-__global__ void __launch_bounds__(256) add_rmsnorm_kernel(float *x, const float *delta, const float *w, float eps, float *out, int d) {
+// x[row] += sum_p delta[row][p] (if delta), out[row] = x[row] * rsqrt(mean(x^2) + eps) * w.  One CTA per row.
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(float *x, const float *delta, int parts, const float *w, float eps, float *out, int d) {
   __shared__ float part[8];
   const int64_t row = blockIdx.x;
   float *xr = x + row * d;
-  const float *dr = delta ? delta + row * d : nullptr;
+  const float *dr = delta ? delta + row * parts * d : nullptr;
   float ss = 0.f;
   for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
     float4 v = *reinterpret_cast<const float4 *>(xr + i);
     if (dr) {
-      const float4 a = *reinterpret_cast<const float4 *>(dr + i);
-      v.x += a.x, v.y += a.y, v.z += a.z, v.w += a.w;
+      for (int p = 0; p < parts; p++) {
+        const float4 a = *reinterpret_cast<const float4 *>(dr + (int64_t)p * d + i);
+        v.x += a.x, v.y += a.y, v.z += a.z, v.w += a.w;
+      }
       *reinterpret_cast<float4 *>(xr + i) = v;
     }
     ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
@@ -191,13 +193,14 @@ using namespace xnq;
 
 extern "C" {
 
-int xnq_add_rmsnorm(float *x, const float *delta, const float *weight, float eps, float *out, int64_t rows, int64_t d, void *stream) {
+int xnq_add_rmsnorm(float *x, const float *delta, int delta_parts, const float *weight, float eps, float *out, int64_t rows, int64_t d, void *stream) {
   clear_error();
   if (!x || !weight || !out) return fail(XNQ_ERR_NULL, "add_rmsnorm: NULL argument");
-  if (rows < 0 || d <= 0 || d % 4) return fail(XNQ_ERR_SHAPE, "add_rmsnorm: rows = %lld, d = %lld (d must be a multiple of 4)", (long long)rows, (long long)d);
+  if (rows < 0 || d <= 0 || d % 4 || (delta && delta_parts < 1))
+    return fail(XNQ_ERR_SHAPE, "add_rmsnorm: rows = %lld, d = %lld (a multiple of 4), delta_parts = %d", (long long)rows, (long long)d, delta_parts);
   if (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) return fail(XNQ_ERR_ALIGN, "add_rmsnorm: pointers must be 16-byte aligned");
   if (rows == 0) return XNQ_OK;
-  add_rmsnorm_kernel<<<(unsigned)rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, delta, weight, eps, out, (int)d);
+  add_rmsnorm_kernel<<<(unsigned)rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, delta, delta_parts, weight, eps, out, (int)d);
   XNQ_CUDA(cudaGetLastError());
   count_launch();
   return XNQ_OK;

@@ -23,11 +23,13 @@ def _f32c(*ts):
 
 
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
-    """In place ``x += delta`` (skipped when ``delta`` is None), then ``out = rmsnorm(x) * weight``; ``x`` is ``[rows, d]``."""
+    """In place ``x += delta`` (skipped when ``delta`` is None), then ``out = rmsnorm(x) * weight``; ``x`` is ``[rows, d]``.
+    ``delta`` may be ``[rows, parts * d]``: its ``parts`` summands per row are all added."""
     _f32c(x, delta, weight, out)
     rows, d = x.shape
+    parts = 1 if delta is None else delta.numel() // (rows * d)
     with torch.cuda.device(x.device):
-        _lib.check(_lib.lib().xnq_add_rmsnorm(_p(x), _p(delta), _p(weight), eps, _p(out), rows, d, _stream_ptr(x.device)))
+        _lib.check(_lib.lib().xnq_add_rmsnorm(_p(x), _p(delta), parts, _p(weight), eps, _p(out), rows, d, _stream_ptr(x.device)))
     return out
 
 

@@ -5,13 +5,16 @@ q/k/v/o projections with grouped-query attention and RoPE, SwiGLU MLP, final nor
 linears held as GGUF-quantized device weights (``QCudaTensor``) instead of dense ``Linear``s, the way
 ``BackendQ::linear_load`` substitutes them (lib.rs:141-156).
 
-Tensor parallelism over ``world`` ranks (one process per GPU), all linears N-sharded:
-  * q/k/v rows are grouped per rank by head, so attention and the KV cache are head-sharded and the
-    fused ``[q_r; k_r; v_r]`` projection needs no exchange;
-  * gate/up rows are grouped per rank, SwiGLU is applied to the local slice (gate and up are only
-    consumed through ``silu(gate) * up``, llama.rs:258-265);
-  * four exchanges per layer: attention output, o_proj output, SwiGLU output, down_proj output, the
-    two matmul ones stored straight into every rank's buffer by the matmul kernel.
+Tensor parallelism over ``world`` ranks (one process per GPU):
+  * q/k/v are N-sharded with rows grouped per rank by head, so attention and the KV cache are
+    head-sharded and the fused ``[q_r; k_r; v_r]`` projection needs no exchange;
+  * gate/up are N-sharded with rows grouped per rank, SwiGLU is applied to the local slice (gate and up
+    are only consumed through ``silu(gate) * up``, llama.rs:258-265);
+  * o_proj and down_proj are K-sharded (each rank multiplies its own slice of the input with the matching
+    column blocks of the weight; a K-shard is whole quantization blocks, so its block dots are exactly
+    the unsharded ones): two exchanges per layer, each done by the matmul kernel itself, which stores
+    its summand into every rank's buffer; the next residual-add + RMSNorm adds the summands;
+  * the LM head is N-sharded and its output columns are gathered the same way.
 
 Prefill runs RMSNorm, RoPE and attention as torch ops. A decode step uses the library's fused operators
 between the linears (residual-add + RMSNorm, RoPE + KV-cache store, single-query attention, SwiGLU), so
@@ -98,12 +101,12 @@ class QLlama:
             wv = rows(_dense((c.n_kv_heads * hd, c.d_model), 0.02, s0 + 2, device), self.kvl * hd)
             L.wqkv = QCudaTensor.from_dense(torch.cat([wq, wk, wv]), c.linear_dtype)
             del wq, wk, wv
-            L.wo = self._shard(_dense((c.d_model, c.n_heads * hd), 0.02, s0 + 3, device), c.linear_dtype)
+            L.wo = self._kshard(_dense((c.d_model, c.n_heads * hd), 0.02, s0 + 3, device), c.linear_dtype)
             wg = rows(_dense((c.ffn, c.d_model), 0.02, s0 + 4, device), c.ffn // G)
             wu = rows(_dense((c.ffn, c.d_model), 0.02, s0 + 5, device), c.ffn // G)
             L.wgu = QCudaTensor.from_dense(torch.cat([wg, wu]), c.linear_dtype)
             del wg, wu
-            L.wdown = self._shard(_dense((c.d_model, c.ffn), 0.02, s0 + 6, device), c.linear_dtype)
+            L.wdown = self._kshard(_dense((c.d_model, c.ffn), 0.02, s0 + 6, device), c.linear_dtype)
             L.norm1 = torch.ones(c.d_model, device=device)
             L.norm2 = torch.ones(c.d_model, device=device)
             L.k_cache = torch.zeros((batch, self.kvl, max_seq, hd), device=device, dtype=torch.bfloat16)
@@ -120,8 +123,8 @@ class QLlama:
         self.pg: Optional[PeerGather] = None
         if world > 1:
             rows_max = max(batch, max_prefill_rows)
-            self.pg = PeerGather(device, rank, world, slot_elems=max(rows_max * c.ffn, batch * c.vocab), nslots=3, group=group)
-            self._gathers_per_step = 4 * c.n_layers + 1
+            self.pg = PeerGather(device, rank, world, slot_elems=max(rows_max * c.d_model * world, batch * c.vocab), nslots=3, group=group)
+            self._gathers_per_step = 2 * c.n_layers + 1
         # decode-step state, all on the device so a captured graph can be replayed
         self.pos = torch.zeros(1, device=device, dtype=torch.int64)
         self.tokens = torch.zeros(batch, device=device, dtype=torch.int64)
@@ -150,11 +153,23 @@ class QLlama:
         blocks = quantize_weight(dense[self.rank * per:(self.rank + 1) * per], dt)
         return QCudaTensor.from_device_rows(dt, blocks, n, k, self.rank * per, per)
 
+    def _kshard(self, dense: torch.Tensor, dt: GgmlDType) -> QCudaTensor:
+        """This rank's column blocks of a row-parallel linear: a whole-N weight over K/world inputs."""
+        per = dense.shape[1] // self.world
+        if per % dt.block_size:
+            raise ValueError(f"k = {dense.shape[1]} does not split into {self.world} runs of whole {dt.name} blocks")
+        return QCudaTensor.from_dense(dense[:, self.rank * per:(self.rank + 1) * per].contiguous(), dt)
+
     def _linear_gathered(self, w: QCudaTensor, x: torch.Tensor) -> torch.Tensor:
+        """N-sharded linear, output columns gathered on every rank."""
         return w.matmul_t(x) if self.pg is None else self.pg.matmul_t(w, x, slot=self._slot())
 
-    def _gather(self, y: torch.Tensor) -> torch.Tensor:
-        return y if self.pg is None else self.pg.gather(y, slot=self._slot())
+    def _linear_parts(self, w: QCudaTensor, x_local: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """K-sharded linear on this rank's input slice: ``(.., world * n)``, the ranks' summands side by side."""
+        return w.matmul_t(x_local, out=out) if self.pg is None else self.pg.matmul_t(w, x_local, slot=self._slot(), parts=True)
+
+    def _sum_parts(self, parts: torch.Tensor) -> torch.Tensor:
+        return parts if self.world == 1 else parts.view(*parts.shape[:-1], self.world, -1).sum(-2)
 
     def _slot(self) -> int:
         # three slots in rotation; a step's last exchange must not land on the slot its first one uses
@@ -189,10 +204,10 @@ class QLlama:
         L.v_cache.index_copy_(2, pos_idx, v.to(torch.bfloat16))
         a = F.scaled_dot_product_attention(q.to(torch.bfloat16), L.k_cache, L.v_cache, attn_mask=mask, enable_gqa=True)
         a = a.transpose(1, 2).reshape(B, S, self.hl * hd).float()
-        x = x + self._linear_gathered(L.wo, self._gather(a))
+        x = x + self._sum_parts(self._linear_parts(L.wo, a))
         gu = L.wgu.matmul_t(self._rms(x, L.norm2))
         g, u = gu.split(c.ffn // self.world, dim=-1)
-        x = x + self._linear_gathered(L.wdown, self._gather(F.silu(g) * u))
+        x = x + self._sum_parts(self._linear_parts(L.wdown, F.silu(g) * u))
         return x
 
     def _forward(self, tokens: torch.Tensor, pos_idx: torch.Tensor) -> torch.Tensor:
@@ -204,10 +219,8 @@ class QLlama:
         for L in self.layers:
             x = self._block(L, x, pos_idx, mask)
         x = self._rms(x[:, -1:, :], self.norm)
-        return self._linear_gathered(self.lm_head, x).view(tokens.shape[0], -1)
-
-    def _linear_gathered_into(self, w: QCudaTensor, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-        return w.matmul_t(x, out=out) if self.pg is None else self.pg.matmul_t(w, x, slot=self._slot())
+        logits = self._linear_gathered(self.lm_head, x).view(tokens.shape[0], -1)
+        return logits if self.pg is None else logits.clone()   # out of the exchange slot before it is reused
 
     def _forward_decode(self) -> torch.Tensor:
         """One token per sequence (self.tokens at position self.pos) -> logits [B, vocab], fused operators."""
@@ -220,13 +233,14 @@ class QLlama:
             L.wqkv.matmul_t(self._xn, out=self._qkv)
             ops.rope_kv_store(self._qkv, self.cos, self.sin, self.pos, self._q, L.k_cache, L.v_cache, self.hl, self.kvl)
             ops.attn_decode(self._q, L.k_cache, L.v_cache, self.pos, self._a.view(self.batch, self.hl, c.head_dim), self.hl, self.kvl)
-            o = self._linear_gathered_into(L.wo, self._gather(self._a), self._o)
+            o = self._linear_parts(L.wo, self._a, self._o)           # world summands per row when sharded
             ops.add_rmsnorm(self._x, o, L.norm2, c.rms_eps, self._xn)
             L.wgu.matmul_t(self._xn, out=self._gu)
             ops.swiglu(self._gu, self._h)
-            delta = self._linear_gathered_into(L.wdown, self._gather(self._h), self._dn)
+            delta = self._linear_parts(L.wdown, self._h, self._dn)
         ops.add_rmsnorm(self._x, delta, self.norm, c.rms_eps, self._xn)
-        return self._linear_gathered(self.lm_head, self._xn)
+        logits = self._linear_gathered(self.lm_head, self._xn)
+        return logits if self.pg is None else logits.clone()
 
     # -- public ----------------------------------------------------------------------------------
     @torch.no_grad()

@@ -102,9 +102,11 @@ class PeerGather:
         self._next = (s + 1) % self.nslots
         return s
 
-    def matmul_t(self, w, lhs: torch.Tensor, slot: Optional[int] = None) -> torch.Tensor:
+    def matmul_t(self, w, lhs: torch.Tensor, slot: Optional[int] = None, parts: bool = False) -> torch.Tensor:
         """``lhs @ W^T`` for the N-sharded ``w`` (a ``QCudaTensor`` shard), gathered: ``(.., n_total)`` on
-        every rank, living in one of this object's slots until that slot is named again."""
+        every rank, living in one of this object's slots until that slot is named again. With ``parts`` the
+        weight is a whole-N one (a K-shard fed with this rank's input slice) and the result is
+        ``(.., world * n)``: every rank's summand side by side, for the consumer to add."""
         import ctypes
 
         from . import _lib
@@ -120,13 +122,14 @@ class PeerGather:
         ws = w.workspace(m)
         out = ctypes.c_void_p()
         with torch.cuda.device(self.device):
-            _lib.check(self._L.xnq_matmul_t_gather(w._h, self._h, slot, ctypes.c_void_p(x.data_ptr()), int(_TORCH_TO_XNQ[x.dtype]), m,
+            _lib.check(self._L.xnq_matmul_t_gather(w._h, self._h, slot, 1 if parts else 0, ctypes.c_void_p(x.data_ptr()), int(_TORCH_TO_XNQ[x.dtype]), m,
                                                   x.stride(0) if m > 1 else w.k, int(_TORCH_TO_XNQ[ydt]), ctypes.c_void_p(ws.data_ptr()),
                                                   ws.numel(), _stream_ptr(self.device), ctypes.byref(out)))
-        y = torch.as_tensor(_DeviceBuffer(out.value, (m, w.n_total), _TYPESTR[ydt]), device=self.device)
+        nt = w.n * self.world if parts else w.n_total
+        y = torch.as_tensor(_DeviceBuffer(out.value, (m, nt), _TYPESTR[ydt]), device=self.device)
         if ydt is torch.bfloat16:
             y = y.view(torch.bfloat16)
-        return y.view(*lhs.shape[:-1], w.n_total)
+        return y.view(*lhs.shape[:-1], nt)
 
     def gather(self, y_local: torch.Tensor, slot: Optional[int] = None) -> torch.Tensor:
         """All-gather ``(.., n_local)`` blocks that each rank already holds into ``(.., world * n_local)``."""
