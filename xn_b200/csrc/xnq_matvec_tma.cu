@@ -575,7 +575,7 @@ matvec_tma_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtype
         } else if (!GATHER) {
           store_out(y, y_dtype, idx, v);
         } else {
-          for (int p = 0; p < g.world; p++) store_out(g.dst[p], y_dtype, g.col0 + idx, v);
+          store_out(g.dst[g.rank], y_dtype, g.col0 + idx, v); // the peers get the CTA's whole run of rows in one sweep below
         }
       }
     }
@@ -584,7 +584,37 @@ matvec_tma_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtype
   }
   if (tr && threadIdx.x == 0) g_matvec_trace[trace_slot][tb + 4] = gtime();
   if (GATHER) {
-    consumer_sync(); // every store of this CTA has been issued
+    consumer_sync(); // the CTA's results are in the local buffer
+    // One coalesced sweep of this CTA's contiguous run of results to every peer: 16-byte vectors where
+    // the run is aligned, single elements at its ragged ends. (One 4-byte store per row and peer from
+    // inside the loop costs a link packet each; at eight ranks that dominated the launch.)
+    if (g.world > 1 && nrows > 0) {
+      const int es = y_dtype == XNQ_F32 ? 4 : 2;
+      const size_t off = (size_t)(g.col0 + row_begin) * es;
+      const char *src = static_cast<const char *>(g.dst[g.rank]) + off;
+      const int nbytes = nrows * es;
+      const int head = min(nbytes, (int)((16 - (reinterpret_cast<uintptr_t>(src) & 15)) & 15));
+      const int nvec = (nbytes - head) / 16, tail0 = head + nvec * 16;
+      for (int v = threadIdx.x; v < nvec; v += CW * 32) {
+        const uint4 val = __ldcg(reinterpret_cast<const uint4 *>(src + head) + v);
+        for (int p = 0; p < g.world; p++)
+          if (p != g.rank) reinterpret_cast<uint4 *>(static_cast<char *>(g.dst[p]) + off + head)[v] = val;
+      }
+      const int nedge = (head + (nbytes - tail0)) / es; // elements before the first and after the last full vector
+      for (int e = threadIdx.x; e < nedge; e += CW * 32) {
+        const int b = e * es < head ? e * es : tail0 + (e * es - head);
+        if (es == 4) {
+          const uint32_t val = __ldcg(reinterpret_cast<const uint32_t *>(src + b));
+          for (int p = 0; p < g.world; p++)
+            if (p != g.rank) *reinterpret_cast<uint32_t *>(static_cast<char *>(g.dst[p]) + off + b) = val;
+        } else {
+          const unsigned short val = __ldcg(reinterpret_cast<const unsigned short *>(src + b));
+          for (int p = 0; p < g.world; p++)
+            if (p != g.rank) *reinterpret_cast<unsigned short *>(static_cast<char *>(g.dst[p]) + off + b) = val;
+        }
+      }
+      consumer_sync();
+    }
     if (threadIdx.x == 0) gather_publish_and_wait(g);
   }
 }
