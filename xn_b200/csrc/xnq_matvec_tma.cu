@@ -1,9 +1,10 @@
 // Decode matvec, m == 1, k <= 4096: persistent TMA-ring kernel.
 //
-// Two CTAs per SM each own a contiguous band of weight rows. A producer thread streams the band
-// through a ring of shared-memory stages with 1-D bulk-async copies (cp.async.bulk, the non-tensor
-// form of TMA; never multicast) that complete on mbarriers, so tens of KB per SM are in flight from
-// the first cycle without holding registers. Eight consumer warps take R rows of a stage each.
+// One CTA per SM owns a contiguous band of weight rows. A producer thread streams the band through
+// a ring of shared-memory stages (up to 225 KB) with 1-D bulk-async copies (cp.async.bulk, the
+// non-tensor form of TMA; never multicast) that complete on mbarriers, so most of the band is in
+// flight from the first cycle without holding registers. Sixteen consumer warps take R rows of a
+// stage each (XNQ_MV_CW = 8 builds the variant with two 8-warp CTAs per SM).
 //
 // The activation row is quantized in the kernel's prologue (same device function, same bytes as the
 // stand-alone quantizer; the reference's quantize_lhs, k_quants.rs:2015-2026) and every lane then
@@ -11,17 +12,21 @@
 // kernel: a lane always works on the same k positions of every row, so the main loop reads shared
 // memory only for weights, and the R rows of a warp share those registers.
 //
-// Launch overlap. A CTA uses at most half an SM (shared memory, registers, threads) and the kernel is
-// launched with programmatic stream serialization: the next launch in the stream may start while
-// this one drains. Its producer begins prefetching weights at once (weights are immutable after
-// upload); only its consumers execute griddepcontrol.wait before they read x or write y, so results
-// are ordered exactly as without the overlap.
+// Launch overlap. The kernel is launched with programmatic stream serialization: CTAs of the next
+// launch in the stream take an SM as soon as this launch's CTA there has left. Their producer begins
+// prefetching weights at once (weights are immutable after upload); only the consumers execute
+// griddepcontrol.wait before they read x or write y, so results are ordered exactly as without the
+// overlap.
+//
+// GATHER variant (N-sharded weights): results go to this rank's slot of the gathered output, each CTA
+// then sweeps its run of results to every peer's slot with coalesced stores, and the last CTA
+// publishes this rank's epoch and waits, bounded, for the peers' (xnq_comm.cu).
 //
 // The dot arithmetic is that of xnq_matvec.cu (exact integer block sums, f32 scales, f32
 // accumulate; k_quants.rs:287-304, 677-691, 1337-1416, 1743-1799).
 //
 // Every mbarrier wait is bounded: on expiry the thread records a status bit, stops consuming and
-// leaves; the producer still waits (bounded) for the copies it has in flight before it returns.
+// goes on to the common epilogue; the producer still waits (bounded) for the copies it has in flight before it returns.
 // Every bulk copy and every store is range-checked first; a refused access is recorded, not made.
 // Every stage is always consumed by the same warps in order, so a parity wait never refers to a
 // phase its waiter has not seen the predecessor of.
