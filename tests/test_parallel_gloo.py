@@ -56,3 +56,10 @@ def test_shard_rows_rejects_bad_splits():
         shard_rows(10, 0, 3)
     with pytest.raises(ValueError):
         shard_rows(8, 2, 2)
+
+
+def test_decoder_config_weight_bytes_match_the_published_layer_arithmetic():
+    """32 layers x 218,103,808 Q4_K parameters (122,683,392 B) + a 32000 x 4096 Q6_K head (107,520,000 B)."""
+    from xn_b200.llama import LlamaConfig
+    c = LlamaConfig.llama_7b()
+    assert c.weight_bytes_per_step() == 32 * 122_683_392 + 107_520_000 == 4_033_388_544

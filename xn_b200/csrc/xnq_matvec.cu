@@ -12,6 +12,8 @@
 // in registers, and runs dp4a against the int8 activations, which the CTA staged in shared memory
 // once. Activation registers are reused across the R rows, shared-memory traffic per weight byte
 // drops by R. Partial sums are reduced with warp shuffles; lane 0 stores.
+#include <algorithm>
+
 #include "xnq_common.cuh"
 #include "xnq_unpack.cuh"
 
@@ -19,6 +21,7 @@ namespace xnq {
 
 namespace {
 
+int g_sms = 148; // set by matvec_init
 constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
 
@@ -114,8 +117,8 @@ __global__ void XNQ_MATVEC_BOUNDS matvec_q4_0(WeightView w, ActView a, void *y, 
   extern __shared__ __align__(16) unsigned char smem[];
   const SmemAct sa = stage_activations(smem, a, QK, true);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t row0 = ((int64_t)blockIdx.x * WARPS + warp) * R;
-  if (row0 >= w.n) return;
+  // persistent over row groups: the activation image is staged once per CTA, not once per WARPS * R rows
+  for (int64_t row0 = ((int64_t)blockIdx.x * WARPS + warp) * R; row0 < w.n; row0 += (int64_t)gridDim.x * WARPS * R) {
   const int m = (int)a.m;
   const int64_t k = w.k, nblk = k / QK;
   float acc[R][MT];
@@ -152,6 +155,7 @@ __global__ void XNQ_MATVEC_BOUNDS matvec_q4_0(WeightView w, ActView a, void *y, 
     }
   }
   reduce_store<MT, R>(acc, lane, row0, w.n, m, y, y_dtype, ldy);
+  }
 }
 
 // ---- Q8_0: one 16-byte chunk = half a block -------------------------------------------------------
@@ -160,8 +164,8 @@ __global__ void XNQ_MATVEC_BOUNDS matvec_q8_0(WeightView w, ActView a, void *y, 
   extern __shared__ __align__(16) unsigned char smem[];
   const SmemAct sa = stage_activations(smem, a, QK, false);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t row0 = ((int64_t)blockIdx.x * WARPS + warp) * R;
-  if (row0 >= w.n) return;
+  // persistent over row groups: the activation image is staged once per CTA, not once per WARPS * R rows
+  for (int64_t row0 = ((int64_t)blockIdx.x * WARPS + warp) * R; row0 < w.n; row0 += (int64_t)gridDim.x * WARPS * R) {
   const int m = (int)a.m;
   const int64_t k = w.k, nblk = k / QK, nch = k / 16;
   float acc[R][MT];
@@ -190,6 +194,7 @@ __global__ void XNQ_MATVEC_BOUNDS matvec_q8_0(WeightView w, ActView a, void *y, 
     }
   }
   reduce_store<MT, R>(acc, lane, row0, w.n, m, y, y_dtype, ldy);
+  }
 }
 
 // ---- Q4_K: 8 lanes per 144-byte super-block (header + 8 chunks of 16 nibble bytes) -----------------
@@ -198,8 +203,8 @@ __global__ void XNQ_MATVEC_BOUNDS matvec_q4k(WeightView w, ActView a, void *y, i
   extern __shared__ __align__(16) unsigned char smem[];
   const SmemAct sa = stage_activations(smem, a, QK_K, true);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t row0 = ((int64_t)blockIdx.x * WARPS + warp) * R;
-  if (row0 >= w.n) return;
+  // persistent over row groups: the activation image is staged once per CTA, not once per WARPS * R rows
+  for (int64_t row0 = ((int64_t)blockIdx.x * WARPS + warp) * R; row0 < w.n; row0 += (int64_t)gridDim.x * WARPS * R) {
   const int m = (int)a.m;
   const int64_t k = w.k, nsb = k / QK_K;
   const int c = lane & 7;      // chunk of the super-block's qs
@@ -251,6 +256,7 @@ __global__ void XNQ_MATVEC_BOUNDS matvec_q4k(WeightView w, ActView a, void *y, i
     }
   }
   reduce_store<MT, R>(acc, lane, row0, w.n, m, y, y_dtype, ldy);
+  }
 }
 
 // ---- Q6_K: 4 lanes per super-block; a lane takes 2 ql chunks + 1 qh chunk = 64 codes ---------------
@@ -259,8 +265,8 @@ __global__ void XNQ_MATVEC_BOUNDS matvec_q6k(WeightView w, ActView a, void *y, i
   extern __shared__ __align__(16) unsigned char smem[];
   const SmemAct sa = stage_activations(smem, a, QK_K, true);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t row0 = ((int64_t)blockIdx.x * WARPS + warp) * R;
-  if (row0 >= w.n) return;
+  // persistent over row groups: the activation image is staged once per CTA, not once per WARPS * R rows
+  for (int64_t row0 = ((int64_t)blockIdx.x * WARPS + warp) * R; row0 < w.n; row0 += (int64_t)gridDim.x * WARPS * R) {
   const int m = (int)a.m;
   const int64_t k = w.k, nsb = k / QK_K;
   const int u = lane & 3, h = u >> 1, lh = u & 1; // half of the super-block, half of its 32 l-values
@@ -310,11 +316,17 @@ __global__ void XNQ_MATVEC_BOUNDS matvec_q6k(WeightView w, ActView a, void *y, i
     }
   }
   reduce_store<MT, R>(acc, lane, row0, w.n, m, y, y_dtype, ldy);
+  }
 }
 
 template <int MT, int R>
 int launch_mt(const WeightView &w, const ActView &a, void *y, int y_dtype, int64_t ldy, cudaStream_t s) {
-  const unsigned grid = (unsigned)((w.n + (int64_t)WARPS * R - 1) / ((int64_t)WARPS * R));
+  const int64_t groups = (w.n + (int64_t)WARPS * R - 1) / ((int64_t)WARPS * R);
+  const int blk = (w.dtype == XNQ_Q4_0 || w.dtype == XNQ_Q8_0) ? QK : QK_K;
+  const size_t image = smem_act_bytes(a.m, a.k, blk, w.dtype != XNQ_Q8_0);
+  const int by_bounds = MT <= 2 ? 4 : (MT <= 4 ? 3 : 2);
+  const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(by_bounds, (220 * 1024) / std::max<size_t>(image + 1024, 1)));
+  const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(groups, (int64_t)g_sms * per_sm));
   switch (w.dtype) {
     case XNQ_Q4_0: {
       const size_t sm = smem_act_bytes(a.m, a.k, QK, true);
@@ -372,17 +384,20 @@ int launch_matvec(const WeightView &w, const ActView &a, void *y, int y_dtype, i
   if (a.m == 1) return launch_mt<1, 2>(w, a, y, y_dtype, ldy, s);
   if (a.m == 2) return launch_mt<2, 2>(w, a, y, y_dtype, ldy, s);
   if (a.m <= 4) return launch_mt<4, 2>(w, a, y, y_dtype, ldy, s);
-  if (a.m <= 8) return launch_mt<8, 1>(w, a, y, y_dtype, ldy, s);
-  return launch_mt<16, 1>(w, a, y, y_dtype, ldy, s);
+  if (a.m <= 8) return launch_mt<8, 2>(w, a, y, y_dtype, ldy, s);
+  return launch_mt<16, 2>(w, a, y, y_dtype, ldy, s);
 }
 
-int matvec_init(int) {
+int matvec_init(int device) {
+  cudaDeviceProp prop;
+  XNQ_CUDA(cudaGetDeviceProperties(&prop, device));
+  g_sms = prop.multiProcessorCount;
   int rc;
   if ((rc = init_mt<1, 2>()) != XNQ_OK) return rc;
   if ((rc = init_mt<2, 2>()) != XNQ_OK) return rc;
   if ((rc = init_mt<4, 2>()) != XNQ_OK) return rc;
-  if ((rc = init_mt<8, 1>()) != XNQ_OK) return rc;
-  if ((rc = init_mt<16, 1>()) != XNQ_OK) return rc;
+  if ((rc = init_mt<8, 2>()) != XNQ_OK) return rc;
+  if ((rc = init_mt<16, 2>()) != XNQ_OK) return rc;
   return XNQ_OK;
 }
 
