@@ -145,7 +145,9 @@ int xnq_matmul_t_static(const xnq_weight *w, const void *x, int x_dtype, int64_t
 /* QLinear::forward on HOST tensors (quantized/mod.rs:352-384): copies x_host [m, k] f32 to the
  * device, runs xnq_matmul_t, adds bias_host[n_local] if non-NULL, copies y back to y_host
  * [m, n_local] and synchronizes. Device staging buffers are owned by the weight handle and grow on
- * demand (first call at a given m allocates). Not for use from several threads on one handle. */
+ * demand (first call at a given m allocates). Not for use from several threads on one handle.
+ * When y_host is page-locked memory (cudaHostAlloc / cudaHostRegister), there is no bias and m <= 16,
+ * the kernel stores the result straight into it and the copy back is skipped. */
 int xnq_linear_forward_host(xnq_weight *w, const float *x_host, int64_t m, const float *bias_host,
                             float *y_host, void *stream);
 

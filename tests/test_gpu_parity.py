@@ -159,6 +159,19 @@ def test_three_d_input_and_bias(Q, O):
     host = lin.weight.forward_host(x, bias)
     assert host.shape == (2, 3, n)
     assert_close_ref(host.reshape(6, n), want, TOL_F32)
+    # a page-locked result array is written by the kernel itself (no bias, m <= 16); a pageable one is copied into
+    for dt2, n2, k2, m2 in [(D.Q4K, 200, 512, 1), (D.Q6K, 96, 256, 5), (D.Q8_0, 64, 8192, 2), (D.Q4_0, 33, 64, 16)]:
+        w2 = synth.make_weight(dt2, n2, k2, seed=82)
+        x2 = synth.make_activation(m2, k2, seed=83)
+        t2 = _upload(Q, dt2, w2, n2, k2)
+        want2 = O.matmul(int(dt2), x2, w2, n2)
+        pinned = torch.full((m2, n2), float("nan"), dtype=torch.float32).pin_memory()
+        got_pinned = t2.forward_host(x2, out=pinned.numpy())
+        assert got_pinned is not None and not np.isnan(pinned.numpy()).any()
+        assert_close_ref(pinned.numpy(), want2, TOL_F32)
+        pageable = np.full((m2, n2), np.nan, np.float32)
+        t2.forward_host(x2, out=pageable)
+        assert np.array_equal(pageable, pinned.numpy())
 
 
 def test_q8_0_reference_known_answer_recipe_on_gpu(Q, O):

@@ -25,6 +25,7 @@ void clear_error() { g_err[0] = 0; }
 static std::atomic<uint64_t> g_launches{0};
 static std::atomic<bool> g_opt_matvec_tma{true};
 static std::atomic<int> g_opt_gather_cta_fence{1};
+static std::atomic<int> g_opt_host_direct_y{1};
 int gather_cta_fence_scope() { return g_opt_gather_cta_fence.load(std::memory_order_relaxed); }
 bool matvec_tma_enabled() { return g_opt_matvec_tma.load(std::memory_order_relaxed); }
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
@@ -201,6 +202,10 @@ int xnq_set_option(const char *name, int value) {
   if (!name) return fail(XNQ_ERR_NULL, "set_option: name is NULL");
   if (std::strcmp(name, "matvec_tma") == 0) {
     g_opt_matvec_tma.store(value != 0);
+    return XNQ_OK;
+  }
+  if (std::strcmp(name, "host_direct_y") == 0) {
+    g_opt_host_direct_y.store(value);
     return XNQ_OK;
   }
   if (std::strcmp(name, "gather_cta_fence") == 0) {
@@ -469,10 +474,22 @@ int xnq_linear_forward_host(xnq_weight *w, const float *x_host, int64_t m, const
   void *ws = base + xb + yb + bb;
   XNQ_CUDA(cudaMemcpyAsync(xd, x_host, (size_t)m * k * 4, cudaMemcpyHostToDevice, s));
   if (bias_host) XNQ_CUDA(cudaMemcpyAsync(bd, bias_host, (size_t)n * 4, cudaMemcpyHostToDevice, s));
-  int rc = xnq_matmul_t(w, xd, XNQ_F32, m, k, yd, XNQ_F32, n, ws, wsb, s);
+  // A page-locked result buffer is written by the kernel itself (posted stores over the host link), which
+  // saves the device-to-host copy and its launch; anything else goes through the staging buffer. The
+  // activations are always copied in: every CTA reads all of x, which must not cross the host link 148 times.
+  float *y_direct = nullptr;
+  if (!bias_host && m <= MATVEC_MAX_M && g_opt_host_direct_y.load(std::memory_order_relaxed)) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, y_host) == cudaSuccess && attr.type == cudaMemoryTypeHost && attr.devicePointer &&
+        (reinterpret_cast<uintptr_t>(attr.devicePointer) & 15) == 0)
+      y_direct = static_cast<float *>(attr.devicePointer);
+    else
+      (void)cudaGetLastError(); // an unregistered pointer is not an error here
+  }
+  int rc = xnq_matmul_t(w, xd, XNQ_F32, m, k, y_direct ? y_direct : yd, XNQ_F32, n, ws, wsb, s);
   if (rc != XNQ_OK) return rc;
   if (bias_host && (rc = launch_add_bias(yd, bd, m, n, n, s)) != XNQ_OK) return rc;
-  XNQ_CUDA(cudaMemcpyAsync(y_host, yd, (size_t)m * n * 4, cudaMemcpyDeviceToHost, s));
+  if (!y_direct) XNQ_CUDA(cudaMemcpyAsync(y_host, yd, (size_t)m * n * 4, cudaMemcpyDeviceToHost, s));
   XNQ_CUDA(cudaStreamSynchronize(s));
   return XNQ_OK;
 }

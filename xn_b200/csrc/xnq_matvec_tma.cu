@@ -60,10 +60,13 @@ __device__ __forceinline__ unsigned long long gtime() {
 #endif
 constexpr int CW = XNQ_MV_CW;            // consumer warps per CTA
 constexpr int NTHREADS = (CW + 1) * 32;  // + one producer warp
-constexpr int CTAS_PER_SM = CW <= 8 ? 2 : 1; // 8 warps: two consecutive launches can share an SM
+#ifndef XNQ_MV_CTAS
+#define XNQ_MV_CTAS (XNQ_MV_CW <= 8 ? 2 : 1)
+#endif
+constexpr int CTAS_PER_SM = XNQ_MV_CTAS; // 2: CTAs of two consecutive launches can share an SM
 constexpr int MAX_STAGES = 8;
 constexpr uint32_t WAIT_LIMIT = 1u << 26; // non-blocking polls (a few ns each): about a second
-constexpr size_t SMEM_BUDGET = (CW <= 8 ? 112 : 225) * 1024; // per CTA: CTAS_PER_SM of them fit the 227 KB of an SM
+constexpr size_t SMEM_BUDGET = (CTAS_PER_SM == 2 ? 112 : 225) * 1024; // per CTA: CTAS_PER_SM of them fit the 227 KB of an SM
 
 struct Ring {
   int nstreams;

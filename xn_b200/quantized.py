@@ -221,15 +221,19 @@ class QCudaTensor:
                                           ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(self.device)))
         return out
 
-    def forward_host(self, x: np.ndarray, bias: Optional[np.ndarray] = None) -> np.ndarray:
-        """``QLinear::forward`` on host arrays (mod.rs:352-384): H2D copy, matmul, optional bias, D2H copy, sync."""
+    def forward_host(self, x: np.ndarray, bias: Optional[np.ndarray] = None, out: Optional[np.ndarray] = None) -> np.ndarray:
+        """``QLinear::forward`` on host arrays (mod.rs:352-384): H2D copy, matmul, optional bias, D2H copy, sync.
+        ``out`` may name the result array (for instance the numpy view of a pinned torch tensor, which the
+        kernel then writes directly)."""
         x = np.ascontiguousarray(x, np.float32)
         if x.ndim < 2:
             raise ValueError(f"input tensor has only one dimension {x.shape}")  # mod.rs:363-365
         if x.shape[-1] != self.k:
             raise ValueError(f"input tensor {x.shape} incompatible with {(self.n, self.k)}")  # mod.rs:368-370
         m = int(np.prod(x.shape[:-1]))
-        y = np.empty(x.shape[:-1] + (self.n,), np.float32)
+        if out is not None and (out.dtype != np.float32 or not out.flags.c_contiguous or out.shape != x.shape[:-1] + (self.n,)):
+            raise ValueError(f"out must be a contiguous float32 array of shape {x.shape[:-1] + (self.n,)}")
+        y = out if out is not None else np.empty(x.shape[:-1] + (self.n,), np.float32)
         b = None if bias is None else np.ascontiguousarray(bias, np.float32)
         if b is not None and b.shape != (self.n,):
             raise ValueError(f"bias shape {b.shape} does not match n={self.n}")
