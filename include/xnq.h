@@ -96,6 +96,19 @@ int xnq_weight_dequantize(const xnq_weight *w, int out_dtype, void *dst, void *s
  * quantized/mod.rs:206-214). Synchronizes `stream`. */
 int xnq_weight_canonical_bytes(const xnq_weight *w, void *host_dst, size_t nbytes, void *stream);
 
+/* Activations quantized ahead of the matmul. The reference quantizes the activations inside every
+ * matmul call (quantize_lhs, k_quants.rs:2015-2026); when several linears read the same input, or the
+ * producer of the input can quantize it as it writes it (xnq_add_rmsnorm, xnq_swiglu), that work is done
+ * once: an "activation image" holds m rows of Q8_0 or Q8_K codes, block scales and 16-element sums in the
+ * planar layout the kernels read, and is passed to xnq_matmul_t / xnq_matmul_t_gather as x with
+ * x_dtype = XNQ_ACT_IMAGE (m <= 16; ldx and the workspace are ignored). The bytes are those the in-call
+ * quantizer produces, so results are identical. act_dtype is XNQ_Q8_0 for Q4_0 / Q8_0 weights and XNQ_Q8K
+ * for Q4_K / Q6_K weights. The image must be 256-byte aligned. */
+#define XNQ_ACT_IMAGE 100
+size_t xnq_act_image_bytes(int act_dtype, int64_t m, int64_t k);
+int xnq_quantize_act_image(int act_dtype, const void *x, int x_dtype, int64_t m, int64_t k, int64_t ldx,
+                           void *image, void *stream);
+
 /* QTensor::quantize_f32 / QLinear::from_linear for a weight that already lives on the device
  * (quantized/mod.rs:290-297, 398-405): x_dev is a dense f32 [n, k] matrix, blocks_dev receives
  * n * k / block GGUF blocks in canonical byte order, bit-identical to the reference's host
@@ -201,11 +214,13 @@ int xnq_comm_free(xnq_comm *c);
  * the path in xn-core/src/models/llama.rs:145-216, 258-265, 300-320; reference kernels rmsnorm / rope /
  * sdpa in cuda-kernels/reduce.cu). All pointers are device memory, f32 unless stated. ------------- */
 /* x[rows, d] += sum over p of delta[rows, p, d] (delta may be NULL; delta_parts >= 1 summands per row,
- * e.g. the per-rank partial results of a row-parallel linear), out = x * rsqrt(mean(x^2) + eps) * weight[d]. */
+ * e.g. the per-rank partial results of a row-parallel linear), out = x * rsqrt(mean(x^2) + eps) * weight[d].
+ * out may be NULL when only the quantized form is wanted. act_image, when not NULL, receives the activation
+ * image (act_dtype XNQ_Q8_0 or XNQ_Q8K) of the normalized rows: exactly what quantizing `out` would give. */
 int xnq_add_rmsnorm(float *x, const float *delta, int delta_parts, const float *weight, float eps, float *out,
-                    int64_t rows, int64_t d, void *stream);
-/* out[rows, f] = silu(gate_up[rows, 0:f]) * gate_up[rows, f:2f]. */
-int xnq_swiglu(const float *gate_up, float *out, int64_t rows, int64_t f, void *stream);
+                    void *act_image, int act_dtype, int64_t rows, int64_t d, void *stream);
+/* out[rows, f] = silu(gate_up[rows, 0:f]) * gate_up[rows, f:2f]; out / act_image as above. */
+int xnq_swiglu(const float *gate_up, float *out, void *act_image, int act_dtype, int64_t rows, int64_t f, void *stream);
 /* One new token per sequence: qkv[batch, (heads + 2 kv_heads) * head_dim] -> rotate-half RoPE at
  * position *pos_dev (cos/sin tables [max_seq, head_dim / 2]); q_out[batch, heads, head_dim]; rotated k
  * and plain v are stored as bf16 into k_cache / v_cache [batch, kv_heads, max_seq, head_dim]. */

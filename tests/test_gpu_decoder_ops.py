@@ -80,3 +80,34 @@ def test_rope_store_and_attention(B, H, KV):
         kk = kc[:, :, : pos_i + 1].float().repeat_interleave(H // KV, 1); vv = vc[:, :, : pos_i + 1].float().repeat_interleave(H // KV, 1)
         w = torch.softmax(torch.einsum("bhd,bhsd->bhs", q, kk) / math.sqrt(hd), -1)
         torch.testing.assert_close(out, torch.einsum("bhs,bhsd->bhd", w, vv), rtol=2e-4, atol=2e-5)
+
+
+def test_activation_images_equal_the_in_call_quantizer():
+    """An image written by the stand-alone quantizer, by add_rmsnorm or by swiglu holds the bytes the matmul's own
+    quantizer would produce from the same f32 rows, so matmul results through an image are bit-identical."""
+    import numpy as np
+    from xn_b200 import decoder_ops as ops, quantized as Q, synth
+    from xn_b200.dtypes import GgmlDType as D
+    torch.manual_seed(3)
+    for dt, n, k in [(D.Q4K, 320, 4096), (D.Q6K, 96, 1024), (D.Q8_0, 200, 4096), (D.Q4_0, 64, 512), (D.Q4K, 128, 14336)]:
+        w = Q.QCudaTensor.from_qtensor(Q.QTensor(synth.make_weight(dt, n, k, seed=40), (n, k), dt), DEV)
+        for m in (1, 3, 16):
+            x = torch.randn(m, k, device=DEV)
+            want = w.matmul_t(x)
+            img = ops.quantize_act_image(x, ops.ActImage.for_weight(dt, m, k, DEV))
+            assert torch.equal(w.matmul_t(img), want), (dt.name, k, m, "quantize_act_image")
+            # add_rmsnorm: the image equals the quantization of its own f32 output
+            res = torch.randn(m, k, device=DEV); dl = torch.randn(m, k, device=DEV); g = torch.rand(k, device=DEV) + 0.5
+            out = torch.empty(m, k, device=DEV); img2 = ops.ActImage.for_weight(dt, m, k, DEV)
+            ops.add_rmsnorm(res.clone(), dl, g, 1e-5, out, img2)
+            assert torch.equal(w.matmul_t(img2), w.matmul_t(out)), (dt.name, k, m, "add_rmsnorm")
+            only = ops.ActImage.for_weight(dt, m, k, DEV)
+            ops.add_rmsnorm(res.clone(), dl, g, 1e-5, None, only)      # image without the f32 rows
+            assert torch.equal(only.buf, img2.buf)
+            if k % 256 == 0:
+                gu = torch.randn(m, 2 * k, device=DEV) * 2
+                h = torch.empty(m, k, device=DEV); img3 = ops.ActImage.for_weight(dt, m, k, DEV)
+                ops.swiglu(gu, h, img3)
+                assert torch.equal(w.matmul_t(img3), w.matmul_t(h)), (dt.name, k, m, "swiglu")
+    with pytest.raises(ValueError):
+        w.matmul_t(ops.ActImage.for_weight(D.Q8_0, 1, 14336, DEV))   # a Q8_0 image does not fit a Q4_K weight

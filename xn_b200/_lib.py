@@ -8,6 +8,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, os.environ.get("XNQ_LIB_NAME", "libxnq.so"))
 
 XNQ_OK = 0
+XNQ_ACT_IMAGE = 100  # x_dtype of an activation image (activations quantized ahead of the matmul)
 STATUS_NAMES = {0: "XNQ_OK", -1: "XNQ_ERR_NULL", -2: "XNQ_ERR_DTYPE", -3: "XNQ_ERR_SHAPE", -4: "XNQ_ERR_ALIGN",
                 -5: "XNQ_ERR_SIZE", -6: "XNQ_ERR_CUDA", -7: "XNQ_ERR_COMM", -8: "XNQ_ERR_UNSUPPORTED"}
 
@@ -47,6 +48,9 @@ def lib() -> ctypes.CDLL:
     L.xnq_weight_dequantize.argtypes = [vp, ci, vp, vp]
     L.xnq_weight_canonical_bytes.argtypes = [vp, vp, sz, vp]
     L.xnq_quantize_act.argtypes = [ci, vp, ci, i64, i64, i64, vp, vp]
+    L.xnq_act_image_bytes.argtypes = [ci, i64, i64]
+    L.xnq_act_image_bytes.restype = sz
+    L.xnq_quantize_act_image.argtypes = [ci, vp, ci, i64, i64, i64, vp, vp]
     L.xnq_quantize_weight.argtypes = [ci, vp, i64, i64, vp, vp]
     L.xnq_matmul_workspace_bytes.argtypes = [vp, i64]
     L.xnq_matmul_workspace_bytes.restype = sz
@@ -62,8 +66,8 @@ def lib() -> ctypes.CDLL:
     L.xnq_comm_status.argtypes = [vp, ctypes.POINTER(ctypes.c_uint)]
     L.xnq_comm_free.argtypes = [vp]
     fp = ctypes.c_float
-    L.xnq_add_rmsnorm.argtypes = [vp, vp, ci, vp, fp, vp, i64, i64, vp]
-    L.xnq_swiglu.argtypes = [vp, vp, i64, i64, vp]
+    L.xnq_add_rmsnorm.argtypes = [vp, vp, ci, vp, fp, vp, vp, ci, i64, i64, vp]
+    L.xnq_swiglu.argtypes = [vp, vp, vp, ci, i64, i64, vp]
     L.xnq_rope_kv_store.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, ci, ci, ci, i64, vp]
     L.xnq_attn_decode_workspace_bytes.argtypes = [i64, ci]
     L.xnq_attn_decode_workspace_bytes.restype = sz

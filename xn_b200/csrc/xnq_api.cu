@@ -106,6 +106,44 @@ int check_activations(const char *who, const void *x, int x_dtype, int64_t m, in
 
 using namespace xnq;
 
+// xnq_matmul_t on activations that were quantized ahead of the call (x_dtype == XNQ_ACT_IMAGE): the decode
+// kernels read the image directly; nothing is quantized and no scratch is used.
+static int matmul_from_image(const xnq_weight *w, const void *image, int64_t m, void *y, int y_dtype, int64_t ldy, cudaStream_t s) {
+  const int64_t k = w->v.k, n = w->v.n;
+  if (m < 0 || m > MATVEC_MAX_M) return fail(XNQ_ERR_SIZE, "matmul_t: an activation image serves 0..%d rows, m = %lld", MATVEC_MAX_M, (long long)m);
+  if (!is_float_dtype(y_dtype)) return fail(XNQ_ERR_DTYPE, "matmul_t: output dtype %d is not f32/f16/bf16", y_dtype);
+  if (ldy < n) return fail(XNQ_ERR_SHAPE, "matmul_t: ldy = %lld is smaller than n = %lld", (long long)ldy, (long long)n);
+  if (m == 0 || n == 0) return XNQ_OK;
+  if (!image || !y) return fail(XNQ_ERR_NULL, "matmul_t: image or y is NULL");
+  if (!aligned(image, 256)) return fail(XNQ_ERR_ALIGN, "matmul_t: the activation image must be 256-byte aligned");
+  if (!aligned(y, type_size(y_dtype))) return fail(XNQ_ERR_ALIGN, "matmul_t: y is not aligned to its element size");
+  const int adt = act_dtype_for(w->v.dtype);
+  int rc;
+  if (matvec_tma_enabled() && matvec_tma_supported(w->v, m)) {
+    profile_mark(s, true);
+    rc = launch_matvec_tma(w->v, image, XNQ_ACT_IMAGE, y, y_dtype, s);
+    profile_mark(s, false);
+    return rc;
+  }
+  const int64_t pass = matvec_rows_per_pass(w->v.dtype, k);
+  if (pass == 0) return fail(XNQ_ERR_SIZE, "matmul_t: k = %lld is too large for the shared-memory staging of one activation row", (long long)k);
+  const ActView all = act_view(const_cast<void *>(image), m, k, adt);
+  const int blk = adt == XNQ_Q8_0 ? QK : QK_K;
+  const size_t yes = type_size(y_dtype);
+  for (int64_t r0 = 0; r0 < m; r0 += pass) {
+    ActView a = all;
+    a.m = (m - r0) < pass ? (m - r0) : pass;
+    a.q += r0 * k;
+    a.d += r0 * (k / blk);
+    a.bsum += r0 * (k / 16);
+    profile_mark(s, true);
+    rc = launch_matvec(w->v, a, static_cast<char *>(y) + (size_t)r0 * ldy * yes, y_dtype, ldy, s);
+    profile_mark(s, false);
+    if (rc != XNQ_OK) return rc;
+  }
+  return XNQ_OK;
+}
+
 extern "C" {
 
 const char *xnq_last_error(void) { return g_err; }
@@ -210,6 +248,10 @@ int xnq_set_option(const char *name, int value) {
   }
   if (std::strcmp(name, "gather_cta_fence") == 0) {
     g_opt_gather_cta_fence.store(value);
+    return XNQ_OK;
+  }
+  if (std::strcmp(name, "prefill_persistent") == 0) {
+    prefill_set_persistent(value);
     return XNQ_OK;
   }
   if (std::strcmp(name, "prefill_dbg") == 0) {
@@ -384,6 +426,25 @@ int xnq_quantize_act(int act_dtype, const void *x, int x_dtype, int64_t m, int64
   return launch_quantize_act_blocks(act_dtype, x, x_dtype, m, k, ldx, dst, static_cast<cudaStream_t>(stream));
 }
 
+size_t xnq_act_image_bytes(int act_dtype, int64_t m, int64_t k) {
+  if ((act_dtype != XNQ_Q8_0 && act_dtype != XNQ_Q8K) || m <= 0 || k <= 0) return 0;
+  return act_workspace_bytes(m, k, act_dtype);
+}
+
+int xnq_quantize_act_image(int act_dtype, const void *x, int x_dtype, int64_t m, int64_t k, int64_t ldx, void *image, void *stream) {
+  clear_error();
+  if (act_dtype != XNQ_Q8_0 && act_dtype != XNQ_Q8K)
+    return fail(XNQ_ERR_DTYPE, "quantize_act_image: %d is not an activation block format (Q8_0=8, Q8K=15)", act_dtype);
+  const int bs = block_size(act_dtype);
+  if (k <= 0 || k % bs != 0) return fail(XNQ_ERR_SHAPE, "quantize_act_image: k = %lld is not a multiple of the %d-value block", (long long)k, bs);
+  int rc = check_activations("quantize_act_image", x, x_dtype, m, k, ldx);
+  if (rc != XNQ_OK) return rc;
+  if (m == 0) return XNQ_OK;
+  if (!image) return fail(XNQ_ERR_NULL, "quantize_act_image: image is NULL");
+  if (!aligned(image, 256)) return fail(XNQ_ERR_ALIGN, "quantize_act_image: image must be 256-byte aligned");
+  return launch_quantize_act_planar(act_view(image, m, k, act_dtype), x, x_dtype, ldx, static_cast<cudaStream_t>(stream));
+}
+
 int xnq_quantize_weight(int ggml_dtype, const float *x_dev, int64_t n, int64_t k, void *blocks_dev, void *stream) {
   clear_error();
   if (!is_weight_dtype(ggml_dtype)) return fail(XNQ_ERR_DTYPE, "quantize_weight: dtype %d is not Q4_0/Q8_0/Q4K/Q6K", ggml_dtype);
@@ -401,7 +462,7 @@ size_t xnq_matmul_workspace_bytes(const xnq_weight *w, int64_t max_m) {
   const int64_t rows = max_m < MATVEC_MAX_M ? max_m : MATVEC_MAX_M;
   const size_t decode = act_workspace_bytes(rows, w->v.k, act_dtype_for(w->v.dtype));
   if (max_m <= MATVEC_MAX_M) return decode;
-  const size_t prefill = prefill_workspace_bytes(max_m, w->v.k); // m > 16 runs on the tensor cores
+  const size_t prefill = prefill_workspace_bytes(max_m, w->v.k, w->v.n); // m > 16 runs on the tensor cores
   return prefill > decode ? prefill : decode;
 }
 
@@ -410,6 +471,7 @@ int xnq_matmul_t(const xnq_weight *w, const void *x, int x_dtype, int64_t m, int
   clear_error();
   if (!w) return fail(XNQ_ERR_NULL, "matmul_t: weight is NULL");
   const int64_t k = w->v.k, n = w->v.n;
+  if (x_dtype == XNQ_ACT_IMAGE) return matmul_from_image(w, x, m, y, y_dtype, ldy, static_cast<cudaStream_t>(stream));
   int rc = check_activations("matmul_t", x, x_dtype, m, k, ldx);
   if (rc != XNQ_OK) return rc;
   if (!is_float_dtype(y_dtype)) return fail(XNQ_ERR_DTYPE, "matmul_t: output dtype %d is not f32/f16/bf16", y_dtype);

@@ -216,7 +216,11 @@ int xnq_matmul_t_gather(const xnq_weight *w, xnq_comm *c, int slot, int layout, 
   char *local = slot_ptr(c, c->rank, slot);
   int rc;
   if (m == 1 && matvec_tma_enabled() && matvec_tma_supported(w->v, 1)) {
-    if ((rc = check_activations("matmul_t_gather", x, x_dtype, m, w->v.k, ldx)) != XNQ_OK) return rc;
+    if (x_dtype == XNQ_ACT_IMAGE) {
+      if (!x || (reinterpret_cast<uintptr_t>(x) & 255)) return fail(XNQ_ERR_ALIGN, "matmul_t_gather: the activation image must be non-NULL and 256-byte aligned");
+    } else if ((rc = check_activations("matmul_t_gather", x, x_dtype, m, w->v.k, ldx)) != XNQ_OK) {
+      return rc;
+    }
     rc = launch_matvec_tma(w->v, x, x_dtype, nullptr, y_dtype, s, &g); // stores go to every rank's slot from inside the kernel
     if (rc != XNQ_OK) return rc;
   } else {

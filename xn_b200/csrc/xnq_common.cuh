@@ -139,6 +139,7 @@ __device__ __forceinline__ void gather_publish_and_wait(const GatherArgs &g) {
     unsigned long long t0;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
     const unsigned int *mine = g.flag[g.rank] - g.rank; // the local epoch row
+    if (g.ctl[3]) return; // a peer was already late once: later launches do not wait again (the host reads ctl[3])
     for (int p = 0; p < g.world; p++) {
       if (p == g.rank) continue;
       for (;;) {
@@ -219,12 +220,13 @@ int matvec_check_record(unsigned long long out[8]);
 int matvec_trace(unsigned long long *out, unsigned int *n);
 
 // xnq_prefill.cu  (m > 16: tcgen05 / TMEM contraction on fp16 operands)
-size_t prefill_workspace_bytes(int64_t m, int64_t k);
+size_t prefill_workspace_bytes(int64_t m, int64_t k, int64_t n);
 int launch_prefill(const WeightView &w, float wscale, const void *x, int x_dtype, int64_t m, int64_t ldx, void *y, int y_dtype, int64_t ldy,
                    void *workspace, cudaStream_t s);
 int prefill_init(int device);
 int prefill_status(unsigned int *bits);
 void prefill_set_dbg(int v);
+void prefill_set_persistent(int v);
 int prefill_trace(unsigned long long out[16]);
 
 // largest |dequantized weight| of the tensor, written to *dev_out (a float in device memory)

@@ -5,6 +5,7 @@
 // its arithmetic: RMSNorm as x * rsqrt(mean(x^2) + eps) * w, rotate-half RoPE, softmax(q k^T / sqrt(d)) v
 // with grouped-query heads, silu(gate) * up. All f32 math; the KV cache is bf16.
 #include "xnq_common.cuh"
+#include "xnq_quantize_act.cuh"
 
 namespace xnq {
 namespace {
@@ -20,45 +21,122 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
-// x[row] += sum_p delta[row][p] (if delta), out[row] = x[row] * rsqrt(mean(x^2) + eps) * w.  One CTA per row.
-__global__ void __launch_bounds__(256) add_rmsnorm_kernel(float *x, const float *delta, int parts, const float *w, float eps, float *out, int d) {
+// Planar activation image of one row (the layout of act_view): codes, block scales, 16-element sums.
+struct RowImage {
+  int8_t *q;
+  float *d;
+  int16_t *bsum;
+};
+__device__ __forceinline__ RowImage row_image(void *image, int64_t rows, int64_t k, int blk, int64_t row) {
+  auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  char *p = static_cast<char *>(image);
+  RowImage r;
+  r.q = reinterpret_cast<int8_t *>(p) + row * k;
+  p += up((size_t)rows * k);
+  r.d = reinterpret_cast<float *>(p) + row * (k / blk);
+  p += up((size_t)rows * (k / blk) * 4);
+  r.bsum = reinterpret_cast<int16_t *>(p) + row * (k / 16);
+  return r;
+}
+// Quantizes the 8 values of this lane (elements c8 * 8 .. of the row; a warp holds 256 consecutive elements)
+// and stores them into the row's image. All 32 lanes call it; lanes past the end of the row pass zeros.
+template <int ACT>
+__device__ __forceinline__ void quantize_store8(const float (&v)[8], bool valid, const RowImage &img, int64_t c8, int lane) {
+  const Quant8 q = ACT == XNQ_Q8_0 ? quantize8_q8_0(v, lane) : quantize8_q8k(v, lane);
+  if (!valid) return;
+  *reinterpret_cast<uint2 *>(img.q + c8 * 8) = make_uint2(q.lo, q.hi);
+  if (ACT == XNQ_Q8_0) {
+    if ((lane & 3) == 0) img.d[c8 / 4] = q.d;
+  } else {
+    if (lane == 0) img.d[c8 / 32] = q.d;
+  }
+  if ((lane & 1) == 0) img.bsum[c8 / 2] = (int16_t)q.sum16;
+}
+
+// x[row] += sum_p delta[row][p] (if delta), out[row] = x[row] * rsqrt(mean(x^2) + eps) * w, and optionally the
+// quantized image of out[row]. One CTA of 256 threads per row, 8 consecutive elements per thread per pass.
+template <int ACT>
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(float *x, const float *delta, int parts, const float *w, float eps, float *out, void *image,
+                                                          int64_t rows, int d) {
   __shared__ float part[8];
   const int64_t row = blockIdx.x;
+  const int lane = threadIdx.x & 31;
   float *xr = x + row * d;
   const float *dr = delta ? delta + row * parts * d : nullptr;
   float ss = 0.f;
-  for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
-    float4 v = *reinterpret_cast<const float4 *>(xr + i);
+  for (int i = threadIdx.x * 8; i < d; i += 2048) {
+    float v[8];
+    load8(xr + i, v);
     if (dr) {
       for (int p = 0; p < parts; p++) {
-        const float4 a = *reinterpret_cast<const float4 *>(dr + (int64_t)p * d + i);
-        v.x += a.x, v.y += a.y, v.z += a.z, v.w += a.w;
+        float a[8];
+        load8(dr + (int64_t)p * d + i, a);
+#pragma unroll
+        for (int e = 0; e < 8; e++) v[e] += a[e];
       }
-      *reinterpret_cast<float4 *>(xr + i) = v;
+      *reinterpret_cast<float4 *>(xr + i) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4 *>(xr + i + 4) = make_float4(v[4], v[5], v[6], v[7]);
     }
-    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+#pragma unroll
+    for (int e = 0; e < 8; e++) ss += v[e] * v[e];
   }
   ss = warp_sum(ss);
-  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+  if (lane == 0) part[threadIdx.x >> 5] = ss;
   __syncthreads();
   float tot = 0.f;
 #pragma unroll
   for (int i = 0; i < 8; i++) tot += part[i];
   const float r = rsqrtf(tot / (float)d + eps);
-  for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
-    const float4 v = *reinterpret_cast<const float4 *>(xr + i), g = *reinterpret_cast<const float4 *>(w + i);
-    *reinterpret_cast<float4 *>(out + row * d + i) = make_float4(v.x * r * g.x, v.y * r * g.y, v.z * r * g.z, v.w * r * g.w);
+  RowImage img{};
+  if (ACT != 0) img = row_image(image, rows, d, ACT == XNQ_Q8_0 ? QK : QK_K, row);
+  for (int base = 0; base < d; base += 2048) { // whole warps stay together for the quantizer's shuffles
+    const int i = base + threadIdx.x * 8;
+    if (base + (threadIdx.x & ~31) * 8 >= d) break;
+    const bool valid = i < d;
+    float v[8];
+    if (valid) {
+      float g[8];
+      load8(xr + i, v); // this thread's own stores of the first pass
+      load8(w + i, g);
+#pragma unroll
+      for (int e = 0; e < 8; e++) v[e] = v[e] * r * g[e];
+      if (out) {
+        *reinterpret_cast<float4 *>(out + row * d + i) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4 *>(out + row * d + i + 4) = make_float4(v[4], v[5], v[6], v[7]);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; e++) v[e] = 0.f;
+    }
+    if (ACT != 0) quantize_store8<ACT>(v, valid, img, i / 8, lane);
   }
 }
 
-// out[row, j] = silu(gu[row, j]) * gu[row, f + j]
-__global__ void __launch_bounds__(256) swiglu_kernel(const float *gu, float *out, int64_t rows, int f) {
-  const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
-  if (i >= rows * f) return;
-  const int64_t r = i / f, j = i - r * f;
-  const float4 g = *reinterpret_cast<const float4 *>(gu + r * 2 * f + j), u = *reinterpret_cast<const float4 *>(gu + r * 2 * f + f + j);
-  auto silu = [](float v) { return v / (1.f + __expf(-v)); };
-  *reinterpret_cast<float4 *>(out + i) = make_float4(silu(g.x) * u.x, silu(g.y) * u.y, silu(g.z) * u.z, silu(g.w) * u.w);
+// out[row, j] = silu(gu[row, j]) * gu[row, f + j], optionally with its quantized image. 8 consecutive
+// elements per thread; f is a multiple of 256 when an image is written, so a warp never straddles two rows.
+template <int ACT>
+__global__ void __launch_bounds__(256) swiglu_kernel(const float *gu, float *out, void *image, int64_t rows, int f) {
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t per_row = f / 8;
+  const bool valid = t < rows * per_row;
+  if (ACT == 0 && !valid) return;
+  const int64_t r = valid ? t / per_row : 0, c8 = valid ? t - r * per_row : 0;
+  float v[8];
+  if (valid) {
+    float g[8], u[8];
+    load8(gu + r * 2 * f + c8 * 8, g);
+    load8(gu + r * 2 * f + f + c8 * 8, u);
+#pragma unroll
+    for (int e = 0; e < 8; e++) v[e] = g[e] / (1.f + __expf(-g[e])) * u[e];
+    if (out) {
+      *reinterpret_cast<float4 *>(out + r * f + c8 * 8) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4 *>(out + r * f + c8 * 8 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; e++) v[e] = 0.f;
+  }
+  if (ACT != 0) quantize_store8<ACT>(v, valid, row_image(image, rows, f, ACT == XNQ_Q8_0 ? QK : QK_K, r), c8, threadIdx.x & 31);
 }
 
 // One token per sequence. qkv [B, (H + 2 KV) * hd] f32 -> q_out [B, H, hd] f32 (rotated), and the rotated k
@@ -193,27 +271,48 @@ using namespace xnq;
 
 extern "C" {
 
-int xnq_add_rmsnorm(float *x, const float *delta, int delta_parts, const float *weight, float eps, float *out, int64_t rows, int64_t d, void *stream) {
+static int check_image(const char *who, const void *image, int act_dtype, int64_t k) {
+  if (!image) return XNQ_OK;
+  if (act_dtype != XNQ_Q8_0 && act_dtype != XNQ_Q8K) return fail(XNQ_ERR_DTYPE, "%s: %d is not an activation block format (Q8_0=8, Q8K=15)", who, act_dtype);
+  const int blk = act_dtype == XNQ_Q8_0 ? QK : QK_K;
+  if (k % blk) return fail(XNQ_ERR_SHAPE, "%s: row length %lld is not a multiple of the %d-value block", who, (long long)k, blk);
+  if (reinterpret_cast<uintptr_t>(image) & 255) return fail(XNQ_ERR_ALIGN, "%s: the activation image must be 256-byte aligned", who);
+  return XNQ_OK;
+}
+
+int xnq_add_rmsnorm(float *x, const float *delta, int delta_parts, const float *weight, float eps, float *out, void *act_image, int act_dtype, int64_t rows,
+                    int64_t d, void *stream) {
   clear_error();
-  if (!x || !weight || !out) return fail(XNQ_ERR_NULL, "add_rmsnorm: NULL argument");
-  if (rows < 0 || d <= 0 || d % 4 || (delta && delta_parts < 1))
-    return fail(XNQ_ERR_SHAPE, "add_rmsnorm: rows = %lld, d = %lld (a multiple of 4), delta_parts = %d", (long long)rows, (long long)d, delta_parts);
+  if (!x || !weight || (!out && !act_image)) return fail(XNQ_ERR_NULL, "add_rmsnorm: NULL argument");
+  if (rows < 0 || d <= 0 || d % 8 || (delta && delta_parts < 1))
+    return fail(XNQ_ERR_SHAPE, "add_rmsnorm: rows = %lld, d = %lld (a multiple of 8), delta_parts = %d", (long long)rows, (long long)d, delta_parts);
   if (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) return fail(XNQ_ERR_ALIGN, "add_rmsnorm: pointers must be 16-byte aligned");
+  int rc = check_image("add_rmsnorm", act_image, act_dtype, d);
+  if (rc != XNQ_OK) return rc;
   if (rows == 0) return XNQ_OK;
-  add_rmsnorm_kernel<<<(unsigned)rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, delta, delta_parts, weight, eps, out, (int)d);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (!act_image) add_rmsnorm_kernel<0><<<(unsigned)rows, 256, 0, s>>>(x, delta, delta_parts, weight, eps, out, nullptr, rows, (int)d);
+  else if (act_dtype == XNQ_Q8_0) add_rmsnorm_kernel<XNQ_Q8_0><<<(unsigned)rows, 256, 0, s>>>(x, delta, delta_parts, weight, eps, out, act_image, rows, (int)d);
+  else add_rmsnorm_kernel<XNQ_Q8K><<<(unsigned)rows, 256, 0, s>>>(x, delta, delta_parts, weight, eps, out, act_image, rows, (int)d);
   XNQ_CUDA(cudaGetLastError());
   count_launch();
   return XNQ_OK;
 }
 
-int xnq_swiglu(const float *gate_up, float *out, int64_t rows, int64_t f, void *stream) {
+int xnq_swiglu(const float *gate_up, float *out, void *act_image, int act_dtype, int64_t rows, int64_t f, void *stream) {
   clear_error();
-  if (!gate_up || !out) return fail(XNQ_ERR_NULL, "swiglu: NULL argument");
-  if (rows < 0 || f <= 0 || f % 4) return fail(XNQ_ERR_SHAPE, "swiglu: rows = %lld, f = %lld (f must be a multiple of 4)", (long long)rows, (long long)f);
+  if (!gate_up || (!out && !act_image)) return fail(XNQ_ERR_NULL, "swiglu: NULL argument");
+  if (rows < 0 || f <= 0 || f % 8) return fail(XNQ_ERR_SHAPE, "swiglu: rows = %lld, f = %lld (f must be a multiple of 8)", (long long)rows, (long long)f);
+  if (act_image && f % 256) return fail(XNQ_ERR_SHAPE, "swiglu: f = %lld must be a multiple of 256 when an activation image is written", (long long)f);
   if (((uintptr_t)gate_up | (uintptr_t)out) & 15) return fail(XNQ_ERR_ALIGN, "swiglu: pointers must be 16-byte aligned");
+  int rc = check_image("swiglu", act_image, act_dtype, f);
+  if (rc != XNQ_OK) return rc;
   if (rows == 0) return XNQ_OK;
-  const int64_t quads = rows * f / 4;
-  swiglu_kernel<<<(unsigned)((quads + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(gate_up, out, rows, (int)f);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const unsigned grid = (unsigned)((rows * f / 8 + 255) / 256);
+  if (!act_image) swiglu_kernel<0><<<grid, 256, 0, s>>>(gate_up, out, nullptr, rows, (int)f);
+  else if (act_dtype == XNQ_Q8_0) swiglu_kernel<XNQ_Q8_0><<<grid, 256, 0, s>>>(gate_up, out, act_image, rows, (int)f);
+  else swiglu_kernel<XNQ_Q8K><<<grid, 256, 0, s>>>(gate_up, out, act_image, rows, (int)f);
   XNQ_CUDA(cudaGetLastError());
   count_launch();
   return XNQ_OK;

@@ -539,7 +539,20 @@ matvec_tma_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtype
   int8_t *sq = reinterpret_cast<int8_t *>(smem + ring.act_off);
   float *sd = reinterpret_cast<float *>(sq + k);
   int16_t *sb = reinterpret_cast<int16_t *>(reinterpret_cast<unsigned char *>(sd) + ((k / (ACT == XNQ_Q8_0 ? QK : QK_K) * 4 + 15) & ~15));
-  quantize_row_to_smem<ACT>(x, x_dtype, k, sq, sd, sb, late_prefetch, tr ? &g_matvec_trace[trace_slot][tb] : nullptr);
+  if (x_dtype == XNQ_ACT_IMAGE) {
+    // activations quantized ahead of the call: copy the row's image (codes | block scales | 16-sums, each
+    // section 256-byte aligned) instead of quantizing
+    const unsigned char *img = static_cast<const unsigned char *>(x);
+    const int nblk = (int)(k / (ACT == XNQ_Q8_0 ? QK : QK_K));
+    const unsigned char *img_d = img + ((k + 255) & ~(int64_t)255);
+    const unsigned char *img_b = img_d + (((int64_t)nblk * 4 + 255) & ~(int64_t)255);
+    for (int i = threadIdx.x; i < k / 16; i += CW * 32) reinterpret_cast<uint4 *>(sq)[i] = reinterpret_cast<const uint4 *>(img)[i];
+    for (int i = threadIdx.x; i < nblk; i += CW * 32) sd[i] = reinterpret_cast<const float *>(img_d)[i];
+    for (int i = threadIdx.x; i < k / 32; i += CW * 32) reinterpret_cast<uint32_t *>(sb)[i] = reinterpret_cast<const uint32_t *>(img_b)[i];
+    if (late_prefetch) asm volatile("bar.arrive 2, %0;" ::"n"(NTHREADS) : "memory");
+  } else {
+    quantize_row_to_smem<ACT>(x, x_dtype, k, sq, sd, sb, late_prefetch, tr ? &g_matvec_trace[trace_slot][tb] : nullptr);
+  }
   if (tr && threadIdx.x == 0) g_matvec_trace[trace_slot][tb + 6] = gtime();
   consumer_sync();
   if (tr && threadIdx.x == 0) g_matvec_trace[trace_slot][tb + 7] = gtime();

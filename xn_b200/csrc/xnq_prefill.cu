@@ -82,6 +82,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
   atomicOr(&g_prefill_status, bit);
   return false;
 }
+// for waits that are long by design (a drain warp waiting out a whole main loop): poll at a low rate so the
+// poller does not take issue slots from the producer warps of its scheduler
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, unsigned int bit) {
+  for (uint32_t i = 0; i < (WAIT_LIMIT >> 4); ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(200);
+  }
+  atomicOr(&g_prefill_status, bit);
+  return false;
+}
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
                "r"(bytes), "r"(bar)
@@ -148,6 +158,12 @@ struct PrefillArgs {
   uint32_t b_stride;      // bytes between B stages (largest mt of the grid x 128, multiple of 1024)
   uint32_t b_off, raw_off; // offsets of the B ring and of the producers' raw rings from the aligned base
   float wscale;           // power of two applied to every dequantized weight
+  // persistent kernel: tile t = tile_n * tiles_m + tile_m; work unit u = t * ksteps + kt; CTA c takes units
+  // [units * c / G, units * (c + 1) / G), or whole tiles when the output cannot be accumulated atomically
+  int tiles_n, tiles_m;
+  long long units;
+  int whole_tiles;
+  unsigned int *tile_cnt; // [tiles] arrival tickets then [tiles] "first partial stored" flags; zeroed by the prepare kernel
   int dbg;                // experiment knobs (0 in production): 1 skip the conversion, 2 skip the raw copies, 4 skip the proxy fence
 };
 
@@ -159,6 +175,31 @@ __device__ __forceinline__ void zero_half_row(uint32_t dst_row, int hf) { // chu
   const int sw = (dst_row >> 7) & 7;
 #pragma unroll
   for (int c = 0; c < 4; c++) sts128(dst_row + (((hf * 4 + c) ^ sw) << 4), 0, 0, 0, 0);
+}
+
+// Writes one 32-column chunk of an accumulator row block: column j of the chunk is activation row
+// m_first + j, this lane's accumulator lane is weight row `row`. MODE: 0 f32 store, 1 f32 atomic add,
+// 2 f16 store, 3 bf16 store.
+template <int MODE>
+__device__ __forceinline__ void drain_chunk(const uint32_t (&v)[32], float ru_lane, void *y, int64_t ldy, int64_t row, int64_t m_first, int64_t m_end,
+                                            bool row_ok) {
+  // a running pointer and one small count: the few warps that drain have nobody to hide instruction latency
+  // behind, so every instruction per column counts
+  const int es = MODE <= 1 ? 4 : 2;
+  char *yp = static_cast<char *>(y) + (m_first * ldy + row) * es;
+  const int64_t step = ldy * es;
+  const int nvalid = row_ok ? (int)min((int64_t)32, m_end - m_first) : 0;
+#pragma unroll
+  for (int j = 0; j < 32; j++) {
+    const float val = __uint_as_float(v[j]) * __shfl_sync(0xffffffffu, ru_lane, j);
+    if (j < nvalid) {
+      if (MODE == 0) *reinterpret_cast<float *>(yp) = val;
+      else if (MODE == 1) atomicAdd(reinterpret_cast<float *>(yp), val);
+      else if (MODE == 2) *reinterpret_cast<__half *>(yp) = __float2half_rn(val);
+      else *reinterpret_cast<__nv_bfloat16 *>(yp) = __float2bfloat16_rn(val);
+    }
+    yp += step;
+  }
 }
 
 template <typename RowT>
@@ -264,20 +305,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) prefill_kernel(PrefillArgs p) {
       for (int c0 = 32 * (warp >> 2); c0 < mt; c0 += 32 * (PRODUCERS / 128)) {
         uint32_t v[32];
         tmem_ld32(lane_addr + c0, v);
+        // one coalesced load of the chunk's 32 row factors, handed round by shuffles (a load per column, each
+        // behind its own bounds check, serialized the drain)
+        const float ru_lane = (m0 + c0 + lane < p.m_pad) ? p.row_unscale[m0 + c0 + lane] : 0.f;
         tmem_ld_wait();
-        if (row_ok) {
-#pragma unroll
-          for (int j = 0; j < 32; j++) {
-            const int64_t mm = m0 + c0 + j;
-            if (mm < p.m) {
-              const float val = __uint_as_float(v[j]) * p.row_unscale[mm];
-              const int64_t idx = mm * p.ldy + row;
-              if (p.y_dtype == XNQ_F32) static_cast<float *>(p.y)[idx] = val;
-              else if (p.y_dtype == XNQ_F16) static_cast<__half *>(p.y)[idx] = __float2half_rn(val);
-              else static_cast<__nv_bfloat16 *>(p.y)[idx] = __float2bfloat16_rn(val);
-            }
-          }
-        }
+        if (p.y_dtype == XNQ_F32) drain_chunk<0>(v, ru_lane, p.y, p.ldy, row, m0 + c0, p.m, row_ok);
+        else if (p.y_dtype == XNQ_F16) drain_chunk<2>(v, ru_lane, p.y, p.ldy, row, m0 + c0, p.m, row_ok);
+        else drain_chunk<3>(v, ru_lane, p.y, p.ldy, row, m0 + c0, p.m, row_ok);
       }
     }
   } else if (warp == LOADER_WARP) {
@@ -353,6 +387,299 @@ __global__ void __launch_bounds__(NTHREADS, 1) prefill_kernel(PrefillArgs p) {
   if (warp == LOADER_WARP) tmem_dealloc(tmem_d, MAX_MT);
 }
 
+// ---- persistent variant -------------------------------------------------------------------------------------
+// One CTA per SM walks a contiguous range of the flattened (tile, k-step) space, so all SMs finish
+// together whatever the tile count, and a tile whose k-steps are split between CTAs is summed in
+// global memory: the first CTA to finish its part stores it and raises the tile's flag, the others add
+// theirs atomically after seeing the flag (two to three parts per split tile; f32 output only - other
+// output types get whole tiles). The accumulator is double-buffered in tensor memory (2 x 256 columns)
+// and drained by four dedicated warps, so the drain of one segment overlaps the MMAs of the next.
+// Operand rings, barriers and producer roles are those of prefill_kernel, with stage counters that run
+// on across segments.
+constexpr int EPI_WARPS = 8; // two per accumulator lane quarter, splitting the columns
+constexpr int EPI_WARP0 = MMA_WARP + 1;
+constexpr int NTHREADS_SK = NTHREADS + EPI_WARPS * 32;
+
+struct Cursor { // position in the flattened (tile, k-step) space; tile = tile_n * tiles_m + tile_m
+  int tile_n, tile_m, kt;
+  __device__ __forceinline__ void advance(int steps, int KT, int tiles_m) {
+    kt += steps;
+    while (kt >= KT) {
+      kt -= KT;
+      if (++tile_m == tiles_m) {
+        tile_m = 0;
+        tile_n++;
+      }
+    }
+  }
+  __device__ __forceinline__ int tile(int tiles_m) const { return tile_n * tiles_m + tile_m; }
+};
+
+template <typename RowT>
+__global__ void __launch_bounds__(NTHREADS_SK, 1) prefill_persistent_kernel(PrefillArgs p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  __shared__ __align__(8) uint64_t bars[4 * 8 + 4]; // a_full, a_empty, b_full, b_empty (8 each), acc_full[2], acc_empty[2]
+  __shared__ uint32_t tmem_slot;
+  __shared__ unsigned int s_ticket;
+  const int S = p.nstages;
+  const int SB = p.b_stages;
+  const uint32_t a_full = smem_u32(bars), a_empty = a_full + 64, b_full = a_full + 128, b_empty = a_full + 192, acc_full = a_full + 256,
+                 acc_empty = a_full + 272;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t a_ring = smem_base, b_ring = smem_base + p.b_off;
+  const int KT = p.ksteps;
+
+  // this CTA's range of work units
+  long long u0, u1;
+  if (p.whole_tiles) {
+    const long long T = (long long)p.tiles_n * p.tiles_m;
+    u0 = (T * blockIdx.x / gridDim.x) * KT;
+    u1 = (T * (blockIdx.x + 1) / gridDim.x) * KT;
+  } else {
+    u0 = p.units * blockIdx.x / gridDim.x;
+    u1 = p.units * (blockIdx.x + 1) / gridDim.x;
+  }
+  const int nsteps = (int)(u1 - u0);
+  const int TM = p.tiles_m;
+  const Cursor start{(int)((u0 / KT) / TM), (int)((u0 / KT) % TM), (int)(u0 % KT)};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; s++) {
+      mbar_init(a_full + 8 * s, GROUP / 32);
+      mbar_init(a_empty + 8 * s, 1);
+    }
+    for (int s = 0; s < SB; s++) {
+      mbar_init(b_full + 8 * s, 1);
+      mbar_init(b_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(acc_full + 8 * b, 1);
+      mbar_init(acc_empty + 8 * b, EPI_WARPS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == LOADER_WARP) {
+    tmem_alloc(smem_u32(&tmem_slot), 2 * MAX_MT);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_d = tmem_slot;
+  const bool trace = (p.dbg & 32) && blockIdx.x == 0;
+  unsigned long long t_begin = 0;
+  if (trace) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_begin));
+#define XNQ_NOW(dst) do { unsigned long long t_; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_)); dst = t_ - t_begin; } while (0)
+
+  if (warp < PRODUCERS / 32) {
+    // ---- producers: group g takes this CTA's steps g, g+2, ... -------------------------------------------
+    const int grp = threadIdx.x / GROUP, tg = threadIdx.x % GROUP;
+    const int r = tg & (TILE_N - 1), hf = tg >> 7;
+    const int sw = r & 7;
+    const uint32_t raw_base = smem_base + p.raw_off;
+    Cursor cur = start, pre = start;
+    cur.advance(grp, KT, TM);
+    pre.advance(grp, KT, TM);
+#pragma unroll
+    for (int j = 0; j < RAW_DEPTH; j++) {
+      if (grp + 2 * j < nsteps) {
+        const int64_t row = (int64_t)pre.tile_n * TILE_N + r;
+        RowT::issue(p.w, row < p.w.n ? row : p.w.n - 1, pre.kt, hf, raw_base + (j * PRODUCERS + threadIdx.x) * RowT::SLOT);
+        pre.advance(2, KT, TM);
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    int rs = 0;
+    bool alive = true;
+    for (int i = grp; i < nsteps && alive; i += 2) {
+      const int s = i % S;
+      const uint32_t round = (uint32_t)(i / S);
+      const uint32_t slot = raw_base + (rs * PRODUCERS + threadIdx.x) * RowT::SLOT;
+      asm volatile("cp.async.wait_group %0;" ::"n"(RAW_DEPTH - 1) : "memory");
+      if (i >= S) {
+        int ok = 1;
+        if (lane == 0) ok = mbar_wait(a_empty + 8 * s, (round - 1) & 1, 1u) ? 1 : 0;
+        __syncwarp();
+        alive = __shfl_sync(0xffffffffu, ok, 0) != 0;
+      }
+      if (!alive) break;
+      const int64_t row = (int64_t)cur.tile_n * TILE_N + r;
+      const uint32_t dst_row = a_ring + s * A_STAGE_BYTES + r * 128;
+      if (row < p.w.n) RowT::store(p.w, slot, cur.kt, hf, p.wscale, dst_row, sw);
+      else zero_half_row(dst_row, hf);
+      if (i + 2 * RAW_DEPTH < nsteps) {
+        const int64_t prow = (int64_t)pre.tile_n * TILE_N + r;
+        RowT::issue(p.w, prow < p.w.n ? prow : p.w.n - 1, pre.kt, hf, slot);
+        pre.advance(2, KT, TM);
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(a_full + 8 * s);
+      rs = (rs + 1 == RAW_DEPTH) ? 0 : rs + 1;
+      cur.advance(2, KT, TM);
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  } else if (warp == LOADER_WARP) {
+    // ---- activation loader ------------------------------------------------------------------------------
+    if (lane == 0) {
+      Cursor cur = start;
+      int issued = 0;
+      for (int i = 0; i < nsteps; i++) {
+        const int s = i % SB;
+        const uint32_t round = (uint32_t)(i / SB);
+        if (round > 0 && !mbar_wait(b_empty + 8 * s, (round - 1) & 1, 2u)) break;
+        const int64_t m0 = (int64_t)cur.tile_m * MAX_MT;
+        const uint32_t bytes = (uint32_t)min((int64_t)MAX_MT, p.m_pad - m0) * 128;
+        mbar_expect_tx(b_full + 8 * s, bytes);
+        bulk_g2s(b_ring + s * p.b_stride, p.xh + ((size_t)cur.kt * p.m_pad + m0) * 128, bytes, b_full + 8 * s);
+        issued = i + 1;
+        cur.advance(1, KT, TM);
+      }
+      for (int i = max(0, issued - SB); i < issued; i++) mbar_wait(b_full + 8 * (i % SB), (i / SB) & 1, 2u); // nothing in flight at exit
+    }
+  } else if (warp == MMA_WARP) {
+    // ---- MMA issuer -------------------------------------------------------------------------------------
+    if (lane == 0) {
+      Cursor cur = start;
+      bool alive = true, a_ready = false, b_ready = false;
+      int i = 0, s = 0, sb = 0;
+      uint32_t round = 0, bround = 0;
+      for (int seg = 0; i < nsteps && alive; seg++) {
+        const int len = min(KT - cur.kt, nsteps - i);
+        const int buf = seg & 1, use = seg >> 1;
+        if (use > 0) alive = mbar_wait(acc_empty + 8 * buf, (use - 1) & 1, 4u); // the drain of this buffer's previous segment
+        if (!alive) break;
+        tc_fence_after();
+        const int64_t m0 = (int64_t)cur.tile_m * MAX_MT;
+        const uint32_t idesc = idesc_f16((int)min((int64_t)MAX_MT, p.m_pad - m0));
+        const uint32_t d = tmem_d + (uint32_t)(buf * MAX_MT);
+        for (int j = 0; j < len && alive; j++, i++) {
+          if (!a_ready) alive = mbar_wait(a_full + 8 * s, round & 1, 4u);
+          if (alive && !b_ready) alive = mbar_wait(b_full + 8 * sb, bround & 1, 4u);
+          if (!alive) break;
+          tc_fence_after();
+          const uint64_t adesc = smem_desc_sw128(a_ring + s * A_STAGE_BYTES);
+          const uint64_t bdesc = smem_desc_sw128(b_ring + sb * p.b_stride);
+          const int cs = s, csb = sb;
+          if (++s == S) {
+            s = 0;
+            round++;
+          }
+          if (++sb == SB) {
+            sb = 0;
+            bround++;
+          }
+          // probe the next step's barriers now: the test's latency hides behind the issue of this step's MMAs
+          a_ready = i + 1 < nsteps && mbar_try_wait(a_full + 8 * s, round & 1);
+          b_ready = i + 1 < nsteps && mbar_try_wait(b_full + 8 * sb, bround & 1);
+#pragma unroll
+          for (int ks = 0; ks < BK / 16; ks++) umma_f16(d, adesc + (uint64_t)(ks * 2), bdesc + (uint64_t)(ks * 2), idesc, (j | ks) ? 1u : 0u);
+          umma_commit(a_empty + 8 * cs);
+          umma_commit(b_empty + 8 * csb);
+          if (trace && i == 0) XNQ_NOW(g_prefill_trace[0]); // first MMAs issued
+        }
+        if (alive) umma_commit(acc_full + 8 * buf);
+        cur.advance(len, KT, TM);
+      }
+      if (trace) {
+        XNQ_NOW(g_prefill_trace[1]); // last MMAs issued
+        g_prefill_trace[2] = (unsigned long long)nsteps;
+      }
+    }
+  } else {
+    // ---- drain: four warps, warp q reads accumulator lanes 32q.. (weight rows), all columns -----------------
+    const int q = warp & 3; // tensor-memory lanes a warp may read are fixed by its index modulo 4
+    const int half = (warp - EPI_WARP0) >> 2; // which half of the 32-column chunks this warp takes
+    const int et = threadIdx.x - EPI_WARP0 * 32; // 0..127
+    Cursor cur = start;
+    bool alive = true;
+    int i = 0;
+    for (int seg = 0; i < nsteps && alive; seg++) {
+      const int len = min(KT - cur.kt, nsteps - i);
+      const bool whole = cur.kt == 0 && len == KT;
+      const int buf = seg & 1, use = seg >> 1;
+      const int tile_n = cur.tile_n, tile_m = cur.tile_m, tile = cur.tile(TM);
+      const int64_t row = (int64_t)tile_n * TILE_N + 32 * q + lane;
+      const int64_t m0 = (int64_t)tile_m * MAX_MT;
+      const int mt = (int)min((int64_t)MAX_MT, p.m_pad - m0);
+      // one thread waits for the accumulator and, for a tile shared with other CTAs, settles who stores and
+      // who adds; the four warps then act on the same answers
+      if (et == 0) {
+        unsigned int t = mbar_wait_relaxed(acc_full + 8 * buf, use & 1, 8u) ? 0u : 0x80000000u;
+        if (!whole && t == 0) {
+          t = atomicAdd(p.tile_cnt + tile, 1u);
+          if (t > 0) { // wait (bounded) until the first finisher's stores are visible
+            const unsigned int *flag = p.tile_cnt + (size_t)p.tiles_n * p.tiles_m + tile;
+            uint32_t spins = 0;
+            unsigned int v = 0;
+            do {
+              asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+            } while (v == 0 && ++spins < WAIT_LIMIT);
+            if (v == 0) {
+              atomicOr(&g_prefill_status, 8u);
+              t = 0x80000000u;
+            }
+          }
+        }
+        s_ticket = t;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+      const unsigned int ticket = s_ticket & 0x7fffffffu;
+      alive = (s_ticket & 0x80000000u) == 0;
+      asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory"); // s_ticket may be rewritten from here on
+      if (trace && et == 0 && seg < 3) XNQ_NOW(g_prefill_trace[4 + 2 * seg]); // accumulator (and ticket) ready
+      if (alive) {
+        tc_fence_after();
+        const uint32_t lane_addr = tmem_d + (uint32_t)(buf * MAX_MT) + ((uint32_t)(32 * q) << 16);
+        for (int c0 = 32 * half; c0 < mt; c0 += 32 * (EPI_WARPS / 4)) {
+          uint32_t v[32];
+          unsigned long long tq0 = 0, tq1 = 0;
+          if (trace && et == 0) XNQ_NOW(tq0);
+          tmem_ld32(lane_addr + c0, v);
+          const float ru_lane = (m0 + c0 + lane < p.m_pad) ? p.row_unscale[m0 + c0 + lane] : 0.f; // the chunk's 32 row factors
+          tmem_ld_wait();
+          if (trace && et == 0) {
+            XNQ_NOW(tq1);
+            g_prefill_trace[12] += tq1 - tq0;
+            g_prefill_trace[13] += 1;
+          }
+          const bool row_ok = row < p.w.n && !(p.dbg & 128);
+          if (p.y_dtype == XNQ_F32) {
+            if (ticket == 0) drain_chunk<0>(v, ru_lane, p.y, p.ldy, row, m0 + c0, p.m, row_ok);
+            else drain_chunk<1>(v, ru_lane, p.y, p.ldy, row, m0 + c0, p.m, row_ok);
+          } else if (p.y_dtype == XNQ_F16) {
+            drain_chunk<2>(v, ru_lane, p.y, p.ldy, row, m0 + c0, p.m, row_ok);
+          } else {
+            drain_chunk<3>(v, ru_lane, p.y, p.ldy, row, m0 + c0, p.m, row_ok);
+          }
+        }
+        tc_fence_before();
+      }
+      __syncwarp();
+      if (trace && et == 0 && seg < 3) XNQ_NOW(g_prefill_trace[5 + 2 * seg]); // drained
+      if (lane == 0) mbar_arrive(acc_empty + 8 * buf); // this warp has read its lanes: the buffer may be overwritten
+      if (!whole && alive) {
+        if (ticket == 0) __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+        if (ticket == 0 && et == 0) {
+          unsigned int *flag = p.tile_cnt + (size_t)p.tiles_n * p.tiles_m + tile;
+          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(1u) : "memory");
+        }
+      }
+      i += len;
+      cur.advance(len, KT, TM);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (trace && threadIdx.x == 0) XNQ_NOW(g_prefill_trace[3]); // all roles done
+#undef XNQ_NOW
+  if (warp == LOADER_WARP) tmem_dealloc(tmem_d, 2 * MAX_MT);
+}
+
 // ---- activation image -----------------------------------------------------------------------------------
 // position of source element e (0..63) of a k-step inside the stored k-step, per weight format
 __device__ __forceinline__ int kpos_q4_0(int e) { // stored chunk (b*4 + wi) holds [j, j+2, j+16, j+18, j+1, j+3, j+17, j+19] + 32b, j = 4wi
@@ -370,9 +697,12 @@ __device__ __forceinline__ int kpos_q4k(int e) { // stored chunk wi holds [l, l+
 // by a power of two so its largest magnitude lands in [2^11, 2^12), store fp16 into the swizzled image.
 template <int ACT, typename XT>
 __global__ void __launch_bounds__(256) prefill_prepare_acts(const XT *__restrict__ x, int64_t m, int64_t k, int64_t ldx, int64_t m_pad, int ksteps,
-                                                            int wdtype, float wscale, uint8_t *__restrict__ xh, float *__restrict__ row_unscale) {
+                                                            int wdtype, float wscale, uint8_t *__restrict__ xh, float *__restrict__ row_unscale,
+                                                            unsigned int *__restrict__ tile_cnt, int tile_words) {
   __shared__ float red[8];
   const int64_t row = blockIdx.x;
+  if (blockIdx.x == 0) // the persistent kernel's per-tile tickets and flags start every call at zero
+    for (int i = threadIdx.x; i < tile_words; i += blockDim.x) tile_cnt[i] = 0;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t per_row = (int64_t)ksteps * 8; // 8-element groups in the padded row
   __half *img = reinterpret_cast<__half *>(xh);
@@ -437,6 +767,7 @@ __global__ void __launch_bounds__(256) prefill_prepare_acts(const XT *__restrict
 
 int g_num_sms = 0;
 int g_prefill_dbg = 0;
+int g_prefill_persistent = 1; // 0: one CTA per tile (prefill_kernel)
 
 template <typename RowT>
 int launch_prefill_fmt(const PrefillArgs &a, dim3 grid, size_t smem, cudaStream_t s) {
@@ -446,14 +777,27 @@ int launch_prefill_fmt(const PrefillArgs &a, dim3 grid, size_t smem, cudaStream_
   return XNQ_OK;
 }
 
+template <typename RowT>
+int launch_persistent_fmt(const PrefillArgs &a, unsigned ctas, size_t smem, cudaStream_t s) {
+  prefill_persistent_kernel<RowT><<<ctas, NTHREADS_SK, smem, s>>>(a);
+  XNQ_CUDA(cudaGetLastError());
+  count_launch();
+  return XNQ_OK;
+}
+
 constexpr size_t PREFILL_SMEM = 226 * 1024; // everything an SM offers minus the static barriers and a reserve
 
 } // namespace
 
-size_t prefill_workspace_bytes(int64_t m, int64_t k) {
+static size_t tile_words(int64_t m_pad, int64_t n) { // tickets + flags of the persistent kernel
+  const size_t tiles = (size_t)((n + TILE_N - 1) / TILE_N) * (size_t)((m_pad + MAX_MT - 1) / MAX_MT);
+  return (2 * tiles * 4 + 255) & ~(size_t)255;
+}
+
+size_t prefill_workspace_bytes(int64_t m, int64_t k, int64_t n) {
   const int64_t m_pad = (m + 15) / 16 * 16;
   const int64_t ksteps = (k + BK - 1) / BK;
-  return (size_t)ksteps * m_pad * 128 + (((size_t)m_pad * 4 + 255) & ~(size_t)255) + 256;
+  return (size_t)ksteps * m_pad * 128 + (((size_t)m_pad * 4 + 255) & ~(size_t)255) + tile_words(m_pad, n) + 256;
 }
 
 int launch_prefill(const WeightView &w, float wscale, const void *x, int x_dtype, int64_t m, int64_t ldx, void *y, int y_dtype, int64_t ldy,
@@ -462,11 +806,13 @@ int launch_prefill(const WeightView &w, float wscale, const void *x, int x_dtype
   const int64_t m_pad = (m + 15) / 16 * 16;
   const int ksteps = (int)((k + BK - 1) / BK);
   float *row_unscale = static_cast<float *>(workspace);
-  uint8_t *xh = static_cast<uint8_t *>(workspace) + ((((size_t)m_pad * 4 + 255) & ~(size_t)255));
+  unsigned int *tile_cnt = reinterpret_cast<unsigned int *>(static_cast<uint8_t *>(workspace) + ((((size_t)m_pad * 4 + 255) & ~(size_t)255)));
+  const size_t cnt_bytes = tile_words(m_pad, w.n);
+  uint8_t *xh = reinterpret_cast<uint8_t *>(tile_cnt) + cnt_bytes;
   const int act = act_dtype_for(w.dtype);
 #define XNQ_PREP(ACT, XT)                                                                                                   \
   prefill_prepare_acts<ACT, XT><<<(unsigned)m_pad, 256, 0, s>>>(static_cast<const XT *>(x), m, k, ldx, m_pad, ksteps, w.dtype, wscale, xh, \
-                                                                row_unscale)
+                                                                row_unscale, tile_cnt, (int)(cnt_bytes / 4))
   if (act == XNQ_Q8_0) {
     if (x_dtype == XNQ_F32) XNQ_PREP(XNQ_Q8_0, float);
     else if (x_dtype == XNQ_F16) XNQ_PREP(XNQ_Q8_0, __half);
@@ -504,8 +850,27 @@ int launch_prefill(const WeightView &w, float wscale, const void *x, int x_dtype
   a.wscale = wscale;
   a.dbg = g_prefill_dbg;
   const dim3 grid((unsigned)((w.n + TILE_N - 1) / TILE_N), (unsigned)((m_pad + MAX_MT - 1) / MAX_MT));
+  a.tiles_n = (int)grid.x;
+  a.tiles_m = (int)grid.y;
+  a.units = (long long)grid.x * grid.y * ksteps;
+  a.whole_tiles = (y_dtype == XNQ_F32 && !(g_prefill_dbg & 64)) ? 0 : 1;
+  a.tile_cnt = tile_cnt;
   profile_mark(s, true);
   int rc;
+  if (g_prefill_persistent) {
+    const long long tiles = (long long)grid.x * grid.y;
+    const long long want = a.whole_tiles ? tiles : std::max<long long>(1, a.units / 8); // at least 8 k-steps per CTA
+    const unsigned ctas = (unsigned)std::min<long long>(g_num_sms, want);
+    switch (w.dtype) {
+      case XNQ_Q4_0: rc = launch_persistent_fmt<RowQ4_0>(a, ctas, PREFILL_SMEM, s); break;
+      case XNQ_Q8_0: rc = launch_persistent_fmt<RowQ8_0>(a, ctas, PREFILL_SMEM, s); break;
+      case XNQ_Q4K: rc = launch_persistent_fmt<RowQ4K>(a, ctas, PREFILL_SMEM, s); break;
+      case XNQ_Q6K: rc = launch_persistent_fmt<RowQ6K>(a, ctas, PREFILL_SMEM, s); break;
+      default: rc = fail(XNQ_ERR_DTYPE, "prefill: dtype %d", w.dtype);
+    }
+    profile_mark(s, false);
+    return rc;
+  }
   switch (w.dtype) {
     case XNQ_Q4_0: rc = launch_prefill_fmt<RowQ4_0>(a, grid, PREFILL_SMEM, s); break;
     case XNQ_Q8_0: rc = launch_prefill_fmt<RowQ8_0>(a, grid, PREFILL_SMEM, s); break;
@@ -525,12 +890,17 @@ int prefill_init(int device) {
   XNQ_CUDA(cudaFuncSetAttribute(prefill_kernel<RowQ8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PREFILL_SMEM));
   XNQ_CUDA(cudaFuncSetAttribute(prefill_kernel<RowQ4K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PREFILL_SMEM));
   XNQ_CUDA(cudaFuncSetAttribute(prefill_kernel<RowQ6K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PREFILL_SMEM));
+  XNQ_CUDA(cudaFuncSetAttribute(prefill_persistent_kernel<RowQ4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PREFILL_SMEM));
+  XNQ_CUDA(cudaFuncSetAttribute(prefill_persistent_kernel<RowQ8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PREFILL_SMEM));
+  XNQ_CUDA(cudaFuncSetAttribute(prefill_persistent_kernel<RowQ4K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PREFILL_SMEM));
+  XNQ_CUDA(cudaFuncSetAttribute(prefill_persistent_kernel<RowQ6K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PREFILL_SMEM));
   unsigned int zero = 0;
   XNQ_CUDA(cudaMemcpyToSymbol(g_prefill_status, &zero, sizeof(zero)));
   return XNQ_OK;
 }
 
 void prefill_set_dbg(int v) { g_prefill_dbg = v; }
+void prefill_set_persistent(int v) { g_prefill_persistent = v; }
 int prefill_trace(unsigned long long out[16]) {
   XNQ_CUDA(cudaMemcpyFromSymbol(out, g_prefill_trace, sizeof(unsigned long long) * 16));
   return XNQ_OK;

@@ -9,7 +9,48 @@ from typing import Optional
 import torch
 
 from . import _lib
+from .dtypes import GgmlDType
 from .quantized import _stream_ptr
+
+
+class ActImage:
+    """Activations quantized ahead of the matmul: ``m`` rows of ``k`` values as Q8_0 or Q8_K codes, block scales
+    and 16-element sums in the planar layout the decode kernels read (``xnq_act_image_bytes``). Written by
+    ``add_rmsnorm`` / ``swiglu`` / ``quantize_act_image``, read by ``QCudaTensor.matmul_t``."""
+
+    def __init__(self, act_dtype: GgmlDType, m: int, k: int, device: torch.device):
+        self.act_dtype, self.m, self.k, self.device = GgmlDType(act_dtype), m, k, device
+        nbytes = int(_lib.lib().xnq_act_image_bytes(int(self.act_dtype), m, k))
+        if nbytes == 0:
+            raise ValueError(f"no activation image for {self.act_dtype.name} [{m}, {k}]")
+        self.buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+
+    @classmethod
+    def for_weight(cls, weight_dtype: GgmlDType, m: int, k: int, device: torch.device) -> "ActImage":
+        return cls(GgmlDType(weight_dtype).vec_dot_type, m, k, device)
+
+    def data_ptr(self) -> int:
+        return self.buf.data_ptr()
+
+
+def quantize_act_image(x: torch.Tensor, image: ActImage) -> ActImage:
+    """Quantize ``x [m, k]`` (f32 / f16 / bf16, contiguous rows) into ``image``."""
+    from .quantized import _TORCH_TO_XNQ
+    m, k = x.shape
+    if (m, k) != (image.m, image.k) or x.stride(-1) != 1:
+        raise ValueError(f"image is [{image.m}, {image.k}], x is {tuple(x.shape)}")
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().xnq_quantize_act_image(int(image.act_dtype), _p(x), int(_TORCH_TO_XNQ[x.dtype]), m, k, x.stride(0) if m > 1 else k,
+                                                     ctypes.c_void_p(image.data_ptr()), _stream_ptr(x.device)))
+    return image
+
+
+def _img(image: Optional[ActImage], rows: int, k: int):
+    if image is None:
+        return None, 0
+    if (image.m, image.k) != (rows, k):
+        raise ValueError(f"image is [{image.m}, {image.k}], rows are [{rows}, {k}]")
+    return ctypes.c_void_p(image.data_ptr()), int(image.act_dtype)
 
 
 def _p(t: Optional[torch.Tensor]):
@@ -22,23 +63,27 @@ def _f32c(*ts):
             raise ValueError("expected contiguous float32 tensors")
 
 
-def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float, out: Optional[torch.Tensor] = None,
+                image: Optional[ActImage] = None) -> Optional[torch.Tensor]:
     """In place ``x += delta`` (skipped when ``delta`` is None), then ``out = rmsnorm(x) * weight``; ``x`` is ``[rows, d]``.
-    ``delta`` may be ``[rows, parts * d]``: its ``parts`` summands per row are all added."""
+    ``delta`` may be ``[rows, parts * d]``: its ``parts`` summands per row are all added. ``image`` also receives the
+    quantized form of the normalized rows (the bytes quantizing ``out`` would give)."""
     _f32c(x, delta, weight, out)
     rows, d = x.shape
     parts = 1 if delta is None else delta.numel() // (rows * d)
+    ip, idt = _img(image, rows, d)
     with torch.cuda.device(x.device):
-        _lib.check(_lib.lib().xnq_add_rmsnorm(_p(x), _p(delta), parts, _p(weight), eps, _p(out), rows, d, _stream_ptr(x.device)))
+        _lib.check(_lib.lib().xnq_add_rmsnorm(_p(x), _p(delta), parts, _p(weight), eps, _p(out), ip, idt, rows, d, _stream_ptr(x.device)))
     return out
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """``out[rows, f] = silu(gate_up[:, :f]) * gate_up[:, f:]``."""
+def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, image: Optional[ActImage] = None) -> Optional[torch.Tensor]:
+    """``out[rows, f] = silu(gate_up[:, :f]) * gate_up[:, f:]``, optionally with its quantized image."""
     _f32c(gate_up, out)
     rows, f2 = gate_up.shape
-    with torch.cuda.device(out.device):
-        _lib.check(_lib.lib().xnq_swiglu(_p(gate_up), _p(out), rows, f2 // 2, _stream_ptr(out.device)))
+    ip, idt = _img(image, rows, f2 // 2)
+    with torch.cuda.device(gate_up.device):
+        _lib.check(_lib.lib().xnq_swiglu(_p(gate_up), _p(out), ip, idt, rows, f2 // 2, _stream_ptr(gate_up.device)))
     return out
 
 

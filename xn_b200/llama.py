@@ -139,6 +139,11 @@ class QLlama:
         self._h = torch.zeros((batch, c.ffn // G), **f32)
         self._o = torch.zeros((batch, c.d_model), **f32)
         self._dn = torch.zeros((batch, c.d_model), **f32)
+        # the norm's and the SwiGLU's outputs are only ever read by quantized linears: they are written as
+        # activation images (quantized once, by their producer) instead of f32 rows
+        self._xn_img = ops.ActImage.for_weight(c.linear_dtype, batch, c.d_model, device) if batch <= 16 else None
+        self._h_img = ops.ActImage.for_weight(c.linear_dtype, batch, c.ffn // G, device) if batch <= 16 and (c.ffn // G) % 256 == 0 else None
+        self._head_img = self._xn_img if c.head_dtype.vec_dot_type == c.linear_dtype.vec_dot_type else None
         for L in self.layers:   # scratch is sized once, before any capture
             for w in (L.wqkv, L.wo, L.wgu, L.wdown):
                 w.workspace(max(batch, max_prefill_rows))
@@ -228,18 +233,20 @@ class QLlama:
         self._gather_idx = 0
         self._x.copy_(self.embed.index_select(0, self.tokens))
         delta = None
+        xi, hi = self._xn_img, self._h_img
         for L in self.layers:
-            ops.add_rmsnorm(self._x, delta, L.norm1, c.rms_eps, self._xn)
-            L.wqkv.matmul_t(self._xn, out=self._qkv)
+            ops.add_rmsnorm(self._x, delta, L.norm1, c.rms_eps, None if xi else self._xn, xi)
+            L.wqkv.matmul_t(xi or self._xn, out=self._qkv)
             ops.rope_kv_store(self._qkv, self.cos, self.sin, self.pos, self._q, L.k_cache, L.v_cache, self.hl, self.kvl)
             ops.attn_decode(self._q, L.k_cache, L.v_cache, self.pos, self._a.view(self.batch, self.hl, c.head_dim), self.hl, self.kvl)
             o = self._linear_parts(L.wo, self._a, self._o)           # world summands per row when sharded
-            ops.add_rmsnorm(self._x, o, L.norm2, c.rms_eps, self._xn)
-            L.wgu.matmul_t(self._xn, out=self._gu)
-            ops.swiglu(self._gu, self._h)
-            delta = self._linear_parts(L.wdown, self._h, self._dn)
-        ops.add_rmsnorm(self._x, delta, self.norm, c.rms_eps, self._xn)
-        logits = self._linear_gathered(self.lm_head, self._xn)
+            ops.add_rmsnorm(self._x, o, L.norm2, c.rms_eps, None if xi else self._xn, xi)
+            L.wgu.matmul_t(xi or self._xn, out=self._gu)
+            ops.swiglu(self._gu, None if hi else self._h, hi)
+            delta = self._linear_parts(L.wdown, hi or self._h, self._dn)
+        fi = self._head_img
+        ops.add_rmsnorm(self._x, delta, self.norm, c.rms_eps, None if fi else self._xn, fi)
+        logits = self._linear_gathered(self.lm_head, fi or self._xn)
         return logits if self.pg is None else logits.clone()
 
     # -- public ----------------------------------------------------------------------------------

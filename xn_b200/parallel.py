@@ -111,25 +111,31 @@ class PeerGather:
 
         from . import _lib
         from .quantized import _TORCH_TO_XNQ, _stream_ptr
-        if lhs.shape[-1] != w.k:
-            raise ValueError(f"cuda quantized matmul: input {tuple(lhs.shape)} does not match weight (n={w.n}, k={w.k})")
-        x = lhs.reshape(-1, w.k)
-        if x.stride(-1) != 1 or (x.shape[0] > 1 and x.stride(0) < w.k):
-            x = x.contiguous()
-        m = x.shape[0]
-        ydt = lhs.dtype if lhs.dtype in _TYPESTR else torch.float32
+        image = hasattr(lhs, "act_dtype")   # an ActImage: activations quantized ahead of the call
+        if (lhs.k if image else lhs.shape[-1]) != w.k:
+            raise ValueError(f"cuda quantized matmul: input does not match weight (n={w.n}, k={w.k})")
+        if image:
+            x, m, xdt, ldx, ydt, lead = lhs, lhs.m, _lib.XNQ_ACT_IMAGE, 0, torch.float32, (lhs.m,)
+        else:
+            x = lhs.reshape(-1, w.k)
+            if x.stride(-1) != 1 or (x.shape[0] > 1 and x.stride(0) < w.k):
+                x = x.contiguous()
+            m = x.shape[0]
+            xdt, ldx = int(_TORCH_TO_XNQ[x.dtype]), (x.stride(0) if m > 1 else w.k)
+            ydt = lhs.dtype if lhs.dtype in _TYPESTR else torch.float32
+            lead = lhs.shape[:-1]
         slot = self.next_slot() if slot is None else slot
         ws = w.workspace(m)
         out = ctypes.c_void_p()
         with torch.cuda.device(self.device):
-            _lib.check(self._L.xnq_matmul_t_gather(w._h, self._h, slot, 1 if parts else 0, ctypes.c_void_p(x.data_ptr()), int(_TORCH_TO_XNQ[x.dtype]), m,
-                                                  x.stride(0) if m > 1 else w.k, int(_TORCH_TO_XNQ[ydt]), ctypes.c_void_p(ws.data_ptr()),
-                                                  ws.numel(), _stream_ptr(self.device), ctypes.byref(out)))
+            _lib.check(self._L.xnq_matmul_t_gather(w._h, self._h, slot, 1 if parts else 0, ctypes.c_void_p(x.data_ptr()), xdt, m, ldx,
+                                                  int(_TORCH_TO_XNQ[ydt]), ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(self.device),
+                                                  ctypes.byref(out)))
         nt = w.n * self.world if parts else w.n_total
         y = torch.as_tensor(_DeviceBuffer(out.value, (m, nt), _TYPESTR[ydt]), device=self.device)
         if ydt is torch.bfloat16:
             y = y.view(torch.bfloat16)
-        return y.view(*lhs.shape[:-1], nt)
+        return y.view(*lead, nt)
 
     def gather(self, y_local: torch.Tensor, slot: Optional[int] = None) -> torch.Tensor:
         """All-gather ``(.., n_local)`` blocks that each rank already holds into ``(.., world * n_local)``."""

@@ -200,6 +200,16 @@ class QCudaTensor:
 
     def matmul_t(self, lhs: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``lhs @ self^T`` with ``lhs`` of shape ``(.., k)``; the result is ``(.., n)`` (q8.rs:116-157)."""
+        if hasattr(lhs, "act_dtype"):   # an ActImage: activations quantized ahead of the call
+            if lhs.k != self.k or lhs.act_dtype != self._dtype.vec_dot_type:
+                raise ValueError(f"cuda quantized matmul: image [{lhs.m}, {lhs.k}] {lhs.act_dtype.name} does not fit weight (k={self.k}, {self._dtype.name})")
+            if out is None:
+                out = torch.empty((lhs.m, self.n), dtype=torch.float32, device=self.device)
+            y = out.view(-1, self.n)
+            with torch.cuda.device(self.device):
+                check(_lib.lib().xnq_matmul_t(self._h, ctypes.c_void_p(lhs.data_ptr()), _lib.XNQ_ACT_IMAGE, lhs.m, 0, ctypes.c_void_p(y.data_ptr()),
+                                              int(_TORCH_TO_XNQ[y.dtype]), y.stride(0) if lhs.m > 1 else self.n, None, 0, _stream_ptr(self.device)))
+            return out
         if lhs.shape[-1] != self.k:
             raise ValueError(f"cuda quantized matmul: input {tuple(lhs.shape)} does not match weight (n={self.n}, k={self.k})")
         if lhs.dtype not in _TORCH_TO_XNQ:
