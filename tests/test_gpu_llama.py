@@ -108,3 +108,25 @@ def test_two_rank_tensor_parallel_decoder_equals_one_rank():
         # the K-sharded o / down projections add their summands in another order, and in prefill each shard's fp16
         # operands carry their own power-of-two scale: logits agree to the prefill path's tolerance, tokens exactly
         assert ret[r]["late"] == 0 and ret[r]["rel"] < 3e-2 and ret[r]["same_tokens"], dict(ret)
+
+
+def test_gguf_file_round_trip_through_device_handles(tmp_path):
+    """Write a GGUF file from device weight handles, map it back, upload whole and as two N-shards: the blocks on
+    disk are the canonical ones and the sharded matmuls tile the unsharded result."""
+    import numpy as np
+    from xn_b200 import gguf, quantized as Q, synth
+    from xn_b200.dtypes import GgmlDType as D
+    dev = torch.device("cuda", 0)
+    specs = [("q4k", D.Q4K, 64, 512), ("q6k", D.Q6K, 32, 256), ("q8_0", D.Q8_0, 64, 128), ("q4_0", D.Q4_0, 96, 64)]
+    host = {name: synth.make_weight(dt, n, k, seed=70 + i) for i, (name, dt, n, k) in enumerate(specs)}
+    on_dev = [(name, Q.QCudaTensor.from_qtensor(Q.QTensor(host[name], (n, k), dt), dev)) for name, dt, n, k in specs]
+    path = tmp_path / "w.gguf"
+    with open(path, "wb") as f:
+        gguf.write(f, [("general.architecture", gguf.Value(gguf.STRING, "test"))], on_dev)
+    c = gguf.Content.read(str(path))
+    for name, dt, n, k in specs:
+        assert np.array_equal(c.tensor_bytes(name), np.asarray(host[name]).reshape(-1))
+        x = torch.randn(3, k, device=dev)
+        full = c.upload(name, dev).matmul_t(x)
+        parts = [c.upload(name, dev, r, 2).matmul_t(x) for r in range(2)]
+        assert torch.equal(torch.cat(parts, dim=-1), full)

@@ -139,11 +139,16 @@ class QLlama:
         self._h = torch.zeros((batch, c.ffn // G), **f32)
         self._o = torch.zeros((batch, c.d_model), **f32)
         self._dn = torch.zeros((batch, c.d_model), **f32)
-        # the norm's and the SwiGLU's outputs are only ever read by quantized linears: they are written as
-        # activation images (quantized once, by their producer) instead of f32 rows
-        self._xn_img = ops.ActImage.for_weight(c.linear_dtype, batch, c.d_model, device) if batch <= 16 else None
-        self._h_img = ops.ActImage.for_weight(c.linear_dtype, batch, c.ffn // G, device) if batch <= 16 and (c.ffn // G) % 256 == 0 else None
+        # The norm's and the SwiGLU's outputs are only ever read by quantized linears, so their producers can write
+        # them as activation images (quantized once). That pays wherever the matmul would otherwise launch its own
+        # quantizer kernel: batches above one, and k above 4096. The one-row k <= 4096 decode kernel quantizes in
+        # its prologue, hidden behind its weight prefetch, and is better left alone.
+        def wants_image(k):
+            return batch <= 16 and k % 256 == 0 and (batch > 1 or k > 4096)
+        self._xn_img = ops.ActImage.for_weight(c.linear_dtype, batch, c.d_model, device) if wants_image(c.d_model) else None
+        self._h_img = ops.ActImage.for_weight(c.linear_dtype, batch, c.ffn // G, device) if wants_image(c.ffn // G) else None
         self._head_img = self._xn_img if c.head_dtype.vec_dot_type == c.linear_dtype.vec_dot_type else None
+
         for L in self.layers:   # scratch is sized once, before any capture
             for w in (L.wqkv, L.wo, L.wgu, L.wdown):
                 w.workspace(max(batch, max_prefill_rows))
