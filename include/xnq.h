@@ -246,7 +246,8 @@ int xnq_device_status(unsigned int *bits);
  * bytes, limit (two spare words). Synchronizes the device. No counterpart in the reference. */
 int xnq_device_check_record(unsigned long long out[8]);
 /* Tuning switches, for A/B measurements: "matvec_tma" (default 1) selects the persistent TMA-ring
- * decode kernel for m == 1, k <= 4096; 0 forces the plain streaming-load kernel. "gather_cta_fence"
+ * decode kernel for m == 1, k <= 4096; 0 forces the plain streaming-load kernel. "matvec_mma" (default 1)
+ * selects the integer-MMA kernel for batches of 5..16 rows on Q4_K weights, 0 the dp4a kernel. "gather_cta_fence"
  * (default 1): scope of the per-CTA fence before the arrival count of a kernel-side gather, 1 = gpu,
  * 0 = system. No counterpart in the reference. */
 int xnq_set_option(const char *name, int value);

@@ -26,6 +26,14 @@ static std::atomic<uint64_t> g_launches{0};
 static std::atomic<bool> g_opt_matvec_tma{true};
 static std::atomic<int> g_opt_gather_cta_fence{1};
 static std::atomic<int> g_opt_host_direct_y{1};
+static std::atomic<int> g_opt_matvec_mma{1};
+// Small batches: the integer-MMA kernel where it serves the weight and wins (Q4_K, five rows and up), else the
+// dp4a kernel. Returns the rows per launch.
+int64_t small_batch_pass(const xnq_weight *w, int64_t m, bool *use_mma) {
+  const int64_t mp = (m >= 5 && g_opt_matvec_mma.load(std::memory_order_relaxed)) ? matvec_mma_rows_per_pass(w->v) : 0;
+  *use_mma = mp > 0;
+  return mp > 0 ? mp : matvec_rows_per_pass(w->v.dtype, w->v.k);
+}
 int gather_cta_fence_scope() { return g_opt_gather_cta_fence.load(std::memory_order_relaxed); }
 bool matvec_tma_enabled() { return g_opt_matvec_tma.load(std::memory_order_relaxed); }
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
@@ -125,7 +133,8 @@ static int matmul_from_image(const xnq_weight *w, const void *image, int64_t m, 
     profile_mark(s, false);
     return rc;
   }
-  const int64_t pass = matvec_rows_per_pass(w->v.dtype, k);
+  bool use_mma = false;
+  const int64_t pass = small_batch_pass(w, m, &use_mma);
   if (pass == 0) return fail(XNQ_ERR_SIZE, "matmul_t: k = %lld is too large for the shared-memory staging of one activation row", (long long)k);
   const ActView all = act_view(const_cast<void *>(image), m, k, adt);
   const int blk = adt == XNQ_Q8_0 ? QK : QK_K;
@@ -137,7 +146,8 @@ static int matmul_from_image(const xnq_weight *w, const void *image, int64_t m, 
     a.d += r0 * (k / blk);
     a.bsum += r0 * (k / 16);
     profile_mark(s, true);
-    rc = launch_matvec(w->v, a, static_cast<char *>(y) + (size_t)r0 * ldy * yes, y_dtype, ldy, s);
+    rc = use_mma ? launch_matvec_mma(w->v, a, static_cast<char *>(y) + (size_t)r0 * ldy * yes, y_dtype, ldy, s)
+                 : launch_matvec(w->v, a, static_cast<char *>(y) + (size_t)r0 * ldy * yes, y_dtype, ldy, s);
     profile_mark(s, false);
     if (rc != XNQ_OK) return rc;
   }
@@ -206,6 +216,7 @@ int xnq_init(int device) {
   if ((rc = layout_init(device)) != XNQ_OK) return rc;
   if ((rc = quantize_init(device)) != XNQ_OK) return rc;
   if ((rc = matvec_init(device)) != XNQ_OK) return rc;
+  if ((rc = matvec_mma_init(device)) != XNQ_OK) return rc;
   if ((rc = matvec_tma_init(device)) != XNQ_OK) return rc;
   if ((rc = prefill_init(device)) != XNQ_OK) return rc;
   return XNQ_OK;
@@ -240,6 +251,10 @@ int xnq_set_option(const char *name, int value) {
   if (!name) return fail(XNQ_ERR_NULL, "set_option: name is NULL");
   if (std::strcmp(name, "matvec_tma") == 0) {
     g_opt_matvec_tma.store(value != 0);
+    return XNQ_OK;
+  }
+  if (std::strcmp(name, "matvec_mma") == 0) {
+    g_opt_matvec_mma.store(value);
     return XNQ_OK;
   }
   if (std::strcmp(name, "host_direct_y") == 0) {
@@ -483,7 +498,8 @@ int xnq_matmul_t(const xnq_weight *w, const void *x, int x_dtype, int64_t m, int
   if (!workspace) return fail(XNQ_ERR_NULL, "matmul_t: workspace is NULL (need %zu bytes)", need);
   if (!aligned(workspace, 256)) return fail(XNQ_ERR_ALIGN, "matmul_t: workspace must be 256-byte aligned");
   if (ws_bytes < need) return fail(XNQ_ERR_SIZE, "matmul_t: workspace has %zu bytes, m = %lld needs %zu", ws_bytes, (long long)m, need);
-  const int64_t pass = matvec_rows_per_pass(w->v.dtype, k);
+  bool use_mma = false;
+  const int64_t pass = small_batch_pass(w, m, &use_mma);
   if (pass == 0) return fail(XNQ_ERR_SIZE, "matmul_t: k = %lld is too large for the shared-memory staging of one activation row", (long long)k);
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -504,7 +520,7 @@ int xnq_matmul_t(const xnq_weight *w, const void *x, int x_dtype, int64_t m, int
     char *yp = static_cast<char *>(y) + (size_t)r0 * ldy * yes;
     if ((rc = launch_quantize_act_planar(a, xp, x_dtype, ldx, s)) != XNQ_OK) return rc;
     profile_mark(s, true);
-    rc = launch_matvec(w->v, a, yp, y_dtype, ldy, s);
+    rc = use_mma ? launch_matvec_mma(w->v, a, yp, y_dtype, ldy, s) : launch_matvec(w->v, a, yp, y_dtype, ldy, s);
     profile_mark(s, false);
     if (rc != XNQ_OK) return rc;
   }

@@ -65,7 +65,8 @@ extern "C" int xnq_matmul_t_static(const xnq_weight *w, const void *x, int x_dty
   if (!aligned_to(x, 16) || (m > 1 && (ldx * xes) % 16 != 0)) return fail(XNQ_ERR_ALIGN, "matmul_t_static: activation rows must start 16-byte aligned");
   if (!aligned_to(y, yes)) return fail(XNQ_ERR_ALIGN, "matmul_t_static: y is not aligned to its element size");
   const int adt = act_dtype_for(w->v.dtype);
-  const int64_t pass = matvec_rows_per_pass(w->v.dtype, k);
+  bool use_mma = false;
+  const int64_t pass = small_batch_pass(w, m, &use_mma); // the kernel xnq_matmul_t takes for this weight, so results are identical
   if (pass == 0) return fail(XNQ_ERR_SIZE, "matmul_t_static: k = %lld is too large for the shared-memory staging of one activation row", (long long)k);
   // rows per pass: what the kernel can stage AND what the built-in array can hold
   int64_t rows_at_once = m < pass ? m : pass;
@@ -90,7 +91,8 @@ extern "C" int xnq_matmul_t_static(const xnq_weight *w, const void *x, int x_dty
     const char *xp = static_cast<const char *>(x) + (size_t)r0 * ldx * xes;
     char *yp = static_cast<char *>(y) + (size_t)r0 * ldy * yes;
     if ((rc = launch_quantize_act_planar(a, xp, x_dtype, ldx, s)) != XNQ_OK) return rc;
-    if ((rc = launch_matvec(w->v, a, yp, y_dtype, ldy, s)) != XNQ_OK) return rc;
+    rc = use_mma ? launch_matvec_mma(w->v, a, yp, y_dtype, ldy, s) : launch_matvec(w->v, a, yp, y_dtype, ldy, s);
+    if (rc != XNQ_OK) return rc;
   }
   return XNQ_OK;
 }
