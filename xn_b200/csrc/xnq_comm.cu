@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(256) gather_push_kernel(GatherArgs g, const vo
     }
   }
   __syncthreads();
-  if (threadIdx.x == 0) gather_publish_and_wait(g);
+  if (threadIdx.x < 32) gather_publish_and_wait(g);
 }
 
 inline bool aligned_to(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }

@@ -116,7 +116,7 @@ struct GatherArgs {
 #ifdef __CUDACC__
 constexpr unsigned long long GATHER_WAIT_LIMIT_NS = 4000000000ull; // a peer that has not published within 4 s is reported, not awaited
 
-// Called by ONE thread of each CTA after a CTA-wide barrier that follows the CTA's stores into the
+// Called by one whole warp of each CTA after a CTA-wide barrier that follows the CTA's stores into the
 // gathered buffers. The last CTA of the launch advances this rank's epoch, stores it with release
 // semantics at system scope into every peer's epoch row, and then waits until every peer's epoch in
 // the local row has reached the same count: when the launch retires, the gathered buffer of this
@@ -127,32 +127,39 @@ constexpr unsigned long long GATHER_WAIT_LIMIT_NS = 4000000000ull; // a peer tha
 // cumulative across scopes). A system-scope fence in every CTA is not needed and costs about 3 us per
 // launch; the "gather_cta_fence" option (0) brings it back for comparison.
 __device__ __forceinline__ void gather_publish_and_wait(const GatherArgs &g) {
-  if (g.cta_fence_gpu) __threadfence();
-  else __threadfence_system();
-  if (atomicAdd(g.ctl + 2, 1u) == gridDim.x - 1) {
-    g.ctl[2] = 0;
-    const unsigned int epoch = g.ctl[0] + 1;
-    g.ctl[0] = epoch;
-    __threadfence_system();
-    for (int p = 0; p < g.world; p++)
-      if (p != g.rank) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(g.flag[p]), "r"(epoch) : "memory");
-    unsigned long long t0;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
-    const unsigned int *mine = g.flag[g.rank] - g.rank; // the local epoch row
-    if (g.ctl[3]) return; // a peer was already late once: later launches do not wait again (the host reads ctl[3])
-    for (int p = 0; p < g.world; p++) {
-      if (p == g.rank) continue;
-      for (;;) {
-        unsigned int v;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine + p) : "memory");
-        if ((int)(v - epoch) >= 0) break;
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        if (t - t0 > GATHER_WAIT_LIMIT_NS) {
-          atomicOr(g.ctl + 3, 1u << p);
-          break;
-        }
-      }
+  // called by the 32 lanes of ONE warp of each CTA, after the CTA-wide barrier that follows its stores
+  const int lane = threadIdx.x & 31;
+  unsigned int last = 0, epoch = 0;
+  if (lane == 0) {
+    if (g.cta_fence_gpu) __threadfence();
+    else __threadfence_system();
+    if (atomicAdd(g.ctl + 2, 1u) == gridDim.x - 1) {
+      g.ctl[2] = 0;
+      epoch = g.ctl[0] + 1;
+      g.ctl[0] = epoch;
+      last = g.ctl[3] ? 2u : 1u; // 2: a peer was already late once, later launches publish but do not wait again
+      __threadfence_system();
+    }
+  }
+  last = __shfl_sync(0xffffffffu, last, 0);
+  if (!last) return;
+  epoch = __shfl_sync(0xffffffffu, epoch, 0);
+  // lane p talks to rank p: all peers are told, and all peers are awaited, at the same time
+  const bool peer = lane < g.world && lane != g.rank;
+  if (peer) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(g.flag[lane]), "r"(epoch) : "memory");
+  if (last == 2u || !peer) return;
+  const unsigned int *mine = g.flag[g.rank] - g.rank + lane; // this peer's word in the local epoch row
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+  for (;;) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if ((int)(v - epoch) >= 0) break;
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    if (t - t0 > GATHER_WAIT_LIMIT_NS) {
+      atomicOr(g.ctl + 3, 1u << lane);
+      break;
     }
   }
 }

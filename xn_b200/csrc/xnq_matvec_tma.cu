@@ -636,7 +636,7 @@ matvec_tma_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtype
       }
       consumer_sync();
     }
-    if (threadIdx.x == 0) gather_publish_and_wait(g);
+    if (threadIdx.x < 32) gather_publish_and_wait(g);
   }
 }
 
