@@ -264,6 +264,11 @@ uint64_t xnq_launch_count(void);
  * Do not use while the stream is being captured into a graph. */
 int xnq_profile_begin(int max_launches);
 int xnq_profile_end(double *total_ms, int *launches);
+/* Device-side timestamps of the kernels' phases, recorded only while the "matvec_tma_dbg" / "prefill_dbg"
+ * options carry their trace bits (4 and 32); used by the measurements behind profiles/, not by the product
+ * path. out / n receive 64 records of 16 words and the record count (decode kernel), or 16 words (prefill). */
+int xnq_debug_trace(unsigned long long *out, unsigned int *n);
+int xnq_debug_prefill_trace(unsigned long long out[16]);
 
 #ifdef __cplusplus
 }

@@ -78,6 +78,8 @@ def lib() -> ctypes.CDLL:
     L.xnq_launch_count.restype = ctypes.c_uint64
     L.xnq_profile_begin.argtypes = [ci]
     L.xnq_profile_end.argtypes = [ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ci)]
+    L.xnq_debug_trace.argtypes = [vp, ctypes.POINTER(ctypes.c_uint)]
+    L.xnq_debug_prefill_trace.argtypes = [vp]
     _lib = L
     return L
 
