@@ -50,9 +50,15 @@ constexpr int LOADER_WARP = PRODUCERS / 32, MMA_WARP = LOADER_WARP + 1;
 constexpr int NTHREADS = PRODUCERS + 64; // warps 0-15 producers/epilogue, then the loader warp and the MMA warp
 constexpr uint32_t WAIT_LIMIT = 1u << 26; // non-blocking polls (a few ns each): about a second
 constexpr int A_STAGE_BYTES = TILE_N * BK * 2; // 16 KB
-constexpr int NSTAGES = 4;         // even: each producer group owns every other A stage
+#ifndef XNQ_PF_NSTAGES
+#define XNQ_PF_NSTAGES 4
+#endif
+#ifndef XNQ_PF_RAW_DEPTH
+#define XNQ_PF_RAW_DEPTH 2
+#endif
+constexpr int NSTAGES = XNQ_PF_NSTAGES; // even: each producer group owns every other A stage
         // A stages (16 KB each)
-constexpr int RAW_DEPTH = 2;       // own k-steps (every other one) of raw weight bytes a producer thread keeps in flight
+constexpr int RAW_DEPTH = XNQ_PF_RAW_DEPTH; // own k-steps (every other one) of raw weight bytes a producer thread keeps in flight
 constexpr int RAW_SLOT_MAX = 80;   // largest per-thread slot (Q6_K)
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
