@@ -174,7 +174,46 @@ def run_reference(args, name, dt, n, k, m):
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    ref_gpu = reference_gpu_kernel(dt, n, k, m)
+    if ref_gpu is not None:
+        line["reference_gpu"] = ref_gpu
     print(json.dumps(line), flush=True)
+
+
+def reference_gpu_kernel(dt, n, k, m):
+    """Q8_0, m <= 16 only: the reference's own CUDA kernel (`matmul_q8_f32_m*`, compiled unmodified for sm_100a into
+    oracle/_ref/reduce.cubin), launched with the reference's geometry on cold weights, timed with CUDA events. It
+    multiplies unquantized activations, so it is a speed reference, not the parity target."""
+    if dt != D.Q8_0 or m > 16:
+        return None
+    try:
+        import torch
+        from oracle import ref_cuda
+        if not ref_cuda.available() or not torch.cuda.is_available():
+            return None
+        dev = torch.device("cuda", 0)
+        l2 = int(getattr(torch.cuda.get_device_properties(dev), "L2_cache_size", 126 * 1024 * 1024))
+        ncopies = int(min(16, max(2, np.ceil(2 * l2 / (n * dt.row_bytes(k))))))
+        refs = [ref_cuda.RefQ8(synth.make_weight(dt, n, k, seed=0, tensor_id=i), n, k, dev) for i in range(ncopies)]
+        x = torch.from_numpy(synth.make_activation(m, k, seed=0)).to(dev)
+        y = torch.empty((m, n), dtype=torch.float32, device=dev)
+        for r in refs:
+            r.matmul_t(x, out=y)
+        torch.cuda.synchronize(dev)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        rounds = 20
+        ev0.record()
+        for _ in range(rounds):
+            for r in refs:
+                r.matmul_t(x, out=y)
+        ev1.record()
+        torch.cuda.synchronize(dev)
+        us = ev0.elapsed_time(ev1) * 1e3 / (rounds * ncopies)
+        return {"kernel": f"matmul_q8_f32_m{1 << (m - 1).bit_length() if m > 1 else 1} (xn-core/cuda-kernels/reduce.cu, grid n/8 x 128 threads)",
+                "launch_us": us, "value": algorithmic_bytes(dt, n, k, m) / (us * 1e-6) / 1e9, "unit": UNIT, "weight_copies": ncopies,
+                "note": "plain launches back to back; activations are not quantized by this kernel"}
+    except Exception as e:  # the CPU arm's line must not depend on this extra
+        return {"unavailable": str(e)[:200]}
 
 
 def run_ours(args, name, dt, n, k, m):

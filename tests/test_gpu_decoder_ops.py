@@ -85,7 +85,6 @@ def test_rope_store_and_attention(B, H, KV):
 def test_activation_images_equal_the_in_call_quantizer():
     """An image written by the stand-alone quantizer, by add_rmsnorm or by swiglu holds the bytes the matmul's own
     quantizer would produce from the same f32 rows, so matmul results through an image are bit-identical."""
-    import numpy as np
     from xn_b200 import decoder_ops as ops, quantized as Q, synth
     from xn_b200.dtypes import GgmlDType as D
     torch.manual_seed(3)

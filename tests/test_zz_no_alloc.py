@@ -6,7 +6,6 @@ library. This file is collected last on purpose: if it fails, every other test h
 It has to pass both on its own in a fresh process and after the rest of the suite."""
 import ctypes
 
-import numpy as np
 import pytest
 import torch
 

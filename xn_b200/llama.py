@@ -23,7 +23,6 @@ one layer is ten launches and the whole step is one CUDA graph.
 from __future__ import annotations
 
 import dataclasses
-import math
 from typing import Optional
 
 import torch
