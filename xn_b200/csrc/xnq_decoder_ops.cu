@@ -189,6 +189,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const float
   __shared__ __align__(16) float s_q[ATT_HD];
   __shared__ float s_m[ATT_WARPS], s_l[ATT_WARPS];
   __shared__ __align__(16) float s_acc[ATT_WARPS][ATT_HD];
+  __shared__ __align__(16) __nv_bfloat16 s_k[ATT_WARPS][32][ATT_HD + 8]; // rows padded to 272 bytes: conflict-free row reads
   __shared__ bool s_last;
   const int head = blockIdx.x, b = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -205,10 +206,22 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const float
   for (long long base = c0 + warp * 32; base < c1; base += ATT_WARPS * 32) {
     const long long p = base + lane;
     float s = -INFINITY;
+    // the 32 k rows of this run (8 KB, contiguous in the cache) come in with coalesced 16-byte loads and are
+    // turned through shared memory, so that each lane can then read ITS row: a lane reading its own row
+    // straight from global memory makes every load instruction touch 32 different lines
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+      const int idx = i * 32 + lane, row = idx >> 4, ch = idx & 15;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (base + row < c1) v = *reinterpret_cast<const uint4 *>(kb + (base + row) * ATT_HD + ch * 8);
+      *reinterpret_cast<uint4 *>(&s_k[warp][row][ch * 8]) = v;
+    }
+    __syncwarp();
     if (p < c1) {
       uint4 kr[16];
 #pragma unroll
-      for (int c = 0; c < 16; c++) kr[c] = *reinterpret_cast<const uint4 *>(kb + p * ATT_HD + c * 8);
+      for (int c = 0; c < 16; c++) kr[c] = *reinterpret_cast<const uint4 *>(&s_k[warp][lane][c * 8]);
       float d = 0.f;
 #pragma unroll
       for (int c = 0; c < 16; c++) {

@@ -109,7 +109,7 @@ __device__ __forceinline__ void reduce_store(float (&acc)[R][MT], int lane, int6
   }
 }
 
-#define XNQ_MATVEC_BOUNDS __launch_bounds__(THREADS, (MT <= 2 ? 4 : (MT <= 4 ? 3 : 2)))
+#define XNQ_MATVEC_BOUNDS __launch_bounds__(THREADS, (R >= 4 ? 2 : (MT <= 2 ? 4 : (MT <= 4 ? 3 : 2))))
 
 // ---- Q4_0: one 16-byte chunk = one block (32 codes) ----------------------------------------------
 template <int MT, int R>
@@ -216,16 +216,45 @@ __global__ void XNQ_MATVEC_BOUNDS matvec_q4k(WeightView w, ActView a, void *y, i
 #pragma unroll
     for (int i = 0; i < MT; i++) acc[r][i] = 0.f;
 
+  // With one or two activation rows there are registers to spare: the next iteration's bytes are requested
+  // before this iteration's are used, which doubles what a warp keeps in flight (the one-row case at large k
+  // is bound by exactly that).
+  constexpr bool PREFETCH = MT <= 2;
+  uint4 nq[R], nhdr[R];
+  if (PREFETCH && (lane >> 3) < nsb) {
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+      const uint8_t *blk = w.qs + (min(row0 + r, w.n - 1) * nsb + (lane >> 3)) * 144;
+      nhdr[r] = ldg_stream(blk);
+      nq[r] = ldg_stream(blk + 16 + 16 * c);
+    }
+  }
   for (int64_t sb = lane >> 3; sb < nsb; sb += 4) {
     uint4 q[R];
     float dd[R], dm[R];
     int sc_lo[R], sc_hi[R], mn_lo[R], mn_hi[R];
+    uint4 hdrs[R];
+    if (PREFETCH) {
+#pragma unroll
+      for (int r = 0; r < R; r++) q[r] = nq[r], hdrs[r] = nhdr[r];
+      if (sb + 4 < nsb) {
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+          const uint8_t *blk = w.qs + (min(row0 + r, w.n - 1) * nsb + sb + 4) * 144;
+          nhdr[r] = ldg_stream(blk);
+          nq[r] = ldg_stream(blk + 16 + 16 * c);
+        }
+      }
+    }
 #pragma unroll
     for (int r = 0; r < R; r++) {
-      const int64_t row = min(row0 + r, w.n - 1);
-      const uint8_t *blk = w.qs + (row * nsb + sb) * 144;
-      const uint4 hdr = ldg_stream(blk);
-      q[r] = ldg_stream(blk + 16 + 16 * c);
+      if (!PREFETCH) {
+        const int64_t row = min(row0 + r, w.n - 1);
+        const uint8_t *blk = w.qs + (row * nsb + sb) * 144;
+        hdrs[r] = ldg_stream(blk);
+        q[r] = ldg_stream(blk + 16 + 16 * c);
+      }
+      const uint4 hdr = hdrs[r];
       const __half2 h = *reinterpret_cast<const __half2 *>(&hdr.x);
       dd[r] = __low2float(h);
       dm[r] = __high2float(h);
@@ -324,7 +353,7 @@ int launch_mt(const WeightView &w, const ActView &a, void *y, int y_dtype, int64
   const int64_t groups = (w.n + (int64_t)WARPS * R - 1) / ((int64_t)WARPS * R);
   const int blk = (w.dtype == XNQ_Q4_0 || w.dtype == XNQ_Q8_0) ? QK : QK_K;
   const size_t image = smem_act_bytes(a.m, a.k, blk, w.dtype != XNQ_Q8_0);
-  const int by_bounds = MT <= 2 ? 4 : (MT <= 4 ? 3 : 2);
+  const int by_bounds = R >= 4 ? 2 : (MT <= 2 ? 4 : (MT <= 4 ? 3 : 2));
   const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(by_bounds, (220 * 1024) / std::max<size_t>(image + 1024, 1)));
   const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(groups, (int64_t)g_sms * per_sm));
   switch (w.dtype) {
@@ -381,7 +410,7 @@ int64_t matvec_rows_per_pass(int wdtype, int64_t k) {
 int launch_matvec(const WeightView &w, const ActView &a, void *y, int y_dtype, int64_t ldy, cudaStream_t s) {
   if (w.n == 0 || a.m == 0) return XNQ_OK;
   if (a.m > MATVEC_MAX_M) return fail(XNQ_ERR_SHAPE, "matvec: m=%lld exceeds %d", (long long)a.m, MATVEC_MAX_M);
-  if (a.m == 1) return launch_mt<1, 2>(w, a, y, y_dtype, ldy, s);
+  if (a.m == 1) return w.dtype == XNQ_Q4K ? launch_mt<1, 4>(w, a, y, y_dtype, ldy, s) : launch_mt<1, 2>(w, a, y, y_dtype, ldy, s);
   if (a.m == 2) return launch_mt<2, 2>(w, a, y, y_dtype, ldy, s);
   if (a.m <= 4) return launch_mt<4, 2>(w, a, y, y_dtype, ldy, s);
   if (a.m <= 8) return launch_mt<8, 2>(w, a, y, y_dtype, ldy, s);
@@ -394,6 +423,7 @@ int matvec_init(int device) {
   g_sms = prop.multiProcessorCount;
   int rc;
   if ((rc = init_mt<1, 2>()) != XNQ_OK) return rc;
+  if ((rc = init_mt<1, 4>()) != XNQ_OK) return rc;
   if ((rc = init_mt<2, 2>()) != XNQ_OK) return rc;
   if ((rc = init_mt<4, 2>()) != XNQ_OK) return rc;
   if ((rc = init_mt<8, 2>()) != XNQ_OK) return rc;
