@@ -327,3 +327,25 @@ def test_activation_quantizer_rounding_ties_and_near_ties(Q, O):
     got = Q.quantize_act(torch.from_numpy(xk).to(DEV), D.Q8K).cpu().numpy()
     want = O.from_float(O.Q8K, xk)
     assert np.array_equal(got, want), np.flatnonzero(got != want)[:10]
+
+
+@pytest.mark.parametrize("m", [5, 9, 16])
+def test_q4k_small_batch_at_large_k_two_staged_halves(Q, O, m):
+    """k = 14336 (the 7B down projection): above 8 rows the activation image of the whole k does not fit shared
+    memory, each CTA stages one half and the halves meet in the output; f16 output takes two passes of 8 rows."""
+    dt, n, k = D.Q4K, 272, 14336
+    w = synth.make_weight(dt, n, k, seed=90)
+    x = synth.make_activation(m, k, seed=91)
+    t = _upload(Q, dt, w, n, k)
+    want = O.matmul(int(dt), x, w, n)
+    xd = torch.from_numpy(x).to(DEV)
+    for rep in range(2):   # the output buffer is reused: the second call must not add onto the first
+        out = torch.full((m, n), 7.0, device=DEV)
+        got = t.matmul_t(xd, out=out).cpu().numpy()
+        assert_close_ref(got, want, TOL_F32)
+    # f16 in and out: the oracle sees the same f16-rounded activations; the f16 output rounds at 5e-4 of each value
+    x16 = x.astype(np.float16)
+    want16 = O.matmul(int(dt), x16.astype(np.float32), w, n)
+    got16 = t.matmul_t(torch.from_numpy(x16).to(DEV)).float().cpu().numpy()
+    rms = float(np.sqrt((want16 ** 2).mean()))
+    assert (np.abs(got16 - want16) / np.maximum(np.abs(want16), rms)).max() < 2e-3

@@ -29,8 +29,8 @@ static std::atomic<int> g_opt_host_direct_y{1};
 static std::atomic<int> g_opt_matvec_mma{1};
 // Small batches: the integer-MMA kernel where it serves the weight and wins (Q4_K, five rows and up), else the
 // dp4a kernel. Returns the rows per launch.
-int64_t small_batch_pass(const xnq_weight *w, int64_t m, bool *use_mma) {
-  const int64_t mp = (m >= 5 && g_opt_matvec_mma.load(std::memory_order_relaxed)) ? matvec_mma_rows_per_pass(w->v) : 0;
+int64_t small_batch_pass(const xnq_weight *w, int64_t m, int y_dtype, bool *use_mma) {
+  const int64_t mp = (m >= 5 && g_opt_matvec_mma.load(std::memory_order_relaxed)) ? matvec_mma_rows_per_pass(w->v, y_dtype) : 0;
   *use_mma = mp > 0;
   return mp > 0 ? mp : matvec_rows_per_pass(w->v.dtype, w->v.k);
 }
@@ -134,7 +134,7 @@ static int matmul_from_image(const xnq_weight *w, const void *image, int64_t m, 
     return rc;
   }
   bool use_mma = false;
-  const int64_t pass = small_batch_pass(w, m, &use_mma);
+  const int64_t pass = small_batch_pass(w, m, y_dtype, &use_mma);
   if (pass == 0) return fail(XNQ_ERR_SIZE, "matmul_t: k = %lld is too large for the shared-memory staging of one activation row", (long long)k);
   const ActView all = act_view(const_cast<void *>(image), m, k, adt);
   const int blk = adt == XNQ_Q8_0 ? QK : QK_K;
@@ -499,7 +499,7 @@ int xnq_matmul_t(const xnq_weight *w, const void *x, int x_dtype, int64_t m, int
   if (!aligned(workspace, 256)) return fail(XNQ_ERR_ALIGN, "matmul_t: workspace must be 256-byte aligned");
   if (ws_bytes < need) return fail(XNQ_ERR_SIZE, "matmul_t: workspace has %zu bytes, m = %lld needs %zu", ws_bytes, (long long)m, need);
   bool use_mma = false;
-  const int64_t pass = small_batch_pass(w, m, &use_mma);
+  const int64_t pass = small_batch_pass(w, m, y_dtype, &use_mma);
   if (pass == 0) return fail(XNQ_ERR_SIZE, "matmul_t: k = %lld is too large for the shared-memory staging of one activation row", (long long)k);
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -213,11 +213,11 @@ int matvec_init(int device);
 int64_t matvec_rows_per_pass(int wdtype, int64_t k);
 
 // xnq_matvec_mma.cu  (5 <= m <= 16, Q4_K: integer tensor-core MMAs)
-int64_t matvec_mma_rows_per_pass(const WeightView &w); // 0: not served
+int64_t matvec_mma_rows_per_pass(const WeightView &w, int y_dtype); // 0: not served
 int launch_matvec_mma(const WeightView &w, const ActView &a, void *y, int y_dtype, int64_t ldy, cudaStream_t s);
 int matvec_mma_init(int device);
 // rows per launch of the small-batch path that xnq_matmul_t takes for this weight, and which kernel that is
-int64_t small_batch_pass(const xnq_weight *w, int64_t m, bool *use_mma);
+int64_t small_batch_pass(const xnq_weight *w, int64_t m, int y_dtype, bool *use_mma);
 
 // xnq_matvec_tma.cu  (m == 1, k <= 4096: persistent TMA-ring kernel that quantizes x in its prologue)
 bool matvec_tma_supported(const WeightView &w, int64_t m);

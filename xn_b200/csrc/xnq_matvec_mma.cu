@@ -74,7 +74,7 @@ __host__ __device__ constexpr size_t stage_bytes(int64_t nspan) {
 }
 
 template <int NB, int DPS>
-__device__ __forceinline__ void stage_acts(const Stage<NB, DPS> &st, const ActView &a, int nspan) {
+__device__ __forceinline__ void stage_acts(const Stage<NB, DPS> &st, const ActView &a, int span0, int nspan) {
   const int64_t k = a.k;
   const int m = (int)a.m;
   // fragments: thread -> (s, nb, g, j, t); (j, t) walk 256 consecutive bytes of one activation row
@@ -82,7 +82,7 @@ __device__ __forceinline__ void stage_acts(const Stage<NB, DPS> &st, const ActVi
     const int t = i & 3, j = (i >> 2) & 7, g = (i >> 5) & 7, nb = (i >> 8) % NB, s = (i >> 8) / NB;
     const int row = nb * 8 + g;
     uint2 v = make_uint2(0, 0);
-    if (row < m) v = *reinterpret_cast<const uint2 *>(a.q + (int64_t)row * k + s * 256 + j * 32 + t * 8);
+    if (row < m) v = *reinterpret_cast<const uint2 *>(a.q + (int64_t)row * k + (span0 + s) * 256 + j * 32 + t * 8);
     *reinterpret_cast<uint2 *>(st.frag + ((size_t)(s * NB + nb) * 32 + g * 4 + t) * LANE_WORDS + 2 * j) = v;
   }
   for (int i = threadIdx.x; i < nspan * NB * 4 * 8 * 2; i += blockDim.x) {
@@ -90,7 +90,7 @@ __device__ __forceinline__ void stage_acts(const Stage<NB, DPS> &st, const ActVi
     const int row = nb * 8 + 2 * t + e;
     int v = 0;
     if (row < m) {
-      const int16_t *b = a.bsum + (int64_t)row * (k / 16) + s * 16 + 2 * j;
+      const int16_t *b = a.bsum + (int64_t)row * (k / 16) + (span0 + s) * 16 + 2 * j;
       v = (int)b[0] + (int)b[1];
     }
     st.bsum[i] = (int16_t)v;
@@ -98,7 +98,7 @@ __device__ __forceinline__ void stage_acts(const Stage<NB, DPS> &st, const ActVi
   for (int i = threadIdx.x; i < nspan * NB * 4 * DPS * 2; i += blockDim.x) {
     const int e = i & 1, dj = (i >> 1) % DPS, t = ((i >> 1) / DPS) & 3, nb = ((i >> 1) / DPS / 4) % NB, s = ((i >> 1) / DPS / 4) / NB;
     const int row = nb * 8 + 2 * t + e;
-    st.dact[i] = row < m ? a.d[(int64_t)row * (k / 256) * DPS + s * DPS + dj] : 0.f;
+    st.dact[i] = row < m ? a.d[(int64_t)row * (k / 256) * DPS + (span0 + s) * DPS + dj] : 0.f;
   }
   __syncthreads();
 }
@@ -106,7 +106,7 @@ __device__ __forceinline__ void stage_acts(const Stage<NB, DPS> &st, const ActVi
 // The ks warps of a row group add their partial sums in a fixed order (k-part 0 first) and part 0 stores.
 template <int NB>
 __device__ __forceinline__ void reduce_and_store(float (&acc)[NB][4], float *red, int ks, int warp, int lane, bool live, int m, int64_t r0, int64_t r1,
-                                                 int64_t n, void *y, int y_dtype, int64_t ldy) {
+                                                 int64_t n, void *y, int y_dtype, int64_t ldy, bool accumulate) {
   const int t = lane & 3;
   if (ks > 1) {
     __syncthreads(); // the previous round's partials have been read
@@ -129,31 +129,38 @@ __device__ __forceinline__ void reduce_and_store(float (&acc)[NB][4], float *red
     for (int v = 0; v < 4; v++) {
       const int act = nb * 8 + 2 * t + (v & 1);
       const int64_t row = (v & 2) ? r1 : r0;
-      if (act < m && row < n) store_y(y, y_dtype, (int64_t)act * ldy + row, acc[nb][v]);
+      if (act < m && row < n) {
+        if (accumulate) atomicAdd(static_cast<float *>(y) + (int64_t)act * ldy + row, acc[nb][v]); // two summands per output: order-free
+        else store_y(y, y_dtype, (int64_t)act * ldy + row, acc[nb][v]);
+      }
     }
 }
 
 // ---- Q4_K ----------------------------------------------------------------------------------------------
 template <int NB>
-__global__ void __launch_bounds__(THREADS, 2) matvec_mma_q4k(WeightView w, ActView a, void *y, int y_dtype, int64_t ldy, int ks) {
+__global__ void __launch_bounds__(THREADS, 2) matvec_mma_q4k(WeightView w, ActView a, void *y, int y_dtype, int64_t ldy, int ks, int nkp) {
   extern __shared__ __align__(16) unsigned char smem[];
   const int nsb = (int)(w.k / QK_K);
-  const Stage<NB, 1> st(smem, nsb);
-  stage_acts<NB, 1>(st, a, nsb);
+  // With nkp > 1 a CTA stages and works on one of nkp runs of super-blocks only (the whole activation image
+  // of a large k does not fit shared memory) and the runs' results meet in y by atomic adds: y starts at zero.
+  const int kp = blockIdx.x % nkp;
+  const int sp0 = nsb * kp / nkp, spn = nsb * (kp + 1) / nkp - sp0;
+  const Stage<NB, 1> st(smem, spn);
+  stage_acts<NB, 1>(st, a, sp0, spn);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   const int m = (int)a.m;
   const int64_t ngroups = (w.n + 15) / 16;
   // ks warps share a group of 16 rows and split its super-blocks, so that enough loads are in flight even
   // when n / 16 is small against the number of warps the machine holds
   const int rgl = warp / ks, kpart = warp % ks, RG = WARPS / ks;
-  const int sb0 = nsb * kpart / ks, sb1 = nsb * (kpart + 1) / ks;
-  float *red = reinterpret_cast<float *>(smem + stage_bytes<NB, 1>(nsb)); // [WARPS][NB * 4][32]
-  for (int64_t cg = blockIdx.x; cg * RG < ngroups; cg += gridDim.x) {
+  const int sb0 = spn * kpart / ks, sb1 = spn * (kpart + 1) / ks; // relative to this CTA's run
+  float *red = reinterpret_cast<float *>(smem + stage_bytes<NB, 1>(spn)); // [WARPS][NB * 4][32]
+  for (int64_t cg = blockIdx.x / nkp; cg * RG < ngroups; cg += gridDim.x / nkp) {
     const int64_t rg = cg * RG + rgl;
     const bool live = rg < ngroups;
     const int64_t r0 = rg * 16 + g, r1 = r0 + 8;
-    const uint8_t *p0 = w.qs + ((r0 < w.n ? r0 : w.n - 1) * nsb + sb0) * 144; // rows past the end read a valid row and are never stored
-    const uint8_t *p1 = w.qs + ((r1 < w.n ? r1 : w.n - 1) * nsb + sb0) * 144;
+    const uint8_t *p0 = w.qs + ((r0 < w.n ? r0 : w.n - 1) * nsb + sp0 + sb0) * 144; // rows past the end read a valid row and are never stored
+    const uint8_t *p1 = w.qs + ((r1 < w.n ? r1 : w.n - 1) * nsb + sp0 + sb0) * 144;
     float acc[NB][4];
 #pragma unroll
     for (int nb = 0; nb < NB; nb++)
@@ -220,7 +227,7 @@ __global__ void __launch_bounds__(THREADS, 2) matvec_mma_q4k(WeightView w, ActVi
         acc[nb][3] += da.y * (d1 * (float)t1[nb][3] - m1 * (float)t2[nb][3]);
       }
     }
-    reduce_and_store<NB>(acc, red, ks, warp, lane, live, m, r0, r1, w.n, y, y_dtype, ldy);
+    reduce_and_store<NB>(acc, red, ks, warp, lane, live, m, r0, r1, w.n, y, y_dtype, ldy, nkp > 1);
   }
 }
 
@@ -229,16 +236,22 @@ constexpr size_t RED_BYTES = (size_t)WARPS * 2 * 4 * 32 * 4; // the k-split part
 template <int NB>
 int launch_nb(const WeightView &w, const ActView &a, void *y, int y_dtype, int64_t ldy, cudaStream_t s) {
   const int64_t nspan = w.k / 256;
-  const size_t sm = stage_bytes<NB, 1>(nspan) + RED_BYTES;
+  // the activation image of the whole k, or of one of two halves of it when that is what fits
+  int nkp = 1;
+  if (stage_bytes<NB, 1>(nspan) + RED_BYTES > MMA_SMEM_LIMIT) nkp = 2;
+  const int64_t spn = (nspan + nkp - 1) / nkp;
+  const size_t sm = stage_bytes<NB, 1>(spn) + RED_BYTES;
+  if (sm > MMA_SMEM_LIMIT || (nkp > 1 && y_dtype != XNQ_F32)) return fail(XNQ_ERR_SIZE, "matvec_mma: k = %lld does not fit", (long long)w.k);
   const int per_sm = sm > 110 * 1024 ? 1 : 2;
   // split k over as many warps as it takes to fill the machine (depends on the weight's shape only, so the
   // summation order of a row is the same for every batch size)
   const int64_t ngroups = (w.n + 15) / 16, slots = (int64_t)g_mma_sms * 2 * WARPS;
   int ks = 1;
-  while (ks < WARPS && ngroups * ks < slots && nspan / (ks * 2) >= 2) ks *= 2;
+  while (ks < WARPS && ngroups * ks * nkp < slots && spn / (ks * 2) >= 2) ks *= 2;
   const int64_t cta_groups = (ngroups + WARPS / ks - 1) / (WARPS / ks);
-  const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(cta_groups, (int64_t)g_mma_sms * per_sm));
-  matvec_mma_q4k<NB><<<grid, THREADS, sm, s>>>(w, a, y, y_dtype, ldy, ks);
+  const unsigned grid = (unsigned)(std::max<int64_t>(1, std::min<int64_t>(cta_groups, (int64_t)g_mma_sms * per_sm / nkp)) * nkp);
+  if (nkp > 1) XNQ_CUDA(cudaMemset2DAsync(y, (size_t)ldy * 4, 0, (size_t)w.n * 4, (size_t)a.m, s)); // the halves add into zeros
+  matvec_mma_q4k<NB><<<grid, THREADS, sm, s>>>(w, a, y, y_dtype, ldy, ks, nkp);
   XNQ_CUDA(cudaGetLastError());
   count_launch();
   return XNQ_OK;
@@ -247,17 +260,18 @@ int launch_nb(const WeightView &w, const ActView &a, void *y, int y_dtype, int64
 } // namespace
 
 // Activation rows one launch can stage for this weight (0: this kernel does not serve it).
-int64_t matvec_mma_rows_per_pass(const WeightView &w) {
+int64_t matvec_mma_rows_per_pass(const WeightView &w, int y_dtype) {
   if (w.dtype != XNQ_Q4K || w.n < 1) return 0;
   const int64_t nspan = w.k / 256;
   if (stage_bytes<2, 1>(nspan) + RED_BYTES <= MMA_SMEM_LIMIT) return 16;
+  if (y_dtype == XNQ_F32 && stage_bytes<2, 1>((nspan + 1) / 2) + RED_BYTES <= MMA_SMEM_LIMIT) return 16; // two half-k images, summed in y
   if (stage_bytes<1, 1>(nspan) + RED_BYTES <= MMA_SMEM_LIMIT) return 8;
   return 0;
 }
 
 int launch_matvec_mma(const WeightView &w, const ActView &a, void *y, int y_dtype, int64_t ldy, cudaStream_t s) {
   if (w.n == 0 || a.m == 0) return XNQ_OK;
-  const int64_t pass = matvec_mma_rows_per_pass(w);
+  const int64_t pass = matvec_mma_rows_per_pass(w, y_dtype);
   if (a.m > pass) return fail(XNQ_ERR_SHAPE, "matvec_mma: m = %lld exceeds the %lld rows one launch stages", (long long)a.m, (long long)pass);
   return a.m <= 8 ? launch_nb<1>(w, a, y, y_dtype, ldy, s) : launch_nb<2>(w, a, y, y_dtype, ldy, s);
 }
