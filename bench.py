@@ -265,7 +265,12 @@ def run_ours(args, name, dt, n, k, m):
     if fused:
         # every weight copy gathers into its own slot, so a replayed step never ends on the slot it starts with
         from xn_b200.parallel import PeerGather
-        pg = PeerGather(dev, rank, world, slot_elems=m * n, nslots=ncopies)
+        try:
+            pg = PeerGather(dev, rank, world, slot_elems=m * n, nslots=ncopies)
+        except RuntimeError as e:   # raised on every rank together: peer mappings unavailable on this box
+            sys.stderr.write(f"[bench] rank {rank}: {e}; gathering with NCCL instead\n")
+            fused, pg = False, None
+            y_full = [torch.empty((world, m, n_local), dtype=torch.float32, device=dev) for _ in range(ncopies)]
     for w in weights:
         w.workspace(m)
 

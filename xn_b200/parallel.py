@@ -92,8 +92,19 @@ class PeerGather:
             if world > 1:
                 handles = [None] * world
                 dist.all_gather_object(handles, bytes(mine.raw), group=group)
-                _lib.check(self._L.xnq_comm_connect(self._h, ctypes.create_string_buffer(b"".join(handles), 64 * world)))
-                dist.barrier(group=group)  # nobody stores into a peer before every peer has mapped everybody
+                error = None
+                try:
+                    _lib.check(self._L.xnq_comm_connect(self._h, ctypes.create_string_buffer(b"".join(handles), 64 * world)))
+                except _lib.XnqError as e:   # e.g. peer mappings are not permitted here: every rank has to learn of it
+                    error = e
+                # nobody stores into a peer before every peer has mapped everybody; the same collective tells all
+                # ranks whether some rank could not map its peers, so that none is left waiting for the others
+                ok = torch.tensor([0 if error else 1], device=device if dist.get_backend(group) == "nccl" else "cpu")
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+                if int(ok.item()) == 0:
+                    self._L.xnq_comm_free(self._h)
+                    self._h = None
+                    raise RuntimeError(f"peer mappings could not be set up on every rank ({error or 'another rank failed'})")
         self._next = 0
         self.slot_elems = slot_elems
 
