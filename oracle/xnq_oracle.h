@@ -11,7 +11,9 @@
  *
  * Pinning status. Q8_0 is pinned by re-running the reference's own known-answer recipes
  * (closed-form inputs, f64 dot of the quantized operands, 1e-4: xn-core/src/quantized/k_quants.rs:2155-2210;
- * "tiled sgemm == per-cell vec_dot exactly": xn-core/tests/quantized_tests.rs:125-218).
+ * "tiled sgemm == per-cell vec_dot exactly": xn-core/tests/quantized_tests.rs:125-218), and its
+ * block layout and to_float by the output of the reference's own CUDA kernel dequant_q8_f32
+ * (xn-core/cuda-kernels/reduce.cu, compiled unmodified by `make ref`), bit for bit.
  * Q4_0, Q4_K, Q6_K and the Q8_K activation quantizer: PARITY UNPINNED - the reference holds no
  * test, golden vector or fixture for them, so this restatement is checked only against the source
  * text of k_quants.rs (struct sizes, round trips, scalar-vs-AVX2 agreement, f64 dots).
