@@ -63,14 +63,18 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(float *x, const float 
   const int lane = threadIdx.x & 31;
   float *xr = x + row * d;
   const float *dr = delta ? delta + row * parts * d : nullptr;
+  // The first KEEP passes of 2048 values (rows of up to 4096 values entirely) stay in registers between the
+  // sum of squares and the scaling, and their norm weights are requested before the block-wide reduction: one
+  // trip to memory instead of three. Longer rows re-read the rest.
+  constexpr int KEEP = 2;
+  float kv[KEEP][8], kg[KEEP][8];
   float ss = 0.f;
-  for (int i = threadIdx.x * 8; i < d; i += 2048) {
-    float v[8];
+  auto first_pass = [&](int i, float (&v)[8]) {
     load8(xr + i, v);
     if (dr) {
-      for (int p = 0; p < parts; p++) {
+      for (int q = 0; q < parts; q++) {
         float a[8];
-        load8(dr + (int64_t)p * d + i, a);
+        load8(dr + (int64_t)q * d + i, a);
 #pragma unroll
         for (int e = 0; e < 8; e++) v[e] += a[e];
       }
@@ -79,6 +83,18 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(float *x, const float 
     }
 #pragma unroll
     for (int e = 0; e < 8; e++) ss += v[e] * v[e];
+  };
+#pragma unroll
+  for (int p = 0; p < KEEP; p++) {
+    const int i = p * 2048 + threadIdx.x * 8;
+    if (i < d) {
+      load8(w + i, kg[p]);
+      first_pass(i, kv[p]);
+    }
+  }
+  for (int i = KEEP * 2048 + threadIdx.x * 8; i < d; i += 2048) {
+    float v[8];
+    first_pass(i, v);
   }
   ss = warp_sum(ss);
   if (lane == 0) part[threadIdx.x >> 5] = ss;
@@ -89,17 +105,17 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(float *x, const float 
   const float r = rsqrtf(tot / (float)d + eps);
   RowImage img{};
   if (ACT != 0) img = row_image(image, rows, d, ACT == XNQ_Q8_0 ? QK : QK_K, row);
-  for (int base = 0; base < d; base += 2048) { // whole warps stay together for the quantizer's shuffles
+  auto second_pass = [&](int base, float (&v)[8], const float (&g)[8], bool loaded) { // whole warps stay together for the quantizer's shuffles
     const int i = base + threadIdx.x * 8;
-    if (base + (threadIdx.x & ~31) * 8 >= d) break;
     const bool valid = i < d;
-    float v[8];
     if (valid) {
-      float g[8];
-      load8(xr + i, v); // this thread's own stores of the first pass
-      load8(w + i, g);
+      float gg[8];
+      if (!loaded) {
+        load8(xr + i, v); // this thread's own stores of the first pass
+        load8(w + i, gg);
+      }
 #pragma unroll
-      for (int e = 0; e < 8; e++) v[e] = v[e] * r * g[e];
+      for (int e = 0; e < 8; e++) v[e] = v[e] * r * (loaded ? g[e] : gg[e]);
       if (out) {
         *reinterpret_cast<float4 *>(out + row * d + i) = make_float4(v[0], v[1], v[2], v[3]);
         *reinterpret_cast<float4 *>(out + row * d + i + 4) = make_float4(v[4], v[5], v[6], v[7]);
@@ -109,6 +125,13 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(float *x, const float 
       for (int e = 0; e < 8; e++) v[e] = 0.f;
     }
     if (ACT != 0) quantize_store8<ACT>(v, valid, img, i / 8, lane);
+  };
+#pragma unroll
+  for (int p = 0; p < KEEP; p++)
+    if (p * 2048 + (threadIdx.x & ~31) * 8 < d) second_pass(p * 2048, kv[p], kg[p], true);
+  for (int base = KEEP * 2048; base + (threadIdx.x & ~31) * 8 < d; base += 2048) {
+    float v[8];
+    second_pass(base, v, v, false);
   }
 }
 
