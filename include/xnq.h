@@ -52,7 +52,10 @@ enum {
 
 /* An immutable quantized [n, k] weight (or an N-shard of one) resident in device memory.
  * Replaces Q8Tensor (xn-core/src/cuda_backend/q8.rs:26-33) and the missing QStorage::Cuda variant
- * (xn-core/src/quantized/mod.rs:32-34). Safe to use from several host threads at once. */
+ * (xn-core/src/quantized/mod.rs:32-34). The weight is immutable after upload: every entry that takes a
+ * `const xnq_weight *` may be called on one handle from several host threads at once. The two entries that
+ * take a non-const handle (xnq_linear_forward_host, xnq_weight_reserve_host_staging) use staging buffers
+ * owned by the handle and must not run concurrently with each other on the same handle. */
 typedef struct xnq_weight xnq_weight;
 
 /* Message of the last failure on the calling thread ("" if none). Replaces the xn::Error text a
@@ -139,6 +142,14 @@ size_t xnq_matmul_workspace_bytes(const xnq_weight *w, int64_t max_m);
 int xnq_matmul_t(const xnq_weight *w, const void *x, int x_dtype, int64_t m, int64_t ldx, void *y,
                  int y_dtype, int64_t ldy, void *workspace, size_t ws_bytes, void *stream);
 
+/* A prefetch hint (no counterpart in the reference): names the weight that the calling thread will multiply
+ * AFTER its next one-row (m == 1) xnq_matmul_t / xnq_matmul_t_gather call. That next call's kernel then asks for
+ * the named weight's bytes to be brought into L2 while it streams its own weight, so HBM stays busy across the
+ * launch boundary (a decoder knows its next linear; a loop over layers names layer l + 1 before multiplying layer
+ * l). One-shot and per host thread; NULL clears it. Results never depend on it. The named weight must stay
+ * alive until that launch has finished; under stream capture the hint is recorded with the launch. */
+int xnq_hint_next_weight(const xnq_weight *w);
+
 /* xnq_matmul_t for callers that can neither supply a workspace nor let the library allocate one:
  * hosts whose allocator owns all device memory, steps being recorded into a CUDA graph, plugins under
  * a fixed memory budget. Same arithmetic and results as xnq_matmul_t's small-batch path, for
@@ -157,12 +168,16 @@ int xnq_matmul_t_static(const xnq_weight *w, const void *x, int x_dtype, int64_t
 
 /* QLinear::forward on HOST tensors (quantized/mod.rs:352-384): copies x_host [m, k] f32 to the
  * device, runs xnq_matmul_t, adds bias_host[n_local] if non-NULL, copies y back to y_host
- * [m, n_local] and synchronizes. Device staging buffers are owned by the weight handle and grow on
- * demand (first call at a given m allocates). Not for use from several threads on one handle.
+ * [m, n_local] and synchronizes. Device staging buffers are owned by the weight handle:
+ * xnq_weight_reserve_host_staging(w, max_m) sizes them ahead of time, after which calls with m <= max_m
+ * allocate nothing; without it the first call at a larger m allocates (and is refused with
+ * XNQ_ERR_UNSUPPORTED if the stream is being captured). One thread at a time per handle.
  * When y_host is page-locked memory (cudaHostAlloc / cudaHostRegister), there is no bias and m <= 16,
  * the kernel stores the result straight into it and the copy back is skipped. */
 int xnq_linear_forward_host(xnq_weight *w, const float *x_host, int64_t m, const float *bias_host,
                             float *y_host, void *stream);
+/* No counterpart in the reference (its QLinear::forward allocates a fresh Vec per call, quantized/mod.rs:373-376). */
+int xnq_weight_reserve_host_staging(xnq_weight *w, int64_t max_m);
 
 /* ---- N-sharded matmul with the output gather done by the kernels (no counterpart in the
  * reference, which runs on one device: cuda_backend/mod.rs:141-167). One process per GPU; rank r of
@@ -245,8 +260,8 @@ int xnq_device_status(unsigned int *bits);
  * instead of performing it; this returns what it recorded first: code, block, iteration, offset,
  * bytes, limit (two spare words). Synchronizes the device. No counterpart in the reference. */
 int xnq_device_check_record(unsigned long long out[8]);
-/* Tuning switches, for A/B measurements: "matvec_tma" (default 1) selects the persistent TMA-ring
- * decode kernel for m == 1, k <= 4096; 0 forces the plain streaming-load kernel. "matvec_mma" (default 1)
+/* Tuning switches, for A/B measurements: "matvec_tma" (default 1) selects the persistent bulk-copy ring
+ * decode kernel for m == 1; 0 forces the plain streaming-load kernel. "matvec_mma" (default 1)
  * selects the integer-MMA kernel for batches of 5..16 rows on Q4_K weights, 0 the dp4a kernel. "gather_cta_fence"
  * (default 1): scope of the per-CTA fence before the arrival count of a kernel-side gather, 1 = gpu,
  * 0 = system. No counterpart in the reference. */
@@ -264,12 +279,6 @@ uint64_t xnq_launch_count(void);
  * Do not use while the stream is being captured into a graph. */
 int xnq_profile_begin(int max_launches);
 int xnq_profile_end(double *total_ms, int *launches);
-/* Device-side timestamps of the kernels' phases, recorded only while the "matvec_tma_dbg" / "prefill_dbg"
- * options carry their trace bits (4 and 32); used by the measurements behind profiles/, not by the product
- * path. out / n receive 64 records of 16 words and the record count (decode kernel), or 16 words (prefill). */
-int xnq_debug_trace(unsigned long long *out, unsigned int *n);
-int xnq_debug_prefill_trace(unsigned long long out[16]);
-
 #ifdef __cplusplus
 }
 #endif

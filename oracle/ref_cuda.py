@@ -22,10 +22,12 @@ def available() -> bool:
     return os.path.exists(CUBIN)
 
 
-def build(ref: str = "/root/reference") -> bool:
-    """Compile the reference's kernels where the reference checkout exists; returns whether the cubin is there."""
+def build(ref: str | None = None) -> bool:
+    """Compile the reference's kernels where a reference checkout is named (argument or the XN_REFERENCE
+    environment variable) and present; returns whether the cubin is there."""
     import subprocess
-    if os.path.exists(os.path.join(ref, "xn-core", "cuda-kernels", "reduce.cu")):
+    ref = ref or os.environ.get("XN_REFERENCE")
+    if ref and os.path.exists(os.path.join(ref, "xn-core", "cuda-kernels", "reduce.cu")):
         subprocess.run(["make", "-C", HERE, "ref", f"REF={ref}"], check=True, capture_output=True)
     return available()
 

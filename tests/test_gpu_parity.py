@@ -202,15 +202,26 @@ def test_golden_vectors_without_oracle(Q):
 
 @pytest.mark.parametrize("dt", WEIGHT_TYPES)
 def test_sharded_upload_concatenates_to_unsharded(Q, O, dt):
-    n, k, m = 64, 1024, 3
+    """Row shards hold exactly the unsharded tensor's rows. One activation row: every output is one warp's dot in a fixed
+    order, so the shards' results are the unsharded ones bit for bit. Several rows: the tensor-core kernel cuts k between
+    SMs according to the launch's size, so the f32 grouping (not the integers) differs between a shard and the whole:
+    equal within the matmul tolerance, and each launch on its own reproducible."""
+    n, k = 64, 1024
     w = synth.make_weight(dt, n, k, seed=90)
-    x = torch.from_numpy(synth.make_activation(m, k, seed=90)).to(DEV)
-    full = _upload(Q, dt, w, n, k).matmul_t(x)
-    for g in (2, 4, 8):
-        parts = [_upload(Q, dt, w, n, k, shard_rank=r, shard_count=g) for r in range(g)]
-        assert [p.row0 for p in parts] == [r * n // g for r in range(g)] and all(p.n_total == n for p in parts)
-        assert torch.equal(torch.cat([p.matmul_t(x) for p in parts], 1), full)
-        assert np.array_equal(np.concatenate([p.data() for p in parts]), w)
+    whole = _upload(Q, dt, w, n, k)
+    for m in (1, 3):
+        x = torch.from_numpy(synth.make_activation(m, k, seed=90)).to(DEV)
+        full = whole.matmul_t(x)
+        assert torch.equal(whole.matmul_t(x), full), "same launch, same bits"
+        for g in (2, 4, 8):
+            parts = [_upload(Q, dt, w, n, k, shard_rank=r, shard_count=g) for r in range(g)]
+            assert [p.row0 for p in parts] == [r * n // g for r in range(g)] and all(p.n_total == n for p in parts)
+            cat = torch.cat([p.matmul_t(x) for p in parts], 1)
+            if m == 1:
+                assert torch.equal(cat, full)
+            else:
+                assert_close_ref(cat.cpu().numpy(), full.cpu().numpy(), TOL_F32, f"{dt.name} {g} shards")
+            assert np.array_equal(np.concatenate([p.data() for p in parts]), w)
 
 
 # ---- the benchmark configurations at full size ---------------------------------------------------
@@ -258,7 +269,9 @@ def test_full_size_properties_without_oracle(Q, dt):
     assert err.max().item() < 2e-3, err.max().item()
     rb = dt.row_bytes(k)
     sub = Q.QCudaTensor.from_rows(dt, w[1000 * rb:1512 * rb], n, k, 1000, 512, DEV)
-    assert torch.equal(sub.matmul_t(x), got[:, 1000:1512])
+    assert torch.equal(sub.matmul_t(x[:1]), t.matmul_t(x[:1])[:, 1000:1512])      # one row: bit for bit
+    sub_err = (sub.matmul_t(x) - got[:, 1000:1512]).abs() / got[:, 1000:1512].abs().clamp(min=1.0)
+    assert sub_err.max().item() < 2e-3, sub_err.max().item()                      # several rows: k is cut by launch size
 
 
 @pytest.mark.parametrize("dt", WEIGHT_TYPES)

@@ -56,6 +56,8 @@ def lib() -> ctypes.CDLL:
     L.xnq_matmul_workspace_bytes.restype = sz
     L.xnq_matmul_t.argtypes = [vp, vp, ci, i64, i64, vp, ci, i64, vp, sz, vp]
     L.xnq_linear_forward_host.argtypes = [vp, vp, i64, vp, vp, vp]
+    L.xnq_weight_reserve_host_staging.argtypes = [vp, i64]
+    L.xnq_hint_next_weight.argtypes = [vp]
     L.xnq_matmul_t_static.argtypes = [vp, vp, ci, i64, i64, vp, ci, i64, vp]
     L.xnq_comm_create.argtypes = [ci, ci, sz, ci, pvp]
     L.xnq_comm_ipc_handle.argtypes = [vp, vp]
@@ -78,8 +80,6 @@ def lib() -> ctypes.CDLL:
     L.xnq_launch_count.restype = ctypes.c_uint64
     L.xnq_profile_begin.argtypes = [ci]
     L.xnq_profile_end.argtypes = [ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ci)]
-    L.xnq_debug_trace.argtypes = [vp, ctypes.POINTER(ctypes.c_uint)]
-    L.xnq_debug_prefill_trace.argtypes = [vp]
     _lib = L
     return L
 

@@ -2,6 +2,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <algorithm>
 #include <atomic>
 #include <mutex>
 #include <new>
@@ -27,6 +28,8 @@ static std::atomic<bool> g_opt_matvec_tma{true};
 static std::atomic<int> g_opt_gather_cta_fence{1};
 static std::atomic<int> g_opt_host_direct_y{1};
 static std::atomic<int> g_opt_matvec_mma{1};
+static std::atomic<int> g_opt_imma{1};
+static bool use_imma(const xnq_weight *w, int64_t m) { return m >= 2 && m <= IMMA_MAX_M && g_opt_imma.load(std::memory_order_relaxed) && imma_supported(w->v, m); }
 // Small batches: the integer-MMA kernel where it serves the weight and wins (Q4_K, five rows and up), else the
 // dp4a kernel. Returns the rows per launch.
 int64_t small_batch_pass(const xnq_weight *w, int64_t m, int y_dtype, bool *use_mma) {
@@ -116,7 +119,8 @@ using namespace xnq;
 
 // xnq_matmul_t on activations that were quantized ahead of the call (x_dtype == XNQ_ACT_IMAGE): the decode
 // kernels read the image directly; nothing is quantized and no scratch is used.
-static int matmul_from_image(const xnq_weight *w, const void *image, int64_t m, void *y, int y_dtype, int64_t ldy, cudaStream_t s) {
+static int matmul_from_image(const xnq_weight *w, const void *image, int64_t m, void *y, int y_dtype, int64_t ldy, void *workspace, size_t ws_bytes,
+                             cudaStream_t s) {
   const int64_t k = w->v.k, n = w->v.n;
   if (m < 0 || m > MATVEC_MAX_M) return fail(XNQ_ERR_SIZE, "matmul_t: an activation image serves 0..%d rows, m = %lld", MATVEC_MAX_M, (long long)m);
   if (!is_float_dtype(y_dtype)) return fail(XNQ_ERR_DTYPE, "matmul_t: output dtype %d is not f32/f16/bf16", y_dtype);
@@ -127,6 +131,9 @@ static int matmul_from_image(const xnq_weight *w, const void *image, int64_t m, 
   if (!aligned(y, type_size(y_dtype))) return fail(XNQ_ERR_ALIGN, "matmul_t: y is not aligned to its element size");
   const int adt = act_dtype_for(w->v.dtype);
   int rc;
+  // two rows and up: the integer tensor-core kernel, where the caller gave it its scratch (it re-lays the image out)
+  if (use_imma(w, m) && workspace && aligned(workspace, 256) && ws_bytes >= imma_workspace_bytes(m, k, n))
+    return launch_imma(w->v, image, XNQ_ACT_IMAGE, m, k, y, y_dtype, ldy, workspace, s);
   if (matvec_tma_enabled() && matvec_tma_supported(w->v, m)) {
     profile_mark(s, true);
     rc = launch_matvec_tma(w->v, image, XNQ_ACT_IMAGE, y, y_dtype, s);
@@ -219,16 +226,18 @@ int xnq_init(int device) {
   if ((rc = matvec_mma_init(device)) != XNQ_OK) return rc;
   if ((rc = matvec_tma_init(device)) != XNQ_OK) return rc;
   if ((rc = prefill_init(device)) != XNQ_OK) return rc;
+  if ((rc = imma_init(device)) != XNQ_OK) return rc;
   return XNQ_OK;
 }
 
 int xnq_device_status(unsigned int *bits) {
   clear_error();
   if (!bits) return fail(XNQ_ERR_NULL, "device_status: bits is NULL");
-  unsigned int mv = 0, pf = 0;
+  unsigned int mv = 0, pf = 0, im = 0;
   int rc = matvec_status(&mv);
   if (rc == XNQ_OK) rc = prefill_status(&pf);
-  *bits = mv | (pf << 8);
+  if (rc == XNQ_OK) rc = imma_status(&im);
+  *bits = mv | (pf << 8) | (im << 16);
   return rc;
 }
 
@@ -238,19 +247,15 @@ int xnq_device_check_record(unsigned long long out[8]) {
   return matvec_check_record(out);
 }
 
-int xnq_debug_prefill_trace(unsigned long long out[16]) { return prefill_trace(out); }
-
-int xnq_debug_trace(unsigned long long *out, unsigned int *n) {
-  clear_error();
-  if (!out || !n) return fail(XNQ_ERR_NULL, "debug_trace: NULL");
-  return matvec_trace(out, n);
-}
-
 int xnq_set_option(const char *name, int value) {
   clear_error();
   if (!name) return fail(XNQ_ERR_NULL, "set_option: name is NULL");
   if (std::strcmp(name, "matvec_tma") == 0) {
     g_opt_matvec_tma.store(value != 0);
+    return XNQ_OK;
+  }
+  if (std::strcmp(name, "imma") == 0) {
+    g_opt_imma.store(value);
     return XNQ_OK;
   }
   if (std::strcmp(name, "matvec_mma") == 0) {
@@ -263,18 +268,6 @@ int xnq_set_option(const char *name, int value) {
   }
   if (std::strcmp(name, "gather_cta_fence") == 0) {
     g_opt_gather_cta_fence.store(value);
-    return XNQ_OK;
-  }
-  if (std::strcmp(name, "prefill_persistent") == 0) {
-    prefill_set_persistent(value);
-    return XNQ_OK;
-  }
-  if (std::strcmp(name, "prefill_dbg") == 0) {
-    prefill_set_dbg(value);
-    return XNQ_OK;
-  }
-  if (std::strcmp(name, "matvec_tma_dbg") == 0) {
-    matvec_tma_set_dbg(value);
     return XNQ_OK;
   }
   return fail(XNQ_ERR_UNSUPPORTED, "set_option: unknown option '%s'", name);
@@ -472,10 +465,17 @@ int xnq_quantize_weight(int ggml_dtype, const float *x_dev, int64_t n, int64_t k
   return launch_quantize_weight(ggml_dtype, x_dev, n, k, blocks_dev, static_cast<cudaStream_t>(stream));
 }
 
+int xnq_hint_next_weight(const xnq_weight *w) {
+  clear_error();
+  matvec_hint_next(w);
+  return XNQ_OK;
+}
+
 size_t xnq_matmul_workspace_bytes(const xnq_weight *w, int64_t max_m) {
   if (!w || max_m <= 0) return 0;
   const int64_t rows = max_m < MATVEC_MAX_M ? max_m : MATVEC_MAX_M;
-  const size_t decode = act_workspace_bytes(rows, w->v.k, act_dtype_for(w->v.dtype));
+  size_t decode = act_workspace_bytes(rows, w->v.k, act_dtype_for(w->v.dtype));
+  if (max_m >= 2 && imma_supported(w->v, 2)) decode = std::max(decode, imma_workspace_bytes(std::min<int64_t>(max_m, IMMA_MAX_M), w->v.k, w->v.n));
   if (max_m <= MATVEC_MAX_M) return decode;
   const size_t prefill = prefill_workspace_bytes(max_m, w->v.k, w->v.n); // m > 16 runs on the tensor cores
   return prefill > decode ? prefill : decode;
@@ -486,7 +486,7 @@ int xnq_matmul_t(const xnq_weight *w, const void *x, int x_dtype, int64_t m, int
   clear_error();
   if (!w) return fail(XNQ_ERR_NULL, "matmul_t: weight is NULL");
   const int64_t k = w->v.k, n = w->v.n;
-  if (x_dtype == XNQ_ACT_IMAGE) return matmul_from_image(w, x, m, y, y_dtype, ldy, static_cast<cudaStream_t>(stream));
+  if (x_dtype == XNQ_ACT_IMAGE) return matmul_from_image(w, x, m, y, y_dtype, ldy, workspace, ws_bytes, static_cast<cudaStream_t>(stream));
   int rc = check_activations("matmul_t", x, x_dtype, m, k, ldx);
   if (rc != XNQ_OK) return rc;
   if (!is_float_dtype(y_dtype)) return fail(XNQ_ERR_DTYPE, "matmul_t: output dtype %d is not f32/f16/bf16", y_dtype);
@@ -498,19 +498,28 @@ int xnq_matmul_t(const xnq_weight *w, const void *x, int x_dtype, int64_t m, int
   if (!workspace) return fail(XNQ_ERR_NULL, "matmul_t: workspace is NULL (need %zu bytes)", need);
   if (!aligned(workspace, 256)) return fail(XNQ_ERR_ALIGN, "matmul_t: workspace must be 256-byte aligned");
   if (ws_bytes < need) return fail(XNQ_ERR_SIZE, "matmul_t: workspace has %zu bytes, m = %lld needs %zu", ws_bytes, (long long)m, need);
-  bool use_mma = false;
-  const int64_t pass = small_batch_pass(w, m, y_dtype, &use_mma);
-  if (pass == 0) return fail(XNQ_ERR_SIZE, "matmul_t: k = %lld is too large for the shared-memory staging of one activation row", (long long)k);
-
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (g_opt_matvec_tma.load(std::memory_order_relaxed) && matvec_tma_supported(w->v, m)) {
-    // decode fast path: one kernel, activations quantized in its prologue, no scratch
+    // decode fast path: one kernel; activations quantized in its prologue (k <= 4096, no scratch) or, for longer
+    // rows, by the stand-alone quantizer into the workspace as an activation image
+    const void *xin = x;
+    int xin_dtype = x_dtype;
+    if (matvec_tma_wants_image(w->v)) {
+      const ActView a = act_view(workspace, 1, k, act_dtype_for(w->v.dtype));
+      if ((rc = launch_quantize_act_planar(a, x, x_dtype, ldx, s)) != XNQ_OK) return rc;
+      xin = workspace;
+      xin_dtype = XNQ_ACT_IMAGE;
+    }
     profile_mark(s, true);
-    rc = launch_matvec_tma(w->v, x, x_dtype, y, y_dtype, s);
+    rc = launch_matvec_tma(w->v, xin, xin_dtype, y, y_dtype, s);
     profile_mark(s, false);
     return rc;
   }
+  if (use_imma(w, m)) return launch_imma(w->v, x, x_dtype, m, ldx, y, y_dtype, ldy, workspace, s); // exact integer dots on the tensor cores
   if (m > MATVEC_MAX_M) return launch_prefill(w->v, w->wscale, x, x_dtype, m, ldx, y, y_dtype, ldy, workspace, s);
+  bool use_mma = false;
+  const int64_t pass = small_batch_pass(w, m, y_dtype, &use_mma);
+  if (pass == 0) return fail(XNQ_ERR_SIZE, "matmul_t: k = %lld is too large for the shared-memory staging of one activation row", (long long)k);
   const int adt = act_dtype_for(w->v.dtype);
   const size_t xes = type_size(x_dtype), yes = type_size(y_dtype);
   for (int64_t r0 = 0; r0 < m; r0 += pass) {
@@ -527,6 +536,29 @@ int xnq_matmul_t(const xnq_weight *w, const void *x, int x_dtype, int64_t m, int
   return XNQ_OK;
 }
 
+// device staging of xnq_linear_forward_host for up to m rows: activations | result | bias | matmul workspace
+static size_t host_staging_bytes(const xnq_weight *w, int64_t m, size_t *xb, size_t *yb, size_t *bb, size_t *wsb) {
+  const int64_t k = w->v.k, n = w->v.n;
+  *xb = up256((size_t)m * k * 4), *yb = up256((size_t)m * n * 4), *bb = up256((size_t)n * 4);
+  *wsb = up256(xnq_matmul_workspace_bytes(w, m));
+  return *xb + *yb + *bb + *wsb;
+}
+
+int xnq_weight_reserve_host_staging(xnq_weight *w, int64_t max_m) {
+  clear_error();
+  if (!w) return fail(XNQ_ERR_NULL, "reserve_host_staging: weight is NULL");
+  if (max_m < 1) return fail(XNQ_ERR_SHAPE, "reserve_host_staging: max_m = %lld", (long long)max_m);
+  size_t xb, yb, bb, wsb;
+  const size_t need = host_staging_bytes(w, max_m, &xb, &yb, &bb, &wsb);
+  if (w->stage_dev_bytes >= need) return XNQ_OK;
+  if (w->stage_dev) cudaFree(w->stage_dev);
+  w->stage_dev = nullptr;
+  w->stage_dev_bytes = 0;
+  XNQ_CUDA(cudaMalloc(&w->stage_dev, need));
+  w->stage_dev_bytes = need;
+  return XNQ_OK;
+}
+
 int xnq_linear_forward_host(xnq_weight *w, const float *x_host, int64_t m, const float *bias_host, float *y_host, void *stream) {
   clear_error();
   if (!w) return fail(XNQ_ERR_NULL, "linear_forward_host: weight is NULL");
@@ -535,15 +567,15 @@ int xnq_linear_forward_host(xnq_weight *w, const float *x_host, int64_t m, const
   if (m == 0 || n == 0) return XNQ_OK;
   if (!x_host || !y_host) return fail(XNQ_ERR_NULL, "linear_forward_host: x_host or y_host is NULL");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const size_t xb = up256((size_t)m * k * 4), yb = up256((size_t)m * n * 4), bb = up256((size_t)n * 4);
-  const size_t wsb = up256(xnq_matmul_workspace_bytes(w, m));
-  const size_t need = xb + yb + bb + wsb;
-  if (w->stage_dev_bytes < need) {
-    if (w->stage_dev) cudaFree(w->stage_dev);
-    w->stage_dev = nullptr;
-    w->stage_dev_bytes = 0;
-    XNQ_CUDA(cudaMalloc(&w->stage_dev, need));
-    w->stage_dev_bytes = need;
+  size_t xb, yb, bb, wsb;
+  const size_t need = host_staging_bytes(w, m, &xb, &yb, &bb, &wsb);
+  if (w->stage_dev_bytes < need) { // not reserved ahead of time: grow now (this allocates, so it must not happen inside a stream capture)
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+      return fail(XNQ_ERR_UNSUPPORTED, "linear_forward_host: m = %lld needs %zu bytes of staging, %zu are reserved, and the stream is being captured; "
+                  "call xnq_weight_reserve_host_staging first", (long long)m, need, w->stage_dev_bytes);
+    const int rc0 = xnq_weight_reserve_host_staging(w, m);
+    if (rc0 != XNQ_OK) return rc0;
   }
   char *base = static_cast<char *>(w->stage_dev);
   float *xd = reinterpret_cast<float *>(base);
@@ -556,7 +588,8 @@ int xnq_linear_forward_host(xnq_weight *w, const float *x_host, int64_t m, const
   // saves the device-to-host copy and its launch; anything else goes through the staging buffer. The
   // activations are always copied in: every CTA reads all of x, which must not cross the host link 148 times.
   float *y_direct = nullptr;
-  if (!bias_host && m <= MATVEC_MAX_M && g_opt_host_direct_y.load(std::memory_order_relaxed)) {
+  // (not where the small-batch kernel splits k between CTAs that add into y atomically: that needs device memory)
+  if (!bias_host && m <= MATVEC_MAX_M && !(m >= 5 && matvec_mma_accumulates_in_y(w->v, m)) && g_opt_host_direct_y.load(std::memory_order_relaxed)) {
     cudaPointerAttributes attr;
     if (cudaPointerGetAttributes(&attr, y_host) == cudaSuccess && attr.type == cudaMemoryTypeHost && attr.devicePointer &&
         (reinterpret_cast<uintptr_t>(attr.devicePointer) & 15) == 0)

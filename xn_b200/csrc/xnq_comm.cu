@@ -221,7 +221,18 @@ int xnq_matmul_t_gather(const xnq_weight *w, xnq_comm *c, int slot, int layout, 
     } else if ((rc = check_activations("matmul_t_gather", x, x_dtype, m, w->v.k, ldx)) != XNQ_OK) {
       return rc;
     }
-    rc = launch_matvec_tma(w->v, x, x_dtype, nullptr, y_dtype, s, &g); // stores go to every rank's slot from inside the kernel
+    const void *xin = x;
+    int xin_dtype = x_dtype;
+    if (x_dtype != XNQ_ACT_IMAGE && matvec_tma_wants_image(w->v)) { // long rows: quantized into the workspace first
+      const size_t need = act_workspace_bytes(1, w->v.k, act_dtype_for(w->v.dtype));
+      if (!workspace || ws_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255))
+        return fail(XNQ_ERR_SIZE, "matmul_t_gather: k = %lld needs a 256-byte aligned workspace of %zu bytes", (long long)w->v.k, need);
+      const ActView a = act_view(workspace, 1, w->v.k, act_dtype_for(w->v.dtype));
+      if ((rc = launch_quantize_act_planar(a, x, x_dtype, ldx, s)) != XNQ_OK) return rc;
+      xin = workspace;
+      xin_dtype = XNQ_ACT_IMAGE;
+    }
+    rc = launch_matvec_tma(w->v, xin, xin_dtype, nullptr, y_dtype, s, &g); // stores go to every rank's slot from inside the kernel
     if (rc != XNQ_OK) return rc;
   } else {
     rc = xnq_matmul_t(w, x, x_dtype, m, ldx, local + (size_t)col0 * es, y_dtype, nt, workspace, ws_bytes, s);

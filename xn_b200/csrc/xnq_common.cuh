@@ -215,12 +215,15 @@ int64_t matvec_rows_per_pass(int wdtype, int64_t k);
 // xnq_matvec_mma.cu  (5 <= m <= 16, Q4_K: integer tensor-core MMAs)
 int64_t matvec_mma_rows_per_pass(const WeightView &w, int y_dtype); // 0: not served
 int launch_matvec_mma(const WeightView &w, const ActView &a, void *y, int y_dtype, int64_t ldy, cudaStream_t s);
+bool matvec_mma_accumulates_in_y(const WeightView &w, int64_t m); // k split between CTAs that add into y atomically
 int matvec_mma_init(int device);
 // rows per launch of the small-batch path that xnq_matmul_t takes for this weight, and which kernel that is
 int64_t small_batch_pass(const xnq_weight *w, int64_t m, int y_dtype, bool *use_mma);
 
-// xnq_matvec_tma.cu  (m == 1, k <= 4096: persistent TMA-ring kernel that quantizes x in its prologue)
+// xnq_matvec_ring.cu  (m == 1: persistent bulk-copy ring kernel; quantizes x in its prologue when k <= 4096)
 bool matvec_tma_supported(const WeightView &w, int64_t m);
+bool matvec_tma_wants_image(const WeightView &w); // k above 4096: the activations must come as an activation image
+void matvec_hint_next(const xnq_weight *w);        // the weight the calling thread's stream multiplies next (one-shot)
 // g != nullptr: results go to column col0 + row of every rank's gathered buffer (y is ignored)
 int launch_matvec_tma(const WeightView &w, const void *x, int x_dtype, void *y, int y_dtype, cudaStream_t s, const GatherArgs *g = nullptr);
 bool matvec_tma_enabled(); // the "matvec_tma" library option
@@ -229,19 +232,23 @@ int gather_cta_fence_scope(); // the "gather_cta_fence" library option
 int check_activations(const char *who, const void *x, int x_dtype, int64_t m, int64_t k, int64_t ldx);
 int matvec_tma_init(int device);
 int matvec_status(unsigned int *bits);
-void matvec_tma_set_dbg(int v);
 int matvec_check_record(unsigned long long out[8]);
-int matvec_trace(unsigned long long *out, unsigned int *n);
 
-// xnq_prefill.cu  (m > 16: tcgen05 / TMEM contraction on fp16 operands)
+// xnq_imma.cu  (2 <= m: tcgen05 kind::i8, exact integer block sums; Q4_0 / Q8_0 / Q4_K)
+bool imma_supported(const WeightView &w, int64_t m);
+size_t imma_workspace_bytes(int64_t m, int64_t k, int64_t n);
+int launch_imma(const WeightView &w, const void *x, int x_dtype, int64_t m, int64_t ldx, void *y, int y_dtype, int64_t ldy, void *workspace,
+                cudaStream_t s);
+int imma_init(int device);
+int imma_status(unsigned int *bits);
+constexpr int64_t IMMA_MAX_M = 64; // batches up to here take the integer tensor-core kernel; larger ones the fp16 one
+
+// xnq_prefill.cu  (m > 64, and Q6_K above 16 rows: tcgen05 / TMEM contraction on fp16 operands)
 size_t prefill_workspace_bytes(int64_t m, int64_t k, int64_t n);
 int launch_prefill(const WeightView &w, float wscale, const void *x, int x_dtype, int64_t m, int64_t ldx, void *y, int y_dtype, int64_t ldy,
                    void *workspace, cudaStream_t s);
 int prefill_init(int device);
 int prefill_status(unsigned int *bits);
-void prefill_set_dbg(int v);
-void prefill_set_persistent(int v);
-int prefill_trace(unsigned long long out[16]);
 
 // largest |dequantized weight| of the tensor, written to *dev_out (a float in device memory)
 int launch_max_abs(const WeightView &w, float *dev_out, cudaStream_t s);

@@ -1,0 +1,891 @@
+// Small batches (2 <= m <= 64 activation rows per pass) on the 5th-generation tensor cores with exact
+// integer arithmetic: tcgen05.mma.kind::i8, one tensor-memory accumulator slice per 32-element block.
+//
+// The reference's dots are exact integer sums over one 32-element (sub-)block, scaled in f32
+// (k_quants.rs:287-304 Q4_0, 677-691 Q8_0, 1337-1416 Q4_K). One MMA
+//
+//     D[128 weight rows, NP activation rows] = A[128, 32] . B[NP, 32]^T          (s8 x s8 -> s32, no accumulation)
+//
+// is exactly those sums for 128 x NP (weight row, activation row) pairs and one block, so every MMA writes
+// its own slice of tensor memory and the drain warps apply the block's scales to it in f32 exactly as the
+// CPU code does: integer sub-block scales and mins for Q4_K (min term from the activations' 32-sums with
+// dp4a), f16 block scale times f16-rounded activation scale for Q4_0 / Q8_0. Nothing is rounded before the
+// f32 scaling, so results stay within the f32-accumulate bound (2e-3) at every batch size served.
+//
+// Roles of the 26 warps of a CTA (one CTA per SM, persistent):
+//   producer (1)    per 256-k step one tiled TMA copy per weight stream (cp.async.bulk.tensor.2d, never multicast:
+//                   a box of 128 rows x the step's bytes, rows past the end arrive as zeros) and 1-D bulk copies of
+//                   the quantized activations (already in the MMA's shared-memory layout) and of their per-block
+//                   metadata, into rings of stages guarded by mbarriers. (One bulk copy per weight row was tried
+//                   first: the copy engine takes some 60 ns per copy whatever its size, 128 small copies per step
+//                   cost more than the step.)
+//   converters (8)  two groups of four warps, one thread per weight row; group h unpacks 4-bit codes to int8 (or
+//                   copies int8 codes) of half h (128 k) of every 256-k step from the raw stage into the
+//                   128-byte-swizzled K-major operand image the MMA reads; group 0 also hands the row's scale
+//                   bytes on to the drain;
+//   MMA issuer (1)  one thread issues four K = 32 MMAs per half step into accumulator buffer h; an MMA of this
+//                   shape occupies the tensor pipe for about 114 cycles whatever N <= 128 is (measured), which
+//                   bounds a tile of k = 4096 at 128 x 114 cycles;
+//   drain (16)      two groups of eight warps; group h owns accumulator buffer h: reads its slices back with
+//                   tcgen05.ld, scales, and keeps f32 sums in registers across the k steps of a tile; two warps
+//                   per accumulator lane quarter split the columns. At the end of a segment the odd half steps'
+//                   sums are added to the even ones' (always in that order).
+//
+// Work is the flattened (tile of 128 weight rows, 256-k step) space, cut into equal contiguous ranges, one
+// per CTA, so all SMs finish together however few tiles there are. A tile whose steps are split between
+// CTAs is summed deterministically: every part is written to a scratch slot, an arrival ticket elects the
+// last part, and that CTA adds the parts in k order and stores y.
+//
+// Every wait is bounded; on expiry a status bit is set and the roles fall through to the common exit, where
+// tensor memory is released.
+#include <cuda.h> // CUtensorMap and the encoder's signature only; the entry point is looked up at run time, nothing links against libcuda
+
+#include <algorithm>
+#include <cstring>
+
+#include "xnq_common.cuh"
+#include "xnq_quantize_act.cuh"
+
+namespace xnq {
+
+__device__ unsigned int g_imma_status; // sticky: 1 producer, 2 converter, 4 mma, 8 drain wait expired
+#ifdef XNQ_DEV_TRACE
+__device__ long long g_imma_trace[32]; // development builds only: cycles block 0's roles spend in each wait
+#define XNQ_T0() long long t0_ = clock64()
+#define XNQ_TACC(i) do { const long long t1_ = clock64(); tacc[i] += t1_ - t0_; t0_ = t1_; } while (0)
+#define XNQ_TDECL long long tacc[6] = {0, 0, 0, 0, 0, 0}; long long t0_ = clock64()
+#define XNQ_TDUMP(base, cond) do { if ((cond) && blockIdx.x == 0) for (int i_ = 0; i_ < 6; i_++) g_imma_trace[(base) + i_] = tacc[i_]; } while (0)
+#else
+#define XNQ_TACC(i) do { } while (0)
+#define XNQ_TDECL do { } while (0)
+#define XNQ_TDUMP(base, cond) do { } while (0)
+#endif
+
+namespace {
+
+constexpr int TILE_N = 128;         // weight rows per tile = UMMA M
+constexpr int MAX_NP = 64;          // activation rows per pass = UMMA N (multiple of 16)
+constexpr int CONV_WARPS = 8, DRAIN_WARPS = 16;
+constexpr int PRODUCER_WARP = 0, MMA_WARP = 1, CONV_WARP0 = 2, DRAIN_WARP0 = CONV_WARP0 + CONV_WARPS;
+constexpr int NTHREADS = (DRAIN_WARP0 + DRAIN_WARPS) * 32; // 832
+constexpr int A_STAGE_BYTES = TILE_N * 128; // one 128-k half step of int8 codes
+constexpr int A_STAGES = 4, SIDE_STAGES = 4, MAX_RAW_STAGES = 4;
+constexpr int HDR_BYTES = TILE_N * 16;      // per 256-k step: 16 bytes of scale data per weight row
+constexpr int ACC_COLS = 256;               // tensor-memory columns of one accumulator buffer: 4 slices x NP <= 256
+constexpr uint32_t WAIT_LIMIT = 1u << 26;   // non-blocking polls (a few ns each): about a second
+constexpr size_t IMMA_SMEM = 226 * 1024;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// bounded wait of one thread
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int bit) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+    if (mbar_test(bar, parity)) return true;
+  atomicOr(&g_imma_status, bit);
+  return false;
+}
+// bounded wait of a whole warp: lane 0 polls (32 lanes polling one word keep the shared-memory pipe busy for
+// nothing), the other lanes park on the warp barrier
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, unsigned int bit) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, bit) ? 1 : 0;
+  __syncwarp();
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+               "r"(bytes), "r"(bar)
+               : "memory");
+}
+// tiled TMA load of the box at (x = byte offset inside the rows, y = first row); x must be a multiple of 16
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+               "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, const uint4 &v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// ---- tcgen05 wrappers --------------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// D = A . B^T (no accumulation: every MMA owns its accumulator slice)
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(0u)
+      : "memory");
+}
+// arrives on the mbarrier once every MMA issued so far by this thread has finished reading smem / writing tmem
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[N]);
+template <>
+__device__ __forceinline__ void tmem_ld<4>(uint32_t taddr, uint32_t (&r)[4]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr) : "memory");
+}
+template <>
+__device__ __forceinline__ void tmem_ld<8>(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, 128-byte-swizzled operand tile: rows of 128 bytes, 8-row groups 1024 bytes apart.
+// Fields: start address >> 4 [0,14), leading byte offset >> 4 [16,30) (unused for swizzled K-major),
+// stride byte offset >> 4 [32,46), descriptor version 1 [46,48), swizzle mode 2 = 128 B [61,64).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3ffffu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// kind::i8 instruction descriptor: D s32 (2 at [4,6)), A and B signed 8-bit (1 at [7,10) / [10,13)), both K-major,
+// N >> 3 at [17,23), M >> 4 at [24,29).
+__device__ __forceinline__ uint32_t idesc_i8(int umma_n) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(umma_n >> 3) << 17) | ((uint32_t)(TILE_N >> 4) << 24);
+}
+__device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c) {
+  int d;
+  asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+struct ImmaArgs {
+  WeightView w;
+  const uint8_t *bimg; // quantized activations in operand layout: [half steps][NP rows x 128 bytes, 128-byte swizzle]
+  const uint8_t *meta; // per 256-k step and activation row: 32 bytes of scales / sums (layout per format below)
+  void *y;
+  int y_dtype;
+  int64_t ldy;
+  int64_t m;           // activation rows of this pass (<= NP)
+  int nsteps;          // 256-k steps per tile
+  int tiles;
+  long long units;     // tiles * nsteps
+  unsigned int *tile_cnt; // [tiles] arrival tickets of split tiles, zeroed by the prepare kernel
+  float *partials;        // [2 * grid][NP][128] partial sums of split tiles
+  float *pair_scratch;    // [grid][NP][128]: the odd half steps' sums on their way to the even ones'
+  // raw weight bytes: per stream a tensor map over [n rows][row bytes] with a box of 128 rows x step_bytes; offset inside a raw stage
+  CUtensorMap tmap[2];
+  int nstreams;
+  uint32_t step_bytes[2], raw_off[2];
+  int raw_stages, b_stages;
+  uint32_t raw_stage_bytes, b_stage_bytes, side_stage_bytes;
+  uint32_t a_off, b_off, raw_off0, side_off; // offsets from the 1024-aligned base of dynamic shared memory
+};
+
+// position in the flattened (tile, step) space
+__device__ __forceinline__ int cta_of(long long u, long long units, int G) {
+  int c = (int)((u * G) / units);
+  while (c + 1 < G && units * (c + 1) / G <= u) c++;
+  while (c > 0 && units * c / G > u) c--;
+  return c;
+}
+
+// ---- converters: raw bytes of (row, 64 of the half step's 128 k) -> 64 bytes of int8 codes ------------------
+// raw: shared address of the row's bytes of the stage (stream 0); h: half step (0/1) of the 256-k step; p: which 64.
+struct ConvQ8_0 { // 256 code bytes per row and step
+  __device__ static __forceinline__ void run(uint32_t raw, int h, int p, uint4 (&out)[4]) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) out[i] = lds128(raw + 128 * h + 64 * p + 16 * i);
+  }
+};
+__device__ __forceinline__ uint32_t nib_lo_s8(uint32_t w) { return (((w & 0x0f0f0f0fu) | 0x80808080u) - 0x08080808u) ^ 0x80808080u; } // code - 8 per byte
+__device__ __forceinline__ uint32_t nib_hi_s8(uint32_t w) { return ((((w >> 4) & 0x0f0f0f0fu) | 0x80808080u) - 0x08080808u) ^ 0x80808080u; }
+struct ConvQ4_0 { // 8 blocks of 16 nibble bytes per row and step; element j < 16 low nibble of byte j, j >= 16 high nibble of byte j - 16
+  __device__ static __forceinline__ void run(uint32_t raw, int h, int p, uint4 (&out)[4]) {
+#pragma unroll
+    for (int bb = 0; bb < 2; bb++) {
+      const uint4 q = lds128(raw + (4 * h + 2 * p + bb) * 16);
+      out[2 * bb] = make_uint4(nib_lo_s8(q.x), nib_lo_s8(q.y), nib_lo_s8(q.z), nib_lo_s8(q.w));
+      out[2 * bb + 1] = make_uint4(nib_hi_s8(q.x), nib_hi_s8(q.y), nib_hi_s8(q.z), nib_hi_s8(q.w));
+    }
+  }
+};
+struct ConvQ4K { // 144-byte super-block: 16 header bytes, then four 32-byte chunks; chunk c = sub-block 2c in the low nibbles, 2c+1 in the high ones
+  __device__ static __forceinline__ void run(uint32_t raw, int h, int p, uint4 (&out)[4]) {
+    const uint4 a = lds128(raw + 16 + 32 * (2 * h + p)), b = lds128(raw + 32 + 32 * (2 * h + p));
+    out[0] = make_uint4(a.x & 0x0f0f0f0fu, a.y & 0x0f0f0f0fu, a.z & 0x0f0f0f0fu, a.w & 0x0f0f0f0fu);
+    out[1] = make_uint4(b.x & 0x0f0f0f0fu, b.y & 0x0f0f0f0fu, b.z & 0x0f0f0f0fu, b.w & 0x0f0f0f0fu);
+    out[2] = make_uint4((a.x >> 4) & 0x0f0f0f0fu, (a.y >> 4) & 0x0f0f0f0fu, (a.z >> 4) & 0x0f0f0f0fu, (a.w >> 4) & 0x0f0f0f0fu);
+    out[3] = make_uint4((b.x >> 4) & 0x0f0f0f0fu, (b.y >> 4) & 0x0f0f0f0fu, (b.z >> 4) & 0x0f0f0f0fu, (b.w >> 4) & 0x0f0f0f0fu);
+  }
+};
+
+// ---- drain: scale the four slices of a half step and add them to the running sums ----------------------------
+// hdr: the row's 16 scale bytes of the 256-k step; meta: shared address of the step's per-activation-row records
+// (32 bytes each); v[j][c]: slice j (block 4h + j of the step), column c of this thread; c0: first column.
+//   Q4_0 / Q8_0  hdr = eight f16 block scales; record = eight f32 activation block scales
+//   Q4_K         hdr = f16 d, f16 dmin, four 24-bit fields sc[2g] | sc[2g+1] << 6 | mn[2g] << 12 | mn[2g+1] << 18;
+//                record = {lo(h=0), hi(h=0), lo(h=1), hi(h=1), f32 d, 0, 0, 0}: the four sub-blocks' 32-sums of the
+//                activation codes, s = 128 * hi + lo with lo in 0..127 (one byte each)
+template <int CH>
+struct DrainBlockScaled {
+  __device__ static __forceinline__ void run(const uint4 &hdr, uint32_t meta, int h, int c0, const uint32_t (&v)[4][CH], float *acc) {
+    const uint32_t w0 = h ? hdr.z : hdr.x, w1 = h ? hdr.w : hdr.y;
+    const __half2 h0 = *reinterpret_cast<const __half2 *>(&w0), h1 = *reinterpret_cast<const __half2 *>(&w1);
+    const float dw[4] = {__low2float(h0), __high2float(h0), __low2float(h1), __high2float(h1)};
+#pragma unroll
+    for (int c = 0; c < CH; c++) {
+      const uint4 da = lds128(meta + (uint32_t)(c0 + c) * 32 + 16 * h);
+      acc[c] += (float)(int)v[0][c] * (dw[0] * __uint_as_float(da.x));
+      acc[c] += (float)(int)v[1][c] * (dw[1] * __uint_as_float(da.y));
+      acc[c] += (float)(int)v[2][c] * (dw[2] * __uint_as_float(da.z));
+      acc[c] += (float)(int)v[3][c] * (dw[3] * __uint_as_float(da.w));
+    }
+  }
+};
+template <int CH>
+struct DrainQ4K {
+  __device__ static __forceinline__ void run(const uint4 &hdr, uint32_t meta, int h, int c0, const uint32_t (&v)[4][CH], float *acc) {
+    const __half2 dm = *reinterpret_cast<const __half2 *>(&hdr.x);
+    const float d = __low2float(dm), dmin = __high2float(dm);
+    // fields 2h and 2h + 1: bits [48h, 48h + 48) of the 96-bit field array in hdr.y, hdr.z, hdr.w
+    const uint32_t lo32 = h ? __funnelshift_r(hdr.z, hdr.w, 16) : hdr.y;
+    const uint32_t hi16 = h ? (hdr.w >> 16) : (hdr.z & 0xffffu);
+    const uint32_t f0 = lo32 & 0xffffffu, f1 = __funnelshift_r(lo32, hi16, 24) & 0xffffffu;
+    const int sc0 = f0 & 63, sc1 = (f0 >> 6) & 63, sc2 = f1 & 63, sc3 = (f1 >> 6) & 63;
+    const uint32_t mins = ((f0 >> 12) & 63) | (((f0 >> 18) & 63) << 8) | (((f1 >> 12) & 63) << 16) | (((f1 >> 18) & 63) << 24);
+#pragma unroll
+    for (int c = 0; c < CH; c++) {
+      const uint32_t rec = meta + (uint32_t)(c0 + c) * 32;
+      const uint2 bs = lds64(rec + 8 * h);
+      const float da = __uint_as_float(lds32(rec + 16));
+      const int isum = sc0 * (int)v[0][c] + sc1 * (int)v[1][c] + sc2 * (int)v[2][c] + sc3 * (int)v[3][c];
+      const int msum = dp4a_uu(mins, bs.x, 0) + dp4a_us(mins, bs.y, 0) * 128;
+      acc[c] += da * (d * (float)isum - dmin * (float)msum);
+    }
+  }
+};
+
+template <typename Conv, template <int> class Drain, int NP>
+__global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant__ ImmaArgs p) {
+  constexpr int NPT = NP / 2; // columns per drain thread: the eight warps of a half-step group are two per accumulator lane quarter
+  constexpr int CH = NPT > 16 ? 4 : (NPT > 8 ? 8 : NPT); // columns read back at a time: what the register budget holds next to the sums
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u; // operand stages need 1024-byte alignment
+  // barriers: raw_full/raw_empty [4], a_full/mma_done [4], b_full/b_empty [4], side_full/side_empty [4], acc_empty [2]
+  __shared__ __align__(8) uint64_t bars[34];
+  __shared__ uint32_t tmem_slot;
+  __shared__ unsigned int s_ticket;
+  const uint32_t raw_full = smem_u32(bars), raw_empty = raw_full + 32, a_full = raw_full + 64, mma_done = raw_full + 96, b_full = raw_full + 128,
+                 b_empty = raw_full + 160, side_full = raw_full + 192, side_empty = raw_full + 224, acc_empty = raw_full + 256;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int RS = p.raw_stages, BS = p.b_stages;
+  const int KT = p.nsteps;
+  const int G = gridDim.x;
+  const long long u0 = p.units * blockIdx.x / G, u1 = p.units * (blockIdx.x + 1) / G;
+  const int nunits = (int)(u1 - u0);
+  const int tile0 = (int)(u0 / KT), kt0 = (int)(u0 % KT);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 4; s++) {
+      mbar_init(raw_full + 8 * s, 1);
+      mbar_init(raw_empty + 8 * s, CONV_WARPS);
+      mbar_init(a_full + 8 * s, CONV_WARPS / 2); // the four converter warps of the half step's group
+      mbar_init(mma_done + 8 * s, 1);            // the half step's MMAs have read their operands and written their slices
+      mbar_init(b_full + 8 * s, 1);
+      mbar_init(b_empty + 8 * s, 1);
+      mbar_init(side_full + 8 * s, 1 + CONV_WARPS / 2); // the producer's transaction + the four converter warps that copy the scale bytes
+      mbar_init(side_empty + 8 * s, DRAIN_WARPS);
+    }
+    for (int b = 0; b < 2; b++) mbar_init(acc_empty + 8 * b, DRAIN_WARPS / 2);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == MMA_WARP) { // one warp owns the tensor-memory allocation
+    tmem_alloc(smem_u32(&tmem_slot), 2 * ACC_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_d = tmem_slot;
+
+  if (warp == PRODUCER_WARP) {
+    // ---- producer: per 256-k step the raw rows of the tile, the activations' operand image, their records ----
+    if (lane == 0) {
+      bool alive = true;
+      XNQ_TDECL;
+      auto load_raw = [&](int i) { // unit i of this CTA's range
+        const long long u = u0 + i;
+        const int tile = (int)(u / KT), kt = (int)(u % KT), rs = i % RS;
+        mbar_expect_tx(raw_full + 8 * rs, (uint32_t)TILE_N * (p.step_bytes[0] + (p.nstreams > 1 ? p.step_bytes[1] : 0u))); // a box counts in full, zero fill included
+        const uint32_t dst = base + p.raw_off0 + rs * p.raw_stage_bytes;
+        tma_load_2d(dst + p.raw_off[0], &p.tmap[0], kt * (int)p.step_bytes[0], tile * TILE_N, raw_full + 8 * rs);
+        if (p.nstreams > 1) tma_load_2d(dst + p.raw_off[1], &p.tmap[1], kt * (int)p.step_bytes[1], tile * TILE_N, raw_full + 8 * rs);
+      };
+      // weights are immutable after upload: the first stages are requested while the kernel that prepares the
+      // activations (the previous one in the stream) is still running
+      for (int i = 0; i < RS && i < nunits; i++) load_raw(i);
+      pdl_wait();
+      int kt = kt0;
+      for (int i = 0; i < nunits && alive; i++) {
+        const int rs = i % RS, bs = i % BS, ss = i % SIDE_STAGES;
+        XNQ_TACC(0);
+        if (i >= RS) {
+          alive = mbar_wait(raw_empty + 8 * rs, ((i / RS) - 1) & 1, 1u);
+          if (alive) load_raw(i);
+        }
+        XNQ_TACC(1);
+        if (alive && i >= BS) alive = mbar_wait(b_empty + 8 * bs, ((i / BS) - 1) & 1, 1u);
+        XNQ_TACC(2);
+        if (alive && i >= SIDE_STAGES) alive = mbar_wait(side_empty + 8 * ss, ((i / SIDE_STAGES) - 1) & 1, 1u);
+        XNQ_TACC(3);
+        if (!alive) break;
+        mbar_expect_tx(b_full + 8 * bs, p.b_stage_bytes);
+        mbar_expect_tx(side_full + 8 * ss, (uint32_t)NP * 32u);
+        bulk_g2s(base + p.b_off + bs * p.b_stage_bytes, p.bimg + ((size_t)kt * 2) * (NP * 128), p.b_stage_bytes, b_full + 8 * bs);
+        bulk_g2s(base + p.side_off + ss * p.side_stage_bytes + HDR_BYTES, p.meta + (size_t)kt * (NP * 32), (uint32_t)NP * 32u, side_full + 8 * ss);
+        if (++kt == KT) kt = 0;
+      }
+      XNQ_TDUMP(0, true);
+    }
+    // nothing may be in flight into this CTA's shared memory when it exits: the consumers wait for every stage they
+    // were promised, so the copies have landed once the other roles are done (they fall through on a timeout only)
+  } else if (warp == MMA_WARP) {
+    // ---- MMA issuer ------------------------------------------------------------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = idesc_i8(NP);
+      bool alive = true;
+      XNQ_TDECL;
+      for (int i = 0; i < nunits && alive; i++) {
+        const int bs = i % BS;
+        XNQ_TACC(0);
+        alive = mbar_wait(b_full + 8 * bs, (i / BS) & 1, 4u);
+        XNQ_TACC(1);
+        for (int h = 0; h < 2 && alive; h++) {
+          const int j = 2 * i + h, sa = j % A_STAGES;
+          XNQ_TACC(0);
+          alive = mbar_wait(a_full + 8 * sa, (j / A_STAGES) & 1, 4u);
+          XNQ_TACC(2);
+          if (alive && i >= 1) alive = mbar_wait(acc_empty + 8 * h, (i - 1) & 1, 4u); // buffer h: the drain of the previous step's half h
+          XNQ_TACC(3);
+          if (!alive) break;
+          tc_fence_after();
+          const uint64_t adesc = smem_desc_sw128(base + p.a_off + sa * A_STAGE_BYTES);
+          const uint64_t bdesc = smem_desc_sw128(base + p.b_off + bs * p.b_stage_bytes + h * (NP * 128));
+#pragma unroll
+          for (int q = 0; q < 4; q++) // K = 32 per instruction: advance 32 bytes inside the swizzle row; slice q of the buffer
+            umma_i8(tmem_d + (uint32_t)(h * ACC_COLS + q * NP), adesc + (uint64_t)(q * 2), bdesc + (uint64_t)(q * 2), idesc);
+          XNQ_TACC(4);
+          umma_commit(mma_done + 8 * sa); // one arrival serves the converters (the stage is free) and the drain (the slices are written)
+          XNQ_TACC(5);
+        }
+        if (alive) umma_commit(b_empty + 8 * bs);
+      }
+      XNQ_TDUMP(6, true);
+    }
+  } else if (warp < DRAIN_WARP0) {
+    // ---- converters: group h (four warps, one thread per weight row) produces half step h of every 256-k step ----
+    const int cw = warp - CONV_WARP0;
+    const int r = (cw & 3) * 32 + lane, h = cw >> 2;
+    const int sw = r & 7;
+    bool alive = true;
+    XNQ_TDECL;
+    for (int i = 0; i < nunits && alive; i++) {
+      const int rs = i % RS, ss = i % SIDE_STAGES;
+      const int j = 2 * i + h, sa = j % A_STAGES;
+      XNQ_TACC(0);
+      alive = mbar_wait_warp(raw_full + 8 * rs, (i / RS) & 1, 2u);
+      XNQ_TACC(1);
+      if (!alive) break;
+      const uint32_t raw = base + p.raw_off0 + rs * p.raw_stage_bytes;
+      if (h == 0) { // hand the row's 16 scale bytes to the drain
+        if (i >= SIDE_STAGES) alive = mbar_wait_warp(side_empty + 8 * ss, ((i / SIDE_STAGES) - 1) & 1, 2u);
+        XNQ_TACC(2);
+        if (!alive) break;
+        const uint4 hv = p.nstreams > 1 ? lds128(raw + p.raw_off[1] + (uint32_t)r * 16) : lds128(raw + (uint32_t)r * p.step_bytes[0]);
+        sts128(base + p.side_off + ss * p.side_stage_bytes + (uint32_t)r * 16, hv);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(side_full + 8 * ss);
+      }
+      XNQ_TACC(0);
+      if (j >= A_STAGES) alive = mbar_wait_warp(mma_done + 8 * sa, ((j / A_STAGES) - 1) & 1, 2u);
+      XNQ_TACC(3);
+      if (!alive) break;
+      uint4 lo[4], hi[4];
+      Conv::run(raw + p.raw_off[0] + (uint32_t)r * p.step_bytes[0], h, 0, lo);
+      Conv::run(raw + p.raw_off[0] + (uint32_t)r * p.step_bytes[0], h, 1, hi);
+      const uint32_t dst_row = base + p.a_off + sa * A_STAGE_BYTES + (uint32_t)r * 128;
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        sts128(dst_row + (uint32_t)((c ^ sw) << 4), lo[c]);
+        sts128(dst_row + (uint32_t)(((4 + c) ^ sw) << 4), hi[c]);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic-proxy stores -> visible to the tensor core
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(a_full + 8 * sa);
+        mbar_arrive(raw_empty + 8 * rs); // this warp has read all it needs of the raw stage
+      }
+    }
+    XNQ_TDUMP(12, threadIdx.x == CONV_WARP0 * 32);
+  } else {
+    // ---- drain: group h (eight warps) owns accumulator buffer h and half step h of every 256-k step. Warp quarter q
+    // reads accumulator lanes 32q.. (weight rows); the two warps of a quarter split the columns. Each group keeps its own
+    // f32 sums; at the end of a segment group 1 hands its sums to group 0 through scratch memory. ----
+    const int dwi = warp - DRAIN_WARP0;
+    const int q = warp & 3, h = dwi >> 3, cg = (dwi >> 2) & 1;
+    const int c0 = cg * NPT;
+    const int et = threadIdx.x - DRAIN_WARP0 * 32; // 0..511
+    pdl_wait(); // the kernel that prepares the activations also zeroes the tiles' tickets
+    bool alive = true;
+    int tile = tile0, kt = kt0;
+    float acc[NPT];
+#pragma unroll
+    for (int c = 0; c < NPT; c++) acc[c] = 0.f;
+    int seg_kt0 = kt0; // first step of the current segment inside its tile
+    float *pair = p.pair_scratch + (size_t)blockIdx.x * NP * TILE_N; // group 1 -> group 0
+    XNQ_TDECL;
+    for (int i = 0; i < nunits; i++) {
+      const int ss = i % SIDE_STAGES;
+      const int j = 2 * i + h, sa = j % A_STAGES;
+      XNQ_TACC(0);
+      if (alive) alive = mbar_wait_warp(side_full + 8 * ss, (i / SIDE_STAGES) & 1, 8u);
+      XNQ_TACC(1);
+      const uint32_t side = base + p.side_off + ss * p.side_stage_bytes;
+      uint4 hdr = make_uint4(0, 0, 0, 0);
+      if (alive) hdr = lds128(side + (uint32_t)(32 * q + lane) * 16);
+      if (alive) alive = mbar_wait_warp(mma_done + 8 * sa, (j / A_STAGES) & 1, 8u);
+      XNQ_TACC(2);
+      if (alive) {
+        tc_fence_after();
+        const uint32_t taddr = tmem_d + ((uint32_t)(32 * q) << 16) + (uint32_t)(h * ACC_COLS + c0);
+#pragma unroll
+        for (int ch = 0; ch < NPT / CH; ch++) { // eight columns at a time keeps the slices' values within the register budget
+          uint32_t v[4][CH];
+#pragma unroll
+          for (int s = 0; s < 4; s++) tmem_ld<CH>(taddr + (uint32_t)(s * NP + ch * CH), v[s]);
+          tmem_ld_wait();
+          XNQ_TACC(3);
+          if (ch == NPT / CH - 1) { // every value of the buffer this warp needs is in registers: it may be overwritten
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty + 8 * h);
+          }
+          Drain<CH>::run(hdr, side + HDR_BYTES, h, c0 + ch * CH, v, acc + ch * CH);
+        }
+      }
+      __syncwarp();
+      if (alive && lane == 0) mbar_arrive(side_empty + 8 * ss);
+      // ---- end of a segment (the tile's last step, or this CTA's last unit): store or hand over the sums ----
+      const bool tile_end = kt == KT - 1, range_end = i == nunits - 1;
+      if (tile_end || range_end) {
+        const int64_t row = (int64_t)tile * TILE_N + 32 * q + lane;
+        // group 1's sums (the odd half steps) join group 0's (the even ones): always even + odd, whatever the timing
+        if (h == 1) {
+#pragma unroll
+          for (int c = 0; c < NPT; c++) pair[(size_t)(c0 + c) * TILE_N + 32 * q + lane] = acc[c];
+          __threadfence_block();
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_WARPS * 32) : "memory");
+        if (h == 0) {
+#pragma unroll
+          for (int c = 0; c < NPT; c++) acc[c] += pair[(size_t)(c0 + c) * TILE_N + 32 * q + lane];
+        }
+        const bool whole = seg_kt0 == 0 && tile_end;
+        if (whole) {
+          if (h == 0 && alive && row < p.w.n) {
+#pragma unroll
+            for (int c = 0; c < NPT; c++) {
+              const int64_t col = c0 + c;
+              if (col < p.m) {
+                const int64_t idx = col * p.ldy + row;
+                if (p.y_dtype == XNQ_F32) static_cast<float *>(p.y)[idx] = acc[c];
+                else if (p.y_dtype == XNQ_F16) static_cast<__half *>(p.y)[idx] = __float2half_rn(acc[c]);
+                else static_cast<__nv_bfloat16 *>(p.y)[idx] = __float2bfloat16_rn(acc[c]);
+              }
+            }
+          }
+          asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_WARPS * 32) : "memory"); // group 0 has read the scratch: it may be rewritten
+        } else {
+          // this CTA's first segment (it starts where the CTA's range starts) uses scratch slot 2c, a later one 2c + 1
+          const long long seg_u0 = (long long)tile * KT + seg_kt0;
+          float *mine = p.partials + ((size_t)2 * blockIdx.x + (seg_u0 == u0 ? 0 : 1)) * NP * TILE_N;
+          if (h == 0) {
+#pragma unroll
+            for (int c = 0; c < NPT; c++) mine[(size_t)(c0 + c) * TILE_N + 32 * q + lane] = acc[c];
+            __threadfence();
+          }
+          asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_WARPS * 32) : "memory");
+          if (et == 0) s_ticket = atomicAdd(p.tile_cnt + tile, 1u);
+          asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_WARPS * 32) : "memory");
+          const unsigned int ticket = s_ticket;
+          asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_WARPS * 32) : "memory"); // s_ticket may be rewritten from here on
+          const long long t_u0 = (long long)tile * KT, t_u1 = t_u0 + KT;
+          const int c_first = cta_of(t_u0, p.units, G), c_last = cta_of(t_u1 - 1, p.units, G);
+          if (h == 0 && (int)ticket == c_last - c_first) { // the last part to arrive adds all parts in k order
+            __threadfence();
+            float (&sum)[NPT] = acc; // the segment's own sums are in its scratch slot by now
+#pragma unroll
+            for (int c = 0; c < NPT; c++) sum[c] = 0.f;
+            for (int cc = c_first; cc <= c_last; cc++) {
+              const long long cu0 = p.units * cc / G;
+              const float *part = p.partials + ((size_t)2 * cc + (cu0 >= t_u0 ? 0 : 1)) * NP * TILE_N;
+#pragma unroll
+              for (int c = 0; c < NPT; c++) sum[c] += __ldcg(part + (size_t)(c0 + c) * TILE_N + 32 * q + lane);
+            }
+            if (row < p.w.n) {
+#pragma unroll
+              for (int c = 0; c < NPT; c++) {
+                const int64_t col = c0 + c;
+                if (col < p.m) {
+                  const int64_t idx = col * p.ldy + row;
+                  if (p.y_dtype == XNQ_F32) static_cast<float *>(p.y)[idx] = sum[c];
+                  else if (p.y_dtype == XNQ_F16) static_cast<__half *>(p.y)[idx] = __float2half_rn(sum[c]);
+                  else static_cast<__nv_bfloat16 *>(p.y)[idx] = __float2bfloat16_rn(sum[c]);
+                }
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < NPT; c++) acc[c] = 0.f;
+        seg_kt0 = 0;
+      }
+      if (++kt == KT) {
+        kt = 0;
+        tile++;
+      }
+    }
+    XNQ_TDUMP(18, threadIdx.x == DRAIN_WARP0 * 32);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+#ifdef XNQ_DEV_TRACE
+  if (blockIdx.x == 0 && threadIdx.x == 0) g_imma_trace[30] = nunits;
+#endif
+  if (warp == MMA_WARP) tmem_dealloc(tmem_d, 2 * ACC_COLS);
+}
+
+// ---- activations: quantize (or take an activation image), lay out as the MMA's B operand, write the records ----
+// One CTA of 256 threads per activation row of the padded pass (rows >= m are zero). Thread t handles elements
+// 8t..8t+7 of each 2048-element stretch; a warp covers one 256-element block.
+template <int ACT, typename XT>
+__global__ void __launch_bounds__(256) imma_prepare(const XT *__restrict__ x, const int8_t *__restrict__ img_q, const float *__restrict__ img_d,
+                                                    const int16_t *__restrict__ img_b, int64_t m, int64_t k, int64_t ldx, int NP, int nsteps,
+                                                    uint8_t *__restrict__ bimg, uint8_t *__restrict__ meta, unsigned int *__restrict__ tile_cnt, int tiles) {
+  const int row = blockIdx.x;
+  if (blockIdx.x == 0)
+    for (int i = threadIdx.x; i < tiles; i += blockDim.x) tile_cnt[i] = 0;
+  const int lane = threadIdx.x & 31;
+  const int64_t kpad = (int64_t)nsteps * 256;
+  const int nblk_act = (int)(k / (ACT == XNQ_Q8_0 ? QK : QK_K));
+  for (int64_t base = 0; base < kpad; base += 2048) {
+    const int64_t k8 = base + (int64_t)threadIdx.x * 8;
+    if (base + (int64_t)(threadIdx.x & ~31) * 8 >= kpad) break; // whole warps leave together
+    uint32_t lo = 0, hi = 0;
+    float d = 0.f;
+    int sum16 = 0;
+    const bool valid = row < m && k8 < k;
+    if (img_q) {
+      if (valid) {
+        const uint2 c = *reinterpret_cast<const uint2 *>(img_q + (int64_t)row * k + k8);
+        lo = c.x, hi = c.y;
+        d = img_d[(int64_t)row * nblk_act + (ACT == XNQ_Q8_0 ? k8 / QK : k8 / QK_K)];
+        sum16 = img_b[(int64_t)row * (k / 16) + k8 / 16];
+      }
+    } else {
+      float v[8];
+      if (valid) load8(x + (int64_t)row * ldx + k8, v);
+      else {
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = 0.f;
+      }
+      const Quant8 qv = ACT == XNQ_Q8_0 ? quantize8_q8_0(v, lane) : quantize8_q8k(v, lane);
+      lo = qv.lo, hi = qv.hi, d = qv.d, sum16 = qv.sum16;
+    }
+    if (k8 < kpad) {
+      // operand image: half step hs = k8 / 128, row `row`, 16-byte chunk (k8 % 128) / 16 swizzled with the row
+      const int64_t hs = k8 >> 7;
+      const int chunk = (int)((k8 & 127) >> 4);
+      uint8_t *dst = bimg + (size_t)hs * (NP * 128) + (size_t)(row >> 3) * 1024 + (size_t)(row & 7) * 128 + (size_t)((chunk ^ (row & 7)) << 4) + (k8 & 8);
+      *reinterpret_cast<uint2 *>(dst) = make_uint2(lo, hi);
+      uint32_t *rec = reinterpret_cast<uint32_t *>(meta + ((size_t)(k8 >> 8) * NP + row) * 32);
+      if (ACT == XNQ_Q8_0) {
+        if ((lane & 3) == 0) rec[(k8 & 255) >> 5] = __float_as_uint(d); // eight f32 block scales (0 beyond k)
+      } else {
+        // 32-sums of the block's eight sub-blocks: lanes 4s .. 4s+3 hold sub-block s; sum16 is the pair sum on both lanes of a pair
+        const int s32 = sum16 + __shfl_xor_sync(0xffffffffu, sum16, 2);
+        const int sub = lane >> 2;
+        uint32_t lo_b = (lane & 3) == 0 ? ((uint32_t)(s32 & 127) << (8 * (sub & 3))) : 0u;
+        uint32_t hi_b = (lane & 3) == 0 ? ((uint32_t)((s32 >> 7) & 0xff) << (8 * (sub & 3))) : 0u;
+        // combine the four sub-blocks of each half of the block: lanes 0..15 -> words 0 / 1, lanes 16..31 -> words 2 / 3
+#pragma unroll
+        for (int off = 4; off <= 8; off <<= 1) {
+          lo_b |= __shfl_xor_sync(0xffffffffu, lo_b, off);
+          hi_b |= __shfl_xor_sync(0xffffffffu, hi_b, off);
+        }
+        if (lane == 0 || lane == 16) {
+          rec[(lane >> 4) * 2] = lo_b;
+          rec[(lane >> 4) * 2 + 1] = hi_b;
+        }
+        if (lane == 0) {
+          rec[4] = __float_as_uint(d);
+          rec[5] = rec[6] = rec[7] = 0u;
+        }
+      }
+    }
+  }
+}
+
+int g_sms = 0;
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode_tiled = nullptr;
+
+// [rows][row_bytes] bytes, box of 128 rows x box_bytes, no swizzle, out-of-range bytes read as zero
+int make_row_map(CUtensorMap *map, const void *base, uint64_t row_bytes, uint64_t rows, uint32_t box_bytes) {
+  if (!g_encode_tiled) return fail(XNQ_ERR_UNSUPPORTED, "imma: the driver's tensor-map encoder was not found");
+  const cuuint64_t dims[2] = {row_bytes, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {box_bytes, (cuuint32_t)TILE_N};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(XNQ_ERR_CUDA, "imma: cuTensorMapEncodeTiled failed (%d) for rows of %llu bytes", (int)r, (unsigned long long)row_bytes);
+  return XNQ_OK;
+}
+
+struct Plan {
+  int NP, nsteps, tiles, grid;
+  size_t bimg_bytes, meta_bytes, cnt_bytes, part_bytes, pair_bytes;
+};
+Plan plan_for(int64_t m, int64_t k, int64_t n) {
+  Plan pl{};
+  pl.NP = m <= 16 ? 16 : (m <= 32 ? 32 : 64);
+  pl.nsteps = (int)((k + 255) / 256);
+  pl.tiles = (int)((n + TILE_N - 1) / TILE_N);
+  const long long units = (long long)pl.tiles * pl.nsteps;
+  pl.grid = (int)std::max<long long>(1, std::min<long long>(g_sms > 0 ? g_sms : 148, units / 2)); // at least two steps per CTA
+  auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  pl.bimg_bytes = up((size_t)pl.nsteps * 2 * pl.NP * 128);
+  pl.meta_bytes = up((size_t)pl.nsteps * pl.NP * 32);
+  pl.cnt_bytes = up((size_t)pl.tiles * 4);
+  pl.part_bytes = up((size_t)2 * (g_sms > 0 ? g_sms : 148) * pl.NP * TILE_N * 4);
+  pl.pair_bytes = up((size_t)(g_sms > 0 ? g_sms : 148) * pl.NP * TILE_N * 4);
+  return pl;
+}
+
+template <typename Conv, template <int> class Drain>
+int launch_np(const ImmaArgs &a, int NP, unsigned grid, cudaStream_t s) {
+  // programmatic stream serialization: the kernel starts while the one that prepares the activations still runs; only
+  // its weight loads are issued before griddepcontrol.wait
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(NTHREADS);
+  cfg.dynamicSmemBytes = IMMA_SMEM;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (NP == 16) XNQ_CUDA(cudaLaunchKernelEx(&cfg, imma_kernel<Conv, Drain, 16>, a));
+  else if (NP == 32) XNQ_CUDA(cudaLaunchKernelEx(&cfg, imma_kernel<Conv, Drain, 32>, a));
+  else XNQ_CUDA(cudaLaunchKernelEx(&cfg, imma_kernel<Conv, Drain, 64>, a));
+  count_launch();
+  return XNQ_OK;
+}
+
+template <typename Conv, template <int> class Drain>
+int init_np() {
+  XNQ_CUDA(cudaFuncSetAttribute(imma_kernel<Conv, Drain, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)IMMA_SMEM));
+  XNQ_CUDA(cudaFuncSetAttribute(imma_kernel<Conv, Drain, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)IMMA_SMEM));
+  XNQ_CUDA(cudaFuncSetAttribute(imma_kernel<Conv, Drain, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)IMMA_SMEM));
+  return XNQ_OK;
+}
+
+} // namespace
+
+bool imma_supported(const WeightView &w, int64_t m) {
+  if (g_sms <= 0 || !g_encode_tiled || m < 1 || w.n < 1) return false;
+  if (w.dtype != XNQ_Q4_0 && w.dtype != XNQ_Q8_0 && w.dtype != XNQ_Q4K) return false;
+  return true;
+}
+
+// scratch of one call: the activations' operand image and records, the split tiles' tickets and partial sums
+size_t imma_workspace_bytes(int64_t m, int64_t k, int64_t n) {
+  const Plan pl = plan_for(std::min<int64_t>(m, MAX_NP), k, n);
+  return pl.bimg_bytes + pl.meta_bytes + pl.cnt_bytes + pl.part_bytes + pl.pair_bytes + 256;
+}
+
+// x: float activations [m, k] (x_dtype F32 / F16 / BF16, row stride ldx) or an activation image (XNQ_ACT_IMAGE) of m rows.
+int launch_imma(const WeightView &w, const void *x, int x_dtype, int64_t m, int64_t ldx, void *y, int y_dtype, int64_t ldy, void *workspace,
+                cudaStream_t s) {
+  const int64_t k = w.k;
+  const int act = act_dtype_for(w.dtype);
+  const size_t yes = type_size(y_dtype);
+  for (int64_t r0 = 0; r0 < m; r0 += MAX_NP) { // passes of at most 64 activation rows
+    const int64_t rows = std::min<int64_t>(MAX_NP, m - r0);
+    const Plan pl = plan_for(rows, k, w.n);
+    uint8_t *ws = static_cast<uint8_t *>(workspace);
+    uint8_t *bimg = ws;
+    uint8_t *meta = bimg + pl.bimg_bytes;
+    unsigned int *cnt = reinterpret_cast<unsigned int *>(meta + pl.meta_bytes);
+    float *partials = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(cnt) + pl.cnt_bytes);
+    // ---- activations ----
+    const int8_t *iq = nullptr;
+    const float *id = nullptr;
+    const int16_t *ib = nullptr;
+    if (x_dtype == XNQ_ACT_IMAGE) {
+      const ActView av = act_view(const_cast<void *>(x), m, k, act);
+      const int blk = act == XNQ_Q8_0 ? QK : QK_K;
+      iq = av.q + r0 * k, id = av.d + r0 * (k / blk), ib = av.bsum + r0 * (k / 16);
+    }
+#define XNQ_IMMA_PREP(ACT, XT)                                                                                                          \
+  imma_prepare<ACT, XT><<<(unsigned)pl.NP, 256, 0, s>>>(iq ? nullptr : static_cast<const XT *>(x) + r0 * ldx, iq, id, ib, rows, k, ldx, pl.NP, \
+                                                        pl.nsteps, bimg, meta, cnt, pl.tiles)
+    if (act == XNQ_Q8_0) {
+      if (x_dtype == XNQ_F16) XNQ_IMMA_PREP(XNQ_Q8_0, __half);
+      else if (x_dtype == XNQ_BF16) XNQ_IMMA_PREP(XNQ_Q8_0, __nv_bfloat16);
+      else XNQ_IMMA_PREP(XNQ_Q8_0, float);
+    } else {
+      if (x_dtype == XNQ_F16) XNQ_IMMA_PREP(XNQ_Q8K, __half);
+      else if (x_dtype == XNQ_BF16) XNQ_IMMA_PREP(XNQ_Q8K, __nv_bfloat16);
+      else XNQ_IMMA_PREP(XNQ_Q8K, float);
+    }
+#undef XNQ_IMMA_PREP
+    XNQ_CUDA(cudaGetLastError());
+    count_launch();
+
+    ImmaArgs a{};
+    a.w = w;
+    a.bimg = bimg;
+    a.meta = meta;
+    a.y = static_cast<char *>(y) + (size_t)r0 * ldy * yes;
+    a.y_dtype = y_dtype;
+    a.ldy = ldy;
+    a.m = rows;
+    a.nsteps = pl.nsteps;
+    a.tiles = pl.tiles;
+    a.units = (long long)pl.tiles * pl.nsteps;
+    a.tile_cnt = cnt;
+    a.partials = partials;
+    a.pair_scratch = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(partials) + pl.part_bytes);
+    int rc;
+    switch (w.dtype) {
+      case XNQ_Q4K:
+        a.nstreams = 1, a.step_bytes[0] = 144;
+        if ((rc = make_row_map(&a.tmap[0], w.qs, (uint64_t)(k / QK_K * 144), (uint64_t)w.n, 144)) != XNQ_OK) return rc;
+        break;
+      case XNQ_Q8_0:
+        a.nstreams = 2, a.step_bytes[0] = 256, a.step_bytes[1] = 16;
+        if ((rc = make_row_map(&a.tmap[0], w.qs, (uint64_t)k, (uint64_t)w.n, 256)) != XNQ_OK) return rc;
+        if ((rc = make_row_map(&a.tmap[1], w.d, (uint64_t)(w.dstride * 2), (uint64_t)w.n, 16)) != XNQ_OK) return rc;
+        break;
+      case XNQ_Q4_0:
+        a.nstreams = 2, a.step_bytes[0] = 128, a.step_bytes[1] = 16;
+        if ((rc = make_row_map(&a.tmap[0], w.qs, (uint64_t)(k / 2), (uint64_t)w.n, 128)) != XNQ_OK) return rc;
+        if ((rc = make_row_map(&a.tmap[1], w.d, (uint64_t)(w.dstride * 2), (uint64_t)w.n, 16)) != XNQ_OK) return rc;
+        break;
+      default: return fail(XNQ_ERR_DTYPE, "imma: dtype %d", w.dtype);
+    }
+    a.raw_off[0] = 0;
+    a.raw_off[1] = TILE_N * a.step_bytes[0];
+    a.raw_stage_bytes = (TILE_N * (a.step_bytes[0] + (a.nstreams > 1 ? a.step_bytes[1] : 0)) + 127) & ~127u;
+    a.b_stage_bytes = (uint32_t)pl.NP * 256;
+    a.side_stage_bytes = HDR_BYTES + (uint32_t)pl.NP * 32;
+    // shared-memory plan: A stages | B stages | side stages | raw stages (as many as fit)
+    a.a_off = 0;
+    a.b_off = A_STAGES * A_STAGE_BYTES;
+    a.b_stages = pl.NP <= 32 ? 4 : 3;
+    a.side_off = a.b_off + a.b_stages * a.b_stage_bytes;
+    a.raw_off0 = (a.side_off + SIDE_STAGES * a.side_stage_bytes + 127) & ~127u;
+    const size_t avail = IMMA_SMEM - 1024 - a.raw_off0; // 1024: alignment slack of the base
+    a.raw_stages = (int)std::min<size_t>(MAX_RAW_STAGES, avail / a.raw_stage_bytes);
+    if (a.raw_stages < 2) return fail(XNQ_ERR_SIZE, "imma: shared-memory plan does not fit");
+    profile_mark(s, true);
+    if (w.dtype == XNQ_Q4K) rc = launch_np<ConvQ4K, DrainQ4K>(a, pl.NP, (unsigned)pl.grid, s);
+    else if (w.dtype == XNQ_Q8_0) rc = launch_np<ConvQ8_0, DrainBlockScaled>(a, pl.NP, (unsigned)pl.grid, s);
+    else rc = launch_np<ConvQ4_0, DrainBlockScaled>(a, pl.NP, (unsigned)pl.grid, s);
+    profile_mark(s, false);
+    if (rc != XNQ_OK) return rc;
+  }
+  return XNQ_OK;
+}
+
+int imma_init(int device) {
+  cudaDeviceProp prop;
+  XNQ_CUDA(cudaGetDeviceProperties(&prop, device));
+  g_sms = prop.multiProcessorCount;
+  if (!g_encode_tiled) { // the driver's encoder, looked up through the runtime so that the library needs no link against libcuda
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+      g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+    else
+      (void)cudaGetLastError();
+  }
+  int rc;
+  if ((rc = init_np<ConvQ4K, DrainQ4K>()) != XNQ_OK) return rc;
+  if ((rc = init_np<ConvQ8_0, DrainBlockScaled>()) != XNQ_OK) return rc;
+  if ((rc = init_np<ConvQ4_0, DrainBlockScaled>()) != XNQ_OK) return rc;
+  unsigned int zero = 0;
+  XNQ_CUDA(cudaMemcpyToSymbol(g_imma_status, &zero, sizeof(zero)));
+  return XNQ_OK;
+}
+
+#ifdef XNQ_DEV_TRACE
+extern "C" int xnq_dev_imma_trace(long long *out) { return cudaMemcpyFromSymbol(out, g_imma_trace, sizeof(long long) * 32) == cudaSuccess ? 0 : -6; }
+#endif
+
+int imma_status(unsigned int *bits) {
+  XNQ_CUDA(cudaMemcpyFromSymbol(bits, g_imma_status, sizeof(*bits)));
+  return XNQ_OK;
+}
+
+} // namespace xnq

@@ -269,6 +269,14 @@ int64_t matvec_mma_rows_per_pass(const WeightView &w, int y_dtype) {
   return 0;
 }
 
+// Whether a launch for m rows splits k between CTAs that add into a zeroed y with atomics (y must then be
+// ordinary device memory: atomics on mapped host memory are not atomic for the host and cross the host link one by one).
+bool matvec_mma_accumulates_in_y(const WeightView &w, int64_t m) {
+  if (w.dtype != XNQ_Q4K) return false;
+  const int64_t nspan = w.k / 256;
+  return (m <= 8 ? stage_bytes<1, 1>(nspan) : stage_bytes<2, 1>(nspan)) + RED_BYTES > MMA_SMEM_LIMIT;
+}
+
 int launch_matvec_mma(const WeightView &w, const ActView &a, void *y, int y_dtype, int64_t ldy, cudaStream_t s) {
   if (w.n == 0 || a.m == 0) return XNQ_OK;
   const int64_t pass = matvec_mma_rows_per_pass(w, y_dtype);
