@@ -50,9 +50,17 @@ WORKLOADS = {
     "C3_q4k_14336x4096_m64": (D.Q4K, 14336, 4096, 64),
     "C3_q4k_14336x4096_m512": (D.Q4K, 14336, 4096, 512),
 }
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
-# summarized under profiles/ (bytes; workloads without a capture report null)
-NCU_TRAFFIC = {"C3_q4k_14336x4096_m1": 33086464, "C3_q4k_14336x4096_m512": 38350000}
+
+
+def captured_traffic(name: str):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of the workload's dominant kernel, as the committed
+    ncu summary of that kernel recorded it (a small JSON file beside the summaries); None without a capture."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    try:
+        return json.load(open(path)).get(name)
+    except Exception:
+        return None
+
 DECODER_WORKLOADS = {"C5_llama7b_q4k_decode_b1": 1, "C5_llama7b_q4k_decode_b16": 16}  # batch
 DEFAULT_WORKLOAD = "C3_q4k_14336x4096_m1"  # the matvec the metric's 75%-of-HBM target is quoted on
 METRIC = "quant matvec HBM GB/s"
@@ -216,29 +224,136 @@ def reference_gpu_kernel(dt, n, k, m):
         return {"unavailable": str(e)[:200]}
 
 
-def run_ours(args, name, dt, n, k, m):
+
+def _graph_us(torch, dev, fn, calls: int, reps: int) -> float:
+    """Microseconds per call of `fn` (which makes `calls` library calls), replayed `reps` times from one CUDA graph and
+    timed with CUDA events on the launching stream."""
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize(dev)
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            fn()
+    torch.cuda.current_stream(dev).wait_stream(side)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    return e0.elapsed_time(e1) * 1e3 / (reps * calls)
+
+
+# the other BASELINE configurations, measured in the same run as the headline: (group, dtype, n, k, batch sizes)
+EXTRA_MATMULS = [
+    ("C1_q4_0_4096x4096", D.Q4_0, 4096, 4096, (1,)),
+    ("C2_q8_0_11008x4096", D.Q8_0, 11008, 4096, (1, 16, 128, 512)),
+    ("C3_q4k_14336x4096", D.Q4K, 14336, 4096, (4, 16, 64, 512)),
+    ("C4_q6k_128256x4096", D.Q6K, 128256, 4096, (1, 32)),
+]
+
+
+def extra_matmul_workloads(torch, L, Q, dev, l2: int, budget_s: float) -> list:
+    """Cold (R distinct weights, R x bytes >= 2 x L2) and warm (one weight again and again) time per call of every other
+    BASELINE matmul configuration, each with its roofline fraction against the measured peaks. Bounded in time: a
+    configuration that would start after the budget is spent is listed as skipped."""
+    peak, peak_tf, peak_kind = measured_peaks()
+    out = []
+    t_start = time.perf_counter()
+    for group, dt, n, k, ms in EXTRA_MATMULS:
+        if time.perf_counter() - t_start > budget_s:
+            out += [{"workload": f"{group}_m{m}", "skipped": "time budget of the default run"} for m in ms]
+            continue
+        wb = n * dt.row_bytes(k)
+        ncopies = int(min(32, max(2, np.ceil(2 * l2 / wb))))
+        weights = []
+        for i in range(ncopies):
+            weights.append(Q.QCudaTensor.from_qtensor(Q.QTensor(synth.make_weight(dt, n, k, seed=0, tensor_id=i), (n, k), dt), dev))
+        ref_gpu = {}
+        for m in ms:
+            x = torch.from_numpy(synth.make_activation(m, k, seed=0)).to(dev)
+            ys = [torch.empty((m, n), dtype=torch.float32, device=dev) for _ in range(ncopies)]
+            for w in weights:
+                w.workspace(m)
+
+            def cold():
+                for i, w in enumerate(weights):
+                    if m == 1:
+                        weights[(i + 1) % ncopies].hint_next()
+                    w.matmul_t(x, out=ys[i])
+
+            def warm():
+                for i in range(ncopies):
+                    weights[0].matmul_t(x, out=ys[0])
+
+            before = L.xnq_launch_count()
+            cold()
+            launches = (L.xnq_launch_count() - before) // ncopies
+            reps = int(max(3, min(40, 4e5 / max(1.0, wb / 1e6 * ncopies))))   # a few hundred ms of device time at most
+            cold_us = _graph_us(torch, dev, cold, ncopies, reps)
+            warm_us = _graph_us(torch, dev, warm, ncopies, reps)
+            bytes_ = algorithmic_bytes(dt, n, k, m)
+            flops = 2.0 * m * n * k
+            gbs, tf = bytes_ / cold_us / 1e3, flops / cold_us / 1e6
+            tensor_bound = m > 16 and (flops / (peak_tf * 1e12)) > (bytes_ / (peak * 1e9))
+            entry = {"workload": f"{group}_m{m}", "ggml_dtype": dt.name, "n": n, "k": k, "m": m, "weight_copies": ncopies,
+                     "cold_us_per_call": cold_us, "warm_us_per_call": warm_us, "launches_per_call": int(launches),
+                     "bound": "tensor" if tensor_bound else "hbm", "hbm_gbs": gbs, "tflops": tf,
+                     "frac": (tf / peak_tf) if tensor_bound else (gbs / peak), "peak_kind": f"of {peak_kind}"}
+            if dt == D.Q8_0 and m <= 16:
+                try:
+                    entry["reference_gpu"] = reference_gpu_kernel(dt, n, k, m)
+                except Exception as e:
+                    entry["reference_gpu"] = {"unavailable": str(e)[:160]}
+            out.append(entry)
+            del ys, x
+        del weights
+        torch.cuda.empty_cache()
+    return out
+
+
+class Ctx:
+    """One process per GPU: device, rank, world, the loaded library."""
+
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+
+        from xn_b200 import _lib, quantized as Q
+        self.torch, self.dist, self.Q = torch, dist, Q
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        if self.world != args.gpus and self.world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+        Q.init(self.dev)
+        self.L = _lib.lib()
+        for opt in args.option:
+            oname, val = opt.split("=")
+            _lib.check(self.L.xnq_set_option(oname.encode(), int(val)))
+
+    def close(self):
+        if self.world > 1:
+            self.dist.destroy_process_group()
+
+
+def measure_matmul(ctx, args, name, dt, n, k, m, with_cpu=True):
+    """The headline measurement of one matmul workload on ctx.world GPUs; returns the JSON line on rank 0, None elsewhere."""
     import ctypes
 
-    import torch
-    import torch.distributed as dist
-
-    from xn_b200 import _lib, quantized as Q
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
-            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    Q.init(dev)
-    L = _lib.lib()
-    for opt in args.option:
-        name, val = opt.split("=")
-        _lib.check(L.xnq_set_option(name.encode(), int(val)))
+    from xn_b200 import _lib
+    torch, dist, Q, L = ctx.torch, ctx.dist, ctx.Q, ctx.L
+    world, rank, local, dev = ctx.world, ctx.rank, ctx.local, ctx.dev
 
     props = torch.cuda.get_device_properties(dev)
     l2 = int(getattr(props, "L2_cache_size", 126 * 1024 * 1024))
@@ -267,6 +382,7 @@ def run_ours(args, name, dt, n, k, m):
         from xn_b200.parallel import PeerGather
         try:
             pg = PeerGather(dev, rank, world, slot_elems=m * n, nslots=ncopies)
+            pg.set_deferred(True)   # every copy gathers into its own slot: one wait per step instead of one barrier per launch
         except RuntimeError as e:   # raised on every rank together: peer mappings unavailable on this box
             sys.stderr.write(f"[bench] rank {rank}: {e}; gathering with NCCL instead\n")
             fused, pg = False, None
@@ -274,18 +390,26 @@ def run_ours(args, name, dt, n, k, m):
     for w in weights:
         w.workspace(m)
 
+    hint = m == 1   # a caller that loops over known weights names the next one: the kernel asks it into L2 as it finishes
+
     def local_step():
         for i, w in enumerate(weights):
+            if hint:
+                L.xnq_hint_next_weight(weights[(i + 1) % ncopies]._h)
             w.matmul_t(x, out=y_local[i])
 
     def step():
         for i, w in enumerate(weights):
+            if hint:
+                L.xnq_hint_next_weight(weights[(i + 1) % ncopies]._h)
             if fused:
                 pg.matmul_t(w, x, slot=i)       # the kernel stores its columns into every rank's slot i
             else:
                 w.matmul_t(x, out=y_local[i])
                 if world > 1:
                     dist.all_gather_into_tensor(y_full[i], y_local[i])
+        if fused:
+            pg.wait()                           # the peers' columns of the step's gathers
 
     def sync_all():
         torch.cuda.synchronize(dev)
@@ -376,7 +500,7 @@ def run_ours(args, name, dt, n, k, m):
                 "achieved": tflops if tensor_bound else achieved, "peak": peak_tf if tensor_bound else peak,
                 "unit": "TFLOP/s" if tensor_bound else "GB/s",
                 "frac": ((tflops / peak_tf) if tensor_bound else (achieved / peak)) if achieved else None,
-                "traffic": NCU_TRAFFIC.get(name) if world == 1 else None,
+                "traffic": captured_traffic(name) if world == 1 else None,
                 "kernel": "prefill_kernel (tcgen05)" if m > 16 else ("matvec_tma_kernel" if (m == 1 and k <= 4096) else "matvec"),
                 "launch_us": kern_ms * 1e3, "launches_timed": cnt.value, "peak_kind": f"of {peak_kind}",
                 "bytes_per_launch": kern_bytes, "flops_per_launch": flops, "hbm_gbs": achieved, "tflops": tflops,
@@ -393,26 +517,76 @@ def run_ours(args, name, dt, n, k, m):
     e2e_steps = max(1, min(args.steps, 50))
     y_pin = torch.empty((m, n_local), dtype=torch.float32, pin_memory=True)   # the result lands in page-locked host memory
     y_host = y_pin.numpy()
-    for w in weights[:2]:
-        w.forward_host(x_host, out=y_host)
-    # the timed calls go through the C entry itself (what a host binding calls), arguments prepared once
-    fwd = L.xnq_linear_forward_host
-    xp, yp = ctypes.c_void_p(x_host.ctypes.data), ctypes.c_void_p(y_host.ctypes.data)
-    sp = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
-    handles = [w._h for w in weights]
+    if world == 1:
+        for w in weights[:2]:
+            w.forward_host(x_host, out=y_host)
     sync_all()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        for h in handles:
-            if fwd(h, xp, m, None, yp, sp) != 0:
-                _lib.check(-1)
-    torch.cuda.synchronize(dev)
-    e2e_s = time.perf_counter() - t0
-    if world > 1:
+    if world == 1:
+        # the timed calls go through the C entry itself (what a host binding calls), arguments prepared once
+        fwd = L.xnq_linear_forward_host
+        xp, yp = ctypes.c_void_p(x_host.ctypes.data), ctypes.c_void_p(y_host.ctypes.data)
+        sp = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        handles = [w._h for w in weights]
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            for h in handles:
+                if fwd(h, xp, m, None, yp, sp) != 0:
+                    _lib.check(-1)
+        torch.cuda.synchronize(dev)
+        e2e_s = time.perf_counter() - t0
+        d2h_per_step = ncopies * m * n_local * 4
+        e2e_note = ("QLinear::forward on pinned host tensors (activations copied in, result stored to the pinned buffer by the kernel for "
+                    "m <= 16, copied back otherwise); one synchronize per call")
+    else:
+        # the whole operator: activations from pinned host memory, sharded matmul, gather, the gathered [m, n] back to host
+        x_dev = torch.empty_like(x)
+        y_pin_full = torch.empty((m * n,), dtype=torch.float32, pin_memory=True)
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            for i, w in enumerate(weights):
+                x_dev.copy_(x_pin, non_blocking=True)
+                if fused:
+                    yg = pg.matmul_t(w, x_dev, slot=i)
+                    pg.wait()
+                else:
+                    w.matmul_t(x_dev, out=y_local[i])
+                    dist.all_gather_into_tensor(y_full[i], y_local[i])
+                    yg = y_full[i]
+                y_pin_full.copy_(yg.reshape(-1), non_blocking=True)
+                torch.cuda.synchronize(dev)
+        e2e_s = time.perf_counter() - t0
         t = torch.tensor([e2e_s], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
+        d2h_per_step = ncopies * m * n * 4
+        e2e_note = "host activations in, N-sharded matmul, gather, the gathered [m, n] back to pinned host memory on every rank; one synchronize per call"
     e2e_value = e2e_steps * step_bytes / e2e_s / 1e9
+
+    # ---- N > 1: one gathered [m, n] per workload against the unsharded product (outside the timed region) ----
+    gather_check = None
+    if world > 1:
+        if fused:
+            got = pg.matmul_t(weights[0], x, slot=0)
+            pg.wait()
+            got = got.clone()
+            pg.matmul_t(weights[1 % ncopies], x, slot=1 % ncopies)   # a slot may not be named twice in a row
+            pg.wait()
+        else:
+            dist.all_gather_into_tensor(y_full[0], weights[0].matmul_t(x, out=y_local[0]))
+            got = y_full[0].permute(1, 0, 2).reshape(m, n).clone()
+        torch.cuda.synchronize(dev)
+        if rank == 0:
+            whole = Q.QCudaTensor.from_qtensor(Q.QTensor(synth.make_weight(dt, n, k, seed=0, tensor_id=0), (n, k), dt), dev)
+            want = whole.matmul_t(x)
+            err = float(((got.view(m, n) - want).abs() / want.abs().clamp(min=1.0)).max().item())
+            del whole
+        else:
+            err = 0.0
+        t = torch.tensor([err], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        gather_check = {"gather_checked": True, "gather_max_err": float(t.item())}
+        if float(t.item()) > 2e-3:
+            raise SystemExit(f"rank {rank}: the gathered result differs from the unsharded one by {float(t.item()):.3e}; the numbers are void")
 
     late = pg.late_peers() if pg is not None else 0
     if pg is not None:
@@ -420,26 +594,28 @@ def run_ours(args, name, dt, n, k, m):
         pg.close()
     if late:
         raise SystemExit(f"rank {rank}: gathers gave up waiting for peers {late:#x}; the numbers are void")
+    del weights
+    torch.cuda.empty_cache()
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
+        return None
 
     # ---- CPU baseline: bounded sample of the same workload on this box's host cores
-    cpu = None
-    try:
-        from oracle import oracle as O
-        threads = O.hw_threads()
-        ncpu = max(2, min(4, int(np.ceil(300e6 / w_bytes_full))))
-        cw = [synth.make_weight(dt, n, k, seed=0, tensor_id=i) for i in range(ncpu)]
-        per0 = cpu_path(dt, n, k, m, cw, x_np, 2, threads)
-        calls = int(max(4, min(400, 3.0 / max(per0, 1e-6))))
-        per = cpu_path(dt, n, k, m, cw, x_np, calls, threads)
-        cpu = {"value": algorithmic_bytes(dt, n, k, m) / per / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
-               "sample": f"{calls} matmul calls of the full workload ({per * 1e3:.3f} ms each), {ncpu} rotating weight copies; "
-                         "AVX2-order C restatement of xn's Rust CPU path"}
-    except Exception as e:
-        cpu = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": f"unavailable: {e}"}
+    if not with_cpu:
+        cpu = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": "not timed for this entry"}
+    else:
+        try:
+            from oracle import oracle as O
+            threads = O.hw_threads()
+            ncpu = max(2, min(4, int(np.ceil(300e6 / w_bytes_full))))
+            cw = [synth.make_weight(dt, n, k, seed=0, tensor_id=i) for i in range(ncpu)]
+            per0 = cpu_path(dt, n, k, m, cw, x_np, 2, threads)
+            calls = int(max(4, min(400, 3.0 / max(per0, 1e-6))))
+            per = cpu_path(dt, n, k, m, cw, x_np, calls, threads)
+            cpu = {"value": algorithmic_bytes(dt, n, k, m) / per / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
+                   "sample": f"{calls} matmul calls of the full workload ({per * 1e3:.3f} ms each), {ncpu} rotating weight copies; "
+                             "AVX2-order C restatement of xn's Rust CPU path"}
+        except Exception as e:
+            cpu = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": f"unavailable: {e}"}
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -454,37 +630,41 @@ def run_ours(args, name, dt, n, k, m):
         "roofline": roofline,
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": ncopies * m * k * 4,
-                "d2h_bytes_per_step": ncopies * m * n_local * 4, "steps": e2e_steps,
-                "note": "QLinear::forward on pinned host tensors (activations copied in, result stored to the pinned buffer by the kernel for m <= 16, copied back otherwise); one synchronize per call"},
+                "d2h_bytes_per_step": d2h_per_step, "steps": e2e_steps, "note": e2e_note},
         "gpu_launches": int(launches_per_step * args.steps),
         "clocks": sampler.summary(),
     }
-    print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    if gather_check:
+        line.update(gather_check)
+    return line
 
 
-def run_decoder(args, name, batch):
-    """Config 5: the 32-layer Q4_K decoder (Q6_K LM head). Prefill 512 random tokens, then args.steps greedy
-    decode steps replayed from one captured CUDA graph; a step is one token for each of `batch` sequences."""
+def summary_of(line: dict) -> dict:
+    """The few figures of a full line that the headline line's "workloads" list carries."""
+    out = {"workload": line["config"]["workload"], "metric": line["metric"], "value": line["value"], "unit": line["unit"],
+           "n_gpus": line["n_gpus"], "ms_per_step": line["ms_per_step"], "frac": line["roofline"]["frac"], "bound": line["roofline"]["bound"],
+           "clocks": line.get("clocks")}
+    for key in ("gather_checked", "gather_max_err", "prefill"):
+        if key in line:
+            out[key] = line[key]
+    if "launch_us" in line["roofline"]:
+        out["cold_us_per_call"] = line["roofline"]["launch_us"]
+    return out
+
+
+def decoder_measure(args, name, batch, dev, rank, world, steps, L):
+    """Config 5: the 32-layer Q4_K decoder (Q6_K LM head). Prefill 512 random tokens, then `steps` greedy decode steps
+    replayed from one captured CUDA graph; a step is one token for each of `batch` sequences. Returns the JSON line
+    (rank 0) or None. The process group, if any, is the caller's."""
     import torch
     import torch.distributed as dist
 
-    from xn_b200 import _lib, quantized as Q
     from xn_b200.llama import LlamaConfig, QLlama
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    Q.init(dev)
-    L = _lib.lib()
+    local = dev.index
     cfg = LlamaConfig.llama_7b()
     prompt_len = 512
-    steps = min(args.steps, 256)
+    steps = min(steps, 256)
     t0 = time.perf_counter()
     model = QLlama(cfg, dev, batch=batch, max_seq=prompt_len + steps + 8, rank=rank, world=world, max_prefill_rows=batch * prompt_len)
     torch.cuda.synchronize(dev)
@@ -513,7 +693,6 @@ def run_decoder(args, name, batch):
     sync_all()
     props = torch.cuda.get_device_properties(dev)
     sampler = ClockSampler(local, str(getattr(props, "uuid", "")) or None)
-    launches_before = L.xnq_launch_count()
     with sampler:
         sync_all()
         t0 = time.perf_counter()
@@ -533,35 +712,35 @@ def run_decoder(args, name, batch):
     if world > 1:
         dist.barrier()
     model.close()
+    del model
+    torch.cuda.empty_cache()
     if late:
         raise SystemExit(f"rank {rank}: exchanges gave up waiting for peers {late:#x}; the numbers are void")
-    if rank == 0:
-        peak, peak_tf, peak_kind = measured_peaks()
-        wbytes = cfg.weight_bytes_per_step()
-        ms_per_step = decode_ms / steps
-        line = {
-            "metric": "7B Q4_K decode tok/s", "value": batch * steps / (decode_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "i8 block dots (dp4a), f32 accumulate; bf16 attention", "data": "synthetic",
-            "config": {"workload": name, "layers": cfg.n_layers, "d_model": cfg.d_model, "heads": f"{cfg.n_heads}q/{cfg.n_kv_heads}kv x {cfg.head_dim}",
-                       "ffn": cfg.ffn, "vocab": cfg.vocab, "linears": cfg.linear_dtype.name, "lm_head": cfg.head_dtype.name, "batch": batch,
-                       "prompt": prompt_len, "decode_steps": steps,
-                       "cache": f"{wbytes / 1e6:.0f} MB of weights per step, far above L2",
-                       "parallelism": f"tensor parallel x{world}: head-sharded attention, N-sharded qkv / gate-up / LM head, K-sharded o / down whose kernels store their summands into every rank (2 exchanges per layer)" if world > 1 else "one GPU",
-                       "launch": "one CUDA graph per decode step"},
-            "roofline": {"bound": "hbm", "achieved": wbytes / (ms_per_step * 1e-3) / 1e9 / world, "peak": peak, "unit": "GB/s",
-                         "frac": wbytes / (ms_per_step * 1e-3) / 1e9 / world / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
-                         "kernel": "whole decode step: weight bytes of all linears per GPU / step time", "bytes_per_step": wbytes},
-            "cpu_baseline": None,
-            "e2e": {"value": batch * steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": batch * 8,
-                    "note": "decode loop timed on the host including the copy of the generated ids back to host memory"},
-            "prefill": {"tokens": batch * prompt_len, "ms": prefill_ms, "tok_s": batch * prompt_len / (prefill_ms * 1e-3)},
-            "build_s": build_s, "gpu_launches": int(launches), "clocks": sampler.summary(),
-            "generated_head": toks_host[0, :8].tolist(),
-        }
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    if rank != 0:
+        return None
+    peak, peak_tf, peak_kind = measured_peaks()
+    wbytes = cfg.weight_bytes_per_step()
+    ms_per_step = decode_ms / steps
+    return {
+        "metric": "7B Q4_K decode tok/s", "value": batch * steps / (decode_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "i8 block dots (dp4a, tcgen05 kind::i8), f32 accumulate; bf16 attention", "data": "synthetic",
+        "config": {"workload": name, "layers": cfg.n_layers, "d_model": cfg.d_model, "heads": f"{cfg.n_heads}q/{cfg.n_kv_heads}kv x {cfg.head_dim}",
+                   "ffn": cfg.ffn, "vocab": cfg.vocab, "linears": cfg.linear_dtype.name, "lm_head": cfg.head_dtype.name, "batch": batch,
+                   "prompt": prompt_len, "decode_steps": steps,
+                   "cache": f"{wbytes / 1e6:.0f} MB of weights per step, far above L2",
+                   "parallelism": f"tensor parallel x{world}: head-sharded attention, N-sharded qkv / gate-up / LM head, K-sharded o / down whose kernels store their summands into every rank (2 exchanges per layer)" if world > 1 else "one GPU",
+                   "launch": "one CUDA graph per decode step"},
+        "roofline": {"bound": "hbm", "achieved": wbytes / (ms_per_step * 1e-3) / 1e9 / world, "peak": peak, "unit": "GB/s",
+                     "frac": wbytes / (ms_per_step * 1e-3) / 1e9 / world / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                     "kernel": "whole decode step: weight bytes of all linears per GPU / step time", "bytes_per_step": wbytes},
+        "cpu_baseline": None,
+        "e2e": {"value": batch * steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": batch * 8,
+                "note": "decode loop timed on the host including the copy of the generated ids back to host memory"},
+        "prefill": {"tokens": batch * prompt_len, "ms": prefill_ms, "tok_s": batch * prompt_len / (prefill_ms * 1e-3)},
+        "build_s": build_s, "gpu_launches": int(launches), "clocks": sampler.summary(),
+        "generated_head": toks_host[0, :8].tolist(),
+    }
 
 
 def main():
@@ -573,17 +752,42 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + sorted(DECODER_WORKLOADS))
     ap.add_argument("--gather", default="peer-stores", choices=["peer-stores", "nccl"], help="N > 1: how output slices are gathered")
     ap.add_argument("--option", action="append", default=[], help="library switch NAME=INT (A/B measurements), e.g. matvec_tma=0")
+    ap.add_argument("--no-extra", action="store_true", help="headline workload only: skip the list of the other BASELINE configurations")
     args = ap.parse_args()
-    if args.workload in DECODER_WORKLOADS:
-        if args.impl == "reference":
+    if args.impl == "reference":
+        if args.workload in DECODER_WORKLOADS:
             print(json.dumps({"impl": "reference", "unavailable": "the decoder workloads have no CPU arm; the matmul workloads do"}), flush=True)
             return
-        return run_decoder(args, args.workload, DECODER_WORKLOADS[args.workload])
-    dt, n, k, m = WORKLOADS[args.workload]
-    if args.impl == "reference":
-        run_reference(args, args.workload, dt, n, k, m)
-    else:
-        run_ours(args, args.workload, dt, n, k, m)
+        dt, n, k, m = WORKLOADS[args.workload]
+        return run_reference(args, args.workload, dt, n, k, m)
+    ctx = Ctx(args)
+    try:
+        if args.workload in DECODER_WORKLOADS:
+            line = decoder_measure(args, args.workload, DECODER_WORKLOADS[args.workload], ctx.dev, ctx.rank, ctx.world, args.steps, ctx.L)
+        else:
+            dt, n, k, m = WORKLOADS[args.workload]
+            line = measure_matmul(ctx, args, args.workload, dt, n, k, m)
+            if args.workload == DEFAULT_WORKLOAD and not args.no_extra and not args.option:
+                # every other BASELINE configuration in the same run (bounded in time), so that one invocation records them all
+                extras = []
+                if ctx.world == 1:
+                    l2 = int(getattr(ctx.torch.cuda.get_device_properties(ctx.dev), "L2_cache_size", 126 * 1024 * 1024))
+                    extras += extra_matmul_workloads(ctx.torch, ctx.L, ctx.Q, ctx.dev, l2, budget_s=150.0)
+                    for dname, batch in sorted(DECODER_WORKLOADS.items()):
+                        dl = decoder_measure(args, dname, batch, ctx.dev, ctx.rank, ctx.world, 64, ctx.L)
+                        extras.append(summary_of(dl))
+                else:
+                    # the configurations BASELINE shards: the Q6_K LM head and the 7B decoder
+                    c4 = measure_matmul(ctx, args, "C4_q6k_128256x4096_m1", *WORKLOADS["C4_q6k_128256x4096_m1"], with_cpu=False)
+                    dl = decoder_measure(args, "C5_llama7b_q4k_decode_b1", 1, ctx.dev, ctx.rank, ctx.world, 64, ctx.L)
+                    if ctx.rank == 0:
+                        extras += [summary_of(c4), summary_of(dl)]
+                if line is not None:
+                    line["workloads"] = extras
+        if line is not None:
+            print(json.dumps(line), flush=True)
+    finally:
+        ctx.close()
 
 
 if __name__ == "__main__":

@@ -152,8 +152,9 @@ int xnq_hint_next_weight(const xnq_weight *w);
 
 /* xnq_matmul_t for callers that can neither supply a workspace nor let the library allocate one:
  * hosts whose allocator owns all device memory, steps being recorded into a CUDA graph, plugins under
- * a fixed memory budget. Same arithmetic and results as xnq_matmul_t's small-batch path, for
- * 0 <= m <= 16; the quantized-activation scratch is a 128 KiB array built into the library (each GPU
+ * a fixed memory budget. Same arithmetic and tolerance as xnq_matmul_t (exact integer block sums, f32
+ * accumulation; the f32 summation order, and so the last bits, can differ from xnq_matmul_t's, which may pick
+ * another kernel for the same shape), for 0 <= m <= 16; the quantized-activation scratch is a 128 KiB array built into the library (each GPU
  * that loads the library holds it until the process exits). Rows are taken in passes that fit the
  * array (1.25 bytes per activation element); a request fails with XNQ_ERR_SIZE only when a single
  * row does not fit, i.e. k above about 104,000, or m > 16. It calls no cudaMalloc / cudaFree and no
@@ -219,6 +220,13 @@ int xnq_matmul_t_gather(const xnq_weight *w, xnq_comm *c, int slot, int layout, 
  * rank r's block in columns [r * n_local, (r + 1) * n_local). Same slot rule as above. */
 int xnq_comm_gather(xnq_comm *c, int slot, const void *src, int elem_dtype, int64_t m, int64_t n_local,
                     int64_t ld_src, void *stream, void **y_out);
+/* Deferred waits. By default the kernel that gathers also waits (bounded) for every peer's columns, so its slot is
+ * complete when it retires: every gather is then a barrier between the ranks. With deferred = 1 a gather only
+ * publishes this rank's columns and retires; xnq_comm_wait enqueues a one-warp kernel that awaits the peers' columns of
+ * ALL gathers issued so far, and must lie between a gather and the first reader of its slot. Several gathers may share
+ * one wait (the gathers of a whole step, each into a slot of its own); between two waits a slot may be written once. */
+int xnq_comm_set_deferred(xnq_comm *c, int deferred);
+int xnq_comm_wait(xnq_comm *c, void *stream);
 /* Bit p set: a wait for rank p's columns gave up after 4 s (the results of that gather are not
  * complete). Synchronizes the device. */
 int xnq_comm_status(const xnq_comm *c, unsigned int *late_peers);

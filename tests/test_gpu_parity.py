@@ -230,7 +230,12 @@ FULL = [
     ("C2", D.Q8_0, 11008, 4096, (1, 16)),
     ("C3", D.Q4K, 14336, 4096, (1, 4, 16)),
     ("C4", D.Q6K, 128256, 4096, (1,)),
+    # one whole layer of the 7B decoder of configuration 5 (fused q/k/v, o, fused gate/up, down) and its Q6_K LM head
+    ("qkv_proj", D.Q4K, 6144, 4096, (1, 16)),
+    ("o_proj", D.Q4K, 4096, 4096, (1, 16)),
+    ("gate_up_proj", D.Q4K, 28672, 4096, (1, 16)),
     ("down_proj", D.Q4K, 4096, 14336, (1, 16)),
+    ("lm_head", D.Q6K, 32000, 4096, (1, 16)),
 ]
 
 
@@ -241,7 +246,7 @@ def test_full_size_configs_against_oracle(Q, O, name, dt, n, k, ms):
     for m in ms:
         x = synth.make_activation(m, k, seed=0)
         got = t.matmul_t(torch.from_numpy(x).to(DEV)).cpu().numpy()
-        want = O.matmul(int(dt), x, w, n)
+        want = O.matmul(int(dt), x, w, n, threads=O.hw_threads())
         assert_close_ref(got, want, TOL_F32, f"{name} m={m}")
         rms = float(np.sqrt((want.astype(np.float64) ** 2).mean()))
         assert np.abs(got - want).max() / rms < TOL_F32, f"{name} m={m}: error relative to output rms"

@@ -1,4 +1,4 @@
-"""The no-allocation entry point, xnq_matmul_t_static, against the regular one.
+"""The no-allocation entry point, xnq_matmul_t_static, against the regular one and against the CPU oracle.
 
 Some callers cannot give the library a workspace and cannot let it allocate (their own pool owns the
 device memory, or they are recording a CUDA graph); for them the scratch is an array inside the
@@ -26,7 +26,7 @@ def _static(L, t, x, y):
 
 
 @pytest.mark.parametrize("dt", [D.Q4_0, D.Q8_0, D.Q4K, D.Q6K])
-def test_static_scratch_entry_matches_regular_entry_twice_in_a_row(dt):
+def test_static_scratch_entry_matches_regular_entry_twice_in_a_row(dt, O):
     from xn_b200 import _lib, quantized as Q
     Q.init(DEV)
     L = _lib.lib()
@@ -41,8 +41,9 @@ def test_static_scratch_entry_matches_regular_entry_twice_in_a_row(dt):
         torch.cuda.synchronize()
         err = (got - want).abs() / want.abs().clamp(min=1.0)     # the suite's matmul tolerance: 2e-3 of max(|w|, 1)
         assert torch.isfinite(got).all() and err.max().item() <= 2e-3, (dt.name, m, err.max().item())
-        if m > 1:                                                # same kernels on the same bytes: identical results
-            assert torch.equal(got, want), (dt.name, m)
+        oracle = torch.from_numpy(O.matmul(int(dt), x.cpu().numpy(), w, n))   # the checker of record: the CPU restatement
+        oerr = (got.cpu() - oracle).abs() / oracle.abs().clamp(min=1.0)
+        assert oerr.max().item() <= 2e-3, (dt.name, m, "vs oracle", oerr.max().item())
         got2 = torch.empty((m, n), device=DEV)
         _static(L, t, x, got2)                                   # second call in a row, same input
         torch.cuda.synchronize()
@@ -68,6 +69,17 @@ def test_static_scratch_entry_rejects_what_does_not_fit():
     torch.cuda.synchronize()
     want = t.matmul_t(x)
     assert ((y - want).abs() / want.abs().clamp(min=1.0)).max().item() <= 2e-3
+    # a long k where the array holds fewer rows than the kernel would take at once: passes of reduced size
+    n, k = 64, 14336
+    w = synth.make_weight(D.Q4K, n, k, seed=313)
+    t4 = Q.QCudaTensor.from_qtensor(Q.QTensor(w, (n, k), D.Q4K), DEV)
+    x4 = torch.from_numpy(synth.make_activation(16, k, seed=314)).to(DEV)
+    y4 = torch.empty((16, n), device=DEV)
+    _static(L, t4, x4, y4)
+    torch.cuda.synchronize()
+    want4 = t4.matmul_t(x4)
+    assert ((y4 - want4).abs() / want4.abs().clamp(min=1.0)).max().item() <= 2e-3
+    n, k = 8, 32768
     rc = L.xnq_matmul_t_static(t._h, ctypes.c_void_p(x.data_ptr()), F32, 17, k, ctypes.c_void_p(y.data_ptr()), F32, n, None)
     assert rc == -5 and b"0..16" in L.xnq_last_error()
     assert L.xnq_matmul_t_static(None, None, F32, 1, 32, None, F32, 8, None) == -1

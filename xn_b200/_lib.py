@@ -65,6 +65,8 @@ def lib() -> ctypes.CDLL:
     L.xnq_comm_slot.argtypes = [vp, ci, pvp, ctypes.POINTER(sz)]
     L.xnq_matmul_t_gather.argtypes = [vp, vp, ci, ci, vp, ci, i64, i64, ci, vp, sz, vp, pvp]
     L.xnq_comm_gather.argtypes = [vp, ci, vp, ci, i64, i64, i64, vp, pvp]
+    L.xnq_comm_set_deferred.argtypes = [vp, ci]
+    L.xnq_comm_wait.argtypes = [vp, vp]
     L.xnq_comm_status.argtypes = [vp, ctypes.POINTER(ctypes.c_uint)]
     L.xnq_comm_free.argtypes = [vp]
     fp = ctypes.c_float

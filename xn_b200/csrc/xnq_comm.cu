@@ -30,6 +30,7 @@ struct xnq_comm {
   unsigned int *ctl;   // local, not shared: {epochs sent, unused, CTAs done, late-peer bits}
   bool connected;
   int last_slot;
+  int deferred;        // 1: gathers publish and retire; xnq_comm_wait awaits the peers
 };
 
 namespace xnq {
@@ -67,6 +68,15 @@ __global__ void __launch_bounds__(256) gather_push_kernel(GatherArgs g, const vo
   }
   __syncthreads();
   if (threadIdx.x < 32) gather_publish_and_wait(g);
+}
+
+// One warp: lane p awaits, bounded, rank p's epoch of the gathers this rank has published so far (every rank issues
+// the same sequence of gathers, so the peers' counts reach this rank's).
+__global__ void __launch_bounds__(32) gather_wait_kernel(GatherArgs g) {
+  const int lane = threadIdx.x & 31;
+  const unsigned int epoch = g.ctl[0];
+  if (g.ctl[3]) return; // a peer was late before: reported once, not awaited again
+  if (lane < g.world && lane != g.rank) gather_await_peer(g, epoch, lane);
 }
 
 inline bool aligned_to(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
@@ -148,6 +158,27 @@ int xnq_comm_status(const xnq_comm *c, unsigned int *late_peers) {
   return XNQ_OK;
 }
 
+int xnq_comm_set_deferred(xnq_comm *c, int deferred) {
+  clear_error();
+  if (!c) return fail(XNQ_ERR_NULL, "comm_set_deferred: comm is NULL");
+  c->deferred = deferred ? 1 : 0;
+  return XNQ_OK;
+}
+
+int xnq_comm_wait(xnq_comm *c, void *stream) {
+  clear_error();
+  if (!c) return fail(XNQ_ERR_NULL, "comm_wait: comm is NULL");
+  if (!c->connected) return fail(XNQ_ERR_UNSUPPORTED, "comm_wait: comm is not connected to its peers");
+  if (c->world == 1) return XNQ_OK;
+  GatherArgs g{};
+  for (int p = 0; p < c->world; p++) g.flag[p] = reinterpret_cast<unsigned int *>(c->peer[p]) + c->rank;
+  g.ctl = c->ctl, g.world = c->world, g.rank = c->rank;
+  gather_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(g);
+  XNQ_CUDA(cudaGetLastError());
+  count_launch();
+  return XNQ_OK;
+}
+
 int xnq_comm_free(xnq_comm *c) {
   clear_error();
   if (!c) return XNQ_OK;
@@ -178,7 +209,7 @@ int xnq_comm_gather(xnq_comm *c, int slot, const void *src, int elem_dtype, int6
     g.dst[p] = slot_ptr(c, p, slot);
     g.flag[p] = reinterpret_cast<unsigned int *>(c->peer[p]) + c->rank;
   }
-  g.ctl = c->ctl, g.world = c->world, g.rank = c->rank, g.col0 = n_local * c->rank, g.ld = nt, g.cta_fence_gpu = gather_cta_fence_scope();
+  g.ctl = c->ctl, g.world = c->world, g.rank = c->rank, g.col0 = n_local * c->rank, g.ld = nt, g.cta_fence_gpu = gather_cta_fence_scope(), g.defer_wait = c->deferred;
   const int64_t units = m * n_local;
   const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(296, (units + 1023) / 1024));
   gather_push_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(g, src, ld_src, m, n_local, (int)es, -1);
@@ -212,7 +243,7 @@ int xnq_matmul_t_gather(const xnq_weight *w, xnq_comm *c, int slot, int layout, 
     g.dst[p] = slot_ptr(c, p, slot);
     g.flag[p] = reinterpret_cast<unsigned int *>(c->peer[p]) + c->rank;
   }
-  g.ctl = c->ctl, g.world = c->world, g.rank = c->rank, g.col0 = col0, g.ld = nt, g.cta_fence_gpu = gather_cta_fence_scope();
+  g.ctl = c->ctl, g.world = c->world, g.rank = c->rank, g.col0 = col0, g.ld = nt, g.cta_fence_gpu = gather_cta_fence_scope(), g.defer_wait = c->deferred;
   char *local = slot_ptr(c, c->rank, slot);
   int rc;
   if (m == 1 && matvec_tma_enabled() && matvec_tma_supported(w->v, 1)) {

@@ -110,6 +110,7 @@ struct GatherArgs {
   unsigned int *ctl;
   int world, rank;
   int cta_fence_gpu; // 1: CTAs order their stores before the arrival count with a gpu-scope fence; the last CTA's system-scope release carries them on
+  int defer_wait;    // 1: the kernel publishes its epoch and retires; the peers' columns are awaited later (xnq_comm_wait)
   int64_t col0, ld; // first column this rank produces; row stride of the gathered buffer (elements)
 };
 
@@ -126,6 +127,7 @@ constexpr unsigned long long GATHER_WAIT_LIMIT_NS = 4000000000ull; // a peer tha
 // CTA's release store at system scope carries every CTA's stores with it (causality order is
 // cumulative across scopes). A system-scope fence in every CTA is not needed and costs about 3 us per
 // launch; the "gather_cta_fence" option (0) brings it back for comparison.
+__device__ __forceinline__ void gather_await_peer(const GatherArgs &g, unsigned int epoch, int lane);
 __device__ __forceinline__ void gather_publish_and_wait(const GatherArgs &g) {
   // called by the 32 lanes of ONE warp of each CTA, after the CTA-wide barrier that follows its stores
   const int lane = threadIdx.x & 31;
@@ -147,7 +149,11 @@ __device__ __forceinline__ void gather_publish_and_wait(const GatherArgs &g) {
   // lane p talks to rank p: all peers are told, and all peers are awaited, at the same time
   const bool peer = lane < g.world && lane != g.rank;
   if (peer) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(g.flag[lane]), "r"(epoch) : "memory");
-  if (last == 2u || !peer) return;
+  if (last == 2u || !peer || g.defer_wait) return;
+  gather_await_peer(g, epoch, lane);
+}
+// lane p (a peer's rank) waits, bounded, until that peer's epoch word in the local row has reached `epoch`
+__device__ __forceinline__ void gather_await_peer(const GatherArgs &g, unsigned int epoch, int lane) {
   const unsigned int *mine = g.flag[g.rank] - g.rank + lane; // this peer's word in the local epoch row
   unsigned long long t0;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));

@@ -51,11 +51,12 @@ namespace xnq {
 __device__ unsigned int g_imma_status; // sticky: 1 producer, 2 converter, 4 mma, 8 drain wait expired
 #ifdef XNQ_DEV_TRACE
 __device__ long long g_imma_trace[32]; // development builds only: cycles block 0's roles spend in each wait
-#define XNQ_T0() long long t0_ = clock64()
+#define XNQ_GT(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) { unsigned long long g_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_)); g_imma_trace[i] = (long long)g_; } } while (0)
 #define XNQ_TACC(i) do { const long long t1_ = clock64(); tacc[i] += t1_ - t0_; t0_ = t1_; } while (0)
 #define XNQ_TDECL long long tacc[6] = {0, 0, 0, 0, 0, 0}; long long t0_ = clock64()
 #define XNQ_TDUMP(base, cond) do { if ((cond) && blockIdx.x == 0) for (int i_ = 0; i_ < 6; i_++) g_imma_trace[(base) + i_] = tacc[i_]; } while (0)
 #else
+#define XNQ_GT(i) do { } while (0)
 #define XNQ_TACC(i) do { } while (0)
 #define XNQ_TDECL do { } while (0)
 #define XNQ_TDUMP(base, cond) do { } while (0)
@@ -69,10 +70,9 @@ constexpr int CONV_WARPS = 8, DRAIN_WARPS = 16;
 constexpr int PRODUCER_WARP = 0, MMA_WARP = 1, CONV_WARP0 = 2, DRAIN_WARP0 = CONV_WARP0 + CONV_WARPS;
 constexpr int NTHREADS = (DRAIN_WARP0 + DRAIN_WARPS) * 32; // 832
 constexpr int A_STAGE_BYTES = TILE_N * 128; // one 128-k half step of int8 codes
-constexpr int A_STAGES = 4, SIDE_STAGES = 4, MAX_RAW_STAGES = 4;
+constexpr int MAX_A_STAGES = 8, SIDE_STAGES = 4, MAX_RAW_STAGES = 4;
 constexpr int HDR_BYTES = TILE_N * 16;      // per 256-k step: 16 bytes of scale data per weight row
-constexpr int ACC_COLS = 256;               // tensor-memory columns of one accumulator buffer: 4 slices x NP <= 256
-constexpr uint32_t WAIT_LIMIT = 1u << 26;   // non-blocking polls (a few ns each): about a second
+constexpr int TMEM_COLS = 512;              // all of the SM's tensor memory: 512 / (4 slices x NP) accumulator buffers, at most 8
 constexpr size_t IMMA_SMEM = 226 * 1024;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -85,20 +85,31 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// One wait attempt: the thread is suspended by the hardware until the phase completes or a system-chosen time limit
+// passes (it takes no issue slots meanwhile, unlike a test_wait spin, which with two dozen polling warps per SM slowed
+// the threads that issue copies and MMAs several times over).
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ unsigned long long wall_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull; // a wait that lasts two seconds is given up
 // bounded wait of one thread
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int bit) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+  if (mbar_test(bar, parity)) return true;
+  const unsigned long long t0 = wall_ns();
+  while (wall_ns() - t0 < WAIT_LIMIT_NS)
     if (mbar_test(bar, parity)) return true;
   atomicOr(&g_imma_status, bit);
   return false;
@@ -221,7 +232,7 @@ struct ImmaArgs {
   CUtensorMap tmap[2];
   int nstreams;
   uint32_t step_bytes[2], raw_off[2];
-  int raw_stages, b_stages;
+  int raw_stages, b_stages, a_stages;
   uint32_t raw_stage_bytes, b_stage_bytes, side_stage_bytes;
   uint32_t a_off, b_off, raw_off0, side_off; // offsets from the 1024-aligned base of dynamic shared memory
 };
@@ -316,14 +327,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
   constexpr int CH = NPT > 16 ? 4 : (NPT > 8 ? 8 : NPT); // columns read back at a time: what the register budget holds next to the sums
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u; // operand stages need 1024-byte alignment
-  // barriers: raw_full/raw_empty [4], a_full/mma_done [4], b_full/b_empty [4], side_full/side_empty [4], acc_empty [2]
-  __shared__ __align__(8) uint64_t bars[34];
+  constexpr int NBUF = TMEM_COLS / (4 * NP) > 8 ? 8 : TMEM_COLS / (4 * NP); // accumulator buffers (even: buffer parity = half step parity)
+  constexpr int BUF_COLS = 4 * NP;
+  // barriers: raw_full/raw_empty [4], b_full [4] (+ 4 spare), side_full/side_empty [4], a_full/mma_done [8], acc_empty [8]
+  __shared__ __align__(8) uint64_t bars[48];
   __shared__ uint32_t tmem_slot;
   __shared__ unsigned int s_ticket;
-  const uint32_t raw_full = smem_u32(bars), raw_empty = raw_full + 32, a_full = raw_full + 64, mma_done = raw_full + 96, b_full = raw_full + 128,
-                 b_empty = raw_full + 160, side_full = raw_full + 192, side_empty = raw_full + 224, acc_empty = raw_full + 256;
+  const uint32_t raw_full = smem_u32(bars), raw_empty = raw_full + 32, b_full = raw_full + 64, side_full = raw_full + 128,
+                 side_empty = raw_full + 160, a_full = raw_full + 192, mma_done = raw_full + 256, acc_empty = raw_full + 320;
+  XNQ_GT(26);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int RS = p.raw_stages, BS = p.b_stages;
+  const int RS = p.raw_stages, BS = p.b_stages, AS = p.a_stages;
+  const int NB = min(NBUF, AS); // accumulator buffers in use: a drain group waiting on mma_done must not be lapped by the MMA thread,
+                                // which can run ahead by NB half steps, so the ring of mma_done barriers (AS) is at least that long
   const int KT = p.nsteps;
   const int G = gridDim.x;
   const long long u0 = p.units * blockIdx.x / G, u1 = p.units * (blockIdx.x + 1) / G;
@@ -331,21 +347,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
   const int tile0 = (int)(u0 / KT), kt0 = (int)(u0 % KT);
 
   if (threadIdx.x == 0) {
+    for (int s = 0; s < 8; s++) {
+      mbar_init(a_full + 8 * s, CONV_WARPS / 2); // the four converter warps of the half step's group
+      mbar_init(mma_done + 8 * s, 1);            // the half step's MMAs have read their operands and written their slices
+      mbar_init(acc_empty + 8 * s, DRAIN_WARPS / 2);
+    }
     for (int s = 0; s < 4; s++) {
       mbar_init(raw_full + 8 * s, 1);
       mbar_init(raw_empty + 8 * s, CONV_WARPS);
-      mbar_init(a_full + 8 * s, CONV_WARPS / 2); // the four converter warps of the half step's group
-      mbar_init(mma_done + 8 * s, 1);            // the half step's MMAs have read their operands and written their slices
       mbar_init(b_full + 8 * s, 1);
-      mbar_init(b_empty + 8 * s, 1);
       mbar_init(side_full + 8 * s, 1 + CONV_WARPS / 2); // the producer's transaction + the four converter warps that copy the scale bytes
       mbar_init(side_empty + 8 * s, DRAIN_WARPS);
     }
-    for (int b = 0; b < 2; b++) mbar_init(acc_empty + 8 * b, DRAIN_WARPS / 2);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == MMA_WARP) { // one warp owns the tensor-memory allocation
-    tmem_alloc(smem_u32(&tmem_slot), 2 * ACC_COLS);
+    tmem_alloc(smem_u32(&tmem_slot), TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -379,7 +396,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
           if (alive) load_raw(i);
         }
         XNQ_TACC(1);
-        if (alive && i >= BS) alive = mbar_wait(b_empty + 8 * bs, ((i / BS) - 1) & 1, 1u);
+        // the B stage of step i - BS is free once that step's second half has been multiplied: BS = AS / 2, so this is
+        // the barrier of half step 2 i + 1 one phase back (a second commit per step cost the issuing thread over a
+        // thousand cycles)
+        if (alive && i >= BS) alive = mbar_wait(mma_done + 8 * ((2 * i + 1) % AS), ((2 * (i - BS) + 1) / AS) & 1, 1u);
         XNQ_TACC(2);
         if (alive && i >= SIDE_STAGES) alive = mbar_wait(side_empty + 8 * ss, ((i / SIDE_STAGES) - 1) & 1, 1u);
         XNQ_TACC(3);
@@ -406,11 +426,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
         alive = mbar_wait(b_full + 8 * bs, (i / BS) & 1, 4u);
         XNQ_TACC(1);
         for (int h = 0; h < 2 && alive; h++) {
-          const int j = 2 * i + h, sa = j % A_STAGES;
+          const int j = 2 * i + h, sa = j % AS, buf = j % NB;
           XNQ_TACC(0);
-          alive = mbar_wait(a_full + 8 * sa, (j / A_STAGES) & 1, 4u);
+          alive = mbar_wait(a_full + 8 * sa, (j / AS) & 1, 4u);
           XNQ_TACC(2);
-          if (alive && i >= 1) alive = mbar_wait(acc_empty + 8 * h, (i - 1) & 1, 4u); // buffer h: the drain of the previous step's half h
+          if (alive && j >= NB) alive = mbar_wait(acc_empty + 8 * buf, ((j / NB) - 1) & 1, 4u); // the drain of the buffer's previous half step
           XNQ_TACC(3);
           if (!alive) break;
           tc_fence_after();
@@ -418,12 +438,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
           const uint64_t bdesc = smem_desc_sw128(base + p.b_off + bs * p.b_stage_bytes + h * (NP * 128));
 #pragma unroll
           for (int q = 0; q < 4; q++) // K = 32 per instruction: advance 32 bytes inside the swizzle row; slice q of the buffer
-            umma_i8(tmem_d + (uint32_t)(h * ACC_COLS + q * NP), adesc + (uint64_t)(q * 2), bdesc + (uint64_t)(q * 2), idesc);
+            umma_i8(tmem_d + (uint32_t)(buf * BUF_COLS + q * NP), adesc + (uint64_t)(q * 2), bdesc + (uint64_t)(q * 2), idesc);
           XNQ_TACC(4);
           umma_commit(mma_done + 8 * sa); // one arrival serves the converters (the stage is free) and the drain (the slices are written)
           XNQ_TACC(5);
         }
-        if (alive) umma_commit(b_empty + 8 * bs);
       }
       XNQ_TDUMP(6, true);
     }
@@ -436,7 +455,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
     XNQ_TDECL;
     for (int i = 0; i < nunits && alive; i++) {
       const int rs = i % RS, ss = i % SIDE_STAGES;
-      const int j = 2 * i + h, sa = j % A_STAGES;
+      const int j = 2 * i + h, sa = j % AS;
       XNQ_TACC(0);
       alive = mbar_wait_warp(raw_full + 8 * rs, (i / RS) & 1, 2u);
       XNQ_TACC(1);
@@ -452,7 +471,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
         if (lane == 0) mbar_arrive(side_full + 8 * ss);
       }
       XNQ_TACC(0);
-      if (j >= A_STAGES) alive = mbar_wait_warp(mma_done + 8 * sa, ((j / A_STAGES) - 1) & 1, 2u);
+      if (j >= AS) alive = mbar_wait_warp(mma_done + 8 * sa, ((j / AS) - 1) & 1, 2u);
       XNQ_TACC(3);
       if (!alive) break;
       uint4 lo[4], hi[4];
@@ -481,6 +500,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
     const int c0 = cg * NPT;
     const int et = threadIdx.x - DRAIN_WARP0 * 32; // 0..511
     pdl_wait(); // the kernel that prepares the activations also zeroes the tiles' tickets
+#ifdef XNQ_DEV_TRACE
+    if (blockIdx.x == 0 && threadIdx.x == DRAIN_WARP0 * 32) { unsigned long long g_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_)); g_imma_trace[28] = (long long)g_; }
+#endif
     bool alive = true;
     int tile = tile0, kt = kt0;
     float acc[NPT];
@@ -491,18 +513,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
     XNQ_TDECL;
     for (int i = 0; i < nunits; i++) {
       const int ss = i % SIDE_STAGES;
-      const int j = 2 * i + h, sa = j % A_STAGES;
+      const int j = 2 * i + h, sa = j % AS, buf = j % NB;
       XNQ_TACC(0);
       if (alive) alive = mbar_wait_warp(side_full + 8 * ss, (i / SIDE_STAGES) & 1, 8u);
       XNQ_TACC(1);
       const uint32_t side = base + p.side_off + ss * p.side_stage_bytes;
       uint4 hdr = make_uint4(0, 0, 0, 0);
       if (alive) hdr = lds128(side + (uint32_t)(32 * q + lane) * 16);
-      if (alive) alive = mbar_wait_warp(mma_done + 8 * sa, (j / A_STAGES) & 1, 8u);
+      if (alive) alive = mbar_wait_warp(mma_done + 8 * sa, (j / AS) & 1, 8u);
       XNQ_TACC(2);
       if (alive) {
         tc_fence_after();
-        const uint32_t taddr = tmem_d + ((uint32_t)(32 * q) << 16) + (uint32_t)(h * ACC_COLS + c0);
+        const uint32_t taddr = tmem_d + ((uint32_t)(32 * q) << 16) + (uint32_t)(buf * BUF_COLS + c0);
 #pragma unroll
         for (int ch = 0; ch < NPT / CH; ch++) { // eight columns at a time keeps the slices' values within the register budget
           uint32_t v[4][CH];
@@ -513,7 +535,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
           if (ch == NPT / CH - 1) { // every value of the buffer this warp needs is in registers: it may be overwritten
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty + 8 * h);
+            if (lane == 0) mbar_arrive(acc_empty + 8 * buf);
           }
           Drain<CH>::run(hdr, side + HDR_BYTES, h, c0 + ch * CH, v, acc + ch * CH);
         }
@@ -607,24 +629,27 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
   __syncthreads();
 #ifdef XNQ_DEV_TRACE
   if (blockIdx.x == 0 && threadIdx.x == 0) g_imma_trace[30] = nunits;
+  XNQ_GT(27);
 #endif
-  if (warp == MMA_WARP) tmem_dealloc(tmem_d, 2 * ACC_COLS);
+  if (warp == MMA_WARP) tmem_dealloc(tmem_d, TMEM_COLS);
 }
 
 // ---- activations: quantize (or take an activation image), lay out as the MMA's B operand, write the records ----
-// One CTA of 256 threads per activation row of the padded pass (rows >= m are zero). Thread t handles elements
-// 8t..8t+7 of each 2048-element stretch; a warp covers one 256-element block.
+// CTAs of 256 threads over (activation row of the padded pass, 2048-element stretch of k); rows >= m are zero.
+// Thread t handles elements 8t..8t+7 of a stretch; a warp covers one 256-element block.
 template <int ACT, typename XT>
 __global__ void __launch_bounds__(256) imma_prepare(const XT *__restrict__ x, const int8_t *__restrict__ img_q, const float *__restrict__ img_d,
                                                     const int16_t *__restrict__ img_b, int64_t m, int64_t k, int64_t ldx, int NP, int nsteps,
                                                     uint8_t *__restrict__ bimg, uint8_t *__restrict__ meta, unsigned int *__restrict__ tile_cnt, int tiles) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); // the matmul kernel may start its set-up and its weight loads now
+  XNQ_GT(24);
   const int row = blockIdx.x;
-  if (blockIdx.x == 0)
+  if (blockIdx.x == 0 && blockIdx.y == 0)
     for (int i = threadIdx.x; i < tiles; i += blockDim.x) tile_cnt[i] = 0;
   const int lane = threadIdx.x & 31;
   const int64_t kpad = (int64_t)nsteps * 256;
   const int nblk_act = (int)(k / (ACT == XNQ_Q8_0 ? QK : QK_K));
-  for (int64_t base = 0; base < kpad; base += 2048) {
+  for (int64_t base = (int64_t)blockIdx.y * 2048; base < kpad; base += (int64_t)gridDim.y * 2048) {
     const int64_t k8 = base + (int64_t)threadIdx.x * 8;
     if (base + (int64_t)(threadIdx.x & ~31) * 8 >= kpad) break; // whole warps leave together
     uint32_t lo = 0, hi = 0;
@@ -680,6 +705,7 @@ __global__ void __launch_bounds__(256) imma_prepare(const XT *__restrict__ x, co
       }
     }
   }
+  XNQ_GT(25);
 }
 
 int g_sms = 0;
@@ -787,7 +813,7 @@ int launch_imma(const WeightView &w, const void *x, int x_dtype, int64_t m, int6
       iq = av.q + r0 * k, id = av.d + r0 * (k / blk), ib = av.bsum + r0 * (k / 16);
     }
 #define XNQ_IMMA_PREP(ACT, XT)                                                                                                          \
-  imma_prepare<ACT, XT><<<(unsigned)pl.NP, 256, 0, s>>>(iq ? nullptr : static_cast<const XT *>(x) + r0 * ldx, iq, id, ib, rows, k, ldx, pl.NP, \
+  imma_prepare<ACT, XT><<<dim3((unsigned)pl.NP, (unsigned)std::min<int64_t>(16, (k + 2047) / 2048)), 256, 0, s>>>(iq ? nullptr : static_cast<const XT *>(x) + r0 * ldx, iq, id, ib, rows, k, ldx, pl.NP, \
                                                         pl.nsteps, bimg, meta, cnt, pl.tiles)
     if (act == XNQ_Q8_0) {
       if (x_dtype == XNQ_F16) XNQ_IMMA_PREP(XNQ_Q8_0, __half);
@@ -839,15 +865,20 @@ int launch_imma(const WeightView &w, const void *x, int x_dtype, int64_t m, int6
     a.raw_stage_bytes = (TILE_N * (a.step_bytes[0] + (a.nstreams > 1 ? a.step_bytes[1] : 0)) + 127) & ~127u;
     a.b_stage_bytes = (uint32_t)pl.NP * 256;
     a.side_stage_bytes = HDR_BYTES + (uint32_t)pl.NP * 32;
-    // shared-memory plan: A stages | B stages | side stages | raw stages (as many as fit)
+    // shared-memory plan: A stages (8, 6 or 4 half steps) | B stages (half as many whole steps) | side stages | raw stages (4..2)
+    const size_t budget = IMMA_SMEM - 1024; // 1024: alignment slack of the base
+    a.a_stages = 0;
+    for (int as = MAX_A_STAGES; as >= 4 && !a.a_stages; as -= 2)
+      for (int rs = MAX_RAW_STAGES; rs >= 2 && !a.a_stages; rs--)
+        if ((size_t)as * A_STAGE_BYTES + (size_t)(as / 2) * a.b_stage_bytes + (size_t)SIDE_STAGES * a.side_stage_bytes + (size_t)rs * a.raw_stage_bytes + 256 <= budget &&
+            (rs >= 3 || as == 4))
+          a.a_stages = as, a.raw_stages = rs;
+    if (!a.a_stages) return fail(XNQ_ERR_SIZE, "imma: shared-memory plan does not fit");
+    a.b_stages = a.a_stages / 2;
     a.a_off = 0;
-    a.b_off = A_STAGES * A_STAGE_BYTES;
-    a.b_stages = pl.NP <= 32 ? 4 : 3;
+    a.b_off = (uint32_t)a.a_stages * A_STAGE_BYTES;
     a.side_off = a.b_off + a.b_stages * a.b_stage_bytes;
     a.raw_off0 = (a.side_off + SIDE_STAGES * a.side_stage_bytes + 127) & ~127u;
-    const size_t avail = IMMA_SMEM - 1024 - a.raw_off0; // 1024: alignment slack of the base
-    a.raw_stages = (int)std::min<size_t>(MAX_RAW_STAGES, avail / a.raw_stage_bytes);
-    if (a.raw_stages < 2) return fail(XNQ_ERR_SIZE, "imma: shared-memory plan does not fit");
     profile_mark(s, true);
     if (w.dtype == XNQ_Q4K) rc = launch_np<ConvQ4K, DrainQ4K>(a, pl.NP, (unsigned)pl.grid, s);
     else if (w.dtype == XNQ_Q8_0) rc = launch_np<ConvQ8_0, DrainBlockScaled>(a, pl.NP, (unsigned)pl.grid, s);

@@ -66,8 +66,11 @@ constexpr int CW = 16;               // consumer warps per CTA (a power of two)
 constexpr int NTHREADS = (CW + 1) * 32; // + one producer warp
 constexpr int MAX_R = 2;             // weight rows per consumer warp and stage: 2 where at least two such stages fit, else 1
 constexpr int MAX_STAGES = 8;
+#ifndef XNQ_MV_EARLY
+#define XNQ_MV_EARLY 1
+#endif
+constexpr int EARLY_STAGES = XNQ_MV_EARLY; // stages requested before the consumers have their activations
 constexpr int SEG_UNITS = 16;        // 256-element units of k one warp keeps in registers
-constexpr uint32_t WAIT_LIMIT = 1u << 26; // non-blocking polls (a few ns each): about a second
 constexpr size_t SMEM_BUDGET = 225 * 1024; // one CTA per SM
 constexpr uint32_t HINT_CHUNK = 16384;    // bytes per L2 prefetch request for the next weight
 
@@ -98,23 +101,34 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// One wait attempt: the thread is suspended by the hardware until the phase completes or a system-chosen time limit
+// passes (it takes no issue slots meanwhile, unlike a test_wait spin, which with two dozen polling warps per SM slowed
+// the threads that issue copies and MMAs several times over).
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ unsigned long long wall_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull; // a wait that lasts two seconds is given up
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 // bounded wait of one thread: false (and a sticky status bit) if the phase never completes
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int bit) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+  if (mbar_test(bar, parity)) return true;
+  const unsigned long long t0 = wall_ns();
+  while (wall_ns() - t0 < WAIT_LIMIT_NS)
     if (mbar_test(bar, parity)) return true;
   atomicOr(&g_matvec_status, bit);
   return false;
@@ -524,12 +538,24 @@ matvec_ring_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtyp
   pdl_launch_dependents(); // the next launch in the stream may start as soon as SMs are free
 
   if (warp == CW) { // ---- producer: weights are immutable after upload, no dependency on earlier kernels ----
-    if (lane == 0) {
-      int issued = 0;
-      for (int it = 0; it < niter; it++) {
-        const int s = it % S;
+    int issued = 0;
+    bool dead = false, synced = false;
+    for (int it = 0; it < niter; it++) {
+      const int s = it % S;
+      // The first stages are requested at once. The rest of the ring is requested only when the consumers have their
+      // activations: requested earlier, its bytes sit in the memory system's queues in front of the loads of x, which
+      // every consumer needs before it can start (measured: x then takes 1 to 3 us instead of half a microsecond), and
+      // those stages are not consumed before the first ones anyway.
+      if (it == EARLY_STAGES) {
+        asm volatile("bar.sync 14, %0;" ::"n"(NTHREADS) : "memory"); // all 32 lanes: the barrier counts threads
+        synced = true;
+      }
+      if (lane == 0 && !dead) {
         if (it == S) pdl_wait(); // nothing is handed back before the previous kernel has retired: do not count that time
-        if (it >= S && !mbar_wait(empty0 + 8 * s, ((it / S) - 1) & 1, 2u)) break;
+        if (it >= S && !mbar_wait(empty0 + 8 * s, ((it / S) - 1) & 1, 2u)) {
+          dead = true;
+          continue;
+        }
         const int rows = min(RPS, nrows - it * RPS);
         issued = it + 1;
         mbar_expect_tx(full0 + 8 * s, (uint32_t)rows * ring.row_bytes_total);
@@ -549,14 +575,19 @@ matvec_ring_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtyp
           }
         }
       }
+    }
+    if (!synced) asm volatile("bar.sync 14, %0;" ::"n"(NTHREADS) : "memory"); // the consumers arrive on it in any case
+    if (lane == 0) {
+      // The weight this stream multiplies next, if the caller named it: this CTA's share is asked into L2 now that
+      // all of the CTA's own rows have been requested, so the requests fill the memory system while the consumers
+      // finish (asked for earlier, they compete with the CTA's own stream and slow it down).
+      if (ring.hint_base && issued == niter) {
+        const unsigned long long share = ((ring.hint_bytes / gridDim.x) + HINT_CHUNK - 1) & ~(unsigned long long)(HINT_CHUNK - 1);
+        const unsigned long long h0 = share * blockIdx.x, h1 = min(h0 + share, ring.hint_bytes & ~15ull);
+        for (unsigned long long o = h0; o < h1; o += HINT_CHUNK) bulk_prefetch_l2(ring.hint_base + o, (uint32_t)min((unsigned long long)HINT_CHUNK, h1 - o));
+      }
       // nothing may be in flight into this CTA's shared memory when it exits
       for (int it = max(0, issued - S); it < issued; it++) mbar_wait(full0 + 8 * (it % S), (it / S) & 1, 2u);
-    } else if (ring.hint_base) {
-      // the weight this stream multiplies next, if the caller named it: this CTA's share is asked into L2
-      const unsigned long long share = ((ring.hint_bytes / gridDim.x) + HINT_CHUNK - 1) & ~(unsigned long long)(HINT_CHUNK - 1);
-      const unsigned long long h0 = share * blockIdx.x, h1 = min(h0 + share, ring.hint_bytes & ~15ull);
-      for (unsigned long long o = h0 + (unsigned long long)(lane - 1) * HINT_CHUNK; o < h1; o += 31ull * HINT_CHUNK)
-        bulk_prefetch_l2(ring.hint_base + o, (uint32_t)min((unsigned long long)HINT_CHUNK, h1 - o));
     }
     return;
   }
@@ -586,6 +617,7 @@ matvec_ring_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtyp
     xr.issue(x, x_dtype, k);
     xr.template finish<ACT>(k, sq, sd, sb);
   }
+  asm volatile("bar.arrive 14, %0;" ::"n"(NTHREADS) : "memory"); // the producer may request the rest of the ring
   consumer_sync();
   XNQ_TRACE_POINT(2);
   LaneT st;

@@ -66,7 +66,7 @@ extern "C" int xnq_matmul_t_static(const xnq_weight *w, const void *x, int x_dty
   if (!aligned_to(y, yes)) return fail(XNQ_ERR_ALIGN, "matmul_t_static: y is not aligned to its element size");
   const int adt = act_dtype_for(w->v.dtype);
   bool use_mma = false;
-  const int64_t pass = small_batch_pass(w, m, y_dtype, &use_mma); // the kernel xnq_matmul_t takes for this weight, so results are identical
+  const int64_t pass = small_batch_pass(w, m, y_dtype, &use_mma); // a kernel that needs nothing but the quantized activations as scratch
   if (pass == 0) return fail(XNQ_ERR_SIZE, "matmul_t_static: k = %lld is too large for the shared-memory staging of one activation row", (long long)k);
   // rows per pass: what the kernel can stage AND what the built-in array can hold
   int64_t rows_at_once = m < pass ? m : pass;

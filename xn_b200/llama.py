@@ -238,15 +238,21 @@ class QLlama:
         self._x.copy_(self.embed.index_select(0, self.tokens))
         delta = None
         xi, hi = self._xn_img, self._h_img
-        for L in self.layers:
+        # one row: every linear's kernel is told which weight comes next, and asks for it to be brought into L2 as it finishes
+        hint = (lambda w: w.hint_next()) if self.batch == 1 else (lambda w: None)
+        for li, L in enumerate(self.layers):
             ops.add_rmsnorm(self._x, delta, L.norm1, c.rms_eps, None if xi else self._xn, xi)
+            hint(L.wo)
             L.wqkv.matmul_t(xi or self._xn, out=self._qkv)
             ops.rope_kv_store(self._qkv, self.cos, self.sin, self.pos, self._q, L.k_cache, L.v_cache, self.hl, self.kvl)
             ops.attn_decode(self._q, L.k_cache, L.v_cache, self.pos, self._a.view(self.batch, self.hl, c.head_dim), self.hl, self.kvl)
+            hint(L.wgu)
             o = self._linear_parts(L.wo, self._a, self._o)           # world summands per row when sharded
             ops.add_rmsnorm(self._x, o, L.norm2, c.rms_eps, None if xi else self._xn, xi)
+            hint(L.wdown)
             L.wgu.matmul_t(xi or self._xn, out=self._gu)
             ops.swiglu(self._gu, None if hi else self._h, hi)
+            hint(self.layers[li + 1].wqkv if li + 1 < len(self.layers) else self.lm_head)
             delta = self._linear_parts(L.wdown, hi or self._h, self._dn)
         fi = self._head_img
         ops.add_rmsnorm(self._x, delta, self.norm, c.rms_eps, None if fi else self._xn, fi)

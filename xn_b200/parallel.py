@@ -108,6 +108,18 @@ class PeerGather:
         self._next = 0
         self.slot_elems = slot_elems
 
+    def set_deferred(self, deferred: bool) -> None:
+        """Deferred waits: gathers publish and retire; ``wait()`` awaits the peers' columns of all gathers issued so far and
+        must lie between a gather and the first reader of its slot (xnq_comm_set_deferred / xnq_comm_wait)."""
+        from . import _lib
+        _lib.check(self._L.xnq_comm_set_deferred(self._h, 1 if deferred else 0))
+
+    def wait(self) -> None:
+        from . import _lib
+        from .quantized import _stream_ptr
+        with torch.cuda.device(self.device):
+            _lib.check(self._L.xnq_comm_wait(self._h, _stream_ptr(self.device)))
+
     def next_slot(self) -> int:
         s = self._next
         self._next = (s + 1) % self.nslots

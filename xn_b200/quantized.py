@@ -198,6 +198,11 @@ class QCudaTensor:
             pool.append(torch.empty(max(need, 256), dtype=torch.uint8, device=self.device))
         return pool[-1]
 
+    def hint_next(self) -> None:
+        """Names this weight as the one the calling thread multiplies after its next one-row matmul: that matmul's kernel
+        asks for these bytes to be brought into L2 while it finishes (xnq_hint_next_weight)."""
+        check(_lib.lib().xnq_hint_next_weight(self._h))
+
     def matmul_t(self, lhs: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``lhs @ self^T`` with ``lhs`` of shape ``(.., k)``; the result is ``(.., n)`` (q8.rs:116-157)."""
         if hasattr(lhs, "act_dtype"):   # an ActImage: activations quantized ahead of the call
@@ -206,9 +211,12 @@ class QCudaTensor:
             if out is None:
                 out = torch.empty((lhs.m, self.n), dtype=torch.float32, device=self.device)
             y = out.view(-1, self.n)
+            ws = self.workspace(lhs.m) if lhs.m > 1 else None   # batches go to the tensor-core kernel, which re-lays the image out in scratch
             with torch.cuda.device(self.device):
                 check(_lib.lib().xnq_matmul_t(self._h, ctypes.c_void_p(lhs.data_ptr()), _lib.XNQ_ACT_IMAGE, lhs.m, 0, ctypes.c_void_p(y.data_ptr()),
-                                              int(_TORCH_TO_XNQ[y.dtype]), y.stride(0) if lhs.m > 1 else self.n, None, 0, _stream_ptr(self.device)))
+                                              int(_TORCH_TO_XNQ[y.dtype]), y.stride(0) if lhs.m > 1 else self.n,
+                                              ctypes.c_void_p(ws.data_ptr()) if ws is not None else None, ws.numel() if ws is not None else 0,
+                                              _stream_ptr(self.device)))
             return out
         if lhs.shape[-1] != self.k:
             raise ValueError(f"cuda quantized matmul: input {tuple(lhs.shape)} does not match weight (n={self.n}, k={self.k})")
