@@ -501,7 +501,8 @@ def measure_matmul(ctx, args, name, dt, n, k, m, with_cpu=True):
                 "unit": "TFLOP/s" if tensor_bound else "GB/s",
                 "frac": ((tflops / peak_tf) if tensor_bound else (achieved / peak)) if achieved else None,
                 "traffic": captured_traffic(name) if world == 1 else None,
-                "kernel": "prefill_kernel (tcgen05)" if m > 16 else ("matvec_tma_kernel" if (m == 1 and k <= 4096) else "matvec"),
+                "kernel": ("matvec_ring_kernel" if m == 1 else "imma_kernel (tcgen05 kind::i8)" if (m <= 64 and dt.name != "Q6K")
+                           else "prefill_persistent_kernel (tcgen05 kind::f16)" if m > 16 else "matvec_q6k (dp4a)"),
                 "launch_us": kern_ms * 1e3, "launches_timed": cnt.value, "peak_kind": f"of {peak_kind}",
                 "bytes_per_launch": kern_bytes, "flops_per_launch": flops, "hbm_gbs": achieved, "tflops": tflops,
                 "isolated_launch_us": isolated_us,

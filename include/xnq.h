@@ -253,15 +253,21 @@ int xnq_rope_kv_store(const float *qkv, const float *cos_table, const float *sin
 /* Single-query attention over cache positions 0..*pos_dev: out[batch, heads, head_dim] =
  * softmax(q k^T / sqrt(head_dim)) v with heads / kv_heads query heads per KV head. head_dim 128. The
  * sequence is split over several CTAs per head; `workspace` (xnq_attn_decode_workspace_bytes, zeroed
- * once after allocation, reusable by every later call on the same stream) holds their partial sums. */
+ * once after allocation, reusable by every later call on the same stream whatever its batch and heads, as long
+ * as it is large enough) holds their partial sums. A position outside [0, max_seq) sets a bit of
+ * xnq_device_status: xnq_rope_kv_store then stores nothing; this call clamps a position past the cache and
+ * writes zeros for a negative one. */
 size_t xnq_attn_decode_workspace_bytes(int64_t batch, int heads);
 int xnq_attn_decode(const float *q, const void *k_cache, const void *v_cache, const long long *pos_dev, float *out,
                     int64_t batch, int heads, int kv_heads, int head_dim, int64_t max_seq, void *workspace,
                     size_t ws_bytes, void *stream);
 
-/* Sticky device-side status bits of this library's kernels on the current device (0 = healthy):
- * bit 0 a consumer's bounded mbarrier wait expired, bit 1 a producer's, bit 2 a self-check refused an
- * access. Synchronizes the device.
+/* Sticky device-side status bits of this library's kernels on the current device (0 = healthy).
+ * Bits 0-7, one-row ring kernel: bit 0 a consumer's bounded mbarrier wait expired, bit 1 a producer's, bit 2 a
+ * self-check refused an access. Bits 8-15: the same for the fp16 tensor-core kernel. Bits 16-23, integer
+ * tensor-core kernel: a wait of the producer (16), a converter (17), the MMA issuer (18), a drain warp (19)
+ * expired. Bits 24-25: a decode position outside [0, max_seq) reached xnq_rope_kv_store (24) or
+ * xnq_attn_decode (25). Synchronizes the device.
  * No counterpart in the reference (its kernels never wait on anything). */
 int xnq_device_status(unsigned int *bits);
 /* When bit 2 of the status is set, a kernel's self-check refused an out-of-range copy or store

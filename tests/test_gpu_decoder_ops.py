@@ -82,6 +82,53 @@ def test_rope_store_and_attention(B, H, KV):
         torch.testing.assert_close(out, torch.einsum("bhs,bhsd->bhd", w, vv), rtol=2e-4, atol=2e-5)
 
 
+def test_attention_workspace_reuse_and_position_range():
+    """One workspace serves calls of different (batch, heads): the arrival counters sit at offsets that depend on the
+    (sequence, head) index alone. A position outside the cache is reported through the status word, never NaN."""
+    import ctypes
+    from xn_b200 import decoder_ops as ops, _lib
+    L = _lib.lib()
+    torch.manual_seed(5)
+    hd, max_seq = 128, 64
+
+    def run(B, H, KV, pos_i, ws):
+        kc = torch.randn(B, KV, max_seq, hd, device=DEV).to(torch.bfloat16); vc = torch.randn(B, KV, max_seq, hd, device=DEV).to(torch.bfloat16)
+        q = torch.randn(B, H, hd, device=DEV); out = torch.full_like(q, float("nan"))
+        pos = torch.tensor([pos_i], device=DEV, dtype=torch.int64)
+        _lib.check(L.xnq_attn_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), pos.data_ptr(), out.data_ptr(), B, H, KV, hd, max_seq, ws.data_ptr(), ws.numel(),
+                                     ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        last = min(max(pos_i, 0), max_seq - 1)
+        kk = kc[:, :, : last + 1].float().repeat_interleave(H // KV, 1); vv = vc[:, :, : last + 1].float().repeat_interleave(H // KV, 1)
+        w = torch.softmax(torch.einsum("bhd,bhsd->bhs", q, kk) / math.sqrt(hd), -1)
+        return out, torch.einsum("bhs,bhsd->bhd", w, vv)
+
+    ws = torch.zeros(int(L.xnq_attn_decode_workspace_bytes(4, 8)), dtype=torch.uint8, device=DEV)
+    for B, H, KV in [(4, 8, 2), (1, 32, 8), (2, 4, 4), (4, 8, 2), (1, 2, 1)]:   # every shape splits the sequence differently
+        out, ref = run(B, H, KV, 40, ws)
+        torch.testing.assert_close(out, ref, rtol=2e-4, atol=2e-5)
+    st = ctypes.c_uint()
+    _lib.check(L.xnq_device_status(ctypes.byref(st)))
+    assert st.value >> 24 == 0
+    out, ref = run(2, 4, 2, max_seq + 5, ws)           # past the cache: clamped and flagged
+    torch.testing.assert_close(out, ref, rtol=2e-4, atol=2e-5)
+    out, _ = run(2, 4, 2, -1, ws)                      # nothing to attend to: zeros and flagged
+    assert torch.equal(out, torch.zeros_like(out))
+    _lib.check(L.xnq_device_status(ctypes.byref(st)))
+    assert (st.value >> 24) & 2
+    # the store kernel writes nothing for a position outside the cache
+    H, KV = 4, 2
+    qkv = torch.randn(1, (H + 2 * KV) * hd, device=DEV)
+    cos = torch.ones(max_seq, hd // 2, device=DEV); sin = torch.zeros(max_seq, hd // 2, device=DEV)
+    kc = torch.zeros(1, KV, max_seq, hd, device=DEV, dtype=torch.bfloat16); vc = torch.zeros_like(kc); q_out = torch.zeros(1, H, hd, device=DEV)
+    ops.rope_kv_store(qkv, cos, sin, torch.tensor([max_seq], device=DEV, dtype=torch.int64), q_out, kc, vc, H, KV)
+    assert not kc.any() and not vc.any() and not q_out.any()
+    _lib.check(L.xnq_device_status(ctypes.byref(st)))
+    assert (st.value >> 24) & 1
+    _lib.check(L.xnq_init(0))                          # clears the sticky bits for the tests that follow
+    _lib.check(L.xnq_device_status(ctypes.byref(st)))
+    assert st.value == 0
+
+
 def test_activation_images_equal_the_in_call_quantizer():
     """An image written by the stand-alone quantizer, by add_rmsnorm or by swiglu holds the bytes the matmul's own
     quantizer would produce from the same f32 rows, so matmul results through an image are bit-identical."""

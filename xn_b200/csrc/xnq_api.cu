@@ -227,17 +227,19 @@ int xnq_init(int device) {
   if ((rc = matvec_tma_init(device)) != XNQ_OK) return rc;
   if ((rc = prefill_init(device)) != XNQ_OK) return rc;
   if ((rc = imma_init(device)) != XNQ_OK) return rc;
+  if ((rc = decoder_ops_init()) != XNQ_OK) return rc;
   return XNQ_OK;
 }
 
 int xnq_device_status(unsigned int *bits) {
   clear_error();
   if (!bits) return fail(XNQ_ERR_NULL, "device_status: bits is NULL");
-  unsigned int mv = 0, pf = 0, im = 0;
+  unsigned int mv = 0, pf = 0, im = 0, dc = 0;
   int rc = matvec_status(&mv);
   if (rc == XNQ_OK) rc = prefill_status(&pf);
   if (rc == XNQ_OK) rc = imma_status(&im);
-  *bits = mv | (pf << 8) | (im << 16);
+  if (rc == XNQ_OK) rc = decoder_status(&dc);
+  *bits = (mv & 0xffu) | ((pf & 0xffu) << 8) | ((im & 0xffu) << 16) | ((dc & 0xffu) << 24);
   return rc;
 }
 

@@ -194,6 +194,33 @@ namespace xnq {
 
 // launch accounting + per-kernel event timing (xnq_api.cu)
 void count_launch(int n = 1);
+
+// ---- programmatic dependent launch ---------------------------------------------------------------------------
+// Every kernel of the decode step is launched with programmatic stream serialization: it lets its successor in the
+// stream start (pdl_launch_dependents, first thing) while it is still running, and itself touches nothing an earlier
+// kernel may still write or read before pdl_wait() returns (the earlier grids have completed and their writes are
+// visible). What a kernel does before pdl_wait() is limited to set-up and to reading immutable data (weights), so
+// results are exactly those of plain stream order; what is gained is the launch latency of every kernel and, for the
+// weight-streaming kernels, the start of their stream. Every CTA executes pdl_wait() before it exits, so a grid never
+// completes before its predecessors.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args &&...args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 void profile_mark(cudaStream_t s, bool start);
 
 // xnq_layout.cu
@@ -247,6 +274,8 @@ int launch_imma(const WeightView &w, const void *x, int x_dtype, int64_t m, int6
                 cudaStream_t s);
 int imma_init(int device);
 int imma_status(unsigned int *bits);
+int decoder_ops_init();
+int decoder_status(unsigned int *bits); // 1 rope/store, 2 attention: a position outside [0, max_seq)
 constexpr int64_t IMMA_MAX_M = 64; // batches up to here take the integer tensor-core kernel; larger ones the fp16 one
 
 // xnq_prefill.cu  (m > 64, and Q6_K above 16 rows: tcgen05 / TMEM contraction on fp16 operands)

@@ -59,6 +59,8 @@ template <int ACT>
 __global__ void __launch_bounds__(256) add_rmsnorm_kernel(float *x, const float *delta, int parts, const float *w, float eps, float *out, void *image,
                                                           int64_t rows, int d) {
   __shared__ float part[8];
+  pdl_launch_dependents();
+  pdl_wait(); // x and delta are earlier kernels' outputs
   const int64_t row = blockIdx.x;
   const int lane = threadIdx.x & 31;
   float *xr = x + row * d;
@@ -139,6 +141,8 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(float *x, const float 
 // elements per thread; f is a multiple of 256 when an image is written, so a warp never straddles two rows.
 template <int ACT>
 __global__ void __launch_bounds__(256) swiglu_kernel(const float *gu, float *out, void *image, int64_t rows, int f) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t per_row = f / 8;
   const bool valid = t < rows * per_row;
@@ -162,14 +166,21 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const float *gu, float *out
   if (ACT != 0) quantize_store8<ACT>(v, valid, row_image(image, rows, f, ACT == XNQ_Q8_0 ? QK : QK_K, r), c8, threadIdx.x & 31);
 }
 
+__device__ unsigned int g_decoder_status; // sticky: 1 rope/store, 2 attention saw a position outside [0, max_seq)
+
 // One token per sequence. qkv [B, (H + 2 KV) * hd] f32 -> q_out [B, H, hd] f32 (rotated), and the rotated k
 // and plain v of every KV head go to the caches [B, KV, max_seq, hd] (bf16) at position *pos.
 // grid (H + 2 KV, B), block hd / 2.
 __global__ void rope_store_kernel(const float *qkv, const float *cos_t, const float *sin_t, const long long *pos_p, float *q_out,
                                   __nv_bfloat16 *k_cache, __nv_bfloat16 *v_cache, int H, int KV, int hd, int max_seq) {
   const int head = blockIdx.x, b = blockIdx.y, i = threadIdx.x, half = hd / 2;
+  pdl_launch_dependents();
+  pdl_wait();
   const long long pos = *pos_p;
-  if (pos < 0 || pos >= max_seq) return;
+  if (pos < 0 || pos >= max_seq) {
+    if (head == 0 && b == 0 && i == 0) atomicOr(&g_decoder_status, 1u);
+    return;
+  }
   const float *src = qkv + ((int64_t)b * (H + 2 * KV) + head) * hd;
   const float x1 = src[i], x2 = src[i + half];
   if (head < H + KV) {
@@ -195,8 +206,14 @@ __global__ void rope_store_kernel(const float *qkv, const float *cos_t, const fl
 // every lane accumulates its own 4 output dimensions over the 32 v rows (coalesced 256-byte rows).
 // Each CTA leaves (max, sum, acc[128]) in the workspace; the last CTA of a (head, sequence) to finish
 // merges the splits. The arrival counters wrap to zero by themselves (atomicInc), so the workspace
-// only has to be zeroed once, when it is allocated.
+// only has to be zeroed once, when it is allocated. Workspace layout: one group per (sequence, head) pair,
+// indexed b * heads + head: a 16-byte slot whose first word is the arrival counter, then ATT_MAX_SPLITS
+// records. A counter's address depends on the pair's linear index alone, so a workspace may be reused by calls
+// of different batch sizes and head counts (one call at a time).
+// A position outside [0, max_seq) sets a sticky status bit (1 rope/store, 2 attention): the rope kernel then
+// stores nothing, attention clamps a position past the cache and writes zeros for a negative one.
 constexpr int ATT_WARPS = 4, ATT_HD = 128, ATT_MAX_SPLITS = 16, ATT_REC = ATT_HD + 2;
+constexpr int ATT_GROUP = 4 + ATT_MAX_SPLITS * ATT_REC; // floats per (sequence, head) group
 
 __device__ __forceinline__ void online_merge(float &m, float &l, float4 &acc, float m2, float l2, const float4 &a2) {
   const float mn = fmaxf(m, m2);
@@ -207,9 +224,9 @@ __device__ __forceinline__ void online_merge(float &m, float &l, float4 &acc, fl
 }
 
 __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const float *q, const __nv_bfloat16 *k_cache, const __nv_bfloat16 *v_cache,
-                                                                      const long long *pos_p, float *out, float *part, unsigned int *arrivals, int H, int KV,
-                                                                      int max_seq, float scale) {
-  __shared__ __align__(16) float s_q[ATT_HD];
+                                                                      const long long *pos_p, float *out, float *part, int H, int KV, int max_seq,
+                                                                      float scale) {
+  __shared__ __align__(16) float s_q[ATT_WARPS][ATT_HD]; // every warp keeps its own copy: no block-wide barrier before the loads
   __shared__ float s_m[ATT_WARPS], s_l[ATT_WARPS];
   __shared__ __align__(16) float s_acc[ATT_WARPS][ATT_HD];
   __shared__ __align__(16) __nv_bfloat16 s_k[ATT_WARPS][32][ATT_HD + 8]; // rows padded to 272 bytes: conflict-free row reads
@@ -217,40 +234,66 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const float
   const int head = blockIdx.x, b = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kvh = head / (H / KV);
-  long long last = *pos_p;
-  if (last >= max_seq) last = max_seq - 1;
-  const long long npos = last + 1, per = (npos + nsplit - 1) / nsplit;
-  const long long c0 = split * per, c1 = min(npos, c0 + per);
-  if (threadIdx.x < ATT_HD) s_q[threadIdx.x] = q[((int64_t)b * H + head) * ATT_HD + threadIdx.x] * scale;
-  __syncthreads();
+  pdl_launch_dependents();
+  pdl_wait(); // q, the caches and the position are earlier kernels' outputs
+  const long long pos = *pos_p;
+  int last = (int)pos;
+  if (pos < 0 || pos >= max_seq) {
+    if (head == 0 && b == 0 && split == 0 && threadIdx.x == 0) atomicOr(&g_decoder_status, 2u);
+    if (pos < 0) { // nothing to attend to: zeros, not 0 / 0
+      if (split == 0 && threadIdx.x < ATT_HD) out[((int64_t)b * H + head) * ATT_HD + threadIdx.x] = 0.f;
+      return;
+    }
+    last = max_seq - 1;
+  }
+  const int npos = last + 1, per = (npos + nsplit - 1) / nsplit;
+  const int c0 = split * per, c1 = min(npos, c0 + per);
+  const float4 qreg = *reinterpret_cast<const float4 *>(q + ((int64_t)b * H + head) * ATT_HD + lane * 4); // in flight together with the first k and v loads
+  bool q_stored = false;
   const __nv_bfloat16 *kb = k_cache + ((int64_t)b * KV + kvh) * max_seq * ATT_HD, *vb = v_cache + ((int64_t)b * KV + kvh) * max_seq * ATT_HD;
   float m = -INFINITY, l = 0.f;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (long long base = c0 + warp * 32; base < c1; base += ATT_WARPS * 32) {
-    const long long p = base + lane;
+  for (int base = c0 + warp * 32; base < c1; base += ATT_WARPS * 32) {
+    const int p = base + lane;
+    const int cnt = min(32, c1 - base);
     float s = -INFINITY;
-    // the 32 k rows of this run (8 KB, contiguous in the cache) come in with coalesced 16-byte loads and are
-    // turned through shared memory, so that each lane can then read ITS row: a lane reading its own row
-    // straight from global memory makes every load instruction touch 32 different lines
-    __syncwarp();
+    // Everything the run needs from memory is requested at once, so that the run costs one trip to memory and not
+    // several in a row: the 32 k rows (8 KB, contiguous in the cache) with coalesced 16-byte loads, and this lane's
+    // four dimensions of the 32 v rows (coalesced 256-byte rows).
+    uint4 kv[16];
 #pragma unroll
     for (int i = 0; i < 16; i++) {
       const int idx = i * 32 + lane, row = idx >> 4, ch = idx & 15;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (base + row < c1) v = *reinterpret_cast<const uint4 *>(kb + (base + row) * ATT_HD + ch * 8);
-      *reinterpret_cast<uint4 *>(&s_k[warp][row][ch * 8]) = v;
+      kv[i] = make_uint4(0, 0, 0, 0);
+      if (row < cnt) kv[i] = *reinterpret_cast<const uint4 *>(kb + (int64_t)(base + row) * ATT_HD + ch * 8);
+    }
+    uint2 vr[32];
+#pragma unroll
+    for (int j = 0; j < 32; j++) {
+      vr[j] = make_uint2(0, 0);
+      if (j < cnt) vr[j] = *reinterpret_cast<const uint2 *>(vb + (int64_t)(base + j) * ATT_HD + lane * 4);
+    }
+    // the k rows are turned through shared memory, so that each lane can then read ITS row: a lane reading its own
+    // row straight from global memory makes every load instruction touch 32 different lines
+    __syncwarp();
+    if (!q_stored) {
+      *reinterpret_cast<float4 *>(&s_q[warp][lane * 4]) = make_float4(qreg.x * scale, qreg.y * scale, qreg.z * scale, qreg.w * scale);
+      q_stored = true;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+      const int idx = i * 32 + lane, row = idx >> 4, ch = idx & 15;
+      *reinterpret_cast<uint4 *>(&s_k[warp][row][ch * 8]) = kv[i];
     }
     __syncwarp();
     if (p < c1) {
-      uint4 kr[16];
-#pragma unroll
-      for (int c = 0; c < 16; c++) kr[c] = *reinterpret_cast<const uint4 *>(&s_k[warp][lane][c * 8]);
       float d = 0.f;
 #pragma unroll
       for (int c = 0; c < 16; c++) {
-        const float4 qa = *reinterpret_cast<const float4 *>(&s_q[c * 8]), qb = *reinterpret_cast<const float4 *>(&s_q[c * 8 + 4]);
-        const float2 k0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&kr[c].x)), k1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&kr[c].y));
-        const float2 k2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&kr[c].z)), k3 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&kr[c].w));
+        const uint4 kr = *reinterpret_cast<const uint4 *>(&s_k[warp][lane][c * 8]);
+        const float4 qa = *reinterpret_cast<const float4 *>(&s_q[warp][c * 8]), qb = *reinterpret_cast<const float4 *>(&s_q[warp][c * 8 + 4]);
+        const float2 k0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&kr.x)), k1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&kr.y));
+        const float2 k2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&kr.z)), k3 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&kr.w));
         d += qa.x * k0.x + qa.y * k0.y + qa.z * k1.x + qa.w * k1.y + qb.x * k2.x + qb.y * k2.y + qb.z * k3.x + qb.w * k3.y;
       }
       s = d;
@@ -259,12 +302,10 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const float
     const float pw = s == -INFINITY ? 0.f : __expf(s - mn), corr = m == -INFINITY ? 0.f : __expf(m - mn);
     l = l * corr + warp_sum(pw);
     acc = make_float4(acc.x * corr, acc.y * corr, acc.z * corr, acc.w * corr);
-    const int cnt = (int)min((long long)32, c1 - base);
-#pragma unroll 8
-    for (int j = 0; j < cnt; j++) {
+#pragma unroll
+    for (int j = 0; j < 32; j++) { // rows past the end have weight 0 and zero values
       const float w = __shfl_sync(0xffffffffu, pw, j);
-      const uint2 vr = *reinterpret_cast<const uint2 *>(vb + (base + j) * ATT_HD + lane * 4);
-      const float2 v01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&vr.x)), v23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&vr.y));
+      const float2 v01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&vr[j].x)), v23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&vr[j].y));
       acc.x += w * v01.x, acc.y += w * v01.y, acc.z += w * v23.x, acc.w += w * v23.y;
     }
     m = mn;
@@ -272,7 +313,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const float
   if (lane == 0) s_m[warp] = m, s_l[warp] = l;
   *reinterpret_cast<float4 *>(&s_acc[warp][lane * 4]) = acc;
   __syncthreads();
-  float *rec = part + (((int64_t)b * H + head) * ATT_MAX_SPLITS + split) * ATT_REC;
+  float *group = part + ((int64_t)b * H + head) * ATT_GROUP;
+  float *rec = group + 4 + split * ATT_REC;
   if (warp == 0) { // merge the CTA's warps; lane owns dims 4*lane..
     float gm = s_m[0], gl = s_l[0];
     float4 ga = *reinterpret_cast<const float4 *>(&s_acc[0][lane * 4]);
@@ -286,11 +328,11 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const float
     rec[2 + lane * 4 + 0] = ga.x, rec[2 + lane * 4 + 1] = ga.y, rec[2 + lane * 4 + 2] = ga.z, rec[2 + lane * 4 + 3] = ga.w;
     __threadfence();
     __syncwarp();
-    if (lane == 0) s_last = atomicInc(arrivals + b * H + head, nsplit - 1) == (unsigned)(nsplit - 1);
+    if (lane == 0) s_last = atomicInc(reinterpret_cast<unsigned int *>(group), nsplit - 1) == (unsigned)(nsplit - 1);
     __syncwarp();
     if (!s_last) return;
     __threadfence();
-    const float *r0 = part + ((int64_t)b * H + head) * ATT_MAX_SPLITS * ATT_REC;
+    const float *r0 = group + 4;
     gm = -INFINITY, gl = 0.f, ga = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int sidx = 0; sidx < nsplit; sidx++) {
       const volatile float *r = r0 + sidx * ATT_REC;
@@ -327,10 +369,10 @@ int xnq_add_rmsnorm(float *x, const float *delta, int delta_parts, const float *
   if (rc != XNQ_OK) return rc;
   if (rows == 0) return XNQ_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (!act_image) add_rmsnorm_kernel<0><<<(unsigned)rows, 256, 0, s>>>(x, delta, delta_parts, weight, eps, out, nullptr, rows, (int)d);
-  else if (act_dtype == XNQ_Q8_0) add_rmsnorm_kernel<XNQ_Q8_0><<<(unsigned)rows, 256, 0, s>>>(x, delta, delta_parts, weight, eps, out, act_image, rows, (int)d);
-  else add_rmsnorm_kernel<XNQ_Q8K><<<(unsigned)rows, 256, 0, s>>>(x, delta, delta_parts, weight, eps, out, act_image, rows, (int)d);
-  XNQ_CUDA(cudaGetLastError());
+  const dim3 grid((unsigned)rows), block(256);
+  if (!act_image) XNQ_CUDA(launch_pdl(add_rmsnorm_kernel<0>, grid, block, 0, s, x, delta, delta_parts, weight, eps, out, nullptr, rows, (int)d));
+  else if (act_dtype == XNQ_Q8_0) XNQ_CUDA(launch_pdl(add_rmsnorm_kernel<XNQ_Q8_0>, grid, block, 0, s, x, delta, delta_parts, weight, eps, out, act_image, rows, (int)d));
+  else XNQ_CUDA(launch_pdl(add_rmsnorm_kernel<XNQ_Q8K>, grid, block, 0, s, x, delta, delta_parts, weight, eps, out, act_image, rows, (int)d));
   count_launch();
   return XNQ_OK;
 }
@@ -346,10 +388,9 @@ int xnq_swiglu(const float *gate_up, float *out, void *act_image, int act_dtype,
   if (rows == 0) return XNQ_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const unsigned grid = (unsigned)((rows * f / 8 + 255) / 256);
-  if (!act_image) swiglu_kernel<0><<<grid, 256, 0, s>>>(gate_up, out, nullptr, rows, (int)f);
-  else if (act_dtype == XNQ_Q8_0) swiglu_kernel<XNQ_Q8_0><<<grid, 256, 0, s>>>(gate_up, out, act_image, rows, (int)f);
-  else swiglu_kernel<XNQ_Q8K><<<grid, 256, 0, s>>>(gate_up, out, act_image, rows, (int)f);
-  XNQ_CUDA(cudaGetLastError());
+  if (!act_image) XNQ_CUDA(launch_pdl(swiglu_kernel<0>, dim3(grid), dim3(256), 0, s, gate_up, out, nullptr, rows, (int)f));
+  else if (act_dtype == XNQ_Q8_0) XNQ_CUDA(launch_pdl(swiglu_kernel<XNQ_Q8_0>, dim3(grid), dim3(256), 0, s, gate_up, out, act_image, rows, (int)f));
+  else XNQ_CUDA(launch_pdl(swiglu_kernel<XNQ_Q8K>, dim3(grid), dim3(256), 0, s, gate_up, out, act_image, rows, (int)f));
   count_launch();
   return XNQ_OK;
 }
@@ -361,16 +402,15 @@ int xnq_rope_kv_store(const float *qkv, const float *cos_table, const float *sin
   if (batch < 0 || heads < 1 || kv_heads < 1 || head_dim < 2 || head_dim % 2 || head_dim > 2048 || max_seq < 1)
     return fail(XNQ_ERR_SHAPE, "rope_kv_store: batch %lld heads %d kv_heads %d head_dim %d max_seq %lld", (long long)batch, heads, kv_heads, head_dim, (long long)max_seq);
   if (batch == 0) return XNQ_OK;
-  rope_store_kernel<<<dim3(heads + 2 * kv_heads, (unsigned)batch), head_dim / 2, 0, static_cast<cudaStream_t>(stream)>>>(
-      qkv, cos_table, sin_table, pos_dev, q_out, static_cast<__nv_bfloat16 *>(k_cache), static_cast<__nv_bfloat16 *>(v_cache), heads, kv_heads, head_dim, (int)max_seq);
-  XNQ_CUDA(cudaGetLastError());
+  XNQ_CUDA(launch_pdl(rope_store_kernel, dim3(heads + 2 * kv_heads, (unsigned)batch), dim3(head_dim / 2), 0, static_cast<cudaStream_t>(stream), qkv, cos_table,
+                      sin_table, pos_dev, q_out, static_cast<__nv_bfloat16 *>(k_cache), static_cast<__nv_bfloat16 *>(v_cache), heads, kv_heads, head_dim, (int)max_seq));
   count_launch();
   return XNQ_OK;
 }
 
 size_t xnq_attn_decode_workspace_bytes(int64_t batch, int heads) {
   if (batch <= 0 || heads <= 0) return 0;
-  return (size_t)batch * heads * (ATT_MAX_SPLITS * ATT_REC * sizeof(float) + sizeof(unsigned int));
+  return (size_t)batch * heads * ATT_GROUP * sizeof(float);
 }
 
 int xnq_attn_decode(const float *q, const void *k_cache, const void *v_cache, const long long *pos_dev, float *out, int64_t batch, int heads,
@@ -387,13 +427,23 @@ int xnq_attn_decode(const float *q, const void *k_cache, const void *v_cache, co
   int splits = (int)(296 / (batch * heads));
   splits = splits < 1 ? 1 : (splits > ATT_MAX_SPLITS ? ATT_MAX_SPLITS : splits);
   float *part = static_cast<float *>(workspace);
-  unsigned int *arrivals = reinterpret_cast<unsigned int *>(part + (size_t)batch * heads * ATT_MAX_SPLITS * ATT_REC);
-  attn_decode_kernel<<<dim3(heads, (unsigned)batch, splits), ATT_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      q, static_cast<const __nv_bfloat16 *>(k_cache), static_cast<const __nv_bfloat16 *>(v_cache), pos_dev, out, part, arrivals, heads, kv_heads, (int)max_seq,
-      1.0f / sqrtf((float)head_dim));
-  XNQ_CUDA(cudaGetLastError());
+  XNQ_CUDA(launch_pdl(attn_decode_kernel, dim3(heads, (unsigned)batch, splits), dim3(ATT_WARPS * 32), 0, static_cast<cudaStream_t>(stream), q,
+                      static_cast<const __nv_bfloat16 *>(k_cache), static_cast<const __nv_bfloat16 *>(v_cache), pos_dev, out, part, heads, kv_heads, (int)max_seq,
+                      1.0f / sqrtf((float)head_dim)));
   count_launch();
   return XNQ_OK;
 }
 
 } // extern "C"
+
+namespace xnq {
+int decoder_status(unsigned int *bits) {
+  XNQ_CUDA(cudaMemcpyFromSymbol(bits, g_decoder_status, sizeof(*bits)));
+  return XNQ_OK;
+}
+int decoder_ops_init() {
+  unsigned int zero = 0;
+  XNQ_CUDA(cudaMemcpyToSymbol(g_decoder_status, &zero, sizeof(zero)));
+  return XNQ_OK;
+}
+} // namespace xnq

@@ -13,16 +13,20 @@
 // f32 scaling, so results stay within the f32-accumulate bound (2e-3) at every batch size served.
 //
 // Roles of the 26 warps of a CTA (one CTA per SM, persistent):
-//   producer (1)    per 256-k step one tiled TMA copy per weight stream (cp.async.bulk.tensor.2d, never multicast:
-//                   a box of 128 rows x the step's bytes, rows past the end arrive as zeros) and 1-D bulk copies of
-//                   the quantized activations (already in the MMA's shared-memory layout) and of their per-block
-//                   metadata, into rings of stages guarded by mbarriers. (One bulk copy per weight row was tried
-//                   first: the copy engine takes some 60 ns per copy whatever its size, 128 small copies per step
-//                   cost more than the step.)
-//   converters (8)  two groups of four warps, one thread per weight row; group h unpacks 4-bit codes to int8 (or
-//                   copies int8 codes) of half h (128 k) of every 256-k step from the raw stage into the
-//                   128-byte-swizzled K-major operand image the MMA reads; group 0 also hands the row's scale
-//                   bytes on to the drain;
+//   producer (1)    one thread requests, per 256-k step, the 1-D bulk copies of the quantized activations (already in
+//                   the MMA's shared-memory layout) and of their per-block metadata into rings of stages guarded by
+//                   mbarriers; when the kernel starts it also asks for the CTA's share of the weight's bytes to be
+//                   brought into L2 in long contiguous runs.
+//   converters (8)  two groups of four warps, one thread per weight row; group h handles half h (128 k) of every
+//                   256-k step. Every warp fetches the code bytes of its own 32 rows itself, several steps ahead, with
+//                   16-byte cp.async copies into a ring of warp-private slots (consecutive lanes take consecutive
+//                   16 bytes of a row, so the requests are whole sectors; nothing but the warp's own
+//                   cp.async.wait_group and __syncwarp orders them), unpacks 4-bit codes to int8 (or copies int8
+//                   codes) into the 128-byte-swizzled K-major operand image the MMA reads; group 0 also hands the
+//                   rows' scale bytes on to the drain. (Tiled TMA boxes of 128 rows x 144..256 bytes were tried first:
+//                   a box took 5000 to 7000 cycles to arrive, with or without the bytes in L2, about 17 cycles per box
+//                   row, which held the whole kernel at a third of the memory's rate. One bulk copy per row before
+//                   that: the copy engine takes some 60 ns per copy whatever its size.)
 //   MMA issuer (1)  one thread issues four K = 32 MMAs per half step into accumulator buffer h; an MMA of this
 //                   shape occupies the tensor pipe for about 114 cycles whatever N <= 128 is (measured), which
 //                   bounds a tile of k = 4096 at 128 x 114 cycles;
@@ -38,9 +42,8 @@
 //
 // Every wait is bounded; on expiry a status bit is set and the roles fall through to the common exit, where
 // tensor memory is released.
-#include <cuda.h> // CUtensorMap and the encoder's signature only; the entry point is looked up at run time, nothing links against libcuda
-
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 
 #include "xnq_common.cuh"
@@ -51,12 +54,15 @@ namespace xnq {
 __device__ unsigned int g_imma_status; // sticky: 1 producer, 2 converter, 4 mma, 8 drain wait expired
 #ifdef XNQ_DEV_TRACE
 __device__ long long g_imma_trace[32]; // development builds only: cycles block 0's roles spend in each wait
+__device__ long long g_imma_tl[8 * 64];  // development builds only: block 0's per-unit time line (clock64), 8 points x 64 units
+#define XNQ_TL(pt, i) do { if (blockIdx.x == 0 && (i) < 64) g_imma_tl[(pt) * 64 + (i)] = clock64(); } while (0)
 #define XNQ_GT(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) { unsigned long long g_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_)); g_imma_trace[i] = (long long)g_; } } while (0)
 #define XNQ_TACC(i) do { const long long t1_ = clock64(); tacc[i] += t1_ - t0_; t0_ = t1_; } while (0)
 #define XNQ_TDECL long long tacc[6] = {0, 0, 0, 0, 0, 0}; long long t0_ = clock64()
 #define XNQ_TDUMP(base, cond) do { if ((cond) && blockIdx.x == 0) for (int i_ = 0; i_ < 6; i_++) g_imma_trace[(base) + i_] = tacc[i_]; } while (0)
 #else
 #define XNQ_GT(i) do { } while (0)
+#define XNQ_TL(pt, i) do { } while (0)
 #define XNQ_TACC(i) do { } while (0)
 #define XNQ_TDECL do { } while (0)
 #define XNQ_TDUMP(base, cond) do { } while (0)
@@ -67,13 +73,15 @@ namespace {
 constexpr int TILE_N = 128;         // weight rows per tile = UMMA M
 constexpr int MAX_NP = 64;          // activation rows per pass = UMMA N (multiple of 16)
 constexpr int CONV_WARPS = 8, DRAIN_WARPS = 16;
-constexpr int PRODUCER_WARP = 0, MMA_WARP = 1, CONV_WARP0 = 2, DRAIN_WARP0 = CONV_WARP0 + CONV_WARPS;
+constexpr int ACT_PRODUCER_WARP = 0, MMA_WARP = 1, CONV_WARP0 = 2, DRAIN_WARP0 = CONV_WARP0 + CONV_WARPS;
 constexpr int NTHREADS = (DRAIN_WARP0 + DRAIN_WARPS) * 32; // 832
 constexpr int A_STAGE_BYTES = TILE_N * 128; // one 128-k half step of int8 codes
-constexpr int MAX_A_STAGES = 8, SIDE_STAGES = 4, MAX_RAW_STAGES = 4;
+constexpr int MAX_A_STAGES = 8, SIDE_STAGES = 4, MAX_RAW_STAGES = 8;
 constexpr int HDR_BYTES = TILE_N * 16;      // per 256-k step: 16 bytes of scale data per weight row
 constexpr int TMEM_COLS = 512;              // all of the SM's tensor memory: 512 / (4 slices x NP) accumulator buffers, at most 8
 constexpr size_t IMMA_SMEM = 226 * 1024;
+constexpr uint32_t PF_CHUNK = 16384;              // bytes per L2 prefetch request
+constexpr size_t PF_MAX_BYTES = 80ull << 20;      // larger weights are not prefetched whole: they would push each other out of L2
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -127,11 +135,27 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
                "r"(bytes), "r"(bar)
                : "memory");
 }
-// tiled TMA load of the box at (x = byte offset inside the rows, y = first row); x must be a multiple of 16
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
-               "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
-               : "memory");
+// asks for a run of global memory to be brought into L2 (a hint; nothing waits for it)
+__device__ __forceinline__ void bulk_prefetch_l2(const void *src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+// 16-byte asynchronous copy global -> shared, bypassing L1; src_bytes 0 writes zeros instead (the address is not read)
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// waits until at most `pending` of this thread's committed groups are still in flight
+__device__ __forceinline__ void cp_async_wait(int pending) {
+  switch (pending) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+    case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
+  }
 }
 __device__ __forceinline__ uint4 lds128(uint32_t a) {
   uint4 v;
@@ -152,7 +176,6 @@ __device__ __forceinline__ void sts128(uint32_t addr, const uint4 &v) {
   asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // ---- tcgen05 wrappers --------------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
@@ -224,50 +247,66 @@ struct ImmaArgs {
   int64_t m;           // activation rows of this pass (<= NP)
   int nsteps;          // 256-k steps per tile
   int tiles;
-  long long units;     // tiles * nsteps
+  int units;           // tiles * nsteps
+  int units_q, units_r; // CTA c works on units [c * units_q + min(c, units_r), + units_q + (c < units_r)): set at launch, so that
+                        // no thread divides 64-bit numbers before its first copy
   unsigned int *tile_cnt; // [tiles] arrival tickets of split tiles, zeroed by the prepare kernel
   float *partials;        // [2 * grid][NP][128] partial sums of split tiles
   float *pair_scratch;    // [grid][NP][128]: the odd half steps' sums on their way to the even ones'
-  // raw weight bytes: per stream a tensor map over [n rows][row bytes] with a box of 128 rows x step_bytes; offset inside a raw stage
-  CUtensorMap tmap[2];
+  // raw weight bytes: stream 0 holds the codes (Q4_K: the whole 144-byte super-blocks), stream 1 the f16 block scales of Q4_0 / Q8_0
+  const uint8_t *src[2];
   int nstreams;
-  uint32_t step_bytes[2], raw_off[2];
+  uint32_t row_bytes[2];  // bytes of one weight row in the stream
+  uint32_t step_bytes[2]; // bytes of one 256-k step of a row
+  uint32_t code_off;      // where the codes start inside a step of stream 0 (Q4_K: after the 16 header bytes)
+  // each CTA asks for its share of every stream (whole, contiguous rows) to be brought into L2 when it starts
+  const uint8_t *pf_base[2];
+  unsigned long long pf_bytes[2], pf_share[2]; // share: a multiple of PF_CHUNK; bytes 0: no prefetch
   int raw_stages, b_stages, a_stages;
   uint32_t raw_stage_bytes, b_stage_bytes, side_stage_bytes;
-  uint32_t a_off, b_off, raw_off0, side_off; // offsets from the 1024-aligned base of dynamic shared memory
+  uint32_t a_off, b_off, raw_off0, side_off; // offsets from the 1024-aligned base of dynamic shared memory; a raw stage holds eight warp slots
 };
 
-// position in the flattened (tile, step) space
-__device__ __forceinline__ int cta_of(long long u, long long units, int G) {
-  int c = (int)((u * G) / units);
-  while (c + 1 < G && units * (c + 1) / G <= u) c++;
-  while (c > 0 && units * c / G > u) c--;
-  return c;
+// the flattened (tile, step) space is cut into contiguous ranges: the first units_r CTAs take units_q + 1 units, the others units_q
+__device__ __forceinline__ int cta_first_unit(int c, int q, int r) { return c * q + min(c, r); }
+__device__ __forceinline__ int cta_of(int u, int q, int r) {
+  const int big = r * (q + 1); // units held by the CTAs that take q + 1
+  return u < big ? u / (q + 1) : r + (u - big) / q;
 }
 
-// ---- converters: raw bytes of (row, 64 of the half step's 128 k) -> 64 bytes of int8 codes ------------------
-// raw: shared address of the row's bytes of the stage (stream 0); h: half step (0/1) of the 256-k step; p: which 64.
+// ---- converters: raw bytes of (row, 64 of the step's 256 k) -> 64 bytes of int8 codes ------------------------
+// A warp slot holds the step's code bytes of the warp's 32 rows, STEP bytes per row; the 16-byte chunk c of row r sits
+// at r * STEP + ((c ^ (r & (STEP / 16 - 1))) << 4), so that 32 lanes reading chunk c of their own rows touch all the
+// banks. row: shared address of the lane's row in the slot; key: the lane's row number in the slot; h: half step;
+// p: which 64 k of the half step.
+template <int STEP>
+__device__ __forceinline__ uint4 raw_chunk(uint32_t row, int key, int c) {
+  return lds128(row + (uint32_t)((c ^ (key & (STEP / 16 - 1))) << 4));
+}
 struct ConvQ8_0 { // 256 code bytes per row and step
-  __device__ static __forceinline__ void run(uint32_t raw, int h, int p, uint4 (&out)[4]) {
+  static constexpr int STEP = 256;
+  __device__ static __forceinline__ void run(uint32_t row, int key, int h, int p, uint4 (&out)[4]) {
 #pragma unroll
-    for (int i = 0; i < 4; i++) out[i] = lds128(raw + 128 * h + 64 * p + 16 * i);
+    for (int i = 0; i < 4; i++) out[i] = raw_chunk<STEP>(row, key, 8 * h + 4 * p + i);
   }
 };
 __device__ __forceinline__ uint32_t nib_lo_s8(uint32_t w) { return (((w & 0x0f0f0f0fu) | 0x80808080u) - 0x08080808u) ^ 0x80808080u; } // code - 8 per byte
 __device__ __forceinline__ uint32_t nib_hi_s8(uint32_t w) { return ((((w >> 4) & 0x0f0f0f0fu) | 0x80808080u) - 0x08080808u) ^ 0x80808080u; }
-struct ConvQ4_0 { // 8 blocks of 16 nibble bytes per row and step; element j < 16 low nibble of byte j, j >= 16 high nibble of byte j - 16
-  __device__ static __forceinline__ void run(uint32_t raw, int h, int p, uint4 (&out)[4]) {
+struct ConvQ4_0 { // eight blocks of 16 nibble bytes per row and step; element j < 16 low nibble of byte j, j >= 16 high nibble of byte j - 16
+  static constexpr int STEP = 128;
+  __device__ static __forceinline__ void run(uint32_t row, int key, int h, int p, uint4 (&out)[4]) {
 #pragma unroll
     for (int bb = 0; bb < 2; bb++) {
-      const uint4 q = lds128(raw + (4 * h + 2 * p + bb) * 16);
+      const uint4 q = raw_chunk<STEP>(row, key, 4 * h + 2 * p + bb);
       out[2 * bb] = make_uint4(nib_lo_s8(q.x), nib_lo_s8(q.y), nib_lo_s8(q.z), nib_lo_s8(q.w));
       out[2 * bb + 1] = make_uint4(nib_hi_s8(q.x), nib_hi_s8(q.y), nib_hi_s8(q.z), nib_hi_s8(q.w));
     }
   }
 };
-struct ConvQ4K { // 144-byte super-block: 16 header bytes, then four 32-byte chunks; chunk c = sub-block 2c in the low nibbles, 2c+1 in the high ones
-  __device__ static __forceinline__ void run(uint32_t raw, int h, int p, uint4 (&out)[4]) {
-    const uint4 a = lds128(raw + 16 + 32 * (2 * h + p)), b = lds128(raw + 32 + 32 * (2 * h + p));
+struct ConvQ4K { // 128 code bytes per row and step: four 32-byte chunks; chunk c = sub-block 2c in the low nibbles, 2c+1 in the high ones
+  static constexpr int STEP = 128;
+  __device__ static __forceinline__ void run(uint32_t row, int key, int h, int p, uint4 (&out)[4]) {
+    const uint4 a = raw_chunk<STEP>(row, key, 2 * (2 * h + p)), b = raw_chunk<STEP>(row, key, 2 * (2 * h + p) + 1);
     out[0] = make_uint4(a.x & 0x0f0f0f0fu, a.y & 0x0f0f0f0fu, a.z & 0x0f0f0f0fu, a.w & 0x0f0f0f0fu);
     out[1] = make_uint4(b.x & 0x0f0f0f0fu, b.y & 0x0f0f0f0fu, b.z & 0x0f0f0f0fu, b.w & 0x0f0f0f0fu);
     out[2] = make_uint4((a.x >> 4) & 0x0f0f0f0fu, (a.y >> 4) & 0x0f0f0f0fu, (a.z >> 4) & 0x0f0f0f0fu, (a.w >> 4) & 0x0f0f0f0fu);
@@ -329,32 +368,29 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u; // operand stages need 1024-byte alignment
   constexpr int NBUF = TMEM_COLS / (4 * NP) > 8 ? 8 : TMEM_COLS / (4 * NP); // accumulator buffers (even: buffer parity = half step parity)
   constexpr int BUF_COLS = 4 * NP;
-  // barriers: raw_full/raw_empty [4], b_full [4] (+ 4 spare), side_full/side_empty [4], a_full/mma_done [8], acc_empty [8]
-  __shared__ __align__(8) uint64_t bars[48];
+  // barriers: b_full [4], side_full/side_empty [4], a_full/mma_done [8], acc_empty [8]
+  __shared__ __align__(8) uint64_t bars[36];
   __shared__ uint32_t tmem_slot;
   __shared__ unsigned int s_ticket;
-  const uint32_t raw_full = smem_u32(bars), raw_empty = raw_full + 32, b_full = raw_full + 64, side_full = raw_full + 128,
-                 side_empty = raw_full + 160, a_full = raw_full + 192, mma_done = raw_full + 256, acc_empty = raw_full + 320;
+  const uint32_t b_full = smem_u32(bars), side_full = b_full + 32, side_empty = b_full + 64, a_full = b_full + 96, mma_done = b_full + 160,
+                 acc_empty = b_full + 224;
   XNQ_GT(26);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int RS = p.raw_stages, BS = p.b_stages, AS = p.a_stages;
   const int NB = min(NBUF, AS); // accumulator buffers in use: a drain group waiting on mma_done must not be lapped by the MMA thread,
                                 // which can run ahead by NB half steps, so the ring of mma_done barriers (AS) is at least that long
   const int KT = p.nsteps;
-  const int G = gridDim.x;
-  const long long u0 = p.units * blockIdx.x / G, u1 = p.units * (blockIdx.x + 1) / G;
-  const int nunits = (int)(u1 - u0);
-  const int tile0 = (int)(u0 / KT), kt0 = (int)(u0 % KT);
+  const int u0 = cta_first_unit((int)blockIdx.x, p.units_q, p.units_r);
+  const int nunits = p.units_q + ((int)blockIdx.x < p.units_r ? 1 : 0);
+  const int tile0 = u0 / KT, kt0 = u0 - tile0 * KT;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < 8; s++) {
-      mbar_init(a_full + 8 * s, CONV_WARPS / 2); // the four converter warps of the half step's group
-      mbar_init(mma_done + 8 * s, 1);            // the half step's MMAs have read their operands and written their slices
+      mbar_init(a_full + 8 * s, CONV_WARPS / 2); // the four converter warps of the step's group (one barrier per step: entries 0 .. BS - 1)
+      mbar_init(mma_done + 8 * s, 1);            // MMAs have read their operands and written their slices: entry 2 bs + 1 after a whole step (NP = 64: every half step)
       mbar_init(acc_empty + 8 * s, DRAIN_WARPS / 2);
     }
     for (int s = 0; s < 4; s++) {
-      mbar_init(raw_full + 8 * s, 1);
-      mbar_init(raw_empty + 8 * s, CONV_WARPS);
       mbar_init(b_full + 8 * s, 1);
       mbar_init(side_full + 8 * s, 1 + CONV_WARPS / 2); // the producer's transaction + the four converter warps that copy the scale bytes
       mbar_init(side_empty + 8 * s, DRAIN_WARPS);
@@ -368,71 +404,61 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_launch_dependents(); // the next kernel in the stream may be set up while this one runs
   const uint32_t tmem_d = tmem_slot;
 
-  if (warp == PRODUCER_WARP) {
-    // ---- producer: per 256-k step the raw rows of the tile, the activations' operand image, their records ----
+  if (warp == ACT_PRODUCER_WARP) {
+    // ---- activation producer: per 256-k step the activations' operand image and their records ----
     if (lane == 0) {
-      bool alive = true;
-      XNQ_TDECL;
-      auto load_raw = [&](int i) { // unit i of this CTA's range
-        const long long u = u0 + i;
-        const int tile = (int)(u / KT), kt = (int)(u % KT), rs = i % RS;
-        mbar_expect_tx(raw_full + 8 * rs, (uint32_t)TILE_N * (p.step_bytes[0] + (p.nstreams > 1 ? p.step_bytes[1] : 0u))); // a box counts in full, zero fill included
-        const uint32_t dst = base + p.raw_off0 + rs * p.raw_stage_bytes;
-        tma_load_2d(dst + p.raw_off[0], &p.tmap[0], kt * (int)p.step_bytes[0], tile * TILE_N, raw_full + 8 * rs);
-        if (p.nstreams > 1) tma_load_2d(dst + p.raw_off[1], &p.tmap[1], kt * (int)p.step_bytes[1], tile * TILE_N, raw_full + 8 * rs);
-      };
-      // weights are immutable after upload: the first stages are requested while the kernel that prepares the
-      // activations (the previous one in the stream) is still running
-      for (int i = 0; i < RS && i < nunits; i++) load_raw(i);
+      // A 256-k step of a tile is 128 separate runs of 144 to 256 bytes, 2 to 4 KB apart. So that DRAM is read in long
+      // contiguous runs all the same, the weight is asked into L2 whole when the kernel starts, every CTA asking for its
+      // share of the bytes (not of the work: any CTA's copies then hit in L2, or go to DRAM when they are early).
+      for (int st = 0; st < p.nstreams; st++) {
+        const unsigned long long o0 = p.pf_share[st] * blockIdx.x, o1 = min(o0 + p.pf_share[st], p.pf_bytes[st]);
+        for (unsigned long long o = o0; o < o1; o += PF_CHUNK) bulk_prefetch_l2(p.pf_base[st] + o, (uint32_t)min((unsigned long long)PF_CHUNK, o1 - o));
+      }
       pdl_wait();
-      int kt = kt0;
+      bool alive = true;
+      int kt = kt0, bs = 0;
+      uint32_t b_ph = 0; // (i / BS) & 1
       for (int i = 0; i < nunits && alive; i++) {
-        const int rs = i % RS, bs = i % BS, ss = i % SIDE_STAGES;
-        XNQ_TACC(0);
-        if (i >= RS) {
-          alive = mbar_wait(raw_empty + 8 * rs, ((i / RS) - 1) & 1, 1u);
-          if (alive) load_raw(i);
-        }
-        XNQ_TACC(1);
+        const int ss = i % SIDE_STAGES;
         // the B stage of step i - BS is free once that step's second half has been multiplied: BS = AS / 2, so this is
         // the barrier of half step 2 i + 1 one phase back (a second commit per step cost the issuing thread over a
         // thousand cycles)
-        if (alive && i >= BS) alive = mbar_wait(mma_done + 8 * ((2 * i + 1) % AS), ((2 * (i - BS) + 1) / AS) & 1, 1u);
-        XNQ_TACC(2);
+        if (i >= BS) alive = mbar_wait(mma_done + 8 * (2 * bs + 1), b_ph ^ 1u, 1u);
         if (alive && i >= SIDE_STAGES) alive = mbar_wait(side_empty + 8 * ss, ((i / SIDE_STAGES) - 1) & 1, 1u);
-        XNQ_TACC(3);
         if (!alive) break;
         mbar_expect_tx(b_full + 8 * bs, p.b_stage_bytes);
         mbar_expect_tx(side_full + 8 * ss, (uint32_t)NP * 32u);
         bulk_g2s(base + p.b_off + bs * p.b_stage_bytes, p.bimg + ((size_t)kt * 2) * (NP * 128), p.b_stage_bytes, b_full + 8 * bs);
         bulk_g2s(base + p.side_off + ss * p.side_stage_bytes + HDR_BYTES, p.meta + (size_t)kt * (NP * 32), (uint32_t)NP * 32u, side_full + 8 * ss);
+        XNQ_TL(1, i);
         if (++kt == KT) kt = 0;
+        if (++bs == BS) bs = 0, b_ph ^= 1u;
       }
-      XNQ_TDUMP(0, true);
     }
-    // nothing may be in flight into this CTA's shared memory when it exits: the consumers wait for every stage they
-    // were promised, so the copies have landed once the other roles are done (they fall through on a timeout only)
   } else if (warp == MMA_WARP) {
     // ---- MMA issuer ------------------------------------------------------------------------------------------
     if (lane == 0) {
       const uint32_t idesc = idesc_i8(NP);
       bool alive = true;
       XNQ_TDECL;
+      int bs = 0, nb = 0; // i % BS, i % (NB / 2): AS and NB are even, so half step j = 2 i + h uses A stage 2 bs + h and buffer 2 nb + h
+      uint32_t b_ph = 0, acc_ph = 0; // (i / BS) & 1 = (j / AS) & 1, (j / NB) & 1
       for (int i = 0; i < nunits && alive; i++) {
-        const int bs = i % BS;
         XNQ_TACC(0);
-        alive = mbar_wait(b_full + 8 * bs, (i / BS) & 1, 4u);
+        alive = mbar_wait(b_full + 8 * bs, b_ph, 4u);
         XNQ_TACC(1);
+        if (alive) alive = mbar_wait(a_full + 8 * bs, b_ph, 4u); // both halves of the step's operand image
+        XNQ_TACC(2);
         for (int h = 0; h < 2 && alive; h++) {
-          const int j = 2 * i + h, sa = j % AS, buf = j % NB;
+          const int sa = 2 * bs + h, buf = 2 * nb + h;
           XNQ_TACC(0);
-          alive = mbar_wait(a_full + 8 * sa, (j / AS) & 1, 4u);
-          XNQ_TACC(2);
-          if (alive && j >= NB) alive = mbar_wait(acc_empty + 8 * buf, ((j / NB) - 1) & 1, 4u); // the drain of the buffer's previous half step
+          if (2 * i >= NB) alive = mbar_wait(acc_empty + 8 * buf, acc_ph ^ 1u, 4u); // the drain of the buffer's previous half step
           XNQ_TACC(3);
           if (!alive) break;
+          if (h == 0) XNQ_TL(4, i);
           tc_fence_after();
           const uint64_t adesc = smem_desc_sw128(base + p.a_off + sa * A_STAGE_BYTES);
           const uint64_t bdesc = smem_desc_sw128(base + p.b_off + bs * p.b_stage_bytes + h * (NP * 128));
@@ -440,56 +466,106 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
           for (int q = 0; q < 4; q++) // K = 32 per instruction: advance 32 bytes inside the swizzle row; slice q of the buffer
             umma_i8(tmem_d + (uint32_t)(buf * BUF_COLS + q * NP), adesc + (uint64_t)(q * 2), bdesc + (uint64_t)(q * 2), idesc);
           XNQ_TACC(4);
-          umma_commit(mma_done + 8 * sa); // one arrival serves the converters (the stage is free) and the drain (the slices are written)
+          // One arrival per step serves the converters and the activation producer (the stages are free) and the drain (the
+          // slices are written): a commit costs the issuing thread about a hundred cycles. With 64 activation rows tensor
+          // memory holds one step only, so the drain of the first half has to start before the second is multiplied.
+          if (NP == 64 || h == 1) umma_commit(mma_done + 8 * sa);
           XNQ_TACC(5);
+          if (h == 1) XNQ_TL(5, i);
         }
+        if (++bs == BS) bs = 0, b_ph ^= 1u;
+        if (2 * ++nb == NB) nb = 0, acc_ph ^= 1u;
       }
       XNQ_TDUMP(6, true);
     }
   } else if (warp < DRAIN_WARP0) {
-    // ---- converters: group h (four warps, one thread per weight row) produces half step h of every 256-k step ----
+    // ---- converters: group g (four warps, one thread per weight row) produces the steps i = g, g + 2, ... of this CTA: a
+    // step's chain of waits, loads, stores and fences has the time of two steps' MMAs to run in ----
+    constexpr int STEP = Conv::STEP, CPR = STEP / 16, RPI = 32 / CPR; // code bytes per row and step; 16-byte chunks per row; rows per copy instruction
+    constexpr uint32_t SLOT = 32 * STEP + 512;                          // a warp's slot: its rows' code bytes, then 16 scale bytes per row
     const int cw = warp - CONV_WARP0;
-    const int r = (cw & 3) * 32 + lane, h = cw >> 2;
+    const int r0 = (cw & 3) * 32, r = r0 + lane, g = cw >> 2;
     const int sw = r & 7;
+    const int D = RS >> 1; // slots per warp: RS steps are in flight per CTA, half of them this group's
+    const uint32_t slot0 = base + p.raw_off0 + (uint32_t)(cw * D) * SLOT;
+    const int64_t n = p.w.n;
+    // the warp's own loads, D of its steps ahead: lane l copies chunk l % CPR of row q * RPI + l / CPR in instruction q
+    int l_i = g, l_tile = tile0, l_kt = kt0 + g, l_s = 0;
+    while (l_kt >= KT) l_kt -= KT, l_tile++;
+    auto issue = [&]() {
+      const uint32_t dst = slot0 + (uint32_t)l_s * SLOT;
+      const int c = lane % CPR;
+      const uint32_t in_row = (uint32_t)l_kt * p.step_bytes[0] + p.code_off + (uint32_t)(c * 16); // a row's bytes end at a multiple of 16
+      const uint32_t bytes = in_row + 16 <= p.row_bytes[0] ? 16u : 0u;
+#pragma unroll
+      for (int q = 0; q < CPR; q++) {
+        const int rw = q * RPI + lane / CPR;
+        const int64_t grow = (int64_t)l_tile * TILE_N + r0 + rw;
+        const bool ok = grow < n;
+        cp_async16(dst + (uint32_t)(rw * STEP + ((c ^ (rw & (CPR - 1))) << 4)), p.src[0] + (size_t)(ok ? grow : n - 1) * p.row_bytes[0] + in_row, ok ? bytes : 0u);
+      }
+      { // the rows' 16 scale bytes of the step: the head of the Q4_K super-block, or eight f16 block scales
+        const int st = p.nstreams - 1;
+        const int64_t grow = (int64_t)l_tile * TILE_N + r;
+        const bool ok = grow < n && (uint32_t)l_kt * p.step_bytes[st] + 16 <= p.row_bytes[st];
+        cp_async16(dst + 32 * STEP + lane * 16, p.src[st] + (size_t)(grow < n ? grow : n - 1) * p.row_bytes[st] + (ok ? (size_t)l_kt * p.step_bytes[st] : 0), ok ? 16u : 0u);
+      }
+      l_i += 2, l_kt += 2;
+      while (l_kt >= KT) l_kt -= KT, l_tile++;
+      if (++l_s == D) l_s = 0;
+    };
+    for (int u = 0; u < D; u++) { // weights are immutable after upload: nothing here waits for the kernel that prepares the activations
+      if (l_i < nunits) issue();
+      cp_async_commit();
+    }
     bool alive = true;
     XNQ_TDECL;
-    for (int i = 0; i < nunits && alive; i++) {
-      const int rs = i % RS, ss = i % SIDE_STAGES;
-      const int j = 2 * i + h, sa = j % AS;
+    int rs = 0, bs = g % BS;
+    uint32_t a_ph = (uint32_t)(g / BS) & 1u; // (i / BS) & 1
+    for (int i = g; i < nunits && alive; i += 2) {
+      const int ss = i % SIDE_STAGES;
       XNQ_TACC(0);
-      alive = mbar_wait_warp(raw_full + 8 * rs, (i / RS) & 1, 2u);
+      cp_async_wait(D - 1); // one group per step and lane, committed in step order: step i's has landed
+      __syncwarp();         // ... for every lane of the warp
       XNQ_TACC(1);
-      if (!alive) break;
-      const uint32_t raw = base + p.raw_off0 + rs * p.raw_stage_bytes;
-      if (h == 0) { // hand the row's 16 scale bytes to the drain
+      if (threadIdx.x == CONV_WARP0 * 32) XNQ_TL(2, i);
+      const uint32_t slot = slot0 + (uint32_t)rs * SLOT;
+      { // hand the row's 16 scale bytes to the drain
         if (i >= SIDE_STAGES) alive = mbar_wait_warp(side_empty + 8 * ss, ((i / SIDE_STAGES) - 1) & 1, 2u);
         XNQ_TACC(2);
         if (!alive) break;
-        const uint4 hv = p.nstreams > 1 ? lds128(raw + p.raw_off[1] + (uint32_t)r * 16) : lds128(raw + (uint32_t)r * p.step_bytes[0]);
+        const uint4 hv = lds128(slot + 32 * STEP + lane * 16);
         sts128(base + p.side_off + ss * p.side_stage_bytes + (uint32_t)r * 16, hv);
         __syncwarp();
         if (lane == 0) mbar_arrive(side_full + 8 * ss);
       }
       XNQ_TACC(0);
-      if (j >= AS) alive = mbar_wait_warp(mma_done + 8 * sa, ((j / AS) - 1) & 1, 2u);
+      if (i >= BS) alive = mbar_wait_warp(mma_done + 8 * (2 * bs + 1), a_ph ^ 1u, 2u); // both halves of the stage have been multiplied
       XNQ_TACC(3);
       if (!alive) break;
-      uint4 lo[4], hi[4];
-      Conv::run(raw + p.raw_off[0] + (uint32_t)r * p.step_bytes[0], h, 0, lo);
-      Conv::run(raw + p.raw_off[0] + (uint32_t)r * p.step_bytes[0], h, 1, hi);
-      const uint32_t dst_row = base + p.a_off + sa * A_STAGE_BYTES + (uint32_t)r * 128;
 #pragma unroll
-      for (int c = 0; c < 4; c++) {
-        sts128(dst_row + (uint32_t)((c ^ sw) << 4), lo[c]);
-        sts128(dst_row + (uint32_t)(((4 + c) ^ sw) << 4), hi[c]);
+      for (int h = 0; h < 2; h++) {
+        uint4 lo[4], hi[4];
+        Conv::run(slot + (uint32_t)lane * STEP, lane, h, 0, lo);
+        Conv::run(slot + (uint32_t)lane * STEP, lane, h, 1, hi);
+        const uint32_t dst_row = base + p.a_off + (2 * bs + h) * A_STAGE_BYTES + (uint32_t)r * 128;
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+          sts128(dst_row + (uint32_t)((c ^ sw) << 4), lo[c]);
+          sts128(dst_row + (uint32_t)(((4 + c) ^ sw) << 4), hi[c]);
+        }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic-proxy stores -> visible to the tensor core
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(a_full + 8 * sa);
-        mbar_arrive(raw_empty + 8 * rs); // this warp has read all it needs of the raw stage
-      }
+      __syncwarp(); // every lane has stored its row and has read all it needs of the slot
+      if (lane == 0) mbar_arrive(a_full + 8 * bs);
+      if (l_i < nunits) issue(); // into the slot just read
+      cp_async_commit();
+      if (threadIdx.x == CONV_WARP0 * 32) XNQ_TL(3, i);
+      if (++rs == D) rs = 0;
+      for (int t = 0; t < 2; t++)
+        if (++bs == BS) bs = 0, a_ph ^= 1u;
     }
+    cp_async_wait(0); // nothing may be in flight into this CTA's shared memory when it exits
     XNQ_TDUMP(12, threadIdx.x == CONV_WARP0 * 32);
   } else {
     // ---- drain: group h (eight warps) owns accumulator buffer h and half step h of every 256-k step. Warp quarter q
@@ -511,17 +587,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
     int seg_kt0 = kt0; // first step of the current segment inside its tile
     float *pair = p.pair_scratch + (size_t)blockIdx.x * NP * TILE_N; // group 1 -> group 0
     XNQ_TDECL;
+    int bs = 0, nb = 0;  // i % BS, i % (NB / 2)
+    uint32_t a_ph = 0;   // (i / BS) & 1
     for (int i = 0; i < nunits; i++) {
       const int ss = i % SIDE_STAGES;
-      const int j = 2 * i + h, sa = j % AS, buf = j % NB;
+      const int sa = 2 * bs + h, buf = 2 * nb + h;
       XNQ_TACC(0);
       if (alive) alive = mbar_wait_warp(side_full + 8 * ss, (i / SIDE_STAGES) & 1, 8u);
       XNQ_TACC(1);
       const uint32_t side = base + p.side_off + ss * p.side_stage_bytes;
       uint4 hdr = make_uint4(0, 0, 0, 0);
       if (alive) hdr = lds128(side + (uint32_t)(32 * q + lane) * 16);
-      if (alive) alive = mbar_wait_warp(mma_done + 8 * sa, (j / AS) & 1, 8u);
+      if (alive) alive = mbar_wait_warp(mma_done + 8 * (NP == 64 ? sa : sa | 1), a_ph, 8u);
       XNQ_TACC(2);
+      if (threadIdx.x == DRAIN_WARP0 * 32) XNQ_TL(6, i);
       if (alive) {
         tc_fence_after();
         const uint32_t taddr = tmem_d + ((uint32_t)(32 * q) << 16) + (uint32_t)(buf * BUF_COLS + c0);
@@ -542,6 +621,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
       }
       __syncwarp();
       if (alive && lane == 0) mbar_arrive(side_empty + 8 * ss);
+      if (threadIdx.x == DRAIN_WARP0 * 32) XNQ_TL(7, i);
       // ---- end of a segment (the tile's last step, or this CTA's last unit): store or hand over the sums ----
       const bool tile_end = kt == KT - 1, range_end = i == nunits - 1;
       if (tile_end || range_end) {
@@ -574,7 +654,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
           asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_WARPS * 32) : "memory"); // group 0 has read the scratch: it may be rewritten
         } else {
           // this CTA's first segment (it starts where the CTA's range starts) uses scratch slot 2c, a later one 2c + 1
-          const long long seg_u0 = (long long)tile * KT + seg_kt0;
+          const int seg_u0 = tile * KT + seg_kt0;
           float *mine = p.partials + ((size_t)2 * blockIdx.x + (seg_u0 == u0 ? 0 : 1)) * NP * TILE_N;
           if (h == 0) {
 #pragma unroll
@@ -586,15 +666,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
           asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_WARPS * 32) : "memory");
           const unsigned int ticket = s_ticket;
           asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_WARPS * 32) : "memory"); // s_ticket may be rewritten from here on
-          const long long t_u0 = (long long)tile * KT, t_u1 = t_u0 + KT;
-          const int c_first = cta_of(t_u0, p.units, G), c_last = cta_of(t_u1 - 1, p.units, G);
+          const int t_u0 = tile * KT, t_u1 = t_u0 + KT;
+          const int c_first = cta_of(t_u0, p.units_q, p.units_r), c_last = cta_of(t_u1 - 1, p.units_q, p.units_r);
           if (h == 0 && (int)ticket == c_last - c_first) { // the last part to arrive adds all parts in k order
             __threadfence();
             float (&sum)[NPT] = acc; // the segment's own sums are in its scratch slot by now
 #pragma unroll
             for (int c = 0; c < NPT; c++) sum[c] = 0.f;
             for (int cc = c_first; cc <= c_last; cc++) {
-              const long long cu0 = p.units * cc / G;
+              const int cu0 = cta_first_unit(cc, p.units_q, p.units_r);
               const float *part = p.partials + ((size_t)2 * cc + (cu0 >= t_u0 ? 0 : 1)) * NP * TILE_N;
 #pragma unroll
               for (int c = 0; c < NPT; c++) sum[c] += __ldcg(part + (size_t)(c0 + c) * TILE_N + 32 * q + lane);
@@ -621,6 +701,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
         kt = 0;
         tile++;
       }
+      if (++bs == BS) bs = 0, a_ph ^= 1u;
+      if (2 * ++nb == NB) nb = 0;
     }
     XNQ_TDUMP(18, threadIdx.x == DRAIN_WARP0 * 32);
   }
@@ -641,7 +723,8 @@ template <int ACT, typename XT>
 __global__ void __launch_bounds__(256) imma_prepare(const XT *__restrict__ x, const int8_t *__restrict__ img_q, const float *__restrict__ img_d,
                                                     const int16_t *__restrict__ img_b, int64_t m, int64_t k, int64_t ldx, int NP, int nsteps,
                                                     uint8_t *__restrict__ bimg, uint8_t *__restrict__ meta, unsigned int *__restrict__ tile_cnt, int tiles) {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); // the matmul kernel may start its set-up and its weight loads now
+  pdl_launch_dependents(); // the matmul kernel may start its set-up and its weight loads now
+  pdl_wait();              // x may be the previous kernel's output; the scratch may still be read by the previous call
   XNQ_GT(24);
   const int row = blockIdx.x;
   if (blockIdx.x == 0 && blockIdx.y == 0)
@@ -709,22 +792,6 @@ __global__ void __launch_bounds__(256) imma_prepare(const XT *__restrict__ x, co
 }
 
 int g_sms = 0;
-using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
-                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn g_encode_tiled = nullptr;
-
-// [rows][row_bytes] bytes, box of 128 rows x box_bytes, no swizzle, out-of-range bytes read as zero
-int make_row_map(CUtensorMap *map, const void *base, uint64_t row_bytes, uint64_t rows, uint32_t box_bytes) {
-  if (!g_encode_tiled) return fail(XNQ_ERR_UNSUPPORTED, "imma: the driver's tensor-map encoder was not found");
-  const cuuint64_t dims[2] = {row_bytes, rows};
-  const cuuint64_t strides[1] = {row_bytes};
-  const cuuint32_t box[2] = {box_bytes, (cuuint32_t)TILE_N};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(XNQ_ERR_CUDA, "imma: cuTensorMapEncodeTiled failed (%d) for rows of %llu bytes", (int)r, (unsigned long long)row_bytes);
-  return XNQ_OK;
-}
 
 struct Plan {
   int NP, nsteps, tiles, grid;
@@ -778,8 +845,9 @@ int init_np() {
 } // namespace
 
 bool imma_supported(const WeightView &w, int64_t m) {
-  if (g_sms <= 0 || !g_encode_tiled || m < 1 || w.n < 1) return false;
+  if (g_sms <= 0 || m < 1 || w.n < 1) return false;
   if (w.dtype != XNQ_Q4_0 && w.dtype != XNQ_Q8_0 && w.dtype != XNQ_Q4K) return false;
+  if (((w.n + TILE_N - 1) / TILE_N) * ((w.k + 255) / 256) >= (1ll << 30)) return false; // the (tile, step) space is indexed with 32-bit integers
   return true;
 }
 
@@ -813,8 +881,8 @@ int launch_imma(const WeightView &w, const void *x, int x_dtype, int64_t m, int6
       iq = av.q + r0 * k, id = av.d + r0 * (k / blk), ib = av.bsum + r0 * (k / 16);
     }
 #define XNQ_IMMA_PREP(ACT, XT)                                                                                                          \
-  imma_prepare<ACT, XT><<<dim3((unsigned)pl.NP, (unsigned)std::min<int64_t>(16, (k + 2047) / 2048)), 256, 0, s>>>(iq ? nullptr : static_cast<const XT *>(x) + r0 * ldx, iq, id, ib, rows, k, ldx, pl.NP, \
-                                                        pl.nsteps, bimg, meta, cnt, pl.tiles)
+  XNQ_CUDA(launch_pdl(imma_prepare<ACT, XT>, dim3((unsigned)pl.NP, (unsigned)std::min<int64_t>(16, (k + 2047) / 2048)), dim3(256), 0, s,     \
+                      iq ? nullptr : static_cast<const XT *>(x) + r0 * ldx, iq, id, ib, rows, k, ldx, pl.NP, pl.nsteps, bimg, meta, cnt, pl.tiles))
     if (act == XNQ_Q8_0) {
       if (x_dtype == XNQ_F16) XNQ_IMMA_PREP(XNQ_Q8_0, __half);
       else if (x_dtype == XNQ_BF16) XNQ_IMMA_PREP(XNQ_Q8_0, __nv_bfloat16);
@@ -825,7 +893,6 @@ int launch_imma(const WeightView &w, const void *x, int x_dtype, int64_t m, int6
       else XNQ_IMMA_PREP(XNQ_Q8K, float);
     }
 #undef XNQ_IMMA_PREP
-    XNQ_CUDA(cudaGetLastError());
     count_launch();
 
     ImmaArgs a{};
@@ -838,41 +905,57 @@ int launch_imma(const WeightView &w, const void *x, int x_dtype, int64_t m, int6
     a.m = rows;
     a.nsteps = pl.nsteps;
     a.tiles = pl.tiles;
-    a.units = (long long)pl.tiles * pl.nsteps;
+    a.units = pl.tiles * pl.nsteps;
+    a.units_q = a.units / pl.grid, a.units_r = a.units % pl.grid;
     a.tile_cnt = cnt;
     a.partials = partials;
     a.pair_scratch = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(partials) + pl.part_bytes);
-    int rc;
+    int rc, step_code; // step_code: code bytes per row and step
     switch (w.dtype) {
       case XNQ_Q4K:
-        a.nstreams = 1, a.step_bytes[0] = 144;
-        if ((rc = make_row_map(&a.tmap[0], w.qs, (uint64_t)(k / QK_K * 144), (uint64_t)w.n, 144)) != XNQ_OK) return rc;
+        a.nstreams = 1, a.src[0] = w.qs, a.row_bytes[0] = (uint32_t)(k / QK_K * 144), a.step_bytes[0] = 144, a.code_off = 16, step_code = ConvQ4K::STEP;
         break;
       case XNQ_Q8_0:
-        a.nstreams = 2, a.step_bytes[0] = 256, a.step_bytes[1] = 16;
-        if ((rc = make_row_map(&a.tmap[0], w.qs, (uint64_t)k, (uint64_t)w.n, 256)) != XNQ_OK) return rc;
-        if ((rc = make_row_map(&a.tmap[1], w.d, (uint64_t)(w.dstride * 2), (uint64_t)w.n, 16)) != XNQ_OK) return rc;
+        a.nstreams = 2, a.src[0] = w.qs, a.row_bytes[0] = (uint32_t)k, a.step_bytes[0] = 256, a.code_off = 0, step_code = ConvQ8_0::STEP;
+        a.src[1] = reinterpret_cast<const uint8_t *>(w.d), a.row_bytes[1] = (uint32_t)(w.dstride * 2), a.step_bytes[1] = 16;
         break;
       case XNQ_Q4_0:
-        a.nstreams = 2, a.step_bytes[0] = 128, a.step_bytes[1] = 16;
-        if ((rc = make_row_map(&a.tmap[0], w.qs, (uint64_t)(k / 2), (uint64_t)w.n, 128)) != XNQ_OK) return rc;
-        if ((rc = make_row_map(&a.tmap[1], w.d, (uint64_t)(w.dstride * 2), (uint64_t)w.n, 16)) != XNQ_OK) return rc;
+        a.nstreams = 2, a.src[0] = w.qs, a.row_bytes[0] = (uint32_t)(k / 2), a.step_bytes[0] = 128, a.code_off = 0, step_code = ConvQ4_0::STEP;
+        a.src[1] = reinterpret_cast<const uint8_t *>(w.d), a.row_bytes[1] = (uint32_t)(w.dstride * 2), a.step_bytes[1] = 16;
         break;
       default: return fail(XNQ_ERR_DTYPE, "imma: dtype %d", w.dtype);
     }
-    a.raw_off[0] = 0;
-    a.raw_off[1] = TILE_N * a.step_bytes[0];
-    a.raw_stage_bytes = (TILE_N * (a.step_bytes[0] + (a.nstreams > 1 ? a.step_bytes[1] : 0)) + 127) & ~127u;
+    {
+      size_t total = 0;
+      for (int st = 0; st < a.nstreams; st++) total += (size_t)a.row_bytes[st] * (size_t)w.n;
+      for (int st = 0; st < 2; st++) {
+        a.pf_base[st] = st < a.nstreams ? a.src[st] : nullptr;
+        a.pf_bytes[st] = st < a.nstreams && total <= PF_MAX_BYTES ? (unsigned long long)(((size_t)a.row_bytes[st] * (size_t)w.n) & ~(size_t)15) : 0ull;
+#ifdef XNQ_DEV_TRACE
+        if (const char *e = getenv("XNQ_IMMA_PF")) if (atoi(e) == 0) a.pf_bytes[st] = 0;
+#endif
+        a.pf_share[st] = ((a.pf_bytes[st] / (unsigned)pl.grid) + PF_CHUNK - 1) & ~(unsigned long long)(PF_CHUNK - 1);
+      }
+    }
+    a.raw_stage_bytes = (uint32_t)(CONV_WARPS / 2) * (32u * (uint32_t)step_code + 512u); // a step in flight: four warp slots of the rows' code bytes and 16 scale bytes per row
     a.b_stage_bytes = (uint32_t)pl.NP * 256;
     a.side_stage_bytes = HDR_BYTES + (uint32_t)pl.NP * 32;
-    // shared-memory plan: A stages (8, 6 or 4 half steps) | B stages (half as many whole steps) | side stages | raw stages (4..2)
+    // shared-memory plan: A stages (half steps) | B stages (half as many whole steps) | side stages | raw stages. The MMA
+    // issuer bounds a step, so the converters and the drain need little slack (six half steps of operand image); what remains
+    // goes to raw stages, which hide the memory latency.
     const size_t budget = IMMA_SMEM - 1024; // 1024: alignment slack of the base
     a.a_stages = 0;
-    for (int as = MAX_A_STAGES; as >= 4 && !a.a_stages; as -= 2)
-      for (int rs = MAX_RAW_STAGES; rs >= 2 && !a.a_stages; rs--)
+    int as_order[3] = {6, 4, 8};
+#ifdef XNQ_DEV_TRACE
+    if (const char *e = getenv("XNQ_IMMA_AS")) as_order[0] = atoi(e);
+#endif
+    for (int ai = 0; ai < 3 && !a.a_stages; ai++) {
+      const int as = as_order[ai];
+      for (int rs = MAX_RAW_STAGES; rs >= 2 && !a.a_stages; rs -= 2) // even: the two converter groups own half of the slots each
         if ((size_t)as * A_STAGE_BYTES + (size_t)(as / 2) * a.b_stage_bytes + (size_t)SIDE_STAGES * a.side_stage_bytes + (size_t)rs * a.raw_stage_bytes + 256 <= budget &&
-            (rs >= 3 || as == 4))
+            (rs >= 4 || as == 4))
           a.a_stages = as, a.raw_stages = rs;
+    }
     if (!a.a_stages) return fail(XNQ_ERR_SIZE, "imma: shared-memory plan does not fit");
     a.b_stages = a.a_stages / 2;
     a.a_off = 0;
@@ -893,14 +976,6 @@ int imma_init(int device) {
   cudaDeviceProp prop;
   XNQ_CUDA(cudaGetDeviceProperties(&prop, device));
   g_sms = prop.multiProcessorCount;
-  if (!g_encode_tiled) { // the driver's encoder, looked up through the runtime so that the library needs no link against libcuda
-    void *fn = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
-      g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
-    else
-      (void)cudaGetLastError();
-  }
   int rc;
   if ((rc = init_np<ConvQ4K, DrainQ4K>()) != XNQ_OK) return rc;
   if ((rc = init_np<ConvQ8_0, DrainBlockScaled>()) != XNQ_OK) return rc;
@@ -912,6 +987,7 @@ int imma_init(int device) {
 
 #ifdef XNQ_DEV_TRACE
 extern "C" int xnq_dev_imma_trace(long long *out) { return cudaMemcpyFromSymbol(out, g_imma_trace, sizeof(long long) * 32) == cudaSuccess ? 0 : -6; }
+extern "C" int xnq_dev_imma_timeline(long long *out) { return cudaMemcpyFromSymbol(out, g_imma_tl, sizeof(long long) * 8 * 64) == cudaSuccess ? 0 : -6; }
 #endif
 
 int imma_status(unsigned int *bits) {

@@ -85,13 +85,18 @@ struct Ring {
   int stage_rows;          // rows per stage = (CW / ks) * rows per warp
   int rows_per_warp;       // 1 or 2
   int nstages;
-  int ks;                  // warps (k segments) per row; divides CW
+  int ks;                  // warps (k segments) per row; a power of two that divides CW
+  int ks_shift;            // log2(ks)
+  // rows of CTA b: rows_q + (b < rows_r), starting at b * rows_q + min(b, rows_r); niter_q = ceil(rows_q / stage_rows) and
+  // niter_q1 = ceil((rows_q + 1) / stage_rows) ring passes (set at launch: the kernel divides by nothing at run time, a
+  // 64-bit division costs every thread several hundred cycles before the first copy can be issued)
+  int rows_q, rows_r, niter_q, niter_q1;
   int seg_units;           // 256-element units per segment (the last segment may hold fewer)
   int nunits;              // units per row = ceil(k / 256)
   uint32_t act_off, part_off, ring_off; // byte offsets in dynamic shared memory
   uint32_t smem_bytes;
   const uint8_t *hint_base; // the weight the stream multiplies next (may be null): asked into L2
-  unsigned long long hint_bytes;
+  unsigned long long hint_bytes, hint_share;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -176,8 +181,6 @@ __device__ __forceinline__ float lds_half(uint32_t a) {
   asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
   return __half2float(__ushort_as_half(v));
 }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void named_barrier(int id, int nthreads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory"); }
 
 __device__ __forceinline__ int dot16(const uint4 &w, const int4 &a, int acc) {
@@ -511,11 +514,11 @@ matvec_ring_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtyp
   const uint32_t full0 = smem_u32(smem), empty0 = full0 + 8 * MAX_STAGES; // full[MAX_STAGES], empty[MAX_STAGES]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t k = w.k;
-  const int64_t row_begin = w.n * (int64_t)blockIdx.x / gridDim.x;
-  const int64_t row_end = w.n * ((int64_t)blockIdx.x + 1) / gridDim.x;
-  const int nrows = (int)(row_end - row_begin);
+  const bool extra_row = (int)blockIdx.x < ring.rows_r;
+  const int nrows = ring.rows_q + (extra_row ? 1 : 0);
+  const int64_t row_begin = (int64_t)blockIdx.x * ring.rows_q + min((int)blockIdx.x, ring.rows_r);
   const int KS = ring.ks, S = ring.nstages, RPS = ring.stage_rows;
-  const int niter = (nrows + RPS - 1) / RPS;
+  const int niter = extra_row ? ring.niter_q1 : ring.niter_q;
   const uint32_t ring0 = smem_u32(smem + ring.ring_off);
 #ifdef XNQ_DEV_TRACE
   __shared__ unsigned int trace_slot;
@@ -540,8 +543,10 @@ matvec_ring_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtyp
   if (warp == CW) { // ---- producer: weights are immutable after upload, no dependency on earlier kernels ----
     int issued = 0;
     bool dead = false, synced = false;
+    int s = -1;
+    uint32_t ph = 0; // stage it % S and (it / S) & 1, kept as counters
     for (int it = 0; it < niter; it++) {
-      const int s = it % S;
+      if (++s == S) s = 0, ph ^= 1u;
       // The first stages are requested at once. The rest of the ring is requested only when the consumers have their
       // activations: requested earlier, its bytes sit in the memory system's queues in front of the loads of x, which
       // every consumer needs before it can start (measured: x then takes 1 to 3 us instead of half a microsecond), and
@@ -552,7 +557,7 @@ matvec_ring_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtyp
       }
       if (lane == 0 && !dead) {
         if (it == S) pdl_wait(); // nothing is handed back before the previous kernel has retired: do not count that time
-        if (it >= S && !mbar_wait(empty0 + 8 * s, ((it / S) - 1) & 1, 2u)) {
+        if (it >= S && !mbar_wait(empty0 + 8 * s, ph ^ 1u, 2u)) {
           dead = true;
           continue;
         }
@@ -582,7 +587,7 @@ matvec_ring_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtyp
       // all of the CTA's own rows have been requested, so the requests fill the memory system while the consumers
       // finish (asked for earlier, they compete with the CTA's own stream and slow it down).
       if (ring.hint_base && issued == niter) {
-        const unsigned long long share = ((ring.hint_bytes / gridDim.x) + HINT_CHUNK - 1) & ~(unsigned long long)(HINT_CHUNK - 1);
+        const unsigned long long share = ring.hint_share; // hint_bytes / grid, rounded up to whole chunks
         const unsigned long long h0 = share * blockIdx.x, h1 = min(h0 + share, ring.hint_bytes & ~15ull);
         for (unsigned long long o = h0; o < h1; o += HINT_CHUNK) bulk_prefetch_l2(ring.hint_base + o, (uint32_t)min((unsigned long long)HINT_CHUNK, h1 - o));
       }
@@ -593,7 +598,7 @@ matvec_ring_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtyp
   }
 
   // ---- consumers ----
-  const int rl = warp / KS, seg = warp - rl * KS;
+  const int rl = warp >> ring.ks_shift, seg = warp - rl * KS;
   const int u0 = seg * ring.seg_units; // first unit of this warp's segment
   const int nu = min(ring.seg_units, ring.nunits - u0);
   pdl_wait(); // x may be the previous kernel's output; y may still be read by it
@@ -630,12 +635,14 @@ matvec_ring_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtyp
   for (int q = 0; q < 4; q++) seg_off[q] = (uint32_t)u0 * ring.unit_bytes[q];
 
   bool alive = true;
+  int s = -1;
+  uint32_t ph = 0; // stage it % S and (it / S) & 1
   for (int it = 0; it < niter; it++) {
-    const int s = it % S;
+    if (++s == S) s = 0, ph ^= 1u;
     float acc[R];
 #pragma unroll
     for (int r = 0; r < R; r++) acc[r] = 0.f;
-    if (alive) alive = mbar_wait_warp(full0 + 8 * s, (it / S) & 1);
+    if (alive) alive = mbar_wait_warp(full0 + 8 * s, ph);
 #ifdef XNQ_DEV_TRACE
     if (it == 0) XNQ_TRACE_POINT(4);
 #endif
@@ -786,6 +793,12 @@ template <typename LaneT, int ACT>
 int launch_fmt(const WeightView &w, const void *x, int x_dtype, void *y, int y_dtype, const Ring &r, cudaStream_t s, const GatherArgs *g) {
   const int64_t max_ctas = (w.n + r.stage_rows - 1) / r.stage_rows; // at least one stage of rows per CTA
   const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>((int64_t)g_num_sms, max_ctas));
+  Ring rr = r;
+  rr.rows_q = (int)(w.n / grid), rr.rows_r = (int)(w.n % grid);
+  rr.niter_q = (rr.rows_q + r.stage_rows - 1) / r.stage_rows, rr.niter_q1 = (rr.rows_q + r.stage_rows) / r.stage_rows;
+  rr.ks_shift = 0;
+  while ((1 << rr.ks_shift) < r.ks) rr.ks_shift++;
+  rr.hint_share = ((r.hint_bytes / grid) + HINT_CHUNK - 1) & ~(unsigned long long)(HINT_CHUNK - 1);
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(NTHREADS);
@@ -797,11 +810,11 @@ int launch_fmt(const WeightView &w, const void *x, int x_dtype, void *y, int y_d
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   if (r.rows_per_warp == 2) {
-    if (g) XNQ_CUDA(cudaLaunchKernelEx(&cfg, matvec_ring_kernel<LaneT, ACT, 2, true>, w, x, x_dtype, y, y_dtype, r, *g));
-    else XNQ_CUDA(cudaLaunchKernelEx(&cfg, matvec_ring_kernel<LaneT, ACT, 2, false>, w, x, x_dtype, y, y_dtype, r, GatherArgs{}));
+    if (g) XNQ_CUDA(cudaLaunchKernelEx(&cfg, matvec_ring_kernel<LaneT, ACT, 2, true>, w, x, x_dtype, y, y_dtype, rr, *g));
+    else XNQ_CUDA(cudaLaunchKernelEx(&cfg, matvec_ring_kernel<LaneT, ACT, 2, false>, w, x, x_dtype, y, y_dtype, rr, GatherArgs{}));
   } else {
-    if (g) XNQ_CUDA(cudaLaunchKernelEx(&cfg, matvec_ring_kernel<LaneT, ACT, 1, true>, w, x, x_dtype, y, y_dtype, r, *g));
-    else XNQ_CUDA(cudaLaunchKernelEx(&cfg, matvec_ring_kernel<LaneT, ACT, 1, false>, w, x, x_dtype, y, y_dtype, r, GatherArgs{}));
+    if (g) XNQ_CUDA(cudaLaunchKernelEx(&cfg, matvec_ring_kernel<LaneT, ACT, 1, true>, w, x, x_dtype, y, y_dtype, rr, *g));
+    else XNQ_CUDA(cudaLaunchKernelEx(&cfg, matvec_ring_kernel<LaneT, ACT, 1, false>, w, x, x_dtype, y, y_dtype, rr, GatherArgs{}));
   }
   count_launch();
   return XNQ_OK;

@@ -100,7 +100,7 @@ def rope_kv_store(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos: 
                                                 max_seq, _stream_ptr(qkv.device)))
 
 
-_attn_ws: dict[tuple[int, int, int], torch.Tensor] = {}
+_attn_ws: dict[tuple[int, int], torch.Tensor] = {}   # (device, stream) -> workspace, grown on demand
 
 
 def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int) -> torch.Tensor:
@@ -108,10 +108,11 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, p
     _f32c(q, out)
     B, _, max_seq, hd = k_cache.shape
     L = _lib.lib()
-    key = (q.device.index or 0, B, heads)
+    key = (q.device.index or 0, int(_stream_ptr(q.device).value or 0))   # calls on different streams may overlap: one workspace each
+    need = max(int(L.xnq_attn_decode_workspace_bytes(B, heads)), 16)
     ws = _attn_ws.get(key)
-    if ws is None:   # zeroed once; the kernel leaves its arrival counters at zero
-        ws = _attn_ws[key] = torch.zeros(max(int(L.xnq_attn_decode_workspace_bytes(B, heads)), 16), dtype=torch.uint8, device=q.device)
+    if ws is None or ws.numel() < need:   # zeroed once; the kernel leaves its arrival counters at zero
+        ws = _attn_ws[key] = torch.zeros(need, dtype=torch.uint8, device=q.device)
     with torch.cuda.device(q.device):
         _lib.check(L.xnq_attn_decode(_p(q), _p(k_cache), _p(v_cache), _p(pos), _p(out), B, heads, kv_heads, hd, max_seq, _p(ws), ws.numel(),
                                      _stream_ptr(q.device)))
