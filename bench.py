@@ -43,6 +43,9 @@ WORKLOADS = {
     "C3_q4k_14336x4096_m4": (D.Q4K, 14336, 4096, 4),
     "C3_q4k_14336x4096_m16": (D.Q4K, 14336, 4096, 16),
     "C4_q6k_128256x4096_m1": (D.Q6K, 128256, 4096, 1),
+    "C4_q6k_128256x4096_m16": (D.Q6K, 128256, 4096, 16),   # the dp4a small-batch kernel (Q6_K has no integer tensor-core path)
+    "C1_q4_0_4096x4096_m16": (D.Q4_0, 4096, 4096, 16),
+    "C1_q4_0_4096x4096_m128": (D.Q4_0, 4096, 4096, 128),
     "C4_q6k_128256x4096_m32": (D.Q6K, 128256, 4096, 32),
     # prefill (m > 16): the tensor-core kernel; roofline is reported against the dense bf16/fp16 tensor peak
     "C2_q8_0_11008x4096_m128": (D.Q8_0, 11008, 4096, 128),
@@ -754,6 +757,7 @@ def main():
     ap.add_argument("--gather", default="peer-stores", choices=["peer-stores", "nccl"], help="N > 1: how output slices are gathered")
     ap.add_argument("--option", action="append", default=[], help="library switch NAME=INT (A/B measurements), e.g. matvec_tma=0")
     ap.add_argument("--no-extra", action="store_true", help="headline workload only: skip the list of the other BASELINE configurations")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.workload in DECODER_WORKLOADS:
@@ -767,7 +771,7 @@ def main():
             line = decoder_measure(args, args.workload, DECODER_WORKLOADS[args.workload], ctx.dev, ctx.rank, ctx.world, args.steps, ctx.L)
         else:
             dt, n, k, m = WORKLOADS[args.workload]
-            line = measure_matmul(ctx, args, args.workload, dt, n, k, m)
+            line = measure_matmul(ctx, args, args.workload, dt, n, k, m, with_cpu=not args.no_cpu)
             if args.workload == DEFAULT_WORKLOAD and not args.no_extra and not args.option:
                 # every other BASELINE configuration in the same run (bounded in time), so that one invocation records them all
                 extras = []

@@ -57,6 +57,7 @@ enum {
  * take a non-const handle (xnq_linear_forward_host, xnq_weight_reserve_host_staging) use staging buffers
  * owned by the handle and must not run concurrently with each other on the same handle. */
 typedef struct xnq_weight xnq_weight;
+typedef struct xnq_comm xnq_comm; /* a rank's end of the kernel-side output exchange, see xnq_comm_create */
 
 /* Message of the last failure on the calling thread ("" if none). Replaces the xn::Error text a
  * Rust caller builds with bail! (xn-core/src/error.rs:153-164). */
@@ -149,6 +150,17 @@ int xnq_matmul_t(const xnq_weight *w, const void *x, int x_dtype, int64_t m, int
  * l). One-shot and per host thread; NULL clears it. Results never depend on it. The named weight must stay
  * alive until that launch has finished; under stream capture the hint is recorded with the launch. */
 int xnq_hint_next_weight(const xnq_weight *w);
+/* One row, three operators in one launch: x_out[k] = x_in[k] + sum of the `delta_parts` rows of delta ([parts][k], may
+ * be NULL with 0 parts), then y[n] = W . quantize(rmsnorm(x_out) * norm_weight). The results are, bit for bit, those of
+ * xnq_add_rmsnorm (with an activation image) followed by xnq_matmul_t: every CTA of the matvec forms the normalised,
+ * quantized row for itself, one of them writes the new residual. x_out must not be x_in. f32 rows of at most 4096
+ * values whose weight the one-row kernel serves; otherwise XNQ_ERR_UNSUPPORTED (call the two operators instead).
+ * `await` (may be NULL): the communicator whose slot holds `delta` when the gather that produced it was left
+ * un-awaited (xnq_comm_set_deferred): the kernel streams its weight while it awaits, bounded, the peers' epochs, and
+ * reads the summands only then.
+ * Reference: the rms_norm + linear pairs of a decoder layer, xn-core/src/models/llama.rs:145-216. */
+int xnq_matvec_normed(const xnq_weight *w, const float *x_in, const float *delta, int delta_parts, const float *norm_weight,
+                      float eps, float *x_out, void *y, int y_dtype, const xnq_comm *await, void *stream);
 
 /* xnq_matmul_t for callers that can neither supply a workspace nor let the library allocate one:
  * hosts whose allocator owns all device memory, steps being recorded into a CUDA graph, plugins under
@@ -187,7 +199,6 @@ int xnq_weight_reserve_host_staging(xnq_weight *w, int64_t max_m);
  * allocations through CUDA IPC, and the matmul kernel stores its output columns into the same slot
  * of every rank; a one-warp kernel then waits (bounded) until every peer's columns have arrived.
  * Every rank must issue the same sequence of gathers. Works inside a captured CUDA graph. --------- */
-typedef struct xnq_comm xnq_comm;
 #define XNQ_IPC_HANDLE_BYTES 64
 /* Allocates this rank's slots on the current device: nslots (2..64) buffers of slot_bytes each. */
 int xnq_comm_create(int rank, int world, size_t slot_bytes, int nslots, xnq_comm **out);

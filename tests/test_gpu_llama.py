@@ -64,6 +64,40 @@ def test_fused_decode_step_agrees_with_the_torch_op_decode_step():
     assert _rel(logits[0], logits[1]) < 3e-2, _rel(logits[0], logits[1])
 
 
+def test_norm_in_the_matvec_prologue_is_bit_identical_to_the_separate_kernels():
+    """One row: xnq_matvec_normed (residual add + RMSNorm + quantizer in the matvec's prologue) against
+    xnq_add_rmsnorm with an image followed by the matmul, for every format; then a whole decoder with and without it."""
+    from xn_b200 import decoder_ops as ops, quantized as Q, synth
+    from xn_b200.dtypes import GgmlDType as D
+    from xn_b200.llama import LlamaConfig, QLlama
+    dev = torch.device("cuda", 0)
+    Q.init(dev)
+    torch.manual_seed(11)
+    for dt, n, k, parts in [(D.Q4K, 6144, 4096, 1), (D.Q4K, 320, 1024, 0), (D.Q6K, 1000, 4096, 2), (D.Q8_0, 256, 2048, 1), (D.Q4_0, 130, 512, 3), (D.Q4K, 96, 256, 1)]:
+        w = Q.QCudaTensor.from_qtensor(Q.QTensor(synth.make_weight(dt, n, k, seed=70), (n, k), dt), dev)
+        assert w.supports_normed()
+        x = torch.randn(1, k, device=dev) * 3; g = torch.rand(k, device=dev) + 0.5
+        delta = torch.randn(1, parts * k, device=dev) if parts else None
+        # separate kernels: the residual is updated in place
+        x_ref = x.clone(); img = ops.ActImage.for_weight(dt, 1, k, dev)
+        ops.add_rmsnorm(x_ref, delta, g, 1e-5, None, img)
+        want = w.matmul_t(img)
+        x_out = torch.full_like(x, float("nan")); got = torch.empty(1, n, device=dev)
+        w.matvec_normed(x, delta, g, 1e-5, x_out, got)
+        assert torch.equal(x_out, x_ref), (dt.name, k, parts, "residual")
+        assert torch.equal(got, want), (dt.name, k, parts, float((got - want).abs().max()))
+    g = torch.Generator(device="cpu"); g.manual_seed(12)
+    prompt = torch.randint(0, 512, (1, 9), generator=g).to(dev)
+    outs = []
+    for fused_norm in (True, False):
+        m = QLlama(LlamaConfig.tiny(), dev, batch=1, max_seq=64, max_prefill_rows=64, fused_norm=fused_norm)
+        m.prefill(prompt)
+        toks = m.decode(12)
+        outs.append((toks.clone(), m.last_logits.clone()))
+    assert torch.equal(outs[0][0], outs[1][0])
+    assert torch.equal(outs[0][1], outs[1][1])
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

@@ -58,6 +58,7 @@ def lib() -> ctypes.CDLL:
     L.xnq_linear_forward_host.argtypes = [vp, vp, i64, vp, vp, vp]
     L.xnq_weight_reserve_host_staging.argtypes = [vp, i64]
     L.xnq_hint_next_weight.argtypes = [vp]
+    L.xnq_matvec_normed.argtypes = [vp, vp, vp, ci, vp, ctypes.c_float, vp, vp, ci, vp, vp]
     L.xnq_matmul_t_static.argtypes = [vp, vp, ci, i64, i64, vp, ci, i64, vp]
     L.xnq_comm_create.argtypes = [ci, ci, sz, ci, pvp]
     L.xnq_comm_ipc_handle.argtypes = [vp, vp]

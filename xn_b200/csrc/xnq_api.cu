@@ -473,6 +473,31 @@ int xnq_hint_next_weight(const xnq_weight *w) {
   return XNQ_OK;
 }
 
+int xnq_matvec_normed(const xnq_weight *w, const float *x_in, const float *delta, int delta_parts, const float *norm_weight, float eps, float *x_out, void *y,
+                      int y_dtype, const xnq_comm *await, void *stream) {
+  clear_error();
+  if (!w || !x_in || !norm_weight || !x_out || !y) return fail(XNQ_ERR_NULL, "matvec_normed: NULL argument");
+  if (x_in == x_out) return fail(XNQ_ERR_SHAPE, "matvec_normed: x_out must not be x_in (every CTA reads x_in while one writes x_out)");
+  if ((delta && delta_parts < 1) || (!delta && delta_parts != 0)) return fail(XNQ_ERR_SHAPE, "matvec_normed: delta_parts = %d", delta_parts);
+  if (!is_float_dtype(y_dtype)) return fail(XNQ_ERR_DTYPE, "matvec_normed: output dtype %d is not f32/f16/bf16", y_dtype);
+  if (((uintptr_t)x_in | (uintptr_t)delta | (uintptr_t)norm_weight | (uintptr_t)x_out) & 15) return fail(XNQ_ERR_ALIGN, "matvec_normed: pointers must be 16-byte aligned");
+  if (!aligned(y, type_size(y_dtype))) return fail(XNQ_ERR_ALIGN, "matvec_normed: y is not aligned to its element size");
+  if (w->v.k % 8 || !matvec_tma_supported(w->v, 1) || matvec_tma_wants_image(w->v))
+    return fail(XNQ_ERR_UNSUPPORTED, "matvec_normed: rows of %lld values (the fused prologue serves rows of up to 4096 values; use xnq_add_rmsnorm + xnq_matmul_t)", (long long)w->v.k);
+  if (w->v.n == 0) return XNQ_OK;
+  NormArgs na;
+  na.x_in = x_in, na.delta = delta, na.parts = delta ? delta_parts : 0, na.weight = norm_weight, na.eps = eps, na.x_out = x_out;
+  if (await) {
+    const int wrc = comm_fill_wait(await, &na);
+    if (wrc != XNQ_OK) return wrc;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  profile_mark(s, true);
+  const int rc = launch_matvec_tma(w->v, x_in, XNQ_F32, y, y_dtype, s, nullptr, &na);
+  profile_mark(s, false);
+  return rc;
+}
+
 size_t xnq_matmul_workspace_bytes(const xnq_weight *w, int64_t max_m) {
   if (!w || max_m <= 0) return 0;
   const int64_t rows = max_m < MATVEC_MAX_M ? max_m : MATVEC_MAX_M;

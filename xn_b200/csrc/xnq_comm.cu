@@ -85,6 +85,16 @@ inline char *slot_ptr(const xnq_comm *c, int r, int slot) { return static_cast<c
 } // namespace
 } // namespace xnq
 
+namespace xnq {
+int comm_fill_wait(const xnq_comm *c, NormArgs *na) {
+  if (!c->connected) return fail(XNQ_ERR_UNSUPPORTED, "comm is not connected to its peers");
+  na->wait_ctl = c->ctl;
+  na->wait_row = reinterpret_cast<const unsigned int *>(c->region);
+  na->wait_world = c->world, na->wait_rank = c->rank;
+  return XNQ_OK;
+}
+} // namespace xnq
+
 using namespace xnq;
 
 extern "C" {

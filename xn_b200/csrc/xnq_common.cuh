@@ -258,7 +258,25 @@ bool matvec_tma_supported(const WeightView &w, int64_t m);
 bool matvec_tma_wants_image(const WeightView &w); // k above 4096: the activations must come as an activation image
 void matvec_hint_next(const xnq_weight *w);        // the weight the calling thread's stream multiplies next (one-shot)
 // g != nullptr: results go to column col0 + row of every rank's gathered buffer (y is ignored)
-int launch_matvec_tma(const WeightView &w, const void *x, int x_dtype, void *y, int y_dtype, cudaStream_t s, const GatherArgs *g = nullptr);
+// Residual add + RMSNorm applied by the one-row matvec in its prologue (x_in null: none). Every CTA forms the row
+// x_in + sum of the `parts` summands, normalises it and quantizes it for itself; CTA 0 also writes the new residual to
+// x_out, which must not be x_in (other CTAs may still be reading x_in).
+struct NormArgs {
+  const float *x_in = nullptr;
+  const float *delta = nullptr; // [parts][k] summands, or null
+  int parts = 0;
+  const float *weight = nullptr;
+  float eps = 0.f;
+  float *x_out = nullptr;
+  // When the summands are the output of a gather that was left un-awaited (xnq_comm_set_deferred): the kernel first awaits,
+  // bounded, that every peer has published as many gathers as this rank (wait_ctl[0]); wait_row is this rank's epoch row.
+  unsigned int *wait_ctl = nullptr;
+  const unsigned int *wait_row = nullptr;
+  int wait_world = 0, wait_rank = 0;
+};
+int comm_fill_wait(const xnq_comm *c, NormArgs *na); // xnq_comm.cu
+int launch_matvec_tma(const WeightView &w, const void *x, int x_dtype, void *y, int y_dtype, cudaStream_t s, const GatherArgs *g = nullptr,
+                      const NormArgs *norm = nullptr);
 bool matvec_tma_enabled(); // the "matvec_tma" library option
 int gather_cta_fence_scope(); // the "gather_cta_fence" library option
 // shared argument checks of the matmul entries (dtype, leading dimension, 16-byte row alignment)

@@ -58,19 +58,23 @@ __device__ __forceinline__ void quantize_store8(const float (&v)[8], bool valid,
 template <int ACT>
 __global__ void __launch_bounds__(256) add_rmsnorm_kernel(float *x, const float *delta, int parts, const float *w, float eps, float *out, void *image,
                                                           int64_t rows, int d) {
-  __shared__ float part[8];
+  constexpr int MAXP = 128; // 256-element partial sums kept apart (rows of up to 32768 values; beyond that they wrap around)
+  __shared__ float part[MAXP];
   pdl_launch_dependents();
   pdl_wait(); // x and delta are earlier kernels' outputs
   const int64_t row = blockIdx.x;
-  const int lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float *xr = x + row * d;
   const float *dr = delta ? delta + row * parts * d : nullptr;
+  const int np = (d + 255) / 256;
+  for (int i = threadIdx.x; i < min(np, MAXP); i += 256) part[i] = 0.f;
+  __syncthreads();
   // The first KEEP passes of 2048 values (rows of up to 4096 values entirely) stay in registers between the
   // sum of squares and the scaling, and their norm weights are requested before the block-wide reduction: one
   // trip to memory instead of three. Longer rows re-read the rest.
   constexpr int KEEP = 2;
   float kv[KEEP][8], kg[KEEP][8];
-  float ss = 0.f;
+  // adds the summands, stores the new residual, returns the sum of squares of the thread's run of 8
   auto first_pass = [&](int i, float (&v)[8]) {
     load8(xr + i, v);
     if (dr) {
@@ -78,33 +82,39 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(float *x, const float 
         float a[8];
         load8(dr + (int64_t)q * d + i, a);
 #pragma unroll
-        for (int e = 0; e < 8; e++) v[e] += a[e];
+        for (int e = 0; e < 8; e++) v[e] = __fadd_rn(v[e], a[e]);
       }
       *reinterpret_cast<float4 *>(xr + i) = make_float4(v[0], v[1], v[2], v[3]);
       *reinterpret_cast<float4 *>(xr + i + 4) = make_float4(v[4], v[5], v[6], v[7]);
     }
-#pragma unroll
-    for (int e = 0; e < 8; e++) ss += v[e] * v[e];
+    return rms_run_sum(v);
+  };
+  // one partial sum per 256 elements: pass p, warp w holds elements 2048 p + 256 w ..
+  auto pass_sum = [&](int p, float run) {
+    if (p * 2048 + warp * 256 >= d) return; // whole warps leave together
+    const float s = rms_warp_sum(run);
+    const int idx = p * 8 + warp;
+    if (lane == 0) part[idx % MAXP] += s; // one writer per entry and pass; entries are reused only by rows longer than 32768
   };
 #pragma unroll
   for (int p = 0; p < KEEP; p++) {
     const int i = p * 2048 + threadIdx.x * 8;
+    float run = 0.f;
     if (i < d) {
       load8(w + i, kg[p]);
-      first_pass(i, kv[p]);
+      run = first_pass(i, kv[p]);
     }
+    pass_sum(p, run);
   }
-  for (int i = KEEP * 2048 + threadIdx.x * 8; i < d; i += 2048) {
+  for (int p = KEEP; p * 2048 < d; p++) {
+    const int i = p * 2048 + threadIdx.x * 8;
     float v[8];
-    first_pass(i, v);
+    pass_sum(p, i < d ? first_pass(i, v) : 0.f);
   }
-  ss = warp_sum(ss);
-  if (lane == 0) part[threadIdx.x >> 5] = ss;
   __syncthreads();
   float tot = 0.f;
-#pragma unroll
-  for (int i = 0; i < 8; i++) tot += part[i];
-  const float r = rsqrtf(tot / (float)d + eps);
+  for (int i = 0; i < min(np, MAXP); i++) tot += part[i];
+  const float r = rms_scale(tot, d, eps);
   RowImage img{};
   if (ACT != 0) img = row_image(image, rows, d, ACT == XNQ_Q8_0 ? QK : QK_K, row);
   auto second_pass = [&](int base, float (&v)[8], const float (&g)[8], bool loaded) { // whole warps stay together for the quantizer's shuffles
@@ -117,7 +127,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(float *x, const float 
         load8(w + i, gg);
       }
 #pragma unroll
-      for (int e = 0; e < 8; e++) v[e] = v[e] * r * (loaded ? g[e] : gg[e]);
+      for (int e = 0; e < 8; e++) v[e] = rms_apply(v[e], r, loaded ? g[e] : gg[e]);
       if (out) {
         *reinterpret_cast<float4 *>(out + row * d + i) = make_float4(v[0], v[1], v[2], v[3]);
         *reinterpret_cast<float4 *>(out + row * d + i + 4) = make_float4(v[4], v[5], v[6], v[7]);

@@ -107,6 +107,21 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// the same with a suspend-time hint in nanoseconds: the hardware may keep the thread suspended that long before it
+// returns false (a plain try_wait returned after a system-chosen, short time, and two dozen waiting warps per SM then
+// spent a large share of the SM's issue slots re-issuing their waits: 60 % issue utilisation, a fifth of it in the
+// unit that executes barrier instructions)
+__device__ __forceinline__ bool mbar_test_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ unsigned long long wall_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -116,9 +131,15 @@ constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull; // a wait that lasts
 // bounded wait of one thread
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int bit) {
   if (mbar_test(bar, parity)) return true;
-  const unsigned long long t0 = wall_ns();
-  while (wall_ns() - t0 < WAIT_LIMIT_NS)
-    if (mbar_test(bar, parity)) return true;
+  unsigned long long t0 = 0;
+  for (unsigned int attempt = 1;; attempt++) { // the wall clock is read on every 16th failed attempt only
+    if (mbar_test_hint(bar, parity, 1000000u)) return true;
+    if ((attempt & 15u) == 0) {
+      const unsigned long long now = wall_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > WAIT_LIMIT_NS) break;
+    }
+  }
   atomicOr(&g_imma_status, bit);
   return false;
 }
@@ -362,7 +383,11 @@ struct DrainQ4K {
 
 template <typename Conv, template <int> class Drain, int NP>
 __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant__ ImmaArgs p) {
-  constexpr int NPT = NP / 2; // columns per drain thread: the eight warps of a half-step group are two per accumulator lane quarter
+  // Drain warps per half-step group: eight, two per accumulator lane quarter, splitting the columns. (Four per group with 16
+  // activation rows, which halves the fixed cost per step, was no faster: each warp's chain of loads from tensor memory and
+  // arithmetic per half step then takes longer than the MMAs of a step.)
+  constexpr int DWG = 8;
+  constexpr int NPT = NP / (DWG / 4); // columns per drain thread
   constexpr int CH = NPT > 16 ? 4 : (NPT > 8 ? 8 : NPT); // columns read back at a time: what the register budget holds next to the sums
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u; // operand stages need 1024-byte alignment
@@ -388,12 +413,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
     for (int s = 0; s < 8; s++) {
       mbar_init(a_full + 8 * s, CONV_WARPS / 2); // the four converter warps of the step's group (one barrier per step: entries 0 .. BS - 1)
       mbar_init(mma_done + 8 * s, 1);            // MMAs have read their operands and written their slices: entry 2 bs + 1 after a whole step (NP = 64: every half step)
-      mbar_init(acc_empty + 8 * s, DRAIN_WARPS / 2);
+      mbar_init(acc_empty + 8 * s, DWG);
     }
     for (int s = 0; s < 4; s++) {
       mbar_init(b_full + 8 * s, 1);
       mbar_init(side_full + 8 * s, 1 + CONV_WARPS / 2); // the producer's transaction + the four converter warps that copy the scale bytes
-      mbar_init(side_empty + 8 * s, DRAIN_WARPS);
+      mbar_init(side_empty + 8 * s, 2 * DWG);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -567,12 +592,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
     }
     cp_async_wait(0); // nothing may be in flight into this CTA's shared memory when it exits
     XNQ_TDUMP(12, threadIdx.x == CONV_WARP0 * 32);
-  } else {
-    // ---- drain: group h (eight warps) owns accumulator buffer h and half step h of every 256-k step. Warp quarter q
-    // reads accumulator lanes 32q.. (weight rows); the two warps of a quarter split the columns. Each group keeps its own
-    // f32 sums; at the end of a segment group 1 hands its sums to group 0 through scratch memory. ----
+  } else if (warp - DRAIN_WARP0 < 2 * DWG) {
+    // ---- drain: group h (DWG warps) owns half step h of every 256-k step and the accumulator buffers of its parity. Warp
+    // quarter q reads accumulator lanes 32q.. (weight rows); with eight warps per group the two warps of a quarter split the
+    // columns. Each group keeps its own f32 sums; at the end of a segment group 1 hands its sums to group 0 through scratch
+    // memory. ----
     const int dwi = warp - DRAIN_WARP0;
-    const int q = warp & 3, h = dwi >> 3, cg = (dwi >> 2) & 1;
+    const int q = warp & 3, h = dwi / DWG, cg = (dwi % DWG) >> 2;
     const int c0 = cg * NPT;
     const int et = threadIdx.x - DRAIN_WARP0 * 32; // 0..511
     pdl_wait(); // the kernel that prepares the activations also zeroes the tiles' tickets
@@ -632,7 +658,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
           for (int c = 0; c < NPT; c++) pair[(size_t)(c0 + c) * TILE_N + 32 * q + lane] = acc[c];
           __threadfence_block();
         }
-        asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_WARPS * 32) : "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(2 * DWG * 32) : "memory");
         if (h == 0) {
 #pragma unroll
           for (int c = 0; c < NPT; c++) acc[c] += pair[(size_t)(c0 + c) * TILE_N + 32 * q + lane];
@@ -651,7 +677,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
               }
             }
           }
-          asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_WARPS * 32) : "memory"); // group 0 has read the scratch: it may be rewritten
+          asm volatile("bar.sync 1, %0;" ::"n"(2 * DWG * 32) : "memory"); // group 0 has read the scratch: it may be rewritten
         } else {
           // this CTA's first segment (it starts where the CTA's range starts) uses scratch slot 2c, a later one 2c + 1
           const int seg_u0 = tile * KT + seg_kt0;
@@ -661,11 +687,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
             for (int c = 0; c < NPT; c++) mine[(size_t)(c0 + c) * TILE_N + 32 * q + lane] = acc[c];
             __threadfence();
           }
-          asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_WARPS * 32) : "memory");
+          asm volatile("bar.sync 1, %0;" ::"n"(2 * DWG * 32) : "memory");
           if (et == 0) s_ticket = atomicAdd(p.tile_cnt + tile, 1u);
-          asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_WARPS * 32) : "memory");
+          asm volatile("bar.sync 1, %0;" ::"n"(2 * DWG * 32) : "memory");
           const unsigned int ticket = s_ticket;
-          asm volatile("bar.sync 1, %0;" ::"n"(DRAIN_WARPS * 32) : "memory"); // s_ticket may be rewritten from here on
+          asm volatile("bar.sync 1, %0;" ::"n"(2 * DWG * 32) : "memory"); // s_ticket may be rewritten from here on
           const int t_u0 = tile * KT, t_u1 = t_u0 + KT;
           const int c_first = cta_of(t_u0, p.units_q, p.units_r), c_last = cta_of(t_u1 - 1, p.units_q, p.units_r);
           if (h == 0 && (int)ticket == c_last - c_first) { // the last part to arrive adds all parts in k order

@@ -120,6 +120,21 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// the same with a suspend-time hint in nanoseconds: the hardware may keep the thread suspended that long before it
+// returns false (a plain try_wait returned after a system-chosen, short time, and two dozen waiting warps per SM then
+// spent a large share of the SM's issue slots re-issuing their waits: 60 % issue utilisation, a fifth of it in the
+// unit that executes barrier instructions)
+__device__ __forceinline__ bool mbar_test_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ unsigned long long wall_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -132,9 +147,15 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // bounded wait of one thread: false (and a sticky status bit) if the phase never completes
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int bit) {
   if (mbar_test(bar, parity)) return true;
-  const unsigned long long t0 = wall_ns();
-  while (wall_ns() - t0 < WAIT_LIMIT_NS)
-    if (mbar_test(bar, parity)) return true;
+  unsigned long long t0 = 0;
+  for (unsigned int attempt = 1;; attempt++) { // the wall clock is read on every 16th failed attempt only
+    if (mbar_test_hint(bar, parity, 1000000u)) return true;
+    if ((attempt & 15u) == 0) {
+      const unsigned long long now = wall_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > WAIT_LIMIT_NS) break;
+    }
+  }
   atomicOr(&g_matvec_status, bit);
   return false;
 }
@@ -509,7 +530,7 @@ __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 15, %0;
 // finish publishes this rank's next epoch to every peer.
 template <typename LaneT, int ACT, int R, bool GATHER>
 __global__ void __launch_bounds__(NTHREADS, 1)
-matvec_ring_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtype, Ring ring, GatherArgs g) {
+matvec_ring_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtype, Ring ring, GatherArgs g, NormArgs na) {
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t full0 = smem_u32(smem), empty0 = full0 + 8 * MAX_STAGES; // full[MAX_STAGES], empty[MAX_STAGES]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -617,6 +638,67 @@ matvec_ring_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtyp
     for (int i = threadIdx.x; i < k / 16; i += CW * 32) reinterpret_cast<uint4 *>(sq)[swz(i)] = reinterpret_cast<const uint4 *>(img)[i];
     for (int i = threadIdx.x; i < nblk; i += CW * 32) sd[i] = reinterpret_cast<const float *>(img_d)[i];
     for (int i = threadIdx.x; i < k / 32; i += CW * 32) reinterpret_cast<uint32_t *>(sb)[i] = reinterpret_cast<const uint32_t *>(img_b)[i];
+  } else if (na.x_in) {
+    // Residual add + RMSNorm of the row, then the quantizer: the arithmetic, and the order of the sum of squares, of the
+    // stand-alone add+RMSNorm kernel (one run of 8 per thread, one 256-element partial sum per warp, partial sums added in
+    // index order), so the image is the one that kernel would have written.
+    static_assert(RowLoad::PASSES == 1, "one run of 8 elements per consumer thread");
+    RowLoad xr;
+    float gw[8];
+    const int per_row = (int)(k / 8), t = threadIdx.x;
+    const bool valid = t < per_row;
+    if (valid) {
+      load8(na.x_in + (int64_t)t * 8, xr.v[0]);
+      load8(na.weight + (int64_t)t * 8, gw);
+    }
+    if (na.wait_ctl) { // the summands come from the peers: await their epochs (lane p awaits rank p), then let the CTA read them
+      if (warp == 0 && lane < na.wait_world && lane != na.wait_rank && na.wait_ctl[3] == 0) {
+        const unsigned int epoch = na.wait_ctl[0];
+        unsigned long long t0;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        for (;;) {
+          unsigned int v;
+          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(na.wait_row + lane) : "memory");
+          if ((int)(v - epoch) >= 0) break;
+          unsigned long long t1;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+          if (t1 - t0 > GATHER_WAIT_LIMIT_NS) { // a late peer is reported once and not awaited again
+            atomicOr(na.wait_ctl + 3, 1u << lane);
+            break;
+          }
+        }
+      }
+      consumer_sync();
+    }
+    if (valid) {
+      for (int q = 0; q < na.parts; q++) {
+        float a[8];
+        load8(na.delta + (int64_t)q * k + (int64_t)t * 8, a);
+#pragma unroll
+        for (int e = 0; e < 8; e++) xr.v[0][e] = __fadd_rn(xr.v[0][e], a[e]);
+      }
+      if (blockIdx.x == 0) {
+        *reinterpret_cast<float4 *>(na.x_out + (int64_t)t * 8) = make_float4(xr.v[0][0], xr.v[0][1], xr.v[0][2], xr.v[0][3]);
+        *reinterpret_cast<float4 *>(na.x_out + (int64_t)t * 8 + 4) = make_float4(xr.v[0][4], xr.v[0][5], xr.v[0][6], xr.v[0][7]);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; e++) xr.v[0][e] = 0.f, gw[e] = 0.f;
+    }
+    float *red = reinterpret_cast<float *>(smem + ring.part_off); // free until the first stage is multiplied
+    const int np = (int)((k + 255) / 256);
+    if (warp < np) {
+      const float s = rms_warp_sum(valid ? rms_run_sum(xr.v[0]) : 0.f);
+      if (lane == 0) red[warp] = s;
+    }
+    consumer_sync();
+    float tot = 0.f;
+    for (int i = 0; i < np; i++) tot += red[i];
+    const float r = rms_scale(tot, (int)k, na.eps);
+#pragma unroll
+    for (int e = 0; e < 8; e++) xr.v[0][e] = rms_apply(xr.v[0][e], r, gw[e]);
+    consumer_sync(); // every warp has read the partial sums: the scratch may be reused
+    xr.template finish<ACT>(k, sq, sd, sb);
   } else {
     RowLoad xr;
     xr.issue(x, x_dtype, k);
@@ -790,7 +872,8 @@ int plan_ring(const WeightView &w, Ring &r) {
 }
 
 template <typename LaneT, int ACT>
-int launch_fmt(const WeightView &w, const void *x, int x_dtype, void *y, int y_dtype, const Ring &r, cudaStream_t s, const GatherArgs *g) {
+int launch_fmt(const WeightView &w, const void *x, int x_dtype, void *y, int y_dtype, const Ring &r, cudaStream_t s, const GatherArgs *g, const NormArgs *norm) {
+  const NormArgs na = norm ? *norm : NormArgs{};
   const int64_t max_ctas = (w.n + r.stage_rows - 1) / r.stage_rows; // at least one stage of rows per CTA
   const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>((int64_t)g_num_sms, max_ctas));
   Ring rr = r;
@@ -810,11 +893,11 @@ int launch_fmt(const WeightView &w, const void *x, int x_dtype, void *y, int y_d
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   if (r.rows_per_warp == 2) {
-    if (g) XNQ_CUDA(cudaLaunchKernelEx(&cfg, matvec_ring_kernel<LaneT, ACT, 2, true>, w, x, x_dtype, y, y_dtype, rr, *g));
-    else XNQ_CUDA(cudaLaunchKernelEx(&cfg, matvec_ring_kernel<LaneT, ACT, 2, false>, w, x, x_dtype, y, y_dtype, rr, GatherArgs{}));
+    if (g) XNQ_CUDA(cudaLaunchKernelEx(&cfg, matvec_ring_kernel<LaneT, ACT, 2, true>, w, x, x_dtype, y, y_dtype, rr, *g, na));
+    else XNQ_CUDA(cudaLaunchKernelEx(&cfg, matvec_ring_kernel<LaneT, ACT, 2, false>, w, x, x_dtype, y, y_dtype, rr, GatherArgs{}, na));
   } else {
-    if (g) XNQ_CUDA(cudaLaunchKernelEx(&cfg, matvec_ring_kernel<LaneT, ACT, 1, true>, w, x, x_dtype, y, y_dtype, rr, *g));
-    else XNQ_CUDA(cudaLaunchKernelEx(&cfg, matvec_ring_kernel<LaneT, ACT, 1, false>, w, x, x_dtype, y, y_dtype, rr, GatherArgs{}));
+    if (g) XNQ_CUDA(cudaLaunchKernelEx(&cfg, matvec_ring_kernel<LaneT, ACT, 1, true>, w, x, x_dtype, y, y_dtype, rr, *g, na));
+    else XNQ_CUDA(cudaLaunchKernelEx(&cfg, matvec_ring_kernel<LaneT, ACT, 1, false>, w, x, x_dtype, y, y_dtype, rr, GatherArgs{}, na));
   }
   count_launch();
   return XNQ_OK;
@@ -846,21 +929,22 @@ bool matvec_tma_wants_image(const WeightView &w) {
 
 void matvec_hint_next(const xnq_weight *w) { t_hint_next = w; }
 
-int launch_matvec_tma(const WeightView &w, const void *x, int x_dtype, void *y, int y_dtype, cudaStream_t s, const GatherArgs *g) {
+int launch_matvec_tma(const WeightView &w, const void *x, int x_dtype, void *y, int y_dtype, cudaStream_t s, const GatherArgs *g, const NormArgs *norm) {
   Ring r;
   const int ks = plan_ring(w, r);
   if (!ks) return fail(XNQ_ERR_SIZE, "matvec_ring: no ring fits k = %lld", (long long)w.k);
   if (x_dtype != XNQ_ACT_IMAGE && (ks > 1 || w.k > 4096)) return fail(XNQ_ERR_SIZE, "matvec_ring: k = %lld needs the activations as an image", (long long)w.k);
+  if (norm && norm->x_in && (x_dtype == XNQ_ACT_IMAGE || w.k % 8)) return fail(XNQ_ERR_SHAPE, "matvec_ring: the norm prologue takes f32 rows of a multiple of 8 values");
   if (t_hint_next) { // one-shot: the named weight is asked into L2 by this launch
     r.hint_base = static_cast<const uint8_t *>(t_hint_next->base);
     r.hint_bytes = t_hint_next->bytes;
     t_hint_next = nullptr;
   }
   switch (w.dtype) {
-    case XNQ_Q4_0: return launch_fmt<Q4_0Lane, XNQ_Q8_0>(w, x, x_dtype, y, y_dtype, r, s, g);
-    case XNQ_Q8_0: return launch_fmt<Q8_0Lane, XNQ_Q8_0>(w, x, x_dtype, y, y_dtype, r, s, g);
-    case XNQ_Q4K: return launch_fmt<Q4KLane, XNQ_Q8K>(w, x, x_dtype, y, y_dtype, r, s, g);
-    case XNQ_Q6K: return launch_fmt<Q6KLane, XNQ_Q8K>(w, x, x_dtype, y, y_dtype, r, s, g);
+    case XNQ_Q4_0: return launch_fmt<Q4_0Lane, XNQ_Q8_0>(w, x, x_dtype, y, y_dtype, r, s, g, norm);
+    case XNQ_Q8_0: return launch_fmt<Q8_0Lane, XNQ_Q8_0>(w, x, x_dtype, y, y_dtype, r, s, g, norm);
+    case XNQ_Q4K: return launch_fmt<Q4KLane, XNQ_Q8K>(w, x, x_dtype, y, y_dtype, r, s, g, norm);
+    case XNQ_Q6K: return launch_fmt<Q6KLane, XNQ_Q8K>(w, x, x_dtype, y, y_dtype, r, s, g, norm);
   }
   return fail(XNQ_ERR_DTYPE, "matvec_ring: dtype %d", w.dtype);
 }

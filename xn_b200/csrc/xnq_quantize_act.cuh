@@ -43,6 +43,24 @@ __device__ __forceinline__ void load8(const __nv_bfloat16 *p, float v[8]) {
   }
 }
 
+// ---- RMSNorm arithmetic, shared by the stand-alone add+RMSNorm kernel and by the one-row matvec that applies the norm in
+// its prologue, so that both produce the same bits. The sum of squares of a row has ONE order: each run of 8 consecutive
+// elements is summed first (fused multiply-adds, element 0 first), 32 consecutive runs (256 elements) are combined by the
+// warp's xor-shuffle tree, and the 256-element partial sums are added in index order.
+__device__ __forceinline__ float rms_run_sum(const float (&v)[8]) {
+  float s = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; e++) s = __fmaf_rn(v[e], v[e], s);
+  return s;
+}
+__device__ __forceinline__ float rms_warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float rms_scale(float total, int d, float eps) { return rsqrtf(__fadd_rn(__fdiv_rn(total, (float)d), eps)); }
+__device__ __forceinline__ float rms_apply(float v, float r, float g) { return __fmul_rn(__fmul_rn(v, r), g); }
+
 // Rust `f32::round` (half away from zero) followed by `as i8` (saturating, NaN -> 0), for the
 // products a quantizer forms (|v| far below 2^22). trunc(v + copysign(0.5, v)) is exact there: v and
 // v + 0.5 share a binade whose ulp divides 0.5, or the sum lands just ABOVE a power of two, so the

@@ -22,6 +22,8 @@ one layer is ten launches and the whole step is one CUDA graph.
 """
 from __future__ import annotations
 
+import os
+
 import dataclasses
 from typing import Optional
 
@@ -79,13 +81,21 @@ class QLlama:
     KV cache of ``max_seq`` positions for ``batch`` sequences, prefill and CUDA-graphed decode."""
 
     def __init__(self, cfg: LlamaConfig, device: torch.device, batch: int = 1, max_seq: int = 1024, rank: int = 0, world: int = 1,
-                 group=None, seed: int = 0, max_prefill_rows: int = 512, fused_decode: bool = True):
+                 group=None, seed: int = 0, max_prefill_rows: int = 512, fused_decode: bool = True, fused_norm: Optional[bool] = None):
         if cfg.n_kv_heads % world or cfg.n_heads % world or cfg.ffn % world or cfg.vocab % world or cfg.d_model % world:
             raise ValueError(f"config does not divide over {world} ranks")
         init(device)
         self.cfg, self.device, self.batch, self.max_seq, self.rank, self.world = cfg, device, batch, max_seq, rank, world
         self.hl, self.kvl = cfg.n_heads // world, cfg.n_kv_heads // world
         self.fused_decode = fused_decode and cfg.head_dim == 128
+        # One-row decode: residual add + RMSNorm in the prologue of the matvec that follows (same bits either way). On one GPU
+        # the separate kernel is faster (it runs under the next matvec's weight prefetch, and only one CTA does the norm); sharded,
+        # the fused kernel is where the exchange of the row-parallel linears is awaited, off the producing kernel's critical path.
+        # XN_FUSED_NORM=0/1 overrides the default for measurements.
+        if fused_norm is None:
+            env = os.environ.get("XN_FUSED_NORM")
+            fused_norm = (env == "1") if env in ("0", "1") else world > 1
+        self.fused_norm = fused_norm
         c, r, G, hd = cfg, rank, world, cfg.head_dim
 
         def rows(w, per):  # this rank's block of `per` consecutive rows
@@ -130,6 +140,8 @@ class QLlama:
         self._graph = None
         f32 = dict(device=device, dtype=torch.float32)
         self._x = torch.zeros((batch, c.d_model), **f32)       # residual stream of the decode step
+        self._x2 = torch.zeros((batch, c.d_model), **f32)      # its second buffer: a fused norm + matvec reads one and writes the other
+        self._logits = torch.zeros((batch, c.vocab), **f32) if world == 1 else None
         self._xn = torch.zeros((batch, c.d_model), **f32)
         self._qkv = torch.zeros((batch, (self.hl + 2 * self.kvl) * hd), **f32)
         self._q = torch.zeros((batch, self.hl, hd), **f32)
@@ -173,9 +185,16 @@ class QLlama:
         """N-sharded linear, output columns gathered on every rank."""
         return w.matmul_t(x) if self.pg is None else self.pg.matmul_t(w, x, slot=self._slot())
 
-    def _linear_parts(self, w: QCudaTensor, x_local: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """K-sharded linear on this rank's input slice: ``(.., world * n)``, the ranks' summands side by side."""
-        return w.matmul_t(x_local, out=out) if self.pg is None else self.pg.matmul_t(w, x_local, slot=self._slot(), parts=True)
+    def _linear_parts(self, w: QCudaTensor, x_local: torch.Tensor, out: Optional[torch.Tensor] = None, defer: bool = False) -> torch.Tensor:
+        """K-sharded linear on this rank's input slice: ``(.., world * n)``, the ranks' summands side by side. ``defer``: the
+        kernel publishes its columns and retires without awaiting the peers'; the consumer of the result awaits them."""
+        if self.pg is None:
+            return w.matmul_t(x_local, out=out)
+        self.pg.set_deferred(defer)
+        try:
+            return self.pg.matmul_t(w, x_local, slot=self._slot(), parts=True)
+        finally:
+            self.pg.set_deferred(False)
 
     def _sum_parts(self, parts: torch.Tensor) -> torch.Tensor:
         return parts if self.world == 1 else parts.view(*parts.shape[:-1], self.world, -1).sum(-2)
@@ -229,6 +248,52 @@ class QLlama:
             x = self._block(L, x, pos_idx, mask)
         x = self._rms(x[:, -1:, :], self.norm)
         logits = self._linear_gathered(self.lm_head, x).view(tokens.shape[0], -1)
+        return logits if self.pg is None else logits.clone()   # out of the exchange slot before it is reused
+
+    def _forward_decode(self) -> torch.Tensor:
+        """One token per sequence (self.tokens at position self.pos) -> logits [B, vocab], fused operators."""
+        c = self.cfg
+        self._gather_idx = 0
+        self._x.copy_(self.embed.index_select(0, self.tokens))
+        delta = None
+        xi, hi = self._xn_img, self._h_img
+        # one row: every linear's kernel is told which weight comes next, and asks for it to be brought into L2 as it finishes
+        hint = (lambda w: w.hint_next()) if self.batch == 1 else (lambda w: None)
+        # One row and rows of at most 4096 values: the residual add, the RMSNorm and the quantizer run in the prologue of the
+        # matvec that consumes them (same bits as the separate kernels), which takes two launches out of every layer.
+        fused = self.batch == 1 and self.fused_norm and self.layers[0].wqkv.supports_normed()
+        cur, nxt = self._x, self._x2
+        # sharded: the K-sharded linears leave their exchange un-awaited, the fused kernel that adds the summands awaits the
+        # peers itself while its weight stream is already running
+        defer = fused and self.pg is not None
+        for li, L in enumerate(self.layers):
+            hint(L.wo)
+            if fused:
+                L.wqkv.matvec_normed(cur, delta, L.norm1, c.rms_eps, nxt, self._qkv, await_comm=self.pg if (defer and delta is not None) else None)
+                cur, nxt = nxt, cur
+            else:
+                ops.add_rmsnorm(cur, delta, L.norm1, c.rms_eps, None if xi else self._xn, xi)
+                L.wqkv.matmul_t(xi or self._xn, out=self._qkv)
+            ops.rope_kv_store(self._qkv, self.cos, self.sin, self.pos, self._q, L.k_cache, L.v_cache, self.hl, self.kvl)
+            ops.attn_decode(self._q, L.k_cache, L.v_cache, self.pos, self._a.view(self.batch, self.hl, c.head_dim), self.hl, self.kvl)
+            hint(L.wgu)
+            o = self._linear_parts(L.wo, self._a, self._o, defer=defer)           # world summands per row when sharded
+            hint(L.wdown)
+            if fused:
+                L.wgu.matvec_normed(cur, o, L.norm2, c.rms_eps, nxt, self._gu, await_comm=self.pg if defer else None)
+                cur, nxt = nxt, cur
+            else:
+                ops.add_rmsnorm(cur, o, L.norm2, c.rms_eps, None if xi else self._xn, xi)
+                L.wgu.matmul_t(xi or self._xn, out=self._gu)
+            ops.swiglu(self._gu, None if hi else self._h, hi)
+            hint(self.layers[li + 1].wqkv if li + 1 < len(self.layers) else self.lm_head)
+            delta = self._linear_parts(L.wdown, hi or self._h, self._dn, defer=defer and li + 1 < len(self.layers))  # the last one feeds an unfused norm
+        fi = self._head_img
+        if fused and self.pg is None and self.lm_head.supports_normed():
+            logits = self.lm_head.matvec_normed(cur, delta, self.norm, c.rms_eps, nxt, self._logits)
+        else:
+            ops.add_rmsnorm(cur, delta, self.norm, c.rms_eps, None if fi else self._xn, fi)
+            logits = self._linear_gathered(self.lm_head, fi or self._xn)
         return logits if self.pg is None else logits.clone()   # out of the exchange slot before it is reused
 
     def _forward_decode(self) -> torch.Tensor:

@@ -203,6 +203,29 @@ class QCudaTensor:
         asks for these bytes to be brought into L2 while it finishes (xnq_hint_next_weight)."""
         check(_lib.lib().xnq_hint_next_weight(self._h))
 
+    def supports_normed(self) -> bool:
+        """Whether :meth:`matvec_normed` serves this weight (rows of at most 4096 values on the one-row kernel)."""
+        return self.k <= 4096 and self.k % 256 == 0
+
+    def matvec_normed(self, x_in: torch.Tensor, delta: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float, x_out: torch.Tensor,
+                      out: torch.Tensor, await_comm=None) -> torch.Tensor:
+        """One row: ``x_out = x_in + delta`` (``delta`` may hold several summands side by side, or be None), then
+        ``out = self . quantize(rmsnorm(x_out) * norm_weight)`` in ONE launch of the one-row kernel; bit for bit what
+        ``add_rmsnorm`` with an activation image followed by :meth:`matmul_t` gives (xnq_matvec_normed; the rms_norm +
+        linear pairs of llama.rs:145-216). ``x_out`` must be another buffer than ``x_in``. ``await_comm``: the ``PeerGather``
+        whose slot holds ``delta`` when that gather was issued in deferred mode (the kernel then awaits the peers itself)."""
+        for t in (x_in, delta, norm_weight, x_out):
+            if t is not None and (t.dtype is not torch.float32 or not t.is_contiguous() or t.device != self.device):
+                raise ValueError("matvec_normed: f32 contiguous tensors on the weight's device")
+        if x_in.numel() != self.k or x_out.numel() != self.k or norm_weight.numel() != self.k or out.numel() != self.n:
+            raise ValueError(f"matvec_normed: shapes do not match weight (n={self.n}, k={self.k})")
+        parts = 0 if delta is None else delta.numel() // self.k
+        p = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None else None
+        with torch.cuda.device(self.device):
+            check(_lib.lib().xnq_matvec_normed(self._h, p(x_in), p(delta), parts, p(norm_weight), eps, p(x_out), p(out), int(_TORCH_TO_XNQ[out.dtype]),
+                                               await_comm._h if await_comm is not None else None, _stream_ptr(self.device)))
+        return out
+
     def matmul_t(self, lhs: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``lhs @ self^T`` with ``lhs`` of shape ``(.., k)``; the result is ``(.., n)`` (q8.rs:116-157)."""
         if hasattr(lhs, "act_dtype"):   # an ActImage: activations quantized ahead of the call
