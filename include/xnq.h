@@ -43,12 +43,22 @@ enum {
   XNQ_F32 = 0,
   XNQ_F16 = 1,
   XNQ_Q4_0 = 2,
+  XNQ_Q4_1 = 3,
+  XNQ_Q5_0 = 6,
+  XNQ_Q5_1 = 7,
   XNQ_Q8_0 = 8,
+  XNQ_Q8_1 = 9, /* activation blocks only */
+  XNQ_Q2K = 10,
+  XNQ_Q3K = 11,
   XNQ_Q4K = 12,
+  XNQ_Q5K = 13,
   XNQ_Q6K = 14,
-  XNQ_Q8K = 15,
+  XNQ_Q8K = 15, /* activation blocks only */
   XNQ_BF16 = 30,
 };
+/* Weight formats: Q4_0, Q8_0, Q4_K, Q6_K (the formats of the benchmark configurations) have their own device layouts and
+ * HBM-streaming / tensor-core kernels. Q4_1, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K are held as the file's blocks and served by one
+ * plain kernel each for to_float and matmul (same results contract; no activation image, gather or static entry). */
 
 /* An immutable quantized [n, k] weight (or an N-shard of one) resident in device memory.
  * Replaces Q8Tensor (xn-core/src/cuda_backend/q8.rs:26-33) and the missing QStorage::Cuda variant

@@ -5,7 +5,7 @@
 //   QTensor                  quantized/mod.rs:27-340              xnq::QTensor      (host blocks + shape)
 //   Q8Tensor                 cuda_backend/q8.rs:26-157            xnq::QCudaTensor  (device weight)
 //   Q8Linear / QLinear       q8.rs:160-185, mod.rs:342-406        xnq::QCudaLinear
-//   Q8<T>: BackendQ          q8.rs:187-224, lib.rs:141-156        xnq::Q40 / Q80 / Q4K / Q6K
+//   Q8<T>: BackendQ          q8.rs:187-224, lib.rs:141-156        xnq::Q40 / Q41 / Q50 / Q51 / Q80 / Q2K / Q3K / Q4K / Q5K / Q6K
 //
 // xn's Tensor<T, Device> does not exist on this side of the ABI, so device tensors are a pointer, a
 // dtype and their dimensions. Errors are exceptions carrying the ABI's status code and message, the
@@ -23,7 +23,10 @@
 
 namespace xnq {
 
-enum class GgmlDType : int { F32 = XNQ_F32, F16 = XNQ_F16, Q4_0 = XNQ_Q4_0, Q8_0 = XNQ_Q8_0, Q4K = XNQ_Q4K, Q6K = XNQ_Q6K, Q8K = XNQ_Q8K, BF16 = XNQ_BF16 };
+enum class GgmlDType : int {
+  F32 = XNQ_F32, F16 = XNQ_F16, Q4_0 = XNQ_Q4_0, Q4_1 = XNQ_Q4_1, Q5_0 = XNQ_Q5_0, Q5_1 = XNQ_Q5_1, Q8_0 = XNQ_Q8_0, Q8_1 = XNQ_Q8_1,
+  Q2K = XNQ_Q2K, Q3K = XNQ_Q3K, Q4K = XNQ_Q4K, Q5K = XNQ_Q5K, Q6K = XNQ_Q6K, Q8K = XNQ_Q8K, BF16 = XNQ_BF16
+};
 
 inline size_t type_size(GgmlDType d) { return (size_t)xnq_type_size((int)d); }   // mod.rs:160-179
 inline size_t block_size(GgmlDType d) { return (size_t)xnq_block_size((int)d); } // mod.rs:182-195
@@ -33,8 +36,15 @@ inline const char *name(GgmlDType d) {
     case GgmlDType::F16: return "F16";
     case GgmlDType::BF16: return "BF16";
     case GgmlDType::Q4_0: return "Q4_0";
+    case GgmlDType::Q4_1: return "Q4_1";
+    case GgmlDType::Q5_0: return "Q5_0";
+    case GgmlDType::Q5_1: return "Q5_1";
     case GgmlDType::Q8_0: return "Q8_0";
+    case GgmlDType::Q8_1: return "Q8_1";
+    case GgmlDType::Q2K: return "Q2K";
+    case GgmlDType::Q3K: return "Q3K";
     case GgmlDType::Q4K: return "Q4K";
+    case GgmlDType::Q5K: return "Q5K";
     case GgmlDType::Q6K: return "Q6K";
     case GgmlDType::Q8K: return "Q8K";
   }
@@ -187,5 +197,12 @@ using Q40 = BackendQ<GgmlDType::Q4_0>;
 using Q80 = BackendQ<GgmlDType::Q8_0>;
 using Q4K = BackendQ<GgmlDType::Q4K>;
 using Q6K = BackendQ<GgmlDType::Q6K>;
+// the remaining weight formats the reference instantiates (mod.rs:444-455): held as the file's blocks, one plain kernel each
+using Q41 = BackendQ<GgmlDType::Q4_1>;
+using Q50 = BackendQ<GgmlDType::Q5_0>;
+using Q51 = BackendQ<GgmlDType::Q5_1>;
+using Q2K = BackendQ<GgmlDType::Q2K>;
+using Q3K = BackendQ<GgmlDType::Q3K>;
+using Q5K = BackendQ<GgmlDType::Q5K>;
 
 } // namespace xnq

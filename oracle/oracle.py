@@ -14,7 +14,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "libxnq_oracle.so")
 
-F32, Q4_0, Q8_0, Q4K, Q6K, Q8K = 0, 2, 8, 12, 14, 15
+F32, Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q8_1, Q2K, Q3K, Q4K, Q5K, Q6K, Q8K = 0, 2, 3, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15
 
 
 def build(force: bool = False) -> str:

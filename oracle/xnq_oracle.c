@@ -81,7 +81,7 @@ int xnqo_type_size(int dtype) {
     case XNQO_Q6K: return (int)sizeof(blk_q6k);
     case XNQO_Q8K: return (int)sizeof(blk_q8k);
   }
-  return -1;
+  return xnqo_more_type_size(dtype);
 }
 
 int xnqo_block_size(int dtype) {
@@ -93,7 +93,7 @@ int xnqo_block_size(int dtype) {
     case XNQO_Q6K:
     case XNQO_Q8K: return QK_K;
   }
-  return -1;
+  return xnqo_more_block_size(dtype);
 }
 
 int xnqo_vec_dot_type(int dtype) {
@@ -104,7 +104,7 @@ int xnqo_vec_dot_type(int dtype) {
     case XNQO_Q6K:
     case XNQO_Q8K: return XNQO_Q8K;
   }
-  return -1;
+  return xnqo_more_vec_dot_type(dtype);
 }
 
 /* Rust `f32::round`: half away from zero. `as i32` / `as i8` / `as u8` saturate, NaN -> 0. */
@@ -224,7 +224,7 @@ int xnqo_to_float(int dtype, const void *blocks, int64_t nelem, float *out) {
     case XNQO_Q6K: q6k_to_float((const blk_q6k *)blocks, nb, out); return 0;
     case XNQO_Q8K: q8k_to_float((const blk_q8k *)blocks, nb, out); return 0;
   }
-  return -1;
+  return xnqo_more_to_float(dtype, blocks, nb, out);
 }
 
 /* ==========================================================================================
@@ -550,7 +550,7 @@ int xnqo_from_float(int dtype, const float *x, int64_t nelem, void *blocks) {
     case XNQO_Q6K: q6k_from_float(x, nb, (blk_q6k *)blocks); return 0;
     case XNQO_Q8K: xnqo_q8k_from_float(x, nb, (blk_q8k *)blocks); return 0;
   }
-  return -1;
+  return xnqo_more_from_float(dtype, x, nb, blocks);
 }
 
 /* ==========================================================================================
@@ -660,7 +660,7 @@ int xnqo_vec_dot(int dtype, int64_t k, const void *w, const void *a, float *out)
     case XNQO_Q4K: *out = dot_q4k(nb, (const blk_q4k *)w, (const blk_q8k *)a); return 0;
     case XNQO_Q6K: *out = dot_q6k(nb, (const blk_q6k *)w, (const blk_q8k *)a); return 0;
   }
-  return -1;
+  return xnqo_more_vec_dot(dtype, nb, w, a, out);
 }
 
 /* ==========================================================================================
@@ -704,8 +704,10 @@ static void mm_scalar_worker(int ith, int nth, void *arg) {
 int xnqo_matmul(int dtype, int64_t m, int64_t k, int64_t n, const float *lhs, const void *rhs, float *dst,
                 int threads) {
   const int bs = xnqo_block_size(dtype);
-  if (bs <= 1 || xnqo_vec_dot_type(dtype) < 0 || dtype == XNQO_Q8K) return -1;
+  if (bs <= 1 || xnqo_vec_dot_type(dtype) < 0 || dtype == XNQO_Q8K || dtype == XNQO_Q8_1) return -1;
   if (m < 0 || n < 0 || k < 0 || k % bs != 0) return -1;
+  /* the dots of Q4_1, Q5_0, Q5_1 refuse an odd number of blocks (k_quants.rs:322-325, 413-415, 523-526) */
+  if ((dtype == XNQO_Q4_1 || dtype == XNQO_Q5_0 || dtype == XNQO_Q5_1) && (k / bs) % 2 != 0) return -1;
   if (m == 0 || n == 0) return 0;
   void *lhs_b = xnqo_quantize_lhs(dtype, m, k, lhs);
   if (!lhs_b) return -2;
@@ -781,7 +783,7 @@ static void mm_f64_worker(int ith, int nth, void *arg) {
 int xnqo_matmul_f64(int dtype, int64_t m, int64_t k, int64_t n, const float *lhs, const void *rhs, double *dst,
                     int threads) {
   const int bs = xnqo_block_size(dtype);
-  if (bs <= 1 || xnqo_vec_dot_type(dtype) < 0 || dtype == XNQO_Q8K) return -1;
+  if (bs <= 1 || xnqo_vec_dot_type(dtype) < 0 || dtype == XNQO_Q8K || dtype == XNQO_Q8_1) return -1;
   if (m < 0 || n < 0 || k < 0 || k % bs != 0) return -1;
   if (m == 0 || n == 0) return 0;
   void *lhs_b = xnqo_quantize_lhs(dtype, m, k, lhs);

@@ -17,6 +17,9 @@
  * Q4_0, Q4_K, Q6_K and the Q8_K activation quantizer: PARITY UNPINNED - the reference holds no
  * test, golden vector or fixture for them, so this restatement is checked only against the source
  * text of k_quants.rs (struct sizes, round trips, scalar-vs-AVX2 agreement, f64 dots).
+ * Q4_1, Q5_0, Q5_1, Q8_1, Q2_K, Q3_K, Q5_K (xnq_oracle_more.c): PARITY UNPINNED for the same reason; to_float,
+ * the scalar-order dots and the simple quantizers are restated, the search-based weight quantizers of the K formats
+ * and the AVX2-order dots are not (their test weights are synthesized as random valid blocks).
  */
 #ifndef XNQ_ORACLE_H
 #define XNQ_ORACLE_H
@@ -32,8 +35,15 @@ extern "C" {
 enum {
   XNQO_F32 = 0,
   XNQO_Q4_0 = 2,
+  XNQO_Q4_1 = 3,
+  XNQO_Q5_0 = 6,
+  XNQO_Q5_1 = 7,
   XNQO_Q8_0 = 8,
+  XNQO_Q8_1 = 9,
+  XNQO_Q2K = 10,
+  XNQO_Q3K = 11,
   XNQO_Q4K = 12,
+  XNQO_Q5K = 13,
   XNQO_Q6K = 14,
   XNQO_Q8K = 15,
 };
@@ -50,7 +60,7 @@ float xnqo_f16_to_f32(uint16_t h);
 
 /* GgmlType::to_float: blocks -> nelem floats. Returns 0, or -1 on a bad dtype / size. */
 int xnqo_to_float(int dtype, const void *blocks, int64_t nelem, float *out);
-/* GgmlType::from_float: nelem floats -> blocks (Q4_0, Q8_0, Q4K, Q6K, Q8K). */
+/* GgmlType::from_float: nelem floats -> blocks (Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q8_1, Q4K, Q6K, Q8K). */
 int xnqo_from_float(int dtype, const float *x, int64_t nelem, void *blocks);
 
 /* GgmlType::vec_dot_unopt (scalar summation order): one k-deep dot of a weight row with the

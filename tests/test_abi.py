@@ -34,10 +34,10 @@ def test_library_exports_every_declared_symbol():
 def test_version_and_geometry():
     L = _lib.lib()
     assert L.xnq_version() == 1
-    for dt in (D.Q4_0, D.Q8_0, D.Q4K, D.Q6K, D.Q8K):
+    for dt in (D.Q4_0, D.Q4_1, D.Q5_0, D.Q5_1, D.Q8_0, D.Q8_1, D.Q2K, D.Q3K, D.Q4K, D.Q5K, D.Q6K, D.Q8K):
         assert L.xnq_type_size(int(dt)) == dt.type_size
         assert L.xnq_block_size(int(dt)) == dt.block_size
-    assert L.xnq_type_size(3) == -1 and L.xnq_block_size(13) == -1  # Q4_1 / Q5K are not handled
+    assert L.xnq_type_size(4) == -1 and L.xnq_block_size(5) == -1 and L.xnq_type_size(16) == -1  # ids GGML retired or never used here
 
 
 def _upload(dtype, buf, nbytes, n, k, rank=0, count=1):
@@ -49,7 +49,8 @@ def _upload(dtype, buf, nbytes, n, k, rank=0, count=1):
 def test_upload_validation_happens_before_cuda():
     buf = np.zeros(4 * 18, np.uint8)
     p = ctypes.c_void_p(buf.ctypes.data)
-    assert _upload(3, p, 72, 4, 32)[0] == -2                      # Q4_1: unsupported dtype
+    assert _upload(9, p, 72, 4, 32)[0] == -2                      # Q8_1 is an activation format, not a weight format
+    assert _upload(4, p, 72, 4, 32)[0] == -2                      # an id GGML retired
     rc, msg = _upload(int(D.Q4_0), p, 72, 4, 33)
     assert rc == -3 and "32-value block" in msg                        # k not a multiple of the block
     rc, msg = _upload(int(D.Q4_0), p, 70, 4, 32)

@@ -165,8 +165,8 @@ extern "C" {
 
 const char *xnq_last_error(void) { return g_err; }
 int xnq_version(void) { return XNQ_VERSION; }
-int xnq_type_size(int dt) { return (is_weight_dtype(dt) || dt == XNQ_Q8K || is_float_dtype(dt)) ? type_size(dt) : -1; }
-int xnq_block_size(int dt) { return (is_weight_dtype(dt) || dt == XNQ_Q8K || is_float_dtype(dt)) ? block_size(dt) : -1; }
+int xnq_type_size(int dt) { return (is_weight_dtype(dt) || dt == XNQ_Q8K || dt == XNQ_Q8_1 || is_float_dtype(dt)) ? type_size(dt) : -1; }
+int xnq_block_size(int dt) { return (is_weight_dtype(dt) || dt == XNQ_Q8K || dt == XNQ_Q8_1 || is_float_dtype(dt)) ? block_size(dt) : -1; }
 
 uint64_t xnq_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
@@ -228,6 +228,7 @@ int xnq_init(int device) {
   if ((rc = prefill_init(device)) != XNQ_OK) return rc;
   if ((rc = imma_init(device)) != XNQ_OK) return rc;
   if ((rc = decoder_ops_init()) != XNQ_OK) return rc;
+  if ((rc = generic_init(device)) != XNQ_OK) return rc;
   return XNQ_OK;
 }
 
@@ -280,7 +281,7 @@ int xnq_weight_upload_rows(int dtype, const void *blocks, size_t nbytes, int64_t
   clear_error();
   if (!out) return fail(XNQ_ERR_NULL, "weight_upload: out is NULL");
   *out = nullptr;
-  if (!is_weight_dtype(dtype)) return fail(XNQ_ERR_DTYPE, "weight_upload: ggml dtype %d is not one of Q4_0(2) Q8_0(8) Q4K(12) Q6K(14)", dtype);
+  if (!is_weight_dtype(dtype)) return fail(XNQ_ERR_DTYPE, "weight_upload: ggml dtype %d is not a quantized weight format (Q4_0 2, Q4_1 3, Q5_0 6, Q5_1 7, Q8_0 8, Q2K 10, Q3K 11, Q4K 12, Q5K 13, Q6K 14)", dtype);
   if (n_total < 0 || k <= 0 || row0 < 0 || n_rows < 0 || row0 + n_rows > n_total)
     return fail(XNQ_ERR_SHAPE, "weight_upload: bad shape n_total=%lld k=%lld rows [%lld, +%lld)", (long long)n_total, (long long)k,
                 (long long)row0, (long long)n_rows);
@@ -300,6 +301,22 @@ int xnq_weight_upload_rows(int dtype, const void *blocks, size_t nbytes, int64_t
   w->n_total = n_total;
   w->row0 = row0;
   w->wscale = 1.0f;
+  if (is_generic_dtype(dtype)) { // held exactly as in the file: canonical blocks, row after row
+    const size_t alloc = nbytes ? ((nbytes + 255) & ~(size_t)255) : 256;
+    cudaError_t ge = cudaMalloc(&w->base, alloc);
+    if (ge == cudaSuccess && nbytes) ge = cudaMemcpyAsync(w->base, blocks, nbytes, cudaMemcpyDefault, s);
+    if (ge == cudaSuccess) ge = cudaStreamSynchronize(s);
+    if (ge != cudaSuccess) {
+      if (w->base) cudaFree(w->base);
+      delete w;
+      return fail(XNQ_ERR_CUDA, "weight_upload: %s", cudaGetErrorString(ge));
+    }
+    w->bytes = alloc;
+    w->v.dtype = dtype, w->v.n = n_rows, w->v.k = k, w->v.dstride = 0;
+    w->v.qs = static_cast<const uint8_t *>(w->base);
+    *out = w;
+    return XNQ_OK;
+  }
   const Plan p = plan_for(dtype, n_rows, k);
   cudaError_t e = cudaMalloc(&w->base, p.total);
   if (e != cudaSuccess) {
@@ -355,7 +372,7 @@ int xnq_weight_upload(int dtype, const void *blocks, size_t nbytes, int64_t n, i
                       xnq_weight **out) {
   clear_error();
   if (out) *out = nullptr;
-  if (!is_weight_dtype(dtype)) return fail(XNQ_ERR_DTYPE, "weight_upload: ggml dtype %d is not one of Q4_0(2) Q8_0(8) Q4K(12) Q6K(14)", dtype);
+  if (!is_weight_dtype(dtype)) return fail(XNQ_ERR_DTYPE, "weight_upload: ggml dtype %d is not a quantized weight format (Q4_0 2, Q4_1 3, Q5_0 6, Q5_1 7, Q8_0 8, Q2K 10, Q3K 11, Q4K 12, Q5K 13, Q6K 14)", dtype);
   if (shard_count < 1 || shard_rank < 0 || shard_rank >= shard_count)
     return fail(XNQ_ERR_SHAPE, "weight_upload: shard %d of %d", shard_rank, shard_count);
   if (n < 0 || k <= 0 || k % block_size(dtype) != 0)
@@ -399,6 +416,7 @@ int xnq_weight_dequantize(const xnq_weight *w, int out_dtype, void *dst, void *s
   if (!is_float_dtype(out_dtype)) return fail(XNQ_ERR_DTYPE, "dequantize: output dtype %d is not f32/f16/bf16", out_dtype);
   if (w->v.n == 0) return XNQ_OK;
   if (!dst) return fail(XNQ_ERR_NULL, "dequantize: dst is NULL");
+  if (is_generic_dtype(w->v.dtype)) return launch_generic_dequantize(w->v, out_dtype, dst, static_cast<cudaStream_t>(stream));
   return launch_dequantize(w->v, out_dtype, dst, static_cast<cudaStream_t>(stream));
 }
 
@@ -410,6 +428,11 @@ int xnq_weight_canonical_bytes(const xnq_weight *w, void *host_dst, size_t nbyte
   if (want == 0) return XNQ_OK;
   if (!host_dst) return fail(XNQ_ERR_NULL, "canonical_bytes: host_dst is NULL");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (is_generic_dtype(w->v.dtype)) { // already canonical on the device
+    XNQ_CUDA(cudaMemcpyAsync(host_dst, w->v.qs, want, cudaMemcpyDeviceToHost, s));
+    XNQ_CUDA(cudaStreamSynchronize(s));
+    return XNQ_OK;
+  }
   void *staging = nullptr;
   XNQ_CUDA(cudaMalloc(&staging, want));
   int rc = launch_to_canonical(w->v, static_cast<uint8_t *>(staging), s);
@@ -424,8 +447,8 @@ int xnq_weight_canonical_bytes(const xnq_weight *w, void *host_dst, size_t nbyte
 
 int xnq_quantize_act(int act_dtype, const void *x, int x_dtype, int64_t m, int64_t k, int64_t ldx, void *dst, void *stream) {
   clear_error();
-  if (act_dtype != XNQ_Q8_0 && act_dtype != XNQ_Q8K)
-    return fail(XNQ_ERR_DTYPE, "quantize_act: %d is not an activation block format (Q8_0=8, Q8K=15)", act_dtype);
+  if (act_dtype != XNQ_Q8_0 && act_dtype != XNQ_Q8_1 && act_dtype != XNQ_Q8K)
+    return fail(XNQ_ERR_DTYPE, "quantize_act: %d is not an activation block format (Q8_0=8, Q8_1=9, Q8K=15)", act_dtype);
   const int bs = block_size(act_dtype);
   if (k <= 0 || k % bs != 0) return fail(XNQ_ERR_SHAPE, "quantize_act: k = %lld is not a multiple of the %d-value block", (long long)k, bs);
   int rc = check_activations("quantize_act", x, x_dtype, m, k, ldx);
@@ -433,6 +456,7 @@ int xnq_quantize_act(int act_dtype, const void *x, int x_dtype, int64_t m, int64
   if (m == 0) return XNQ_OK;
   if (!dst) return fail(XNQ_ERR_NULL, "quantize_act: dst_blocks is NULL");
   if (!aligned(dst, 4)) return fail(XNQ_ERR_ALIGN, "quantize_act: dst_blocks must be 4-byte aligned");
+  if (act_dtype == XNQ_Q8_1) return launch_quantize_q8_1(x, x_dtype, m, k, ldx, dst, static_cast<cudaStream_t>(stream));
   return launch_quantize_act_blocks(act_dtype, x, x_dtype, m, k, ldx, dst, static_cast<cudaStream_t>(stream));
 }
 
@@ -457,7 +481,7 @@ int xnq_quantize_act_image(int act_dtype, const void *x, int x_dtype, int64_t m,
 
 int xnq_quantize_weight(int ggml_dtype, const float *x_dev, int64_t n, int64_t k, void *blocks_dev, void *stream) {
   clear_error();
-  if (!is_weight_dtype(ggml_dtype)) return fail(XNQ_ERR_DTYPE, "quantize_weight: dtype %d is not Q4_0/Q8_0/Q4K/Q6K", ggml_dtype);
+  if (!is_fast_dtype(ggml_dtype)) return fail(XNQ_ERR_DTYPE, "quantize_weight: dtype %d is not Q4_0/Q8_0/Q4K/Q6K (the other formats have no device quantizer)", ggml_dtype);
   const int bs = block_size(ggml_dtype);
   if (n < 0 || k <= 0 || k % bs != 0)
     return fail(XNQ_ERR_SHAPE, "quantize_weight: quantized tensor must have their last dim divisible by block size [%lld, %lld] %d", (long long)n, (long long)k, bs);
@@ -500,6 +524,7 @@ int xnq_matvec_normed(const xnq_weight *w, const float *x_in, const float *delta
 
 size_t xnq_matmul_workspace_bytes(const xnq_weight *w, int64_t max_m) {
   if (!w || max_m <= 0) return 0;
+  if (is_generic_dtype(w->v.dtype)) return generic_workspace_bytes(w->v, max_m);
   const int64_t rows = max_m < MATVEC_MAX_M ? max_m : MATVEC_MAX_M;
   size_t decode = act_workspace_bytes(rows, w->v.k, act_dtype_for(w->v.dtype));
   if (max_m >= 2 && imma_supported(w->v, 2)) decode = std::max(decode, imma_workspace_bytes(std::min<int64_t>(max_m, IMMA_MAX_M), w->v.k, w->v.n));
@@ -513,6 +538,7 @@ int xnq_matmul_t(const xnq_weight *w, const void *x, int x_dtype, int64_t m, int
   clear_error();
   if (!w) return fail(XNQ_ERR_NULL, "matmul_t: weight is NULL");
   const int64_t k = w->v.k, n = w->v.n;
+  if (x_dtype == XNQ_ACT_IMAGE && is_generic_dtype(w->v.dtype)) return fail(XNQ_ERR_UNSUPPORTED, "matmul_t: dtype %d takes float activations only (no activation image)", w->v.dtype);
   if (x_dtype == XNQ_ACT_IMAGE) return matmul_from_image(w, x, m, y, y_dtype, ldy, workspace, ws_bytes, static_cast<cudaStream_t>(stream));
   int rc = check_activations("matmul_t", x, x_dtype, m, k, ldx);
   if (rc != XNQ_OK) return rc;
@@ -526,6 +552,7 @@ int xnq_matmul_t(const xnq_weight *w, const void *x, int x_dtype, int64_t m, int
   if (!aligned(workspace, 256)) return fail(XNQ_ERR_ALIGN, "matmul_t: workspace must be 256-byte aligned");
   if (ws_bytes < need) return fail(XNQ_ERR_SIZE, "matmul_t: workspace has %zu bytes, m = %lld needs %zu", ws_bytes, (long long)m, need);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (is_generic_dtype(w->v.dtype)) return launch_generic_matmul(w->v, x, x_dtype, m, ldx, y, y_dtype, ldy, workspace, s);
   if (g_opt_matvec_tma.load(std::memory_order_relaxed) && matvec_tma_supported(w->v, m)) {
     // decode fast path: one kernel; activations quantized in its prologue (k <= 4096, no scratch) or, for longer
     // rows, by the stand-alone quantizer into the workspace as an activation image

@@ -35,8 +35,15 @@ inline int type_size(int dt) {
     case XNQ_F16: return 2;
     case XNQ_BF16: return 2;
     case XNQ_Q4_0: return 18;
+    case XNQ_Q4_1: return 20;
+    case XNQ_Q5_0: return 22;
+    case XNQ_Q5_1: return 24;
     case XNQ_Q8_0: return 34;
+    case XNQ_Q8_1: return 36;
+    case XNQ_Q2K: return 84;
+    case XNQ_Q3K: return 110;
     case XNQ_Q4K: return 144;
+    case XNQ_Q5K: return 176;
     case XNQ_Q6K: return 210;
     case XNQ_Q8K: return 292;
   }
@@ -48,16 +55,36 @@ inline int block_size(int dt) {
     case XNQ_F16:
     case XNQ_BF16: return 1;
     case XNQ_Q4_0:
-    case XNQ_Q8_0: return QK;
+    case XNQ_Q4_1:
+    case XNQ_Q5_0:
+    case XNQ_Q5_1:
+    case XNQ_Q8_0:
+    case XNQ_Q8_1: return QK;
+    case XNQ_Q2K:
+    case XNQ_Q3K:
     case XNQ_Q4K:
+    case XNQ_Q5K:
     case XNQ_Q6K:
     case XNQ_Q8K: return QK_K;
   }
   return -1;
 }
-inline bool is_weight_dtype(int dt) { return dt == XNQ_Q4_0 || dt == XNQ_Q8_0 || dt == XNQ_Q4K || dt == XNQ_Q6K; }
+// the four formats with their own device layouts and fast kernels, and the six held as canonical blocks (xnq_generic.cu)
+inline bool is_fast_dtype(int dt) { return dt == XNQ_Q4_0 || dt == XNQ_Q8_0 || dt == XNQ_Q4K || dt == XNQ_Q6K; }
+bool is_generic_dtype(int dt);
+inline bool is_weight_dtype(int dt) { return is_fast_dtype(dt) || is_generic_dtype(dt); }
 inline bool is_float_dtype(int dt) { return dt == XNQ_F32 || dt == XNQ_F16 || dt == XNQ_BF16; }
-inline int act_dtype_for(int wdt) { return (wdt == XNQ_Q4_0 || wdt == XNQ_Q8_0) ? XNQ_Q8_0 : XNQ_Q8K; }
+// GgmlType::VecDotType (k_quants.rs:210,310,405,511,615,883,1046,1321,1510,1727)
+inline int act_dtype_for(int wdt) {
+  switch (wdt) {
+    case XNQ_Q4_0:
+    case XNQ_Q5_0:
+    case XNQ_Q8_0: return XNQ_Q8_0;
+    case XNQ_Q4_1:
+    case XNQ_Q5_1: return XNQ_Q8_1;
+    default: return XNQ_Q8K;
+  }
+}
 
 // ------------------------------------------------------------------------------------------------
 // Device layout of a weight (or N-shard): what the kernels read.
@@ -227,6 +254,13 @@ void profile_mark(cudaStream_t s, bool start);
 int launch_relayout(const WeightView &dst, const uint8_t *canonical_dev, cudaStream_t s);   // GGUF -> device layout
 int launch_to_canonical(const WeightView &src, uint8_t *canonical_dev, cudaStream_t s);     // device layout -> GGUF
 int launch_dequantize(const WeightView &w, int out_dtype, void *dst, cudaStream_t s);
+// formats held as canonical blocks (xnq_generic.cu)
+int generic_init(int device);
+int launch_generic_dequantize(const WeightView &w, int out_dtype, void *dst, cudaStream_t s);
+int launch_quantize_q8_1(const void *x, int x_dtype, int64_t m, int64_t k, int64_t ldx, void *dst, cudaStream_t s);
+size_t generic_workspace_bytes(const WeightView &w, int64_t m);
+int launch_generic_matmul(const WeightView &w, const void *x, int x_dtype, int64_t m, int64_t ldx, void *y, int y_dtype, int64_t ldy, void *workspace,
+                          cudaStream_t s);
 int layout_init(int device);
 
 // xnq_quantize_act.cu

@@ -53,6 +53,7 @@ extern "C" int xnq_matmul_t_static(const xnq_weight *w, const void *x, int x_dty
   clear_error();
   if (!w) return fail(XNQ_ERR_NULL, "matmul_t_static: weight is NULL");
   const int64_t k = w->v.k, n = w->v.n;
+  if (!is_fast_dtype(w->v.dtype)) return fail(XNQ_ERR_UNSUPPORTED, "matmul_t_static: weight dtype %d is served by xnq_matmul_t only", w->v.dtype);
   if (!is_float_dtype(x_dtype) || !is_float_dtype(y_dtype)) return fail(XNQ_ERR_DTYPE, "matmul_t_static: x / y dtype must be f32, f16 or bf16");
   if (m < 0 || m > MATVEC_MAX_M)
     return fail(XNQ_ERR_SIZE, "matmul_t_static: m = %lld; this entry serves 0..%d rows (larger batches need xnq_matmul_t and a caller-owned workspace)",

@@ -104,8 +104,8 @@ class QCudaTensor:
                      shard_count: int = 1) -> "QCudaTensor":
         """Take GGUF blocks as they are (``Q8Tensor::from_q8_0``, q8.rs:60-85)."""
         device = torch.device(device)
-        if qt.dtype() not in (GgmlDType.Q4_0, GgmlDType.Q8_0, GgmlDType.Q4K, GgmlDType.Q6K):
-            raise ValueError(f"cuda quantized: expected a Q4_0/Q8_0/Q4K/Q6K tensor, got {qt.dtype().name}")
+        if not qt.dtype().is_quantized_weight:
+            raise ValueError(f"cuda quantized: expected a quantized weight format, got {qt.dtype().name}")
         if qt.rank() != 2:
             raise ValueError(f"cuda quantized: expected a 2-d weight, got shape {qt.shape()}")
         n, k = qt.shape()
@@ -205,7 +205,7 @@ class QCudaTensor:
 
     def supports_normed(self) -> bool:
         """Whether :meth:`matvec_normed` serves this weight (rows of at most 4096 values on the one-row kernel)."""
-        return self.k <= 4096 and self.k % 256 == 0
+        return self._dtype.has_fast_kernels and self.k <= 4096 and self.k % 256 == 0
 
     def matvec_normed(self, x_in: torch.Tensor, delta: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float, x_out: torch.Tensor,
                       out: torch.Tensor, await_comm=None) -> torch.Tensor:
@@ -330,7 +330,7 @@ def quantize_weight(weight: torch.Tensor, dtype: GgmlDType) -> torch.Tensor:
 
 
 def quantize_act(x: torch.Tensor, act_dtype: GgmlDType) -> torch.Tensor:
-    """Canonical Q8_0 / Q8_K activation blocks of ``x`` ``[m, k]`` as a uint8 device tensor."""
+    """Canonical Q8_0 / Q8_1 / Q8_K activation blocks of ``x`` ``[m, k]`` as a uint8 device tensor."""
     act_dtype = GgmlDType(act_dtype)
     if x.dim() != 2 or x.stride(-1) != 1:
         raise ValueError("quantize_act wants a 2-d tensor with contiguous rows")
@@ -376,4 +376,30 @@ class Q6K(_BackendQ):
     DTYPE = GgmlDType.Q6K
 
 
-__all__ = ["QTensor", "QCudaTensor", "QCudaLinear", "Q40", "Q80", "Q4K", "Q6K", "GgmlDType", "XnqError", "init", "quantize_act"]
+# the remaining weight formats the reference instantiates as BackendQ (mod.rs:444-455): held as the file's blocks, one plain kernel each
+class Q41(_BackendQ):
+    DTYPE = GgmlDType.Q4_1
+
+
+class Q50(_BackendQ):
+    DTYPE = GgmlDType.Q5_0
+
+
+class Q51(_BackendQ):
+    DTYPE = GgmlDType.Q5_1
+
+
+class Q2K(_BackendQ):
+    DTYPE = GgmlDType.Q2K
+
+
+class Q3K(_BackendQ):
+    DTYPE = GgmlDType.Q3K
+
+
+class Q5K(_BackendQ):
+    DTYPE = GgmlDType.Q5K
+
+
+__all__ = ["QTensor", "QCudaTensor", "QCudaLinear", "Q40", "Q41", "Q50", "Q51", "Q80", "Q2K", "Q3K", "Q4K", "Q5K", "Q6K", "GgmlDType", "XnqError", "init",
+           "quantize_act"]

@@ -105,6 +105,12 @@ DEFAULT_DSCALE = {
     GgmlDType.Q8_0: 0.01,
     GgmlDType.Q4K: 0.01,
     GgmlDType.Q6K: 0.005,
+    GgmlDType.Q4_1: 0.02,
+    GgmlDType.Q5_0: 0.01,
+    GgmlDType.Q5_1: 0.01,
+    GgmlDType.Q2K: 0.01,
+    GgmlDType.Q3K: 0.01,
+    GgmlDType.Q5K: 0.005,
 }
 
 
@@ -126,7 +132,27 @@ def _gen_group(dtype: GgmlDType, rows: int, k: int, dscale: float, g: np.random.
         d = np.abs(g.standard_normal((rows, nb), np.float32)) * np.float32(dscale)
         sc = g.integers(-64, 64, (rows, nb, 16), np.int8)
         return pack_q6_k(d, sc, g.integers(0, 64, (rows, nb, 256), np.uint8))
-    raise ValueError(f"no synthetic generator for {dtype}")
+    # The formats beyond the four of the benchmark configurations: random valid blocks laid out as the reference's
+    # #[repr(C)] structs (k_quants.rs:100-186): f16 scales from |N(0,1)| * dscale, every code / scale / mask bit uniform.
+    f16s = lambda: _f16_bytes(np.abs(g.standard_normal((rows, nb), np.float32)) * np.float32(dscale))   # noqa: E731
+    rnd = lambda n: g.integers(0, 256, (rows, nb, n), np.uint8)                                          # noqa: E731
+    out = np.empty((rows, nb, dtype.type_size), np.uint8)
+    if dtype == GgmlDType.Q4_1:     # {f16 d; f16 m; u8 qs[16]}
+        out[..., 0:2], out[..., 2:4], out[..., 4:20] = f16s(), _f16_bytes(g.standard_normal((rows, nb), np.float32) * np.float32(dscale * 4)), rnd(16)
+    elif dtype == GgmlDType.Q5_0:   # {f16 d; u8 qh[4]; u8 qs[16]}
+        out[..., 0:2], out[..., 2:6], out[..., 6:22] = f16s(), rnd(4), rnd(16)
+    elif dtype == GgmlDType.Q5_1:   # {f16 d; f16 m; u8 qh[4]; u8 qs[16]}
+        out[..., 0:2], out[..., 2:4] = f16s(), _f16_bytes(g.standard_normal((rows, nb), np.float32) * np.float32(dscale * 8))
+        out[..., 4:8], out[..., 8:24] = rnd(4), rnd(16)
+    elif dtype == GgmlDType.Q2K:    # {u8 scales[16]; u8 qs[64]; f16 d; f16 dmin}
+        out[..., 0:16], out[..., 16:80], out[..., 80:82], out[..., 82:84] = rnd(16), rnd(64), f16s(), f16s()
+    elif dtype == GgmlDType.Q3K:    # {u8 hmask[32]; u8 qs[64]; u8 scales[12]; f16 d}
+        out[..., 0:32], out[..., 32:96], out[..., 96:108], out[..., 108:110] = rnd(32), rnd(64), rnd(12), f16s()
+    elif dtype == GgmlDType.Q5K:    # {f16 d; f16 dmin; u8 scales[12]; u8 qh[32]; u8 qs[128]}
+        out[..., 0:2], out[..., 2:4], out[..., 4:16], out[..., 16:48], out[..., 48:176] = f16s(), f16s(), rnd(12), rnd(32), rnd(128)
+    else:
+        raise ValueError(f"no synthetic generator for {dtype}")
+    return out
 
 
 def make_weight(dtype: GgmlDType, n: int, k: int, seed: int = 0, tensor_id: int = 0,
