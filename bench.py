@@ -393,7 +393,7 @@ def measure_matmul(ctx, args, name, dt, n, k, m, with_cpu=True):
     for w in weights:
         w.workspace(m)
 
-    hint = m == 1   # a caller that loops over known weights names the next one: the kernel asks it into L2 as it finishes
+    hint = m == 1 and not args.no_hint   # a caller that loops over known weights names the next one: the kernel asks it into L2 as it finishes
 
     def local_step():
         for i, w in enumerate(weights):
@@ -758,6 +758,8 @@ def main():
     ap.add_argument("--option", action="append", default=[], help="library switch NAME=INT (A/B measurements), e.g. matvec_tma=0")
     ap.add_argument("--no-extra", action="store_true", help="headline workload only: skip the list of the other BASELINE configurations")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg (profiling runs)")
+    ap.add_argument("--no-hint", action="store_true", help="one-row workloads: do not name the next weight (xnq_hint_next_weight); a profiler that flushes the "
+                    "caches between kernels would count the hinted prefetch as traffic of the launch")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.workload in DECODER_WORKLOADS:

@@ -283,6 +283,14 @@ int xnq_attn_decode(const float *q, const void *k_cache, const void *v_cache, co
                     int64_t batch, int heads, int kv_heads, int head_dim, int64_t max_seq, void *workspace,
                     size_t ws_bytes, void *stream);
 
+/* xnq_rope_kv_store and xnq_attn_decode in one launch: every CTA rotates its own head's q from `qkv`
+ * ([batch, (heads + 2 kv_heads) * head_dim] f32, the fused q/k/v projection), the CTAs whose run of positions holds *pos_dev
+ * rotate that position's k (and take its v) from `qkv` instead of the cache, and the first query head of every KV head stores
+ * them into the caches. Bit for bit the result of the two separate calls; the q_out buffer is not needed. */
+int xnq_rope_attn_decode(const float *qkv, const float *cos_table, const float *sin_table, const long long *pos_dev, void *k_cache,
+                         void *v_cache, float *out, int64_t batch, int heads, int kv_heads, int head_dim, int64_t max_seq,
+                         void *workspace, size_t ws_bytes, void *stream);
+
 /* Sticky device-side status bits of this library's kernels on the current device (0 = healthy).
  * Bits 0-7, one-row ring kernel: bit 0 a consumer's bounded mbarrier wait expired, bit 1 a producer's, bit 2 a
  * self-check refused an access. Bits 8-15: the same for the fp16 tensor-core kernel. Bits 16-23, integer

@@ -82,6 +82,28 @@ def test_rope_store_and_attention(B, H, KV):
         torch.testing.assert_close(out, torch.einsum("bhs,bhsd->bhd", w, vv), rtol=2e-4, atol=2e-5)
 
 
+@pytest.mark.parametrize("B,H,KV", [(1, 32, 8), (3, 8, 2), (2, 4, 4)])
+def test_rope_inside_the_attention_kernel_is_bit_identical(B, H, KV):
+    """xnq_rope_attn_decode == xnq_rope_kv_store followed by xnq_attn_decode: outputs and both caches, over several steps."""
+    from xn_b200 import decoder_ops as ops
+    torch.manual_seed(9)
+    hd, max_seq = 128, 160
+    inv = 1.0 / (10000.0 ** (torch.arange(0, hd, 2, device=DEV, dtype=torch.float32) / hd))
+    ang = torch.arange(max_seq, device=DEV, dtype=torch.float32)[:, None] * inv[None]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    kc = torch.randn(B, KV, max_seq, hd, device=DEV).to(torch.bfloat16); vc = torch.randn(B, KV, max_seq, hd, device=DEV).to(torch.bfloat16)
+    kc2, vc2 = kc.clone(), vc.clone()
+    for pos_i in [0, 1, 31, 32, 33, 95, 96, 150, 159]:   # first position, run boundaries, the last one
+        pos = torch.tensor([pos_i], device=DEV, dtype=torch.int64)
+        qkv = torch.randn(B, (H + 2 * KV) * hd, device=DEV)
+        q = torch.empty(B, H, hd, device=DEV); want = torch.empty(B, H, hd, device=DEV); got = torch.full_like(want, float("nan"))
+        ops.rope_kv_store(qkv, cos, sin, pos, q, kc, vc, H, KV)
+        ops.attn_decode(q, kc, vc, pos, want, H, KV)
+        ops.rope_attn_decode(qkv, cos, sin, pos, kc2, vc2, got, H, KV)
+        assert torch.equal(got, want), (pos_i, float((got - want).abs().max()))
+        assert torch.equal(kc2, kc) and torch.equal(vc2, vc), pos_i
+
+
 def test_attention_workspace_reuse_and_position_range():
     """One workspace serves calls of different (batch, heads): the arrival counters sit at offsets that depend on the
     (sequence, head) index alone. A position outside the cache is reported through the status word, never NaN."""

@@ -77,6 +77,7 @@ def lib() -> ctypes.CDLL:
     L.xnq_attn_decode_workspace_bytes.argtypes = [i64, ci]
     L.xnq_attn_decode_workspace_bytes.restype = sz
     L.xnq_attn_decode.argtypes = [vp, vp, vp, vp, vp, i64, ci, ci, ci, i64, vp, sz, vp]
+    L.xnq_rope_attn_decode.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, ci, ci, ci, i64, vp, sz, vp]
     L.xnq_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint)]
     L.xnq_device_check_record.argtypes = [ctypes.POINTER(ctypes.c_ulonglong)]
     L.xnq_set_option.argtypes = [ctypes.c_char_p, ci]

@@ -178,6 +178,11 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const float *gu, float *out
 
 __device__ unsigned int g_decoder_status; // sticky: 1 rope/store, 2 attention saw a position outside [0, max_seq)
 
+// Rotate-half RoPE of the pair (x1 = element i, x2 = element i + hd / 2) with every operation rounded separately, so that the
+// stand-alone kernel and the attention kernel that rotates in its prologue produce the same bits.
+__device__ __forceinline__ float rope_lo(float x1, float x2, float c, float s) { return __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s)); }
+__device__ __forceinline__ float rope_hi(float x1, float x2, float c, float s) { return __fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s)); }
+
 // One token per sequence. qkv [B, (H + 2 KV) * hd] f32 -> q_out [B, H, hd] f32 (rotated), and the rotated k
 // and plain v of every KV head go to the caches [B, KV, max_seq, hd] (bf16) at position *pos.
 // grid (H + 2 KV, B), block hd / 2.
@@ -195,7 +200,7 @@ __global__ void rope_store_kernel(const float *qkv, const float *cos_t, const fl
   const float x1 = src[i], x2 = src[i + half];
   if (head < H + KV) {
     const float c = cos_t[pos * half + i], s = sin_t[pos * half + i];
-    const float r1 = x1 * c - x2 * s, r2 = x2 * c + x1 * s;
+    const float r1 = rope_lo(x1, x2, c, s), r2 = rope_hi(x1, x2, c, s);
     if (head < H) {
       float *q = q_out + ((int64_t)b * H + head) * hd;
       q[i] = r1, q[i + half] = r2;
@@ -233,9 +238,13 @@ __device__ __forceinline__ void online_merge(float &m, float &l, float4 &acc, fl
   m = mn;
 }
 
-__global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const float *q, const __nv_bfloat16 *k_cache, const __nv_bfloat16 *v_cache,
-                                                                      const long long *pos_p, float *out, float *part, int H, int KV, int max_seq,
-                                                                      float scale) {
+// ROPE: q is the projection output qkv [B, (H + 2 KV) * hd]; the CTA rotates its own head's q, and the CTAs whose run of positions holds the
+// current one rotate that position's k (and take its v) from qkv instead of reading the cache; the first query head of every KV head also
+// stores them into the caches for the steps to come. Same bits as rope_store_kernel followed by the plain kernel, one launch less.
+template <bool ROPE>
+__global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const float *q, __nv_bfloat16 *k_cache, __nv_bfloat16 *v_cache, const long long *pos_p,
+                                                                      float *out, float *part, int H, int KV, int max_seq, float scale, const float *cos_t,
+                                                                      const float *sin_t) {
   __shared__ __align__(16) float s_q[ATT_WARPS][ATT_HD]; // every warp keeps its own copy: no block-wide barrier before the loads
   __shared__ float s_m[ATT_WARPS], s_l[ATT_WARPS];
   __shared__ __align__(16) float s_acc[ATT_WARPS][ATT_HD];
@@ -249,7 +258,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const float
   const long long pos = *pos_p;
   int last = (int)pos;
   if (pos < 0 || pos >= max_seq) {
-    if (head == 0 && b == 0 && split == 0 && threadIdx.x == 0) atomicOr(&g_decoder_status, 2u);
+    if (head == 0 && b == 0 && split == 0 && threadIdx.x == 0) atomicOr(&g_decoder_status, ROPE ? 3u : 2u);
     if (pos < 0) { // nothing to attend to: zeros, not 0 / 0
       if (split == 0 && threadIdx.x < ATT_HD) out[((int64_t)b * H + head) * ATT_HD + threadIdx.x] = 0.f;
       return;
@@ -258,9 +267,23 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const float
   }
   const int npos = last + 1, per = (npos + nsplit - 1) / nsplit;
   const int c0 = split * per, c1 = min(npos, c0 + per);
-  const float4 qreg = *reinterpret_cast<const float4 *>(q + ((int64_t)b * H + head) * ATT_HD + lane * 4); // in flight together with the first k and v loads
+  const int fresh = ROPE && pos == last ? last : -1; // the position whose k and v are still in qkv
+  const float *qsrc = ROPE ? q + ((int64_t)b * (H + 2 * KV) + head) * ATT_HD : q + ((int64_t)b * H + head) * ATT_HD;
+  float4 qreg = *reinterpret_cast<const float4 *>(qsrc + lane * 4); // in flight together with the first k and v loads
+  if (ROPE) { // lanes 0..15 hold elements i < 64, lanes 16..31 their partners i + 64
+    const float4 cs = *reinterpret_cast<const float4 *>(cos_t + (int64_t)last * (ATT_HD / 2) + (lane & 15) * 4);
+    const float4 sn = *reinterpret_cast<const float4 *>(sin_t + (int64_t)last * (ATT_HD / 2) + (lane & 15) * 4);
+    float4 o;
+    o.x = __shfl_xor_sync(0xffffffffu, qreg.x, 16), o.y = __shfl_xor_sync(0xffffffffu, qreg.y, 16);
+    o.z = __shfl_xor_sync(0xffffffffu, qreg.z, 16), o.w = __shfl_xor_sync(0xffffffffu, qreg.w, 16);
+    if (pos == last) { // a position past the cache rotates nothing, as the stand-alone kernel stores nothing
+      if (lane < 16) qreg = make_float4(rope_lo(qreg.x, o.x, cs.x, sn.x), rope_lo(qreg.y, o.y, cs.y, sn.y), rope_lo(qreg.z, o.z, cs.z, sn.z), rope_lo(qreg.w, o.w, cs.w, sn.w));
+      else qreg = make_float4(rope_hi(o.x, qreg.x, cs.x, sn.x), rope_hi(o.y, qreg.y, cs.y, sn.y), rope_hi(o.z, qreg.z, cs.z, sn.z), rope_hi(o.w, qreg.w, cs.w, sn.w));
+    }
+  }
+  const bool writer = ROPE && head % (H / KV) == 0; // one query head per KV head stores the new k and v
   bool q_stored = false;
-  const __nv_bfloat16 *kb = k_cache + ((int64_t)b * KV + kvh) * max_seq * ATT_HD, *vb = v_cache + ((int64_t)b * KV + kvh) * max_seq * ATT_HD;
+  __nv_bfloat16 *kb = k_cache + ((int64_t)b * KV + kvh) * max_seq * ATT_HD, *vb = v_cache + ((int64_t)b * KV + kvh) * max_seq * ATT_HD;
   float m = -INFINITY, l = 0.f;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int base = c0 + warp * 32; base < c1; base += ATT_WARPS * 32) {
@@ -275,13 +298,39 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const float
     for (int i = 0; i < 16; i++) {
       const int idx = i * 32 + lane, row = idx >> 4, ch = idx & 15;
       kv[i] = make_uint4(0, 0, 0, 0);
-      if (row < cnt) kv[i] = *reinterpret_cast<const uint4 *>(kb + (int64_t)(base + row) * ATT_HD + ch * 8);
+      if (ROPE && base + row == fresh) { // elements 8 ch .. 8 ch + 7 of the new k row, rotated and rounded to the cache's bf16
+        const float *ksrc = q + ((int64_t)b * (H + 2 * KV) + H + kvh) * ATT_HD;
+        const int d0 = (ch & 7) * 8;
+        float x1[8], x2[8], c[8], sn[8];
+        load8(ksrc + d0, x1);
+        load8(ksrc + d0 + ATT_HD / 2, x2);
+        load8(cos_t + (int64_t)last * (ATT_HD / 2) + d0, c);
+        load8(sin_t + (int64_t)last * (ATT_HD / 2) + d0, sn);
+        __nv_bfloat162 r[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          const float a = ch < 8 ? rope_lo(x1[2 * e], x2[2 * e], c[2 * e], sn[2 * e]) : rope_hi(x1[2 * e], x2[2 * e], c[2 * e], sn[2 * e]);
+          const float bb = ch < 8 ? rope_lo(x1[2 * e + 1], x2[2 * e + 1], c[2 * e + 1], sn[2 * e + 1]) : rope_hi(x1[2 * e + 1], x2[2 * e + 1], c[2 * e + 1], sn[2 * e + 1]);
+          r[e] = __halves2bfloat162(__float2bfloat16_rn(a), __float2bfloat16_rn(bb));
+        }
+        kv[i] = *reinterpret_cast<const uint4 *>(r);
+        if (writer) *reinterpret_cast<uint4 *>(kb + (int64_t)fresh * ATT_HD + ch * 8) = kv[i];
+      } else if (row < cnt) {
+        kv[i] = *reinterpret_cast<const uint4 *>(kb + (int64_t)(base + row) * ATT_HD + ch * 8);
+      }
     }
     uint2 vr[32];
 #pragma unroll
     for (int j = 0; j < 32; j++) {
       vr[j] = make_uint2(0, 0);
-      if (j < cnt) vr[j] = *reinterpret_cast<const uint2 *>(vb + (int64_t)(base + j) * ATT_HD + lane * 4);
+      if (ROPE && base + j == fresh) {
+        const float4 vv = *reinterpret_cast<const float4 *>(q + ((int64_t)b * (H + 2 * KV) + H + KV + kvh) * ATT_HD + lane * 4);
+        __nv_bfloat162 r[2] = {__halves2bfloat162(__float2bfloat16_rn(vv.x), __float2bfloat16_rn(vv.y)), __halves2bfloat162(__float2bfloat16_rn(vv.z), __float2bfloat16_rn(vv.w))};
+        vr[j] = *reinterpret_cast<const uint2 *>(r);
+        if (writer) *reinterpret_cast<uint2 *>(vb + (int64_t)fresh * ATT_HD + lane * 4) = vr[j];
+      } else if (j < cnt) {
+        vr[j] = *reinterpret_cast<const uint2 *>(vb + (int64_t)(base + j) * ATT_HD + lane * 4);
+      }
     }
     // the k rows are turned through shared memory, so that each lane can then read ITS row: a lane reading its own
     // row straight from global memory makes every load instruction touch 32 different lines
@@ -437,9 +486,30 @@ int xnq_attn_decode(const float *q, const void *k_cache, const void *v_cache, co
   int splits = (int)(296 / (batch * heads));
   splits = splits < 1 ? 1 : (splits > ATT_MAX_SPLITS ? ATT_MAX_SPLITS : splits);
   float *part = static_cast<float *>(workspace);
-  XNQ_CUDA(launch_pdl(attn_decode_kernel, dim3(heads, (unsigned)batch, splits), dim3(ATT_WARPS * 32), 0, static_cast<cudaStream_t>(stream), q,
-                      static_cast<const __nv_bfloat16 *>(k_cache), static_cast<const __nv_bfloat16 *>(v_cache), pos_dev, out, part, heads, kv_heads, (int)max_seq,
-                      1.0f / sqrtf((float)head_dim)));
+  XNQ_CUDA(launch_pdl(attn_decode_kernel<false>, dim3(heads, (unsigned)batch, splits), dim3(ATT_WARPS * 32), 0, static_cast<cudaStream_t>(stream), q,
+                      static_cast<__nv_bfloat16 *>(const_cast<void *>(k_cache)), static_cast<__nv_bfloat16 *>(const_cast<void *>(v_cache)), pos_dev, out, part, heads,
+                      kv_heads, (int)max_seq, 1.0f / sqrtf((float)head_dim), static_cast<const float *>(nullptr), static_cast<const float *>(nullptr)));
+  count_launch();
+  return XNQ_OK;
+}
+
+int xnq_rope_attn_decode(const float *qkv, const float *cos_table, const float *sin_table, const long long *pos_dev, void *k_cache, void *v_cache, float *out,
+                         int64_t batch, int heads, int kv_heads, int head_dim, int64_t max_seq, void *workspace, size_t ws_bytes, void *stream) {
+  clear_error();
+  if (!qkv || !cos_table || !sin_table || !pos_dev || !k_cache || !v_cache || !out) return fail(XNQ_ERR_NULL, "rope_attn_decode: NULL argument");
+  if (head_dim != ATT_HD) return fail(XNQ_ERR_UNSUPPORTED, "rope_attn_decode: head_dim %d (this kernel is written for %d)", head_dim, ATT_HD);
+  if (batch < 0 || heads < 1 || kv_heads < 1 || heads % kv_heads || max_seq < 1)
+    return fail(XNQ_ERR_SHAPE, "rope_attn_decode: batch %lld heads %d kv_heads %d max_seq %lld", (long long)batch, heads, kv_heads, (long long)max_seq);
+  if (((uintptr_t)qkv | (uintptr_t)cos_table | (uintptr_t)sin_table | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out | (uintptr_t)workspace) & 15)
+    return fail(XNQ_ERR_ALIGN, "rope_attn_decode: pointers must be 16-byte aligned");
+  if (batch == 0) return XNQ_OK;
+  const size_t need = xnq_attn_decode_workspace_bytes(batch, heads);
+  if (!workspace || ws_bytes < need) return fail(XNQ_ERR_SIZE, "rope_attn_decode: workspace has %zu bytes, needs %zu (zero it once after allocating)", ws_bytes, need);
+  int splits = (int)(296 / (batch * heads));
+  splits = splits < 1 ? 1 : (splits > ATT_MAX_SPLITS ? ATT_MAX_SPLITS : splits);
+  XNQ_CUDA(launch_pdl(attn_decode_kernel<true>, dim3(heads, (unsigned)batch, splits), dim3(ATT_WARPS * 32), 0, static_cast<cudaStream_t>(stream), qkv,
+                      static_cast<__nv_bfloat16 *>(k_cache), static_cast<__nv_bfloat16 *>(v_cache), pos_dev, out, static_cast<float *>(workspace), heads, kv_heads,
+                      (int)max_seq, 1.0f / sqrtf((float)head_dim), cos_table, sin_table));
   count_launch();
   return XNQ_OK;
 }

@@ -103,16 +103,37 @@ def rope_kv_store(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos: 
 _attn_ws: dict[tuple[int, int], torch.Tensor] = {}   # (device, stream) -> workspace, grown on demand
 
 
+def _attn_workspace(device: torch.device, B: int, heads: int) -> torch.Tensor:
+    L = _lib.lib()
+    key = (device.index or 0, int(_stream_ptr(device).value or 0))   # calls on different streams may overlap: one workspace each
+    need = max(int(L.xnq_attn_decode_workspace_bytes(B, heads)), 16)
+    ws = _attn_ws.get(key)
+    if ws is None or ws.numel() < need:   # zeroed once; the kernel leaves its arrival counters at zero
+        ws = _attn_ws[key] = torch.zeros(need, dtype=torch.uint8, device=device)
+    return ws
+
+
+def rope_attn_decode(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                     out: torch.Tensor, heads: int, kv_heads: int) -> torch.Tensor:
+    """:func:`rope_kv_store` and :func:`attn_decode` in one launch (same bits): rotates q and the new k inside the attention
+    kernel, which also stores the new k and v into the caches. ``qkv`` is ``[B, (heads + 2 kv_heads) * hd]``."""
+    _f32c(qkv, cos, sin, out)
+    B, _, max_seq, hd = k_cache.shape
+    if k_cache.dtype is not torch.bfloat16 or not k_cache.is_contiguous() or not v_cache.is_contiguous() or pos.dtype is not torch.int64:
+        raise ValueError("rope_attn_decode: caches must be contiguous bf16 [B, kv_heads, max_seq, hd] and pos an int64 device scalar")
+    ws = _attn_workspace(qkv.device, B, heads)
+    with torch.cuda.device(qkv.device):
+        _lib.check(_lib.lib().xnq_rope_attn_decode(_p(qkv), _p(cos), _p(sin), _p(pos), _p(k_cache), _p(v_cache), _p(out), B, heads, kv_heads, hd, max_seq,
+                                                    _p(ws), ws.numel(), _stream_ptr(qkv.device)))
+    return out
+
+
 def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int) -> torch.Tensor:
     """Single-query attention over cache positions ``0..pos``; ``q`` and ``out`` are ``[B, heads, hd]``."""
     _f32c(q, out)
     B, _, max_seq, hd = k_cache.shape
     L = _lib.lib()
-    key = (q.device.index or 0, int(_stream_ptr(q.device).value or 0))   # calls on different streams may overlap: one workspace each
-    need = max(int(L.xnq_attn_decode_workspace_bytes(B, heads)), 16)
-    ws = _attn_ws.get(key)
-    if ws is None or ws.numel() < need:   # zeroed once; the kernel leaves its arrival counters at zero
-        ws = _attn_ws[key] = torch.zeros(need, dtype=torch.uint8, device=q.device)
+    ws = _attn_workspace(q.device, B, heads)
     with torch.cuda.device(q.device):
         _lib.check(L.xnq_attn_decode(_p(q), _p(k_cache), _p(v_cache), _p(pos), _p(out), B, heads, kv_heads, hd, max_seq, _p(ws), ws.numel(),
                                      _stream_ptr(q.device)))

@@ -81,7 +81,7 @@ class QLlama:
     KV cache of ``max_seq`` positions for ``batch`` sequences, prefill and CUDA-graphed decode."""
 
     def __init__(self, cfg: LlamaConfig, device: torch.device, batch: int = 1, max_seq: int = 1024, rank: int = 0, world: int = 1,
-                 group=None, seed: int = 0, max_prefill_rows: int = 512, fused_decode: bool = True, fused_norm: Optional[bool] = None):
+                 group=None, seed: int = 0, max_prefill_rows: int = 512, fused_decode: bool = True, fused_norm: Optional[bool] = None, fused_rope: bool = True):
         if cfg.n_kv_heads % world or cfg.n_heads % world or cfg.ffn % world or cfg.vocab % world or cfg.d_model % world:
             raise ValueError(f"config does not divide over {world} ranks")
         init(device)
@@ -96,6 +96,7 @@ class QLlama:
             env = os.environ.get("XN_FUSED_NORM")
             fused_norm = (env == "1") if env in ("0", "1") else world > 1
         self.fused_norm = fused_norm
+        self.fused_rope = fused_rope
         c, r, G, hd = cfg, rank, world, cfg.head_dim
 
         def rows(w, per):  # this rank's block of `per` consecutive rows
@@ -274,8 +275,11 @@ class QLlama:
             else:
                 ops.add_rmsnorm(cur, delta, L.norm1, c.rms_eps, None if xi else self._xn, xi)
                 L.wqkv.matmul_t(xi or self._xn, out=self._qkv)
-            ops.rope_kv_store(self._qkv, self.cos, self.sin, self.pos, self._q, L.k_cache, L.v_cache, self.hl, self.kvl)
-            ops.attn_decode(self._q, L.k_cache, L.v_cache, self.pos, self._a.view(self.batch, self.hl, c.head_dim), self.hl, self.kvl)
+            if self.fused_rope:   # RoPE and the KV-cache store inside the attention kernel: one launch less per layer, same bits
+                ops.rope_attn_decode(self._qkv, self.cos, self.sin, self.pos, L.k_cache, L.v_cache, self._a.view(self.batch, self.hl, c.head_dim), self.hl, self.kvl)
+            else:
+                ops.rope_kv_store(self._qkv, self.cos, self.sin, self.pos, self._q, L.k_cache, L.v_cache, self.hl, self.kvl)
+                ops.attn_decode(self._q, L.k_cache, L.v_cache, self.pos, self._a.view(self.batch, self.hl, c.head_dim), self.hl, self.kvl)
             hint(L.wgu)
             o = self._linear_parts(L.wo, self._a, self._o, defer=defer)           # world summands per row when sharded
             hint(L.wdown)
@@ -309,8 +313,11 @@ class QLlama:
             ops.add_rmsnorm(self._x, delta, L.norm1, c.rms_eps, None if xi else self._xn, xi)
             hint(L.wo)
             L.wqkv.matmul_t(xi or self._xn, out=self._qkv)
-            ops.rope_kv_store(self._qkv, self.cos, self.sin, self.pos, self._q, L.k_cache, L.v_cache, self.hl, self.kvl)
-            ops.attn_decode(self._q, L.k_cache, L.v_cache, self.pos, self._a.view(self.batch, self.hl, c.head_dim), self.hl, self.kvl)
+            if self.fused_rope:   # RoPE and the KV-cache store inside the attention kernel: one launch less per layer, same bits
+                ops.rope_attn_decode(self._qkv, self.cos, self.sin, self.pos, L.k_cache, L.v_cache, self._a.view(self.batch, self.hl, c.head_dim), self.hl, self.kvl)
+            else:
+                ops.rope_kv_store(self._qkv, self.cos, self.sin, self.pos, self._q, L.k_cache, L.v_cache, self.hl, self.kvl)
+                ops.attn_decode(self._q, L.k_cache, L.v_cache, self.pos, self._a.view(self.batch, self.hl, c.head_dim), self.hl, self.kvl)
             hint(L.wgu)
             o = self._linear_parts(L.wo, self._a, self._o)           # world summands per row when sharded
             ops.add_rmsnorm(self._x, o, L.norm2, c.rms_eps, None if xi else self._xn, xi)
