@@ -286,7 +286,10 @@ int xnq_attn_decode(const float *q, const void *k_cache, const void *v_cache, co
 /* xnq_rope_kv_store and xnq_attn_decode in one launch: every CTA rotates its own head's q from `qkv`
  * ([batch, (heads + 2 kv_heads) * head_dim] f32, the fused q/k/v projection), the CTAs whose run of positions holds *pos_dev
  * rotate that position's k (and take its v) from `qkv` instead of the cache, and the first query head of every KV head stores
- * them into the caches. Bit for bit the result of the two separate calls; the q_out buffer is not needed. */
+ * them into the caches. Bit for bit the result of the two separate calls; the q_out buffer is not needed.
+ * The kernel reads *pos_dev and requests the cache rows below it before it waits for the kernel that produces qkv, so both
+ * must be final when that producer STARTS: written in an earlier step, with at least one normally launched kernel or copy
+ * (one that is not programmatically dependent, e.g. the step's sampling) in between. A decode loop satisfies this by itself. */
 int xnq_rope_attn_decode(const float *qkv, const float *cos_table, const float *sin_table, const long long *pos_dev, void *k_cache,
                          void *v_cache, float *out, int64_t batch, int heads, int kv_heads, int head_dim, int64_t max_seq,
                          void *workspace, size_t ws_bytes, void *stream);

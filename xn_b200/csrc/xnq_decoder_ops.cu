@@ -61,19 +61,23 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(float *x, const float 
   constexpr int MAXP = 128; // 256-element partial sums kept apart (rows of up to 32768 values; beyond that they wrap around)
   __shared__ float part[MAXP];
   pdl_launch_dependents();
-  pdl_wait(); // x and delta are earlier kernels' outputs
   const int64_t row = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // The norm weights never change, and in a decode step they come from DRAM (the step's 4 GB of linear weights have been
+  // through L2 since their last use): they are requested before the wait for the kernel that produces x and delta.
+  constexpr int KEEP = 2;
+  float kv[KEEP][8], kg[KEEP][8];
+#pragma unroll
+  for (int p = 0; p < KEEP; p++)
+    if (p * 2048 + threadIdx.x * 8 < d) load8(w + p * 2048 + threadIdx.x * 8, kg[p]);
+  pdl_wait(); // x and delta are earlier kernels' outputs
   float *xr = x + row * d;
   const float *dr = delta ? delta + row * parts * d : nullptr;
   const int np = (d + 255) / 256;
   for (int i = threadIdx.x; i < min(np, MAXP); i += 256) part[i] = 0.f;
   __syncthreads();
   // The first KEEP passes of 2048 values (rows of up to 4096 values entirely) stay in registers between the
-  // sum of squares and the scaling, and their norm weights are requested before the block-wide reduction: one
-  // trip to memory instead of three. Longer rows re-read the rest.
-  constexpr int KEEP = 2;
-  float kv[KEEP][8], kg[KEEP][8];
+  // sum of squares and the scaling: one trip to memory instead of three. Longer rows re-read the rest.
   // adds the summands, stores the new residual, returns the sum of squares of the thread's run of 8
   auto first_pass = [&](int i, float (&v)[8]) {
     load8(xr + i, v);
@@ -100,10 +104,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(float *x, const float 
   for (int p = 0; p < KEEP; p++) {
     const int i = p * 2048 + threadIdx.x * 8;
     float run = 0.f;
-    if (i < d) {
-      load8(w + i, kg[p]);
-      run = first_pass(i, kv[p]);
-    }
+    if (i < d) run = first_pass(i, kv[p]);
     pass_sum(p, run);
   }
   for (int p = KEEP; p * 2048 < d; p++) {
@@ -254,10 +255,18 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const float
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kvh = head / (H / KV);
   pdl_launch_dependents();
-  pdl_wait(); // q, the caches and the position are earlier kernels' outputs
+  // Plain form: q, the cache row of the current position and possibly the position itself are the previous kernels' outputs.
+  // ROPE form: only qkv is. The position was advanced at the end of the previous decode step and the cache rows below it were
+  // stored in earlier steps, both behind kernels launched without programmatic overlap (sampling, the embedding gather), which
+  // complete before anything of this step starts; so the position is read and the first run of k and v rows is requested BEFORE
+  // griddepcontrol.wait, under the projection kernel that is still producing qkv: the cache's trip to DRAM leaves the critical path.
+  bool waited = !ROPE;
+  if (!ROPE) pdl_wait();
   const long long pos = *pos_p;
   int last = (int)pos;
   if (pos < 0 || pos >= max_seq) {
+    if (!waited) pdl_wait();
+    waited = true;
     if (head == 0 && b == 0 && split == 0 && threadIdx.x == 0) atomicOr(&g_decoder_status, ROPE ? 3u : 2u);
     if (pos < 0) { // nothing to attend to: zeros, not 0 / 0
       if (split == 0 && threadIdx.x < ATT_HD) out[((int64_t)b * H + head) * ATT_HD + threadIdx.x] = 0.f;
@@ -269,10 +278,15 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const float
   const int c0 = split * per, c1 = min(npos, c0 + per);
   const int fresh = ROPE && pos == last ? last : -1; // the position whose k and v are still in qkv
   const float *qsrc = ROPE ? q + ((int64_t)b * (H + 2 * KV) + head) * ATT_HD : q + ((int64_t)b * H + head) * ATT_HD;
-  float4 qreg = *reinterpret_cast<const float4 *>(qsrc + lane * 4); // in flight together with the first k and v loads
-  if (ROPE) { // lanes 0..15 hold elements i < 64, lanes 16..31 their partners i + 64
-    const float4 cs = *reinterpret_cast<const float4 *>(cos_t + (int64_t)last * (ATT_HD / 2) + (lane & 15) * 4);
-    const float4 sn = *reinterpret_cast<const float4 *>(sin_t + (int64_t)last * (ATT_HD / 2) + (lane & 15) * 4);
+  float4 qreg = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (!ROPE) qreg = *reinterpret_cast<const float4 *>(qsrc + lane * 4); // in flight together with the first k and v loads
+  float4 cs = make_float4(1.f, 1.f, 1.f, 1.f), sn = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (ROPE) { // the tables never change
+    cs = *reinterpret_cast<const float4 *>(cos_t + (int64_t)last * (ATT_HD / 2) + (lane & 15) * 4);
+    sn = *reinterpret_cast<const float4 *>(sin_t + (int64_t)last * (ATT_HD / 2) + (lane & 15) * 4);
+  }
+  auto load_rotate_q = [&]() { // lanes 0..15 hold elements i < 64, lanes 16..31 their partners i + 64
+    qreg = *reinterpret_cast<const float4 *>(qsrc + lane * 4);
     float4 o;
     o.x = __shfl_xor_sync(0xffffffffu, qreg.x, 16), o.y = __shfl_xor_sync(0xffffffffu, qreg.y, 16);
     o.z = __shfl_xor_sync(0xffffffffu, qreg.z, 16), o.w = __shfl_xor_sync(0xffffffffu, qreg.w, 16);
@@ -280,7 +294,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const float
       if (lane < 16) qreg = make_float4(rope_lo(qreg.x, o.x, cs.x, sn.x), rope_lo(qreg.y, o.y, cs.y, sn.y), rope_lo(qreg.z, o.z, cs.z, sn.z), rope_lo(qreg.w, o.w, cs.w, sn.w));
       else qreg = make_float4(rope_hi(o.x, qreg.x, cs.x, sn.x), rope_hi(o.y, qreg.y, cs.y, sn.y), rope_hi(o.z, qreg.z, cs.z, sn.z), rope_hi(o.w, qreg.w, cs.w, sn.w));
     }
-  }
+  };
   const bool writer = ROPE && head % (H / KV) == 0; // one query head per KV head stores the new k and v
   bool q_stored = false;
   __nv_bfloat16 *kb = k_cache + ((int64_t)b * KV + kvh) * max_seq * ATT_HD, *vb = v_cache + ((int64_t)b * KV + kvh) * max_seq * ATT_HD;
@@ -298,39 +312,49 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const float
     for (int i = 0; i < 16; i++) {
       const int idx = i * 32 + lane, row = idx >> 4, ch = idx & 15;
       kv[i] = make_uint4(0, 0, 0, 0);
-      if (ROPE && base + row == fresh) { // elements 8 ch .. 8 ch + 7 of the new k row, rotated and rounded to the cache's bf16
-        const float *ksrc = q + ((int64_t)b * (H + 2 * KV) + H + kvh) * ATT_HD;
-        const int d0 = (ch & 7) * 8;
-        float x1[8], x2[8], c[8], sn[8];
-        load8(ksrc + d0, x1);
-        load8(ksrc + d0 + ATT_HD / 2, x2);
-        load8(cos_t + (int64_t)last * (ATT_HD / 2) + d0, c);
-        load8(sin_t + (int64_t)last * (ATT_HD / 2) + d0, sn);
-        __nv_bfloat162 r[4];
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-          const float a = ch < 8 ? rope_lo(x1[2 * e], x2[2 * e], c[2 * e], sn[2 * e]) : rope_hi(x1[2 * e], x2[2 * e], c[2 * e], sn[2 * e]);
-          const float bb = ch < 8 ? rope_lo(x1[2 * e + 1], x2[2 * e + 1], c[2 * e + 1], sn[2 * e + 1]) : rope_hi(x1[2 * e + 1], x2[2 * e + 1], c[2 * e + 1], sn[2 * e + 1]);
-          r[e] = __halves2bfloat162(__float2bfloat16_rn(a), __float2bfloat16_rn(bb));
-        }
-        kv[i] = *reinterpret_cast<const uint4 *>(r);
-        if (writer) *reinterpret_cast<uint4 *>(kb + (int64_t)fresh * ATT_HD + ch * 8) = kv[i];
-      } else if (row < cnt) {
-        kv[i] = *reinterpret_cast<const uint4 *>(kb + (int64_t)(base + row) * ATT_HD + ch * 8);
-      }
+      if (row < cnt && base + row != fresh) kv[i] = *reinterpret_cast<const uint4 *>(kb + (int64_t)(base + row) * ATT_HD + ch * 8);
     }
     uint2 vr[32];
 #pragma unroll
     for (int j = 0; j < 32; j++) {
       vr[j] = make_uint2(0, 0);
-      if (ROPE && base + j == fresh) {
-        const float4 vv = *reinterpret_cast<const float4 *>(q + ((int64_t)b * (H + 2 * KV) + H + KV + kvh) * ATT_HD + lane * 4);
-        __nv_bfloat162 r[2] = {__halves2bfloat162(__float2bfloat16_rn(vv.x), __float2bfloat16_rn(vv.y)), __halves2bfloat162(__float2bfloat16_rn(vv.z), __float2bfloat16_rn(vv.w))};
-        vr[j] = *reinterpret_cast<const uint2 *>(r);
-        if (writer) *reinterpret_cast<uint2 *>(vb + (int64_t)fresh * ATT_HD + lane * 4) = vr[j];
-      } else if (j < cnt) {
-        vr[j] = *reinterpret_cast<const uint2 *>(vb + (int64_t)(base + j) * ATT_HD + lane * 4);
+      if (j < cnt && base + j != fresh) vr[j] = *reinterpret_cast<const uint2 *>(vb + (int64_t)(base + j) * ATT_HD + lane * 4);
+    }
+    if (!waited) { // ROPE form: from here on qkv is read
+      pdl_wait();
+      waited = true;
+    }
+    if (ROPE && !q_stored) load_rotate_q();
+    if (ROPE && fresh >= base && fresh < base + cnt) { // the new row: rotated k and plain v from qkv, rounded to the cache's bf16
+#pragma unroll
+      for (int i = 0; i < 16; i++) {
+        const int idx = i * 32 + lane, row = idx >> 4, ch = idx & 15;
+        if (base + row == fresh) { // elements 8 ch .. 8 ch + 7 of the row
+          const float *ksrc = q + ((int64_t)b * (H + 2 * KV) + H + kvh) * ATT_HD;
+          const int d0 = (ch & 7) * 8;
+          float x1[8], x2[8], c[8], sn8[8];
+          load8(ksrc + d0, x1);
+          load8(ksrc + d0 + ATT_HD / 2, x2);
+          load8(cos_t + (int64_t)last * (ATT_HD / 2) + d0, c);
+          load8(sin_t + (int64_t)last * (ATT_HD / 2) + d0, sn8);
+          __nv_bfloat162 r[4];
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            const float a = ch < 8 ? rope_lo(x1[2 * e], x2[2 * e], c[2 * e], sn8[2 * e]) : rope_hi(x1[2 * e], x2[2 * e], c[2 * e], sn8[2 * e]);
+            const float bb = ch < 8 ? rope_lo(x1[2 * e + 1], x2[2 * e + 1], c[2 * e + 1], sn8[2 * e + 1]) : rope_hi(x1[2 * e + 1], x2[2 * e + 1], c[2 * e + 1], sn8[2 * e + 1]);
+            r[e] = __halves2bfloat162(__float2bfloat16_rn(a), __float2bfloat16_rn(bb));
+          }
+          kv[i] = *reinterpret_cast<const uint4 *>(r);
+          if (writer) *reinterpret_cast<uint4 *>(kb + (int64_t)fresh * ATT_HD + ch * 8) = kv[i];
+        }
       }
+      const float4 vv = *reinterpret_cast<const float4 *>(q + ((int64_t)b * (H + 2 * KV) + H + KV + kvh) * ATT_HD + lane * 4);
+      __nv_bfloat162 r2[2] = {__halves2bfloat162(__float2bfloat16_rn(vv.x), __float2bfloat16_rn(vv.y)), __halves2bfloat162(__float2bfloat16_rn(vv.z), __float2bfloat16_rn(vv.w))};
+      const uint2 vnew = *reinterpret_cast<const uint2 *>(r2);
+#pragma unroll
+      for (int j = 0; j < 32; j++)
+        if (base + j == fresh) vr[j] = vnew;
+      if (writer) *reinterpret_cast<uint2 *>(vb + (int64_t)fresh * ATT_HD + lane * 4) = vnew;
     }
     // the k rows are turned through shared memory, so that each lane can then read ITS row: a lane reading its own
     // row straight from global memory makes every load instruction touch 32 different lines
@@ -369,6 +393,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const float
     }
     m = mn;
   }
+  if (!waited) pdl_wait(); // warps without a run of their own: the grid must not complete before its predecessor
   if (lane == 0) s_m[warp] = m, s_l[warp] = l;
   *reinterpret_cast<float4 *>(&s_acc[warp][lane * 4]) = acc;
   __syncthreads();
