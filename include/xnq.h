@@ -308,7 +308,10 @@ int xnq_device_status(unsigned int *bits);
 int xnq_device_check_record(unsigned long long out[8]);
 /* Tuning switches, for A/B measurements: "matvec_tma" (default 1) selects the persistent bulk-copy ring
  * decode kernel for m == 1; 0 forces the plain streaming-load kernel. "matvec_mma" (default 1)
- * selects the integer-MMA kernel for batches of 5..16 rows on Q4_K weights, 0 the dp4a kernel. "gather_cta_fence"
+ * selects the integer-MMA kernel for batches of 5..16 rows on Q4_K weights, 0 the dp4a kernel. "imma" (default 1):
+ * batches of 2..64 rows on Q4_0 / Q8_0 / Q4_K weights take the tcgen05 integer kernel; 0 sends them to the older
+ * kernels. "imma_fold" (default 1): the Q4_K variant of that kernel which folds the sub-block scales into the weight
+ * operand is used where it is faster (17..32 rows); 0 never, 2 for every batch of 2..64 rows. "gather_cta_fence"
  * (default 1): scope of the per-CTA fence before the arrival count of a kernel-side gather, 1 = gpu,
  * 0 = system. No counterpart in the reference. */
 int xnq_set_option(const char *name, int value);

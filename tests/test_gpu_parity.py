@@ -160,7 +160,8 @@ def test_three_d_input_and_bias(Q, O):
     assert host.shape == (2, 3, n)
     assert_close_ref(host.reshape(6, n), want, TOL_F32)
     # a page-locked result array is written by the kernel itself (no bias, m <= 16); a pageable one is copied into
-    for dt2, n2, k2, m2 in [(D.Q4K, 200, 512, 1), (D.Q6K, 96, 256, 5), (D.Q8_0, 64, 8192, 2), (D.Q4_0, 33, 64, 16)]:
+    # (the Q4_K rows of 11008 values at 16 rows are the shape whose kernel once accumulated into y with atomics: it must not be handed mapped host memory)
+    for dt2, n2, k2, m2 in [(D.Q4K, 200, 512, 1), (D.Q6K, 96, 256, 5), (D.Q8_0, 64, 8192, 2), (D.Q4_0, 33, 64, 16), (D.Q4K, 64, 11008, 16), (D.Q5K, 40, 512, 3)]:
         w2 = synth.make_weight(dt2, n2, k2, seed=82)
         x2 = synth.make_activation(m2, k2, seed=83)
         t2 = _upload(Q, dt2, w2, n2, k2)
@@ -307,6 +308,34 @@ def test_tma_ring_decode_kernel_matches_oracle_and_plain_kernel(Q, O, dt, n, k):
         got_h = t.matmul_t(xh.to(DEV)).float().cpu().numpy()
         err = np.abs(got_h - want_h) / np.maximum(np.abs(want_h), 1.0)
         assert err.max() <= (2e-3 if td == torch.float16 else 1e-2)
+
+
+@pytest.mark.parametrize("m", [2, 8, 16, 17, 32, 33, 48, 64])
+@pytest.mark.parametrize("n,k", [(128, 256), (200, 1024), (1000, 4096), (300, 11008)])
+def test_q4k_small_batch_folded_scales_match_oracle_and_per_block_kernel(Q, O, m, n, k):
+    """Q4_K small batches run with the sub-block scales folded into the weight operand (two unsigned planes,
+    one drain per 256 block; option 2 forces it for every batch size, the default takes it for 17..32 rows)
+    or, with the option 0, with one accumulator slice per 32 elements. Both are
+    exact integer sums followed by the same f32 scaling, so both must meet the reference's bound against the
+    oracle, and each other up to f32 summation order."""
+    from xn_b200 import _lib
+    L = _lib.lib()
+    dt = D.Q4K
+    w = synth.make_weight(dt, n, k, seed=7 + m)
+    t = _upload(Q, dt, w, n, k)
+    x = _tricky(m, k, 50 + m)
+    xd = torch.from_numpy(x).to(DEV)
+    want = O.matmul(int(dt), x, w, n)
+    try:
+        _lib.check(L.xnq_set_option(b"imma_fold", 2))
+        got_fold = t.matmul_t(xd).cpu().numpy()
+        _lib.check(L.xnq_set_option(b"imma_fold", 0))
+        got_blk = t.matmul_t(xd).cpu().numpy()
+    finally:
+        _lib.check(L.xnq_set_option(b"imma_fold", 1))
+    assert_close_ref(got_fold, want, TOL_F32, f"fold m={m} n={n} k={k}")
+    assert_close_ref(got_blk, want, TOL_F32, f"per-block m={m} n={n} k={k}")
+    assert_close_ref(got_fold, got_blk, 5e-4, "fold vs per-block")
 
 
 def test_zz_device_status_is_clean(Q):

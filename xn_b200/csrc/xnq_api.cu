@@ -257,6 +257,10 @@ int xnq_set_option(const char *name, int value) {
     g_opt_matvec_tma.store(value != 0);
     return XNQ_OK;
   }
+  if (std::strcmp(name, "imma_fold") == 0) {
+    imma_set_fold(value);
+    return XNQ_OK;
+  }
   if (std::strcmp(name, "imma") == 0) {
     g_opt_imma.store(value);
     return XNQ_OK;

@@ -325,6 +325,7 @@ size_t imma_workspace_bytes(int64_t m, int64_t k, int64_t n);
 int launch_imma(const WeightView &w, const void *x, int x_dtype, int64_t m, int64_t ldx, void *y, int y_dtype, int64_t ldy, void *workspace,
                 cudaStream_t s);
 int imma_init(int device);
+void imma_set_fold(int mode); // Q4_K kernel with the sub-block scales folded into the weight operand: 0 never, 1 where it is faster (17..32 rows), 2 always
 int imma_status(unsigned int *bits);
 int decoder_ops_init();
 int decoder_status(unsigned int *bits); // 1 rope/store, 2 attention: a position outside [0, max_seq)

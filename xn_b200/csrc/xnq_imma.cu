@@ -12,24 +12,25 @@
 // dp4a), f16 block scale times f16-rounded activation scale for Q4_0 / Q8_0. Nothing is rounded before the
 // f32 scaling, so results stay within the f32-accumulate bound (2e-3) at every batch size served.
 //
-// Roles of the 26 warps of a CTA (one CTA per SM, persistent):
+// Roles of the 27 warps of a CTA (one CTA per SM, persistent):
 //   producer (1)    one thread requests, per 256-k step, the 1-D bulk copies of the quantized activations (already in
 //                   the MMA's shared-memory layout) and of their per-block metadata into rings of stages guarded by
 //                   mbarriers; when the kernel starts it also asks for the CTA's share of the weight's bytes to be
 //                   brought into L2 in long contiguous runs.
-//   converters (8)  two groups of four warps, one thread per weight row; group h handles half h (128 k) of every
-//                   256-k step. Every warp fetches the code bytes of its own 32 rows itself, several steps ahead, with
+//   converters (8)  two groups of four warps, one thread per weight row; the groups take alternate 256-k steps, so a step's
+//                   chain of waits, loads, stores and fences has two steps' time to run in. Every warp fetches the code bytes of its own 32 rows itself, several steps ahead, with
 //                   16-byte cp.async copies into a ring of warp-private slots (consecutive lanes take consecutive
 //                   16 bytes of a row, so the requests are whole sectors; nothing but the warp's own
 //                   cp.async.wait_group and __syncwarp orders them), unpacks 4-bit codes to int8 (or copies int8
-//                   codes) into the 128-byte-swizzled K-major operand image the MMA reads; group 0 also hands the
-//                   rows' scale bytes on to the drain. (Tiled TMA boxes of 128 rows x 144..256 bytes were tried first:
+//                   codes) into the 128-byte-swizzled K-major operand image the MMA reads, and hands the rows' scale
+//                   bytes on to the drain. (Tiled TMA boxes of 128 rows x 144..256 bytes were tried first:
 //                   a box took 5000 to 7000 cycles to arrive, with or without the bytes in L2, about 17 cycles per box
 //                   row, which held the whole kernel at a third of the memory's rate. One bulk copy per row before
 //                   that: the copy engine takes some 60 ns per copy whatever its size.)
-//   MMA issuer (1)  one thread issues four K = 32 MMAs per half step into accumulator buffer h; an MMA of this
-//                   shape occupies the tensor pipe for about 114 cycles whatever N <= 128 is (measured), which
-//                   bounds a tile of k = 4096 at 128 x 114 cycles;
+//   MMA issuers (2) one thread per half step issues its four K = 32 MMAs into accumulator buffer h and commits them; an
+//                   MMA of this shape keeps its issuing thread busy for about 134 cycles whatever M (64 / 128) and
+//                   N <= 128 are, while two issuing threads reach twice the rate (measured), so the halves of a step
+//                   are issued by two warps;
 //   drain (16)      two groups of eight warps; group h owns accumulator buffer h: reads its slices back with
 //                   tcgen05.ld, scales, and keeps f32 sums in registers across the k steps of a tile; two warps
 //                   per accumulator lane quarter split the columns. At the end of a segment the odd half steps'
@@ -43,6 +44,7 @@
 // Every wait is bounded; on expiry a status bit is set and the roles fall through to the common exit, where
 // tensor memory is released.
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 
@@ -54,6 +56,9 @@ namespace xnq {
 __device__ unsigned int g_imma_status; // sticky: 1 producer, 2 converter, 4 mma, 8 drain wait expired
 #ifdef XNQ_DEV_TRACE
 __device__ long long g_imma_trace[32]; // development builds only: cycles block 0's roles spend in each wait
+__device__ long long g_cta_times[160 * 4]; // development builds only: per CTA of the last launch: entry, activation wait released, first step drained, exit (ns)
+#define XNQ_CT(slot) do { unsigned long long g_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_)); if (blockIdx.x < 160) g_cta_times[blockIdx.x * 4 + (slot)] = (long long)g_; } while (0)
+__device__ int g_dev_prep_trig;        // development builds only: where the activation kernel releases its dependents (0 entry, 1 after its wait, 2 exit)
 __device__ long long g_imma_tl[8 * 64];  // development builds only: block 0's per-unit time line (clock64), 8 points x 64 units
 #define XNQ_TL(pt, i) do { if (blockIdx.x == 0 && (i) < 64) g_imma_tl[(pt) * 64 + (i)] = clock64(); } while (0)
 #define XNQ_GT(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) { unsigned long long g_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_)); g_imma_trace[i] = (long long)g_; } } while (0)
@@ -62,6 +67,7 @@ __device__ long long g_imma_tl[8 * 64];  // development builds only: block 0's p
 #define XNQ_TDUMP(base, cond) do { if ((cond) && blockIdx.x == 0) for (int i_ = 0; i_ < 6; i_++) g_imma_trace[(base) + i_] = tacc[i_]; } while (0)
 #else
 #define XNQ_GT(i) do { } while (0)
+#define XNQ_CT(slot) do { } while (0)
 #define XNQ_TL(pt, i) do { } while (0)
 #define XNQ_TACC(i) do { } while (0)
 #define XNQ_TDECL do { } while (0)
@@ -73,10 +79,11 @@ namespace {
 constexpr int TILE_N = 128;         // weight rows per tile = UMMA M
 constexpr int MAX_NP = 64;          // activation rows per pass = UMMA N (multiple of 16)
 constexpr int CONV_WARPS = 8, DRAIN_WARPS = 16;
-constexpr int ACT_PRODUCER_WARP = 0, MMA_WARP = 1, CONV_WARP0 = 2, DRAIN_WARP0 = CONV_WARP0 + CONV_WARPS;
-constexpr int NTHREADS = (DRAIN_WARP0 + DRAIN_WARPS) * 32; // 832
+constexpr int ACT_PRODUCER_WARP = 0, MMA_WARP = 1, CONV_WARP0 = 3, DRAIN_WARP0 = CONV_WARP0 + CONV_WARPS; // MMA issuers: warps 1 and 2
+constexpr int NTHREADS = (DRAIN_WARP0 + DRAIN_WARPS) * 32; // 864
 constexpr int A_STAGE_BYTES = TILE_N * 128; // one 128-k half step of int8 codes
-constexpr int MAX_A_STAGES = 8, SIDE_STAGES = 4, MAX_RAW_STAGES = 8;
+constexpr int MAX_A_STAGES = 8, SIDE_STAGES = 8, MAX_RAW_STAGES = 8; // side stages are small (scale bytes and records of one step): enough of them that
+                                                                   // the converters, which fill them, never wait for the drain, which frees them
 constexpr int HDR_BYTES = TILE_N * 16;      // per 256-k step: 16 bytes of scale data per weight row
 constexpr int TMEM_COLS = 512;              // all of the SM's tensor memory: 512 / (4 slices x NP) accumulator buffers, at most 8
 constexpr size_t IMMA_SMEM = 226 * 1024;
@@ -393,13 +400,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u; // operand stages need 1024-byte alignment
   constexpr int NBUF = TMEM_COLS / (4 * NP) > 8 ? 8 : TMEM_COLS / (4 * NP); // accumulator buffers (even: buffer parity = half step parity)
   constexpr int BUF_COLS = 4 * NP;
-  // barriers: b_full [4], side_full/side_empty [4], a_full/mma_done [8], acc_empty [8]
-  __shared__ __align__(8) uint64_t bars[36];
+  // barriers: b_full [4], side_full/side_empty [8], a_full/mma_done [8], acc_empty [8]
+  __shared__ __align__(8) uint64_t bars[44];
   __shared__ uint32_t tmem_slot;
   __shared__ unsigned int s_ticket;
-  const uint32_t b_full = smem_u32(bars), side_full = b_full + 32, side_empty = b_full + 64, a_full = b_full + 96, mma_done = b_full + 160,
-                 acc_empty = b_full + 224;
+  const uint32_t b_full = smem_u32(bars), side_full = b_full + 32, side_empty = b_full + 96, a_full = b_full + 160, mma_done = b_full + 224,
+                 acc_empty = b_full + 288;
   XNQ_GT(26);
+  if (threadIdx.x == 0) XNQ_CT(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int RS = p.raw_stages, BS = p.b_stages, AS = p.a_stages;
   const int NB = min(NBUF, AS); // accumulator buffers in use: a drain group waiting on mma_done must not be lapped by the MMA thread,
@@ -412,14 +420,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
   if (threadIdx.x == 0) {
     for (int s = 0; s < 8; s++) {
       mbar_init(a_full + 8 * s, CONV_WARPS / 2); // the four converter warps of the step's group (one barrier per step: entries 0 .. BS - 1)
-      mbar_init(mma_done + 8 * s, 1);            // MMAs have read their operands and written their slices: entry 2 bs + 1 after a whole step (NP = 64: every half step)
+      mbar_init(mma_done + 8 * s, 1);            // the half step's MMAs have read their operands and written their slices
       mbar_init(acc_empty + 8 * s, DWG);
-    }
-    for (int s = 0; s < 4; s++) {
-      mbar_init(b_full + 8 * s, 1);
       mbar_init(side_full + 8 * s, 1 + CONV_WARPS / 2); // the producer's transaction + the four converter warps that copy the scale bytes
       mbar_init(side_empty + 8 * s, 2 * DWG);
     }
+    for (int s = 0; s < 4; s++) mbar_init(b_full + 8 * s, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == MMA_WARP) { // one warp owns the tensor-memory allocation
@@ -443,6 +449,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
         for (unsigned long long o = o0; o < o1; o += PF_CHUNK) bulk_prefetch_l2(p.pf_base[st] + o, (uint32_t)min((unsigned long long)PF_CHUNK, o1 - o));
       }
       pdl_wait();
+      XNQ_CT(1);
       bool alive = true;
       int kt = kt0, bs = 0;
       uint32_t b_ph = 0; // (i / BS) & 1
@@ -451,7 +458,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
         // the B stage of step i - BS is free once that step's second half has been multiplied: BS = AS / 2, so this is
         // the barrier of half step 2 i + 1 one phase back (a second commit per step cost the issuing thread over a
         // thousand cycles)
-        if (i >= BS) alive = mbar_wait(mma_done + 8 * (2 * bs + 1), b_ph ^ 1u, 1u);
+        if (i >= BS) alive = mbar_wait(mma_done + 8 * (2 * bs), b_ph ^ 1u, 1u) && mbar_wait(mma_done + 8 * (2 * bs + 1), b_ph ^ 1u, 1u);
         if (alive && i >= SIDE_STAGES) alive = mbar_wait(side_empty + 8 * ss, ((i / SIDE_STAGES) - 1) & 1, 1u);
         if (!alive) break;
         mbar_expect_tx(b_full + 8 * bs, p.b_stage_bytes);
@@ -463,8 +470,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
         if (++bs == BS) bs = 0, b_ph ^= 1u;
       }
     }
-  } else if (warp == MMA_WARP) {
-    // ---- MMA issuer ------------------------------------------------------------------------------------------
+  } else if (warp == MMA_WARP || warp == MMA_WARP + 1) {
+    // ---- MMA issuers: one thread per half step. A tcgen05.mma of this shape keeps the thread that issues it busy for about
+    // 134 cycles, but two threads issuing into different accumulator slices get twice the rate (measured up to N = 64), so
+    // the two halves of a step are issued by two warps, each with its own commit. ----
+    const int hh = warp - MMA_WARP;
     if (lane == 0) {
       const uint32_t idesc = idesc_i8(NP);
       bool alive = true;
@@ -477,10 +487,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
         XNQ_TACC(1);
         if (alive) alive = mbar_wait(a_full + 8 * bs, b_ph, 4u); // both halves of the step's operand image
         XNQ_TACC(2);
-        for (int h = 0; h < 2 && alive; h++) {
+        {
+          const int h = hh;
           const int sa = 2 * bs + h, buf = 2 * nb + h;
           XNQ_TACC(0);
-          if (2 * i >= NB) alive = mbar_wait(acc_empty + 8 * buf, acc_ph ^ 1u, 4u); // the drain of the buffer's previous half step
+          if (alive && 2 * i >= NB) alive = mbar_wait(acc_empty + 8 * buf, acc_ph ^ 1u, 4u); // the drain of the buffer's previous half step
           XNQ_TACC(3);
           if (!alive) break;
           if (h == 0) XNQ_TL(4, i);
@@ -491,17 +502,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
           for (int q = 0; q < 4; q++) // K = 32 per instruction: advance 32 bytes inside the swizzle row; slice q of the buffer
             umma_i8(tmem_d + (uint32_t)(buf * BUF_COLS + q * NP), adesc + (uint64_t)(q * 2), bdesc + (uint64_t)(q * 2), idesc);
           XNQ_TACC(4);
-          // One arrival per step serves the converters and the activation producer (the stages are free) and the drain (the
-          // slices are written): a commit costs the issuing thread about a hundred cycles. With 64 activation rows tensor
-          // memory holds one step only, so the drain of the first half has to start before the second is multiplied.
-          if (NP == 64 || h == 1) umma_commit(mma_done + 8 * sa);
+          // the arrival serves the drain (the slices are written) and, together with the other half's, the converters and the
+          // activation producer (the stages are free)
+          umma_commit(mma_done + 8 * sa);
           XNQ_TACC(5);
           if (h == 1) XNQ_TL(5, i);
         }
         if (++bs == BS) bs = 0, b_ph ^= 1u;
         if (2 * ++nb == NB) nb = 0, acc_ph ^= 1u;
       }
-      XNQ_TDUMP(6, true);
+      XNQ_TDUMP(6, hh == 0);
     }
   } else if (warp < DRAIN_WARP0) {
     // ---- converters: group g (four warps, one thread per weight row) produces the steps i = g, g + 2, ... of this CTA: a
@@ -565,7 +575,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
         if (lane == 0) mbar_arrive(side_full + 8 * ss);
       }
       XNQ_TACC(0);
-      if (i >= BS) alive = mbar_wait_warp(mma_done + 8 * (2 * bs + 1), a_ph ^ 1u, 2u); // both halves of the stage have been multiplied
+      if (i >= BS) alive = mbar_wait_warp(mma_done + 8 * (2 * bs), a_ph ^ 1u, 2u) && mbar_wait_warp(mma_done + 8 * (2 * bs + 1), a_ph ^ 1u, 2u); // both halves of the stage have been multiplied
       XNQ_TACC(3);
       if (!alive) break;
 #pragma unroll
@@ -624,7 +634,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
       const uint32_t side = base + p.side_off + ss * p.side_stage_bytes;
       uint4 hdr = make_uint4(0, 0, 0, 0);
       if (alive) hdr = lds128(side + (uint32_t)(32 * q + lane) * 16);
-      if (alive) alive = mbar_wait_warp(mma_done + 8 * (NP == 64 ? sa : sa | 1), a_ph, 8u);
+      if (alive) alive = mbar_wait_warp(mma_done + 8 * sa, a_ph, 8u);
       XNQ_TACC(2);
       if (threadIdx.x == DRAIN_WARP0 * 32) XNQ_TL(6, i);
       if (alive) {
@@ -648,6 +658,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
       __syncwarp();
       if (alive && lane == 0) mbar_arrive(side_empty + 8 * ss);
       if (threadIdx.x == DRAIN_WARP0 * 32) XNQ_TL(7, i);
+      if (threadIdx.x == DRAIN_WARP0 * 32 && i == 0) XNQ_CT(2);
       // ---- end of a segment (the tile's last step, or this CTA's last unit): store or hand over the sums ----
       const bool tile_end = kt == KT - 1, range_end = i == nunits - 1;
       if (tile_end || range_end) {
@@ -738,8 +749,371 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
 #ifdef XNQ_DEV_TRACE
   if (blockIdx.x == 0 && threadIdx.x == 0) g_imma_trace[30] = nunits;
   XNQ_GT(27);
+  if (threadIdx.x == 0) XNQ_CT(3);
 #endif
   if (warp == MMA_WARP) tmem_dealloc(tmem_d, TMEM_COLS);
+}
+
+// =====================================================================================================================
+// Q4_K with the sub-block scales folded into the weight operand.
+//
+// The kernel above drains one accumulator slice per 32-element block, because a block's scale cannot be applied on the
+// tensor core. For Q4_K the scales are small integers: a code q (0..15) times its 6-bit sub-block scale sc (0..63) is an
+// integer below 1024, and written as q = 4 q_hi + q_lo (two bits each) both q_lo sc and q_hi sc fit one unsigned byte
+// (<= 189). So the converters write TWO operand planes, P_lo = q_lo sc and P_hi = q_hi sc (one packed multiply per four
+// codes, no carries between bytes), the MMAs ACCUMULATE over the four sub-blocks of a half step,
+//     D_lo = sum_i P_lo[r, i] a[c, i],  D_hi likewise,    sum_g sc_g sum_{i in g} q_i a_i = 4 D_hi + D_lo   (exact integers),
+// and the drain applies d, d_min and the activation scale once per 256-element block, as the CPU code does
+// (k_quants.rs:1380-1410). Per 256-k step that is 16 MMAs instead of 8, issued by four threads (plane x half step; an
+// MMA of this shape costs its issuing thread 134 cycles but several threads issue concurrently), and 4 accumulator
+// slices to drain instead of 8, with the integer scale multiplies gone from the drain, which is what bounded the kernel
+// above (instruction issue). 21 warps: activation producer, 4 MMA issuers, 8 converter warps (group h converts half h of
+// every step into a ring of four half-step stages), 8 drain warps (two groups that take alternate steps; a thread owns
+// one weight row and all NP activation columns). NP is 16 or 32; larger batches run in passes of 32 rows.
+// =====================================================================================================================
+constexpr int F_ISSUERS = 4, F_CONV_WARPS = 8, F_DRAIN_WARPS = 8;
+constexpr int F_ACT_WARP = 0, F_MMA_WARP0 = 1, F_CONV_WARP0 = F_MMA_WARP0 + F_ISSUERS, F_DRAIN_WARP0 = F_CONV_WARP0 + F_CONV_WARPS;
+constexpr int F_NTHREADS = (F_DRAIN_WARP0 + F_DRAIN_WARPS) * 32; // 672
+constexpr int F_RING = 3;                         // stages of the rings that are freed by the drain (activation operand, scale bytes and records)
+constexpr int F_ASTAGES = 4;                      // half-step stages of the weight operand (two steps), two planes each
+constexpr int F_A_STAGE_BYTES = 2 * A_STAGE_BYTES; // plane lo, plane hi
+constexpr uint32_t F_SLOT = 32 * 64 + 512;        // a converter warp's raw slot: 64 code bytes of the half step per row, then the rows' 16 header bytes
+
+// kind::i8 with an UNSIGNED A operand (the scaled codes reach 189) and a signed B operand
+__device__ __forceinline__ uint32_t idesc_u8s8(int umma_n) {
+  return (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(umma_n >> 3) << 17) | ((uint32_t)(TILE_N >> 4) << 24);
+}
+__device__ __forceinline__ void umma_i8_acc(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// a ring position: index in 0..n-1 and the parity of the lap, advanced without a division
+struct RingPos {
+  int idx;
+  uint32_t ph;
+  __device__ __forceinline__ void advance(int by, int n) {
+    idx += by;
+    if (idx >= n) idx -= n, ph ^= 1u;
+  }
+};
+
+template <int NP>
+__global__ void __launch_bounds__(F_NTHREADS, 1) imma_q4k_fold_kernel(const __grid_constant__ ImmaArgs p) {
+  constexpr int NBUF = TMEM_COLS / (4 * NP) > 8 ? 8 : TMEM_COLS / (4 * NP); // accumulator buffers of one step (four slices): 8 or 4, a power of two
+  constexpr int BUF_COLS = 4 * NP;
+  constexpr int CH = 8; // columns read back at a time
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  // barriers: b_full, side_full, side_empty [F_RING]; a_full [F_ASTAGES]; acc_full, acc_empty [8] (NBUF of them in use)
+  __shared__ __align__(8) uint64_t bars[3 * F_RING + F_ASTAGES + 16];
+  __shared__ uint32_t tmem_slot;
+  __shared__ unsigned int s_ticket;
+  const uint32_t b_full = smem_u32(bars), side_full = b_full + 8 * F_RING, side_empty = side_full + 8 * F_RING, a_full = side_empty + 8 * F_RING,
+                 acc_full = a_full + 8 * F_ASTAGES, acc_empty = acc_full + 64;
+  // One commit per issuer and step, on the step's accumulator buffer (acc_full, all four issuers): it tells the drain that the
+  // slices are written and the converters that the operand stages of that step have been read. A barrier per operand stage
+  // would be lapped: the issuers may run NBUF steps ahead of the drain, and a waiter that misses two phases waits for ever.
+  if (threadIdx.x == 0) XNQ_CT(0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int D = p.raw_stages; // raw slots per converter warp
+  const int KT = p.nsteps;
+  const int u0 = cta_first_unit((int)blockIdx.x, p.units_q, p.units_r);
+  const int nunits = p.units_q + ((int)blockIdx.x < p.units_r ? 1 : 0);
+  const int tile0 = u0 / KT, kt0 = u0 - tile0 * KT;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < F_RING; s++) {
+      mbar_init(b_full + 8 * s, 1);
+      mbar_init(side_full + 8 * s, 1 + F_CONV_WARPS / 2); // the producer's transaction + the four converter warps of half 0, which copy the header bytes
+      mbar_init(side_empty + 8 * s, F_DRAIN_WARPS / 2);   // the step's drain group
+    }
+    for (int s = 0; s < F_ASTAGES; s++) mbar_init(a_full + 8 * s, F_CONV_WARPS / 2); // the four converter warps of the half step
+    for (int s = 0; s < 8; s++) {
+      mbar_init(acc_full + 8 * s, F_ISSUERS);
+      mbar_init(acc_empty + 8 * s, F_DRAIN_WARPS / 2);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == F_MMA_WARP0) {
+    tmem_alloc(smem_u32(&tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  pdl_launch_dependents();
+  const uint32_t tmem_d = tmem_slot;
+
+  if (warp == F_ACT_WARP) {
+    // ---- activation producer ----
+    if (lane == 0) {
+      for (int st = 0; st < p.nstreams; st++) { // the CTA's share of the weight's bytes into L2, in long contiguous runs
+        const unsigned long long o0 = p.pf_share[st] * blockIdx.x, o1 = min(o0 + p.pf_share[st], p.pf_bytes[st]);
+        for (unsigned long long o = o0; o < o1; o += PF_CHUNK) bulk_prefetch_l2(p.pf_base[st] + o, (uint32_t)min((unsigned long long)PF_CHUNK, o1 - o));
+      }
+      pdl_wait();
+      XNQ_CT(1);
+      int kt = kt0;
+      RingPos rp{0, 0};
+      for (int i = 0; i < nunits; i++) {
+        // the stage was last used by step i - 3; it is free once that step's drain group has read its records, which also
+        // means the step's MMAs have read the activation operand
+        if (i >= F_RING && !mbar_wait(side_empty + 8 * rp.idx, rp.ph ^ 1u, 1u)) break;
+        mbar_expect_tx(b_full + 8 * rp.idx, p.b_stage_bytes);
+        mbar_expect_tx(side_full + 8 * rp.idx, (uint32_t)NP * 32u);
+        bulk_g2s(base + p.b_off + rp.idx * p.b_stage_bytes, p.bimg + ((size_t)kt * 2) * (NP * 128), p.b_stage_bytes, b_full + 8 * rp.idx);
+        bulk_g2s(base + p.side_off + rp.idx * p.side_stage_bytes + HDR_BYTES, p.meta + (size_t)kt * (NP * 32), (uint32_t)NP * 32u, side_full + 8 * rp.idx);
+        if (++kt == KT) kt = 0;
+        rp.advance(1, F_RING);
+      }
+    }
+  } else if (warp < F_CONV_WARP0) {
+    // ---- MMA issuers: plane pl (0: q_lo sc, 1: q_hi sc) of half step h ----
+    const int pl = (warp - F_MMA_WARP0) >> 1, h = (warp - F_MMA_WARP0) & 1;
+    if (lane == 0) {
+      const uint32_t idesc = idesc_u8s8(NP);
+      RingPos rp{0, 0}; // step i in the drain-freed ring
+      uint32_t acc_ph = 0;
+      for (int i = 0; i < nunits; i++) {
+        const int buf = i & (NBUF - 1), st = 2 * (i & 1) + h; // half step j = 2 i + h uses operand stage j % 4
+        if (!mbar_wait(b_full + 8 * rp.idx, rp.ph, 4u)) break;
+        if (!mbar_wait(a_full + 8 * st, (uint32_t)(i >> 1) & 1u, 4u)) break;
+        if (i >= NBUF && !mbar_wait(acc_empty + 8 * buf, acc_ph ^ 1u, 4u)) break; // the drain of the buffer's previous step
+        tc_fence_after();
+        const uint64_t adesc = smem_desc_sw128(base + p.a_off + st * F_A_STAGE_BYTES + pl * A_STAGE_BYTES);
+        const uint64_t bdesc = smem_desc_sw128(base + p.b_off + rp.idx * p.b_stage_bytes + h * (NP * 128));
+        const uint32_t dcol = tmem_d + (uint32_t)(buf * BUF_COLS + (pl * 2 + h) * NP);
+#pragma unroll
+        for (int q = 0; q < 4; q++) umma_i8_acc(dcol, adesc + (uint64_t)(q * 2), bdesc + (uint64_t)(q * 2), idesc, q > 0 ? 1u : 0u);
+        umma_commit(acc_full + 8 * buf);
+        rp.advance(1, F_RING);
+        if (buf == NBUF - 1) acc_ph ^= 1u;
+      }
+    }
+  } else if (warp < F_DRAIN_WARP0) {
+    // ---- converters: group h (four warps, one thread per weight row) writes both planes of half step h of every step ----
+    const int cw = warp - F_CONV_WARP0;
+    const int r0 = (cw & 3) * 32, r = r0 + lane, h = cw >> 2;
+    const int sw = r & 7;
+    const uint32_t slot0 = base + p.raw_off0 + (uint32_t)(cw * D) * F_SLOT;
+    const int64_t n = p.w.n;
+    int l_i = 0, l_tile = tile0, l_kt = kt0, l_s = 0;
+    auto issue = [&]() { // lane l copies chunk l % 4 of row q * 8 + l / 4 in instruction q; then its own row's header
+      const uint32_t dst = slot0 + (uint32_t)l_s * F_SLOT;
+      const int c = lane & 3;
+      const uint32_t in_row = (uint32_t)l_kt * 144u + 16u + (uint32_t)(h * 64 + c * 16);
+#pragma unroll
+      for (int q = 0; q < 4; q++) {
+        const int rw = q * 8 + (lane >> 2);
+        const int64_t grow = (int64_t)l_tile * TILE_N + r0 + rw;
+        const bool ok = grow < n;
+        cp_async16(dst + (uint32_t)(rw * 64 + ((c ^ (rw & 3)) << 4)), p.src[0] + (size_t)(ok ? grow : n - 1) * p.row_bytes[0] + in_row, ok ? 16u : 0u);
+      }
+      const int64_t grow = (int64_t)l_tile * TILE_N + r;
+      cp_async16(dst + 2048 + lane * 16, p.src[0] + (size_t)(grow < n ? grow : n - 1) * p.row_bytes[0] + (size_t)l_kt * 144u, grow < n ? 16u : 0u);
+      l_i++;
+      if (++l_kt == KT) l_kt = 0, l_tile++;
+      if (++l_s == D) l_s = 0;
+    };
+    for (int u = 0; u < D; u++) {
+      if (l_i < nunits) issue();
+      cp_async_commit();
+    }
+    bool alive = true;
+    int rs = 0;
+    RingPos rp{0, 0};
+    for (int i = 0; i < nunits && alive; i++) {
+      const int st = 2 * (i & 1) + h;
+      cp_async_wait(D - 1);
+      __syncwarp();
+      const uint32_t slot = slot0 + (uint32_t)rs * F_SLOT;
+      const uint4 hdr = lds128(slot + 2048 + lane * 16);
+      if (h == 0) { // hand the row's header on to the drain
+        if (i >= F_RING) alive = mbar_wait_warp(side_empty + 8 * rp.idx, rp.ph ^ 1u, 2u);
+        if (!alive) break;
+        sts128(base + p.side_off + rp.idx * p.side_stage_bytes + (uint32_t)r * 16, hdr);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(side_full + 8 * rp.idx);
+      }
+      // the stage's previous half step belongs to step i - 2: all of that step's MMAs have been committed
+      if (i >= 2) alive = mbar_wait_warp(acc_full + 8 * ((i - 2) & (NBUF - 1)), (uint32_t)((i - 2) / NBUF) & 1u, 2u);
+      if (!alive) break;
+      // the four sub-block scales of this half step: fields 2h and 2h + 1 of the repacked header
+      const uint32_t lo32 = h ? __funnelshift_r(hdr.z, hdr.w, 16) : hdr.y;
+      const uint32_t hi16 = h ? (hdr.w >> 16) : (hdr.z & 0xffffu);
+      const uint32_t f0 = lo32 & 0xffffffu, f1 = __funnelshift_r(lo32, hi16, 24) & 0xffffffu;
+      const uint32_t sc[4] = {f0 & 63u, (f0 >> 6) & 63u, f1 & 63u, (f1 >> 6) & 63u};
+      const uint32_t row = slot + (uint32_t)lane * 64;
+      const uint4 raw[4] = {raw_chunk<64>(row, lane, 0), raw_chunk<64>(row, lane, 1), raw_chunk<64>(row, lane, 2), raw_chunk<64>(row, lane, 3)};
+      const uint32_t a_stage = base + p.a_off + st * F_A_STAGE_BYTES + (uint32_t)r * 128;
+#pragma unroll
+      for (int pl = 0; pl < 2; pl++) {
+#pragma unroll
+        for (int pair = 0; pair < 2; pair++) { // 32-byte chunk `pair` of the half step: sub-blocks 2 pair (low nibbles) and 2 pair + 1 (high nibbles)
+#pragma unroll
+          for (int nib = 0; nib < 2; nib++) {
+            const int sh = 4 * nib + 2 * pl;
+            const uint32_t m = sc[2 * pair + nib];
+#pragma unroll
+            for (int half16 = 0; half16 < 2; half16++) { // the chunk's first and second 16 bytes: elements 0..15 and 16..31 of the sub-block
+              const uint4 w = raw[2 * pair + half16];
+              const uint4 o = make_uint4(((w.x >> sh) & 0x03030303u) * m, ((w.y >> sh) & 0x03030303u) * m, ((w.z >> sh) & 0x03030303u) * m,
+                                         ((w.w >> sh) & 0x03030303u) * m);
+              const int chunk = (2 * pair + nib) * 2 + half16; // 16-byte chunk of the 128-byte operand row
+              sts128(a_stage + pl * A_STAGE_BYTES + (uint32_t)((chunk ^ sw) << 4), o);
+            }
+          }
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(a_full + 8 * st);
+      if (l_i < nunits) issue();
+      cp_async_commit();
+      if (++rs == D) rs = 0;
+      rp.advance(1, F_RING);
+    }
+    cp_async_wait(0);
+  } else {
+    // ---- drain: group dg (four warps, a thread per weight row, all NP columns) takes the steps i = dg, dg + 2, ... ----
+    const int dwi = warp - F_DRAIN_WARP0;
+    const int q = warp & 3, dg = dwi >> 2;
+    const int et = threadIdx.x - F_DRAIN_WARP0 * 32; // 0..255
+    pdl_wait(); // the kernel that prepares the activations also zeroes the tiles' tickets
+    bool alive = true;
+    int tile = tile0, kt = kt0;
+    float acc[NP];
+#pragma unroll
+    for (int c = 0; c < NP; c++) acc[c] = 0.f;
+    int seg_kt0 = kt0;
+    float *pair = p.pair_scratch + (size_t)blockIdx.x * NP * TILE_N;
+    RingPos rp{0, 0};
+    for (int i = 0; i < nunits; i++) {
+      const int buf = i & (NBUF - 1);
+      if ((i & 1) == dg) {
+        if (alive) alive = mbar_wait_warp(side_full + 8 * rp.idx, rp.ph, 8u);
+        const uint32_t side = base + p.side_off + rp.idx * p.side_stage_bytes;
+        uint4 hdr = make_uint4(0, 0, 0, 0);
+        if (alive) hdr = lds128(side + (uint32_t)(32 * q + lane) * 16);
+        if (alive) alive = mbar_wait_warp(acc_full + 8 * buf, (uint32_t)(i / NBUF) & 1u, 8u);
+        if (alive) {
+          tc_fence_after();
+          const __half2 dm = *reinterpret_cast<const __half2 *>(&hdr.x);
+          const float d = __low2float(dm), dmin = __high2float(dm);
+          // the eight 6-bit mins as bytes: fields F0..F3 hold mn[2g] at bit 12 and mn[2g+1] at bit 18
+          const uint32_t F0 = hdr.y & 0xffffffu, F1 = __funnelshift_r(hdr.y, hdr.z, 24) & 0xffffffu, F2 = __funnelshift_r(hdr.z, hdr.w, 16) & 0xffffffu, F3 = hdr.w >> 8;
+          const uint32_t mins0 = ((F0 >> 12) & 63u) | (((F0 >> 18) & 63u) << 8) | (((F1 >> 12) & 63u) << 16) | (((F1 >> 18) & 63u) << 24);
+          const uint32_t mins1 = ((F2 >> 12) & 63u) | (((F2 >> 18) & 63u) << 8) | (((F3 >> 12) & 63u) << 16) | (((F3 >> 18) & 63u) << 24);
+          const uint32_t taddr = tmem_d + ((uint32_t)(32 * q) << 16) + (uint32_t)(buf * BUF_COLS);
+#pragma unroll
+          for (int ch = 0; ch < NP / CH; ch++) {
+            uint32_t v[4][CH]; // slices: plane lo half 0, lo half 1, hi half 0, hi half 1
+#pragma unroll
+            for (int sl = 0; sl < 4; sl++) tmem_ld<CH>(taddr + (uint32_t)(sl * NP + ch * CH), v[sl]);
+            tmem_ld_wait();
+            if (ch == NP / CH - 1) { // every value of the buffer is in registers: it may be overwritten
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(acc_empty + 8 * buf);
+            }
+#pragma unroll
+            for (int c = 0; c < CH; c++) {
+              const uint32_t rec = side + HDR_BYTES + (uint32_t)(ch * CH + c) * 32;
+              const uint4 bs = lds128(rec); // {lo bytes half 0, hi bytes half 0, lo bytes half 1, hi bytes half 1} of the activations' 32-sums
+              const float da = __uint_as_float(lds32(rec + 16));
+              const int isum = 4 * ((int)v[2][c] + (int)v[3][c]) + ((int)v[0][c] + (int)v[1][c]);
+              const int msum = dp4a_uu(mins0, bs.x, dp4a_uu(mins1, bs.z, 0)) + 128 * dp4a_us(mins0, bs.y, dp4a_us(mins1, bs.w, 0));
+              acc[ch * CH + c] += da * (d * (float)isum - dmin * (float)msum);
+            }
+          }
+        }
+        __syncwarp();
+        if (alive && lane == 0) mbar_arrive(side_empty + 8 * rp.idx);
+        if (i == 0 && et == 0) XNQ_CT(2);
+      }
+      // ---- end of a segment (the tile's last step, or this CTA's last unit): store or hand over the sums ----
+      const bool tile_end = kt == KT - 1, range_end = i == nunits - 1;
+      if (tile_end || range_end) {
+        const int64_t row = (int64_t)tile * TILE_N + 32 * q + lane;
+        if (dg == 1) { // the odd steps' sums join the even ones': always even + odd, whatever the timing
+#pragma unroll
+          for (int c = 0; c < NP; c++) pair[(size_t)c * TILE_N + 32 * q + lane] = acc[c];
+          __threadfence_block();
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(F_DRAIN_WARPS * 32) : "memory");
+        if (dg == 0) {
+#pragma unroll
+          for (int c = 0; c < NP; c++) acc[c] += pair[(size_t)c * TILE_N + 32 * q + lane];
+        }
+        const bool whole = seg_kt0 == 0 && tile_end;
+        if (whole) {
+          if (dg == 0 && alive && row < p.w.n) {
+#pragma unroll
+            for (int c = 0; c < NP; c++) {
+              if (c < p.m) {
+                const int64_t idx = (int64_t)c * p.ldy + row;
+                if (p.y_dtype == XNQ_F32) static_cast<float *>(p.y)[idx] = acc[c];
+                else if (p.y_dtype == XNQ_F16) static_cast<__half *>(p.y)[idx] = __float2half_rn(acc[c]);
+                else static_cast<__nv_bfloat16 *>(p.y)[idx] = __float2bfloat16_rn(acc[c]);
+              }
+            }
+          }
+          asm volatile("bar.sync 1, %0;" ::"n"(F_DRAIN_WARPS * 32) : "memory"); // group 0 has read the scratch: it may be rewritten
+        } else {
+          const int seg_u0 = tile * KT + seg_kt0;
+          float *mine = p.partials + ((size_t)2 * blockIdx.x + (seg_u0 == u0 ? 0 : 1)) * NP * TILE_N;
+          if (dg == 0) {
+#pragma unroll
+            for (int c = 0; c < NP; c++) mine[(size_t)c * TILE_N + 32 * q + lane] = acc[c];
+            __threadfence();
+          }
+          asm volatile("bar.sync 1, %0;" ::"n"(F_DRAIN_WARPS * 32) : "memory");
+          if (et == 0) s_ticket = atomicAdd(p.tile_cnt + tile, 1u);
+          asm volatile("bar.sync 1, %0;" ::"n"(F_DRAIN_WARPS * 32) : "memory");
+          const unsigned int ticket = s_ticket;
+          asm volatile("bar.sync 1, %0;" ::"n"(F_DRAIN_WARPS * 32) : "memory");
+          const int t_u0 = tile * KT, t_u1 = t_u0 + KT;
+          const int c_first = cta_of(t_u0, p.units_q, p.units_r), c_last = cta_of(t_u1 - 1, p.units_q, p.units_r);
+          if (dg == 0 && (int)ticket == c_last - c_first) { // the last part to arrive adds all parts in k order
+            __threadfence();
+#pragma unroll
+            for (int c = 0; c < NP; c++) acc[c] = 0.f;
+            for (int cc = c_first; cc <= c_last; cc++) {
+              const int cu0 = cta_first_unit(cc, p.units_q, p.units_r);
+              const float *part = p.partials + ((size_t)2 * cc + (cu0 >= t_u0 ? 0 : 1)) * NP * TILE_N;
+#pragma unroll
+              for (int c = 0; c < NP; c++) acc[c] += __ldcg(part + (size_t)c * TILE_N + 32 * q + lane);
+            }
+            if (row < p.w.n) {
+#pragma unroll
+              for (int c = 0; c < NP; c++) {
+                if (c < p.m) {
+                  const int64_t idx = (int64_t)c * p.ldy + row;
+                  if (p.y_dtype == XNQ_F32) static_cast<float *>(p.y)[idx] = acc[c];
+                  else if (p.y_dtype == XNQ_F16) static_cast<__half *>(p.y)[idx] = __float2half_rn(acc[c]);
+                  else static_cast<__nv_bfloat16 *>(p.y)[idx] = __float2bfloat16_rn(acc[c]);
+                }
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < NP; c++) acc[c] = 0.f;
+        seg_kt0 = 0;
+      }
+      if (++kt == KT) kt = 0, tile++;
+      rp.advance(1, F_RING);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0) XNQ_CT(3);
+  if (warp == F_MMA_WARP0) tmem_dealloc(tmem_d, TMEM_COLS);
 }
 
 // ---- activations: quantize (or take an activation image), lay out as the MMA's B operand, write the records ----
@@ -749,8 +1123,14 @@ template <int ACT, typename XT>
 __global__ void __launch_bounds__(256) imma_prepare(const XT *__restrict__ x, const int8_t *__restrict__ img_q, const float *__restrict__ img_d,
                                                     const int16_t *__restrict__ img_b, int64_t m, int64_t k, int64_t ldx, int NP, int nsteps,
                                                     uint8_t *__restrict__ bimg, uint8_t *__restrict__ meta, unsigned int *__restrict__ tile_cnt, int tiles) {
+#ifdef XNQ_DEV_TRACE
+  if (g_dev_prep_trig == 0) pdl_launch_dependents();
+  pdl_wait();
+  if (g_dev_prep_trig == 1) pdl_launch_dependents();
+#else
   pdl_launch_dependents(); // the matmul kernel may start its set-up and its weight loads now
   pdl_wait();              // x may be the previous kernel's output; the scratch may still be read by the previous call
+#endif
   XNQ_GT(24);
   const int row = blockIdx.x;
   if (blockIdx.x == 0 && blockIdx.y == 0)
@@ -818,6 +1198,7 @@ __global__ void __launch_bounds__(256) imma_prepare(const XT *__restrict__ x, co
 }
 
 int g_sms = 0;
+std::atomic<int> g_fold{1}; // Q4_K, imma_q4k_fold_kernel: 0 never, 1 for the batch sizes it is faster at, 2 whenever the weight is Q4_K
 
 struct Plan {
   int NP, nsteps, tiles, grid;
@@ -853,6 +1234,10 @@ int launch_np(const ImmaArgs &a, int NP, unsigned grid, cudaStream_t s) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+#ifdef XNQ_DEV_TRACE
+  static const int dev_pdl_main = [] { const char *e = getenv("XNQ_PDL_MAIN"); return e ? atoi(e) : 1; }();
+  cfg.numAttrs = dev_pdl_main ? 1 : 0;
+#endif
   if (NP == 16) XNQ_CUDA(cudaLaunchKernelEx(&cfg, imma_kernel<Conv, Drain, 16>, a));
   else if (NP == 32) XNQ_CUDA(cudaLaunchKernelEx(&cfg, imma_kernel<Conv, Drain, 32>, a));
   else XNQ_CUDA(cudaLaunchKernelEx(&cfg, imma_kernel<Conv, Drain, 64>, a));
@@ -889,8 +1274,13 @@ int launch_imma(const WeightView &w, const void *x, int x_dtype, int64_t m, int6
   const int64_t k = w.k;
   const int act = act_dtype_for(w.dtype);
   const size_t yes = type_size(y_dtype);
-  for (int64_t r0 = 0; r0 < m; r0 += MAX_NP) { // passes of at most 64 activation rows
-    const int64_t rows = std::min<int64_t>(MAX_NP, m - r0);
+  // Q4_K: sub-block scales folded into the weight operand. Measured on the 14336 x 4096 weight: as fast as the per-block
+  // kernel up to 16 rows, 8 % faster for 17..32, slower beyond (it runs in passes of 32 rows), so by default it takes 17..32.
+  const int fold_opt = g_fold.load(std::memory_order_relaxed);
+  const bool fold = w.dtype == XNQ_Q4K && (fold_opt == 2 || (fold_opt == 1 && m > 16 && m <= 32));
+  const int64_t pass_rows = fold ? 32 : MAX_NP;
+  for (int64_t r0 = 0; r0 < m; r0 += pass_rows) { // passes of at most 64 (32) activation rows
+    const int64_t rows = std::min<int64_t>(pass_rows, m - r0);
     const Plan pl = plan_for(rows, k, w.n);
     uint8_t *ws = static_cast<uint8_t *>(workspace);
     uint8_t *bimg = ws;
@@ -909,6 +1299,20 @@ int launch_imma(const WeightView &w, const void *x, int x_dtype, int64_t m, int6
 #define XNQ_IMMA_PREP(ACT, XT)                                                                                                          \
   XNQ_CUDA(launch_pdl(imma_prepare<ACT, XT>, dim3((unsigned)pl.NP, (unsigned)std::min<int64_t>(16, (k + 2047) / 2048)), dim3(256), 0, s,     \
                       iq ? nullptr : static_cast<const XT *>(x) + r0 * ldx, iq, id, ib, rows, k, ldx, pl.NP, pl.nsteps, bimg, meta, cnt, pl.tiles))
+#ifdef XNQ_DEV_TRACE
+    static const int dev_skip = [] { const char *e = getenv("XNQ_IMMA_SKIP"); return e ? atoi(e) : 0; }();
+    static const int dev_pdl_main = [] { const char *e = getenv("XNQ_PDL_MAIN"); return e ? atoi(e) : 1; }();
+    static const int dev_trig = [] {
+      const char *e = getenv("XNQ_PREP_TRIG");
+      const int v = e ? atoi(e) : 0;
+      cudaMemcpyToSymbol(g_dev_prep_trig, &v, sizeof(int));
+      return v;
+    }();
+    (void)dev_trig;
+    if (dev_skip != 1) {
+#else
+    {
+#endif
     if (act == XNQ_Q8_0) {
       if (x_dtype == XNQ_F16) XNQ_IMMA_PREP(XNQ_Q8_0, __half);
       else if (x_dtype == XNQ_BF16) XNQ_IMMA_PREP(XNQ_Q8_0, __nv_bfloat16);
@@ -918,8 +1322,9 @@ int launch_imma(const WeightView &w, const void *x, int x_dtype, int64_t m, int6
       else if (x_dtype == XNQ_BF16) XNQ_IMMA_PREP(XNQ_Q8K, __nv_bfloat16);
       else XNQ_IMMA_PREP(XNQ_Q8K, float);
     }
+      count_launch();
+    }
 #undef XNQ_IMMA_PREP
-    count_launch();
 
     ImmaArgs a{};
     a.w = w;
@@ -963,6 +1368,39 @@ int launch_imma(const WeightView &w, const void *x, int x_dtype, int64_t m, int6
         a.pf_share[st] = ((a.pf_bytes[st] / (unsigned)pl.grid) + PF_CHUNK - 1) & ~(unsigned long long)(PF_CHUNK - 1);
       }
     }
+#ifdef XNQ_DEV_TRACE
+    if (dev_skip == 2) continue;
+#endif
+    if (fold) {
+      a.b_stage_bytes = (uint32_t)pl.NP * 256;
+      a.side_stage_bytes = HDR_BYTES + (uint32_t)pl.NP * 32;
+      a.a_off = 0;
+      a.b_off = (uint32_t)F_ASTAGES * F_A_STAGE_BYTES;
+      a.side_off = a.b_off + F_RING * a.b_stage_bytes;
+      a.raw_off0 = (a.side_off + F_RING * a.side_stage_bytes + 127) & ~127u;
+      const size_t left = IMMA_SMEM - 1024 - a.raw_off0;
+      a.raw_stages = (int)std::min<size_t>(6, left / ((size_t)F_CONV_WARPS * F_SLOT)); // raw slots per converter warp
+      if (a.raw_stages < 2) return fail(XNQ_ERR_SIZE, "imma: shared-memory plan does not fit");
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = dim3((unsigned)pl.grid);
+      cfg.blockDim = dim3(F_NTHREADS);
+      cfg.dynamicSmemBytes = IMMA_SMEM;
+      cfg.stream = s;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+#ifdef XNQ_DEV_TRACE
+      cfg.numAttrs = dev_pdl_main ? 1 : 0;
+#endif
+      profile_mark(s, true);
+      if (pl.NP == 16) XNQ_CUDA(cudaLaunchKernelEx(&cfg, imma_q4k_fold_kernel<16>, a));
+      else XNQ_CUDA(cudaLaunchKernelEx(&cfg, imma_q4k_fold_kernel<32>, a));
+      count_launch();
+      profile_mark(s, false);
+      continue;
+    }
     a.raw_stage_bytes = (uint32_t)(CONV_WARPS / 2) * (32u * (uint32_t)step_code + 512u); // a step in flight: four warp slots of the rows' code bytes and 16 scale bytes per row
     a.b_stage_bytes = (uint32_t)pl.NP * 256;
     a.side_stage_bytes = HDR_BYTES + (uint32_t)pl.NP * 32;
@@ -1004,6 +1442,8 @@ int imma_init(int device) {
   g_sms = prop.multiProcessorCount;
   int rc;
   if ((rc = init_np<ConvQ4K, DrainQ4K>()) != XNQ_OK) return rc;
+  XNQ_CUDA(cudaFuncSetAttribute(imma_q4k_fold_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)IMMA_SMEM));
+  XNQ_CUDA(cudaFuncSetAttribute(imma_q4k_fold_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)IMMA_SMEM));
   if ((rc = init_np<ConvQ8_0, DrainBlockScaled>()) != XNQ_OK) return rc;
   if ((rc = init_np<ConvQ4_0, DrainBlockScaled>()) != XNQ_OK) return rc;
   unsigned int zero = 0;
@@ -1012,9 +1452,12 @@ int imma_init(int device) {
 }
 
 #ifdef XNQ_DEV_TRACE
+extern "C" int xnq_dev_cta_times(long long *out) { return cudaMemcpyFromSymbol(out, g_cta_times, sizeof(long long) * 640) == cudaSuccess ? 0 : -6; }
 extern "C" int xnq_dev_imma_trace(long long *out) { return cudaMemcpyFromSymbol(out, g_imma_trace, sizeof(long long) * 32) == cudaSuccess ? 0 : -6; }
 extern "C" int xnq_dev_imma_timeline(long long *out) { return cudaMemcpyFromSymbol(out, g_imma_tl, sizeof(long long) * 8 * 64) == cudaSuccess ? 0 : -6; }
 #endif
+
+void imma_set_fold(int on) { g_fold.store(on); }
 
 int imma_status(unsigned int *bits) {
   XNQ_CUDA(cudaMemcpyFromSymbol(bits, g_imma_status, sizeof(*bits)));
