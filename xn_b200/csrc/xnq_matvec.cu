@@ -78,14 +78,22 @@ __host__ __device__ inline size_t smem_act_bytes(int64_t m, int64_t k, int blk, 
   return b;
 }
 
-__device__ __forceinline__ SmemAct stage_activations(unsigned char *smem, const ActView &a, int blk, bool with_bsum) {
+// swizzle: 16-byte chunk g of the codes sits at chunk g ^ (((g >> 3) & 3) << 1). A 128-bit shared load is served a
+// quarter warp at a time; the eight lanes of a quarter read chunks that differ in bits 0, 3 and 4 of g only (16-element
+// half, half of the 256-element block, odd / even block), so without the swizzle they fall into two of the eight bank
+// groups (four wavefronts per quarter) and with it into all eight (one).
+__device__ __forceinline__ int64_t swz_chunk(int64_t g) { return g ^ (((g >> 3) & 3) << 1); }
+__device__ __forceinline__ int4 act_chunk_swz(const int8_t *q, int64_t byte_off) { // byte_off: a multiple of 16
+  return *reinterpret_cast<const int4 *>(q + 16 * swz_chunk(byte_off >> 4));
+}
+__device__ __forceinline__ SmemAct stage_activations(unsigned char *smem, const ActView &a, int blk, bool with_bsum, bool swizzle = false) {
   const int64_t qbytes = a.m * a.k;
   const int64_t dcount = a.m * (a.k / blk);
   int8_t *sq = reinterpret_cast<int8_t *>(smem);
   float *sd = reinterpret_cast<float *>(smem + qbytes);
   int16_t *sb = reinterpret_cast<int16_t *>(smem + qbytes + ((dcount * 4 + 15) & ~(int64_t)15));
   for (int64_t i = threadIdx.x; i < qbytes / 16; i += blockDim.x)
-    reinterpret_cast<uint4 *>(sq)[i] = reinterpret_cast<const uint4 *>(a.q)[i];
+    reinterpret_cast<uint4 *>(sq)[swizzle ? swz_chunk(i) : i] = reinterpret_cast<const uint4 *>(a.q)[i];
   for (int64_t i = threadIdx.x; i < dcount; i += blockDim.x) sd[i] = a.d[i];
   if (with_bsum) {
     const int64_t bwords = a.m * (a.k / 16) / 2; // k/16 is even: pairs of int16
@@ -292,7 +300,7 @@ __global__ void XNQ_MATVEC_BOUNDS matvec_q4k(WeightView w, ActView a, void *y, i
 template <int MT, int R>
 __global__ void XNQ_MATVEC_BOUNDS matvec_q6k(WeightView w, ActView a, void *y, int y_dtype, int64_t ldy) {
   extern __shared__ __align__(16) unsigned char smem[];
-  const SmemAct sa = stage_activations(smem, a, QK_K, true);
+  const SmemAct sa = stage_activations(smem, a, QK_K, true, true);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // persistent over row groups: the activation image is staged once per CTA, not once per WARPS * R rows
   for (int64_t row0 = ((int64_t)blockIdx.x * WARPS + warp) * R; row0 < w.n; row0 += (int64_t)gridDim.x * WARPS * R) {
@@ -305,6 +313,59 @@ __global__ void XNQ_MATVEC_BOUNDS matvec_q6k(WeightView w, ActView a, void *y, i
 #pragma unroll
     for (int i = 0; i < MT; i++) acc[r][i] = 0.f;
 
+  if constexpr (MT >= 8) {
+  for (int64_t sb = lane >> 2; sb < nsb; sb += 8) {
+    const int64_t kbase = sb * QK_K + 128 * h + 16 * lh; // group gg adds 32*gg
+    // The R rows' codes are unpacked first and every activation row's 64 codes are then read from shared memory ONCE for
+    // all of them: with the activation loads inside the row loop the kernel was bound by shared-memory bandwidth
+    // (one activation byte per multiply-add).
+    uint4 code[R][4];
+    int sc[R][4];
+    float dw[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+      const int64_t row = min(row0 + r, w.n - 1);
+      const int64_t blk = row * nsb + sb;
+      const uint4 qa = ldg_stream(w.qs + blk * 128 + 64 * h + 16 * lh);
+      const uint4 qb = ldg_stream(w.qs + blk * 128 + 64 * h + 32 + 16 * lh);
+      const uint4 qh = ldg_stream(w.qh + blk * 64 + 32 * h + 16 * lh);
+      const uint2 scw = ldg_stream8(w.sc + blk * 16 + 8 * h);
+      dw[r] = __half2float(w.d[row * w.dstride + sb]);
+      // 6-bit codes 0..63 of the four 16-element groups (k_quants.rs:1763-1770)
+      code[r][0] = or4(and4(qa, 0x0f0f0f0fu), and4(shl4(qh, 4), 0x30303030u));
+      code[r][1] = or4(and4(qb, 0x0f0f0f0fu), and4(shl4(qh, 2), 0x30303030u));
+      code[r][2] = or4(and4(shr4(qa, 4), 0x0f0f0f0fu), and4(qh, 0x30303030u));
+      code[r][3] = or4(and4(shr4(qb, 4), 0x0f0f0f0fu), and4(shr4(qh, 2), 0x30303030u));
+      // int8 scales of groups gg: byte index lh + 2*gg of the half's 8 scale bytes
+      const uint64_t sc64 = ((uint64_t)scw.y << 32) | scw.x;
+#pragma unroll
+      for (int gg = 0; gg < 4; gg++) sc[r][gg] = (int)(int8_t)((sc64 >> (8 * (lh + 2 * gg))) & 0xff);
+    }
+#pragma unroll
+    for (int i = 0; i < MT; i++) {
+      if (i < m) {
+        // the half block's eight 16-sums in one load: group gg of this lane is element lh + 2 gg
+        const int4 b8 = *reinterpret_cast<const int4 *>(sa.bsum + (int64_t)i * (k / 16) + sb * 16 + 8 * h);
+        const int bw[4] = {b8.x, b8.y, b8.z, b8.w};
+        const float da = sa.d[(int64_t)i * nsb + sb];
+        int4 av[4];
+        int off32[4];
+#pragma unroll
+        for (int gg = 0; gg < 4; gg++) {
+          av[gg] = act_chunk_swz(sa.q, (int64_t)i * k + kbase + 32 * gg);
+          off32[gg] = 32 * (int)(int16_t)(bw[gg] >> (16 * lh)); // codes are stored +32
+        }
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+          int t = 0;
+#pragma unroll
+          for (int gg = 0; gg < 4; gg++) t += sc[r][gg] * (dot16(code[r][gg], av[gg], 0) - off32[gg]);
+          acc[r][i] += (dw[r] * da) * (float)t;
+        }
+      }
+    }
+  }
+  } else { // few activation rows: the registers do not hold R rows' codes beside the sums, and the loads are few anyway
   for (int64_t sb = lane >> 2; sb < nsb; sb += 8) {
     const int64_t kbase = sb * QK_K + 128 * h + 16 * lh; // group gg adds 32*gg
 #pragma unroll
@@ -330,12 +391,11 @@ __global__ void XNQ_MATVEC_BOUNDS matvec_q6k(WeightView w, ActView a, void *y, i
 #pragma unroll
       for (int i = 0; i < MT; i++) {
         if (i < m) {
-          const int8_t *aq = sa.q + (int64_t)i * k + kbase;
           const int16_t *bs = sa.bsum + (int64_t)i * (k / 16) + (kbase >> 4);
           int t = 0;
 #pragma unroll
           for (int gg = 0; gg < 4; gg++) {
-            const int4 av = *reinterpret_cast<const int4 *>(aq + 32 * gg);
+            const int4 av = act_chunk_swz(sa.q, (int64_t)i * k + kbase + 32 * gg);
             const int s = dot16(code[gg], av, 0) - 32 * (int)bs[2 * gg]; // codes are stored +32
             t += sc[gg] * s;
           }
@@ -343,6 +403,7 @@ __global__ void XNQ_MATVEC_BOUNDS matvec_q6k(WeightView w, ActView a, void *y, i
         }
       }
     }
+  }
   }
   reduce_store<MT, R>(acc, lane, row0, w.n, m, y, y_dtype, ldy);
   }
