@@ -56,9 +56,6 @@ namespace xnq {
 __device__ unsigned int g_imma_status; // sticky: 1 producer, 2 converter, 4 mma, 8 drain wait expired
 #ifdef XNQ_DEV_TRACE
 __device__ long long g_imma_trace[32]; // development builds only: cycles block 0's roles spend in each wait
-__device__ long long g_cta_times[160 * 4]; // development builds only: per CTA of the last launch: entry, activation wait released, first step drained, exit (ns)
-#define XNQ_CT(slot) do { unsigned long long g_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_)); if (blockIdx.x < 160) g_cta_times[blockIdx.x * 4 + (slot)] = (long long)g_; } while (0)
-__device__ int g_dev_prep_trig;        // development builds only: where the activation kernel releases its dependents (0 entry, 1 after its wait, 2 exit)
 __device__ long long g_imma_tl[8 * 64];  // development builds only: block 0's per-unit time line (clock64), 8 points x 64 units
 #define XNQ_TL(pt, i) do { if (blockIdx.x == 0 && (i) < 64) g_imma_tl[(pt) * 64 + (i)] = clock64(); } while (0)
 #define XNQ_GT(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) { unsigned long long g_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_)); g_imma_trace[i] = (long long)g_; } } while (0)
@@ -67,7 +64,6 @@ __device__ long long g_imma_tl[8 * 64];  // development builds only: block 0's p
 #define XNQ_TDUMP(base, cond) do { if ((cond) && blockIdx.x == 0) for (int i_ = 0; i_ < 6; i_++) g_imma_trace[(base) + i_] = tacc[i_]; } while (0)
 #else
 #define XNQ_GT(i) do { } while (0)
-#define XNQ_CT(slot) do { } while (0)
 #define XNQ_TL(pt, i) do { } while (0)
 #define XNQ_TACC(i) do { } while (0)
 #define XNQ_TDECL do { } while (0)
@@ -407,7 +403,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
   const uint32_t b_full = smem_u32(bars), side_full = b_full + 32, side_empty = b_full + 96, a_full = b_full + 160, mma_done = b_full + 224,
                  acc_empty = b_full + 288;
   XNQ_GT(26);
-  if (threadIdx.x == 0) XNQ_CT(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int RS = p.raw_stages, BS = p.b_stages, AS = p.a_stages;
   const int NB = min(NBUF, AS); // accumulator buffers in use: a drain group waiting on mma_done must not be lapped by the MMA thread,
@@ -449,7 +444,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
         for (unsigned long long o = o0; o < o1; o += PF_CHUNK) bulk_prefetch_l2(p.pf_base[st] + o, (uint32_t)min((unsigned long long)PF_CHUNK, o1 - o));
       }
       pdl_wait();
-      XNQ_CT(1);
       bool alive = true;
       int kt = kt0, bs = 0;
       uint32_t b_ph = 0; // (i / BS) & 1
@@ -658,7 +652,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
       __syncwarp();
       if (alive && lane == 0) mbar_arrive(side_empty + 8 * ss);
       if (threadIdx.x == DRAIN_WARP0 * 32) XNQ_TL(7, i);
-      if (threadIdx.x == DRAIN_WARP0 * 32 && i == 0) XNQ_CT(2);
       // ---- end of a segment (the tile's last step, or this CTA's last unit): store or hand over the sums ----
       const bool tile_end = kt == KT - 1, range_end = i == nunits - 1;
       if (tile_end || range_end) {
@@ -749,7 +742,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
 #ifdef XNQ_DEV_TRACE
   if (blockIdx.x == 0 && threadIdx.x == 0) g_imma_trace[30] = nunits;
   XNQ_GT(27);
-  if (threadIdx.x == 0) XNQ_CT(3);
 #endif
   if (warp == MMA_WARP) tmem_dealloc(tmem_d, TMEM_COLS);
 }
@@ -817,7 +809,6 @@ __global__ void __launch_bounds__(F_NTHREADS, 1) imma_q4k_fold_kernel(const __gr
   // One commit per issuer and step, on the step's accumulator buffer (acc_full, all four issuers): it tells the drain that the
   // slices are written and the converters that the operand stages of that step have been read. A barrier per operand stage
   // would be lapped: the issuers may run NBUF steps ahead of the drain, and a waiter that misses two phases waits for ever.
-  if (threadIdx.x == 0) XNQ_CT(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int D = p.raw_stages; // raw slots per converter warp
   const int KT = p.nsteps;
@@ -856,7 +847,6 @@ __global__ void __launch_bounds__(F_NTHREADS, 1) imma_q4k_fold_kernel(const __gr
         for (unsigned long long o = o0; o < o1; o += PF_CHUNK) bulk_prefetch_l2(p.pf_base[st] + o, (uint32_t)min((unsigned long long)PF_CHUNK, o1 - o));
       }
       pdl_wait();
-      XNQ_CT(1);
       int kt = kt0;
       RingPos rp{0, 0};
       for (int i = 0; i < nunits; i++) {
@@ -1033,7 +1023,6 @@ __global__ void __launch_bounds__(F_NTHREADS, 1) imma_q4k_fold_kernel(const __gr
         }
         __syncwarp();
         if (alive && lane == 0) mbar_arrive(side_empty + 8 * rp.idx);
-        if (i == 0 && et == 0) XNQ_CT(2);
       }
       // ---- end of a segment (the tile's last step, or this CTA's last unit): store or hand over the sums ----
       const bool tile_end = kt == KT - 1, range_end = i == nunits - 1;
@@ -1112,7 +1101,6 @@ __global__ void __launch_bounds__(F_NTHREADS, 1) imma_q4k_fold_kernel(const __gr
 
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) XNQ_CT(3);
   if (warp == F_MMA_WARP0) tmem_dealloc(tmem_d, TMEM_COLS);
 }
 
@@ -1123,14 +1111,8 @@ template <int ACT, typename XT>
 __global__ void __launch_bounds__(256) imma_prepare(const XT *__restrict__ x, const int8_t *__restrict__ img_q, const float *__restrict__ img_d,
                                                     const int16_t *__restrict__ img_b, int64_t m, int64_t k, int64_t ldx, int NP, int nsteps,
                                                     uint8_t *__restrict__ bimg, uint8_t *__restrict__ meta, unsigned int *__restrict__ tile_cnt, int tiles) {
-#ifdef XNQ_DEV_TRACE
-  if (g_dev_prep_trig == 0) pdl_launch_dependents();
-  pdl_wait();
-  if (g_dev_prep_trig == 1) pdl_launch_dependents();
-#else
   pdl_launch_dependents(); // the matmul kernel may start its set-up and its weight loads now
   pdl_wait();              // x may be the previous kernel's output; the scratch may still be read by the previous call
-#endif
   XNQ_GT(24);
   const int row = blockIdx.x;
   if (blockIdx.x == 0 && blockIdx.y == 0)
@@ -1234,10 +1216,6 @@ int launch_np(const ImmaArgs &a, int NP, unsigned grid, cudaStream_t s) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-#ifdef XNQ_DEV_TRACE
-  static const int dev_pdl_main = [] { const char *e = getenv("XNQ_PDL_MAIN"); return e ? atoi(e) : 1; }();
-  cfg.numAttrs = dev_pdl_main ? 1 : 0;
-#endif
   if (NP == 16) XNQ_CUDA(cudaLaunchKernelEx(&cfg, imma_kernel<Conv, Drain, 16>, a));
   else if (NP == 32) XNQ_CUDA(cudaLaunchKernelEx(&cfg, imma_kernel<Conv, Drain, 32>, a));
   else XNQ_CUDA(cudaLaunchKernelEx(&cfg, imma_kernel<Conv, Drain, 64>, a));
@@ -1299,20 +1277,6 @@ int launch_imma(const WeightView &w, const void *x, int x_dtype, int64_t m, int6
 #define XNQ_IMMA_PREP(ACT, XT)                                                                                                          \
   XNQ_CUDA(launch_pdl(imma_prepare<ACT, XT>, dim3((unsigned)pl.NP, (unsigned)std::min<int64_t>(16, (k + 2047) / 2048)), dim3(256), 0, s,     \
                       iq ? nullptr : static_cast<const XT *>(x) + r0 * ldx, iq, id, ib, rows, k, ldx, pl.NP, pl.nsteps, bimg, meta, cnt, pl.tiles))
-#ifdef XNQ_DEV_TRACE
-    static const int dev_skip = [] { const char *e = getenv("XNQ_IMMA_SKIP"); return e ? atoi(e) : 0; }();
-    static const int dev_pdl_main = [] { const char *e = getenv("XNQ_PDL_MAIN"); return e ? atoi(e) : 1; }();
-    static const int dev_trig = [] {
-      const char *e = getenv("XNQ_PREP_TRIG");
-      const int v = e ? atoi(e) : 0;
-      cudaMemcpyToSymbol(g_dev_prep_trig, &v, sizeof(int));
-      return v;
-    }();
-    (void)dev_trig;
-    if (dev_skip != 1) {
-#else
-    {
-#endif
     if (act == XNQ_Q8_0) {
       if (x_dtype == XNQ_F16) XNQ_IMMA_PREP(XNQ_Q8_0, __half);
       else if (x_dtype == XNQ_BF16) XNQ_IMMA_PREP(XNQ_Q8_0, __nv_bfloat16);
@@ -1322,9 +1286,8 @@ int launch_imma(const WeightView &w, const void *x, int x_dtype, int64_t m, int6
       else if (x_dtype == XNQ_BF16) XNQ_IMMA_PREP(XNQ_Q8K, __nv_bfloat16);
       else XNQ_IMMA_PREP(XNQ_Q8K, float);
     }
-      count_launch();
-    }
 #undef XNQ_IMMA_PREP
+    count_launch();
 
     ImmaArgs a{};
     a.w = w;
@@ -1368,9 +1331,6 @@ int launch_imma(const WeightView &w, const void *x, int x_dtype, int64_t m, int6
         a.pf_share[st] = ((a.pf_bytes[st] / (unsigned)pl.grid) + PF_CHUNK - 1) & ~(unsigned long long)(PF_CHUNK - 1);
       }
     }
-#ifdef XNQ_DEV_TRACE
-    if (dev_skip == 2) continue;
-#endif
     if (fold) {
       a.b_stage_bytes = (uint32_t)pl.NP * 256;
       a.side_stage_bytes = HDR_BYTES + (uint32_t)pl.NP * 32;
@@ -1391,9 +1351,6 @@ int launch_imma(const WeightView &w, const void *x, int x_dtype, int64_t m, int6
       attr[0].val.programmaticStreamSerializationAllowed = 1;
       cfg.attrs = attr;
       cfg.numAttrs = 1;
-#ifdef XNQ_DEV_TRACE
-      cfg.numAttrs = dev_pdl_main ? 1 : 0;
-#endif
       profile_mark(s, true);
       if (pl.NP == 16) XNQ_CUDA(cudaLaunchKernelEx(&cfg, imma_q4k_fold_kernel<16>, a));
       else XNQ_CUDA(cudaLaunchKernelEx(&cfg, imma_q4k_fold_kernel<32>, a));
@@ -1452,7 +1409,6 @@ int imma_init(int device) {
 }
 
 #ifdef XNQ_DEV_TRACE
-extern "C" int xnq_dev_cta_times(long long *out) { return cudaMemcpyFromSymbol(out, g_cta_times, sizeof(long long) * 640) == cudaSuccess ? 0 : -6; }
 extern "C" int xnq_dev_imma_trace(long long *out) { return cudaMemcpyFromSymbol(out, g_imma_trace, sizeof(long long) * 32) == cudaSuccess ? 0 : -6; }
 extern "C" int xnq_dev_imma_timeline(long long *out) { return cudaMemcpyFromSymbol(out, g_imma_tl, sizeof(long long) * 8 * 64) == cudaSuccess ? 0 : -6; }
 #endif
