@@ -484,6 +484,13 @@ struct RowLoad {
       }
     }
   }
+  // returns once the loads of issue() have arrived (a use of every load's result)
+  __device__ __forceinline__ void landed() const {
+    float s = 0.f;
+#pragma unroll
+    for (int p = 0; p < PASSES; p++) s += v[p][0] + v[p][4];
+    asm volatile("" ::"f"(s) : "memory");
+  }
   template <int ACT>
   __device__ __forceinline__ void finish(int64_t k, int8_t *sq, float *sd, int16_t *sb) const {
     const int lane = threadIdx.x & 31;
@@ -629,6 +636,7 @@ matvec_ring_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtyp
   const int nblk = (int)(k / act_blk);
   float *sd = reinterpret_cast<float *>(sq + ((k + 127) & ~(int64_t)127)); // the swizzle permutes chunks inside aligned groups of eight
   int16_t *sb = reinterpret_cast<int16_t *>(reinterpret_cast<unsigned char *>(sd) + ((nblk * 4 + 15) & ~15));
+  bool told = false; // whether the producer has been told that the activations are here
   if (x_dtype == XNQ_ACT_IMAGE) {
     // activations quantized ahead of the call: copy the row's image (codes | block scales | 16-sums, each
     // section 256-byte aligned), swizzling the code chunks on the way
@@ -702,9 +710,12 @@ matvec_ring_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtyp
   } else {
     RowLoad xr;
     xr.issue(x, x_dtype, k);
+    xr.landed();
+    asm volatile("bar.arrive 14, %0;" ::"n"(NTHREADS) : "memory"); // the row is here: the rest of the ring may be requested while it is quantized
+    told = true;
     xr.template finish<ACT>(k, sq, sd, sb);
   }
-  asm volatile("bar.arrive 14, %0;" ::"n"(NTHREADS) : "memory"); // the producer may request the rest of the ring
+  if (!told) asm volatile("bar.arrive 14, %0;" ::"n"(NTHREADS) : "memory"); // the producer may request the rest of the ring
   consumer_sync();
   XNQ_TRACE_POINT(2);
   LaneT st;
