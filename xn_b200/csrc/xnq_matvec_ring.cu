@@ -693,6 +693,9 @@ matvec_ring_kernel(WeightView w, const void *x, int x_dtype, void *y, int y_dtyp
 #pragma unroll
       for (int e = 0; e < 8; e++) xr.v[0][e] = 0.f, gw[e] = 0.f;
     }
+    xr.landed(); // the row and its summands are here: the rest of the ring may be requested while the norm is computed
+    asm volatile("bar.arrive 14, %0;" ::"n"(NTHREADS) : "memory");
+    told = true;
     float *red = reinterpret_cast<float *>(smem + ring.part_off); // free until the first stage is multiplied
     const int np = (int)((k + 255) / 256);
     if (warp < np) {
