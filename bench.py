@@ -50,6 +50,7 @@ WORKLOADS = {
     # prefill (m > 16): the tensor-core kernel; roofline is reported against the dense bf16/fp16 tensor peak
     "C2_q8_0_11008x4096_m128": (D.Q8_0, 11008, 4096, 128),
     "C2_q8_0_11008x4096_m512": (D.Q8_0, 11008, 4096, 512),
+    "C3_q4k_14336x4096_m32": (D.Q4K, 14336, 4096, 32),   # the folded-scale variant of the integer tensor-core kernel (17..32 rows)
     "C3_q4k_14336x4096_m64": (D.Q4K, 14336, 4096, 64),
     "C3_q4k_14336x4096_m512": (D.Q4K, 14336, 4096, 512),
 }
