@@ -125,6 +125,19 @@ def test_guard_words_after_output_are_untouched(Q, O):
     assert_close_ref(out.cpu().numpy(), O.matmul(int(dt), x, w, n), TOL_F32)
 
 
+@pytest.mark.parametrize("m", [2, 5, 8, 9, 13, 16])
+@pytest.mark.parametrize("n,k", [(70, 256), (130, 4096), (67, 11008), (40, 14336)])
+def test_q6k_small_batch_dp4a_shapes(Q, O, m, n, k):
+    """Q6_K batches of 2..16 rows stay on the dp4a kernel: from 8 rows on it walks the activation rows once for both weight
+    rows of a warp and reads their codes from a swizzled shared-memory image; long rows run in passes of fewer activation
+    rows. Ragged row counts, one to 56 super-blocks per row."""
+    dt = D.Q6K
+    w = synth.make_weight(dt, n, k, seed=300 + m)
+    x = _tricky(m, k, 300 + m)
+    got = _upload(Q, dt, w, n, k).matmul_t(torch.from_numpy(x).to(DEV)).cpu().numpy()
+    assert_close_ref(got, O.matmul(int(dt), x, w, n), TOL_F32, f"Q6K m={m} n={n} k={k}")
+
+
 @pytest.mark.parametrize("dt", WEIGHT_TYPES)
 def test_half_precision_io(Q, O, dt):
     n, k, m = 96, 1024, 4
