@@ -263,6 +263,14 @@ int xnq_comm_free(xnq_comm *c);
  * image (act_dtype XNQ_Q8_0 or XNQ_Q8K) of the normalized rows: exactly what quantizing `out` would give. */
 int xnq_add_rmsnorm(float *x, const float *delta, int delta_parts, const float *weight, float eps, float *out,
                     void *act_image, int act_dtype, int64_t rows, int64_t d, void *stream);
+/* The two ends of a decode step (llama.rs:300-320, the embedding lookup and the greedy choice of the next token).
+ * xnq_embed_rows: x[rows, d] (f32) = table[tokens[r], :] of a bf16 table [vocab, d]; a token outside the table gives zeros
+ * and sets status bit 26. It is launched as a plain kernel, never programmatically overlapped: as the first kernel of a
+ * step it separates the step from the stores of the step before (xnq_rope_attn_decode relies on that).
+ * xnq_argmax_advance: tokens[r] = index of the first largest value of logits[r, 0:n] (torch.argmax's rule; a row without
+ * any finite candidate gives 0), then *pos += 1 if pos is not NULL. */
+int xnq_embed_rows(const void *table_bf16, const long long *tokens, float *x, int64_t rows, int64_t d, int64_t vocab, void *stream);
+int xnq_argmax_advance(const float *logits, int64_t rows, int64_t n, long long *tokens, long long *pos, void *stream);
 /* out[rows, f] = silu(gate_up[rows, 0:f]) * gate_up[rows, f:2f]; out / act_image as above. */
 int xnq_swiglu(const float *gate_up, float *out, void *act_image, int act_dtype, int64_t rows, int64_t f, void *stream);
 /* One new token per sequence: qkv[batch, (heads + 2 kv_heads) * head_dim] -> rotate-half RoPE at
@@ -299,7 +307,7 @@ int xnq_rope_attn_decode(const float *qkv, const float *cos_table, const float *
  * self-check refused an access. Bits 8-15: the same for the fp16 tensor-core kernel. Bits 16-23, integer
  * tensor-core kernel: a wait of the producer (16), a converter (17), the MMA issuer (18), a drain warp (19)
  * expired. Bits 24-25: a decode position outside [0, max_seq) reached xnq_rope_kv_store (24) or
- * xnq_attn_decode (25). Synchronizes the device.
+ * xnq_attn_decode (25); bit 26: xnq_embed_rows met a token outside the table. Synchronizes the device.
  * No counterpart in the reference (its kernels never wait on anything). */
 int xnq_device_status(unsigned int *bits);
 /* When bit 2 of the status is set, a kernel's self-check refused an out-of-range copy or store

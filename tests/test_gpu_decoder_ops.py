@@ -45,6 +45,29 @@ def test_swiglu():
         torch.testing.assert_close(out, F.silu(gu[:, :f]) * gu[:, f:], rtol=1e-5, atol=1e-6)
 
 
+def test_embedding_rows_and_greedy_choice():
+    from xn_b200 import decoder_ops as ops
+    torch.manual_seed(3)
+    table = (torch.randn(1000, 512, device=DEV) * 0.02).to(torch.bfloat16)
+    for rows in (1, 16):
+        tokens = torch.randint(0, 1000, (rows,), device=DEV)
+        out = torch.full((rows, 512), float("nan"), device=DEV)
+        ops.embed_rows(table, tokens, out)
+        assert torch.equal(out, table.index_select(0, tokens).float())
+    for rows, n in [(1, 32000), (16, 32000), (3, 7), (2, 128256)]:
+        logits = torch.randn(rows, n, device=DEV)
+        logits[0, n // 3] = logits[0, n - 1] = 9.0          # equal maxima: the first one wins
+        if rows > 1:
+            logits[1, :] = -1.5                               # a constant row: index 0
+        tokens = torch.full((rows,), -7, device=DEV, dtype=torch.int64)
+        pos = torch.tensor([41], device=DEV, dtype=torch.int64)
+        ops.argmax_advance(logits, tokens, pos)
+        assert torch.equal(tokens, logits.argmax(-1)), (rows, n)
+        assert int(pos.item()) == 42
+        ops.argmax_advance(logits, tokens, None)
+        assert int(pos.item()) == 42
+
+
 def _rope_ref(x, cos, sin):
     x1, x2 = x[..., :64], x[..., 64:]
     return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], -1)

@@ -73,6 +73,8 @@ def lib() -> ctypes.CDLL:
     fp = ctypes.c_float
     L.xnq_add_rmsnorm.argtypes = [vp, vp, ci, vp, fp, vp, vp, ci, i64, i64, vp]
     L.xnq_swiglu.argtypes = [vp, vp, vp, ci, i64, i64, vp]
+    L.xnq_embed_rows.argtypes = [vp, vp, vp, i64, i64, i64, vp]
+    L.xnq_argmax_advance.argtypes = [vp, i64, i64, vp, vp, vp]
     L.xnq_rope_kv_store.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, ci, ci, ci, i64, vp]
     L.xnq_attn_decode_workspace_bytes.argtypes = [i64, ci]
     L.xnq_attn_decode_workspace_bytes.restype = sz

@@ -177,7 +177,62 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const float *gu, float *out
   if (ACT != 0) quantize_store8<ACT>(v, valid, row_image(image, rows, f, ACT == XNQ_Q8_0 ? QK : QK_K, r), c8, threadIdx.x & 31);
 }
 
-__device__ unsigned int g_decoder_status; // sticky: 1 rope/store, 2 attention saw a position outside [0, max_seq)
+// x[row, :] = table[tokens[row], :] widened to f32 (bf16 table). One CTA per row, 8 elements per thread and pass. A token outside
+// [0, vocab) gives a row of zeros and sets status bit 4. Launched as a plain (not programmatically dependent) kernel: it is the
+// step's first kernel, and everything behind it may rely on the previous step's stores (position, tokens, cache rows) being complete.
+__global__ void __launch_bounds__(256) embed_rows_kernel(const __nv_bfloat16 *table, const long long *tokens, float *x, int d, long long vocab);
+
+// tokens[row] = index of the first largest logit of the row (torch.argmax's rule), then *pos += 1 (one thread). One CTA per row.
+__global__ void __launch_bounds__(256) argmax_advance_kernel(const float *logits, long long n, long long *tokens, long long *pos);
+
+__device__ unsigned int g_decoder_status; // sticky: 1 rope/store, 2 attention saw a position outside [0, max_seq), 4 an embedding token outside the table
+
+__global__ void __launch_bounds__(256) embed_rows_kernel(const __nv_bfloat16 *table, const long long *tokens, float *x, int d, long long vocab) {
+  const long long tok = tokens[blockIdx.x];
+  const bool ok = tok >= 0 && tok < vocab;
+  if (!ok && threadIdx.x == 0) atomicOr(&g_decoder_status, 4u);
+  const __nv_bfloat16 *src = table + (ok ? tok : 0) * (long long)d;
+  float *dst = x + (long long)blockIdx.x * d;
+  for (int i = threadIdx.x * 8; i < d; i += 256 * 8) {
+    float v[8];
+    if (ok) load8(src + i, v);
+    else {
+#pragma unroll
+      for (int e = 0; e < 8; e++) v[e] = 0.f;
+    }
+    *reinterpret_cast<float4 *>(dst + i) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4 *>(dst + i + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+}
+
+__global__ void __launch_bounds__(256) argmax_advance_kernel(const float *logits, long long n, long long *tokens, long long *pos) {
+  __shared__ float s_v[8];
+  __shared__ long long s_i[8];
+  pdl_launch_dependents();
+  pdl_wait(); // the logits are the previous kernel's output
+  const float *row = logits + (long long)blockIdx.x * n;
+  float best = -INFINITY;
+  long long bi = n; // no candidate yet
+  for (long long i = threadIdx.x; i < n; i += 256) {
+    const float v = row[i];
+    if (v > best || (v == best && i < bi)) best = v, bi = i;
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+    const long long oi = __shfl_xor_sync(0xffffffffu, bi, off);
+    if (ov > best || (ov == best && oi < bi)) best = ov, bi = oi;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) s_v[warp] = best, s_i[warp] = bi;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; w++)
+      if (s_v[w] > best || (s_v[w] == best && s_i[w] < bi)) best = s_v[w], bi = s_i[w];
+    tokens[blockIdx.x] = bi < n ? bi : 0; // a row of -inf / NaN only: token 0
+    if (blockIdx.x == 0 && pos) *pos += 1;
+  }
+}
 
 // Rotate-half RoPE of the pair (x1 = element i, x2 = element i + hd / 2) with every operation rounded separately, so that the
 // stand-alone kernel and the attention kernel that rotates in its prologue produce the same bits.
@@ -488,6 +543,28 @@ int xnq_rope_kv_store(const float *qkv, const float *cos_table, const float *sin
   if (batch == 0) return XNQ_OK;
   XNQ_CUDA(launch_pdl(rope_store_kernel, dim3(heads + 2 * kv_heads, (unsigned)batch), dim3(head_dim / 2), 0, static_cast<cudaStream_t>(stream), qkv, cos_table,
                       sin_table, pos_dev, q_out, static_cast<__nv_bfloat16 *>(k_cache), static_cast<__nv_bfloat16 *>(v_cache), heads, kv_heads, head_dim, (int)max_seq));
+  count_launch();
+  return XNQ_OK;
+}
+
+int xnq_embed_rows(const void *table_bf16, const long long *tokens, float *x, int64_t rows, int64_t d, int64_t vocab, void *stream) {
+  clear_error();
+  if (!table_bf16 || !tokens || !x) return fail(XNQ_ERR_NULL, "embed_rows: NULL argument");
+  if (rows < 0 || d <= 0 || d % 8 || vocab < 1) return fail(XNQ_ERR_SHAPE, "embed_rows: rows = %lld, d = %lld (a multiple of 8), vocab = %lld", (long long)rows, (long long)d, (long long)vocab);
+  if (((uintptr_t)table_bf16 | (uintptr_t)x) & 15) return fail(XNQ_ERR_ALIGN, "embed_rows: pointers must be 16-byte aligned");
+  if (rows == 0) return XNQ_OK;
+  embed_rows_kernel<<<dim3((unsigned)rows), dim3(256), 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16 *>(table_bf16), tokens, x, (int)d, (long long)vocab);
+  XNQ_CUDA(cudaGetLastError());
+  count_launch();
+  return XNQ_OK;
+}
+
+int xnq_argmax_advance(const float *logits, int64_t rows, int64_t n, long long *tokens, long long *pos, void *stream) {
+  clear_error();
+  if (!logits || !tokens) return fail(XNQ_ERR_NULL, "argmax_advance: NULL argument");
+  if (rows < 0 || n < 1) return fail(XNQ_ERR_SHAPE, "argmax_advance: rows = %lld, n = %lld", (long long)rows, (long long)n);
+  if (rows == 0) return XNQ_OK;
+  XNQ_CUDA(launch_pdl(argmax_advance_kernel, dim3((unsigned)rows), dim3(256), 0, static_cast<cudaStream_t>(stream), logits, (long long)n, tokens, pos));
   count_launch();
   return XNQ_OK;
 }

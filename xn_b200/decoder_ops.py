@@ -87,6 +87,33 @@ def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, image: Opt
     return out
 
 
+def embed_rows(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[r, :] = table[tokens[r], :]`` widened to f32 (bf16 table ``[vocab, d]``, int64 tokens): the embedding lookup of a
+    decode step as one plain launch (xnq_embed_rows)."""
+    if table.dtype is not torch.bfloat16 or tokens.dtype is not torch.int64 or out.dtype is not torch.float32:
+        raise ValueError("embed_rows: bf16 table, int64 tokens, f32 output")
+    if not (table.is_contiguous() and tokens.is_contiguous() and out.is_contiguous()):
+        raise ValueError("embed_rows: contiguous tensors")
+    rows, d = tokens.numel(), table.shape[1]
+    if out.numel() != rows * d:
+        raise ValueError("embed_rows: output shape")
+    with torch.cuda.device(table.device):
+        _lib.check(_lib.lib().xnq_embed_rows(_p(table), _p(tokens), _p(out), rows, d, table.shape[0], _stream_ptr(table.device)))
+    return out
+
+
+def argmax_advance(logits: torch.Tensor, tokens: torch.Tensor, pos: Optional[torch.Tensor]) -> None:
+    """``tokens[r] = argmax(logits[r])`` (first of equal maxima), then ``pos += 1``: the greedy choice and the position advance of
+    a decode step in one launch (xnq_argmax_advance)."""
+    if logits.dtype is not torch.float32 or not logits.is_contiguous() or tokens.dtype is not torch.int64 or (pos is not None and pos.dtype is not torch.int64):
+        raise ValueError("argmax_advance: f32 contiguous logits, int64 tokens and position")
+    rows, n = logits.shape
+    if tokens.numel() != rows:
+        raise ValueError("argmax_advance: one token per row")
+    with torch.cuda.device(logits.device):
+        _lib.check(_lib.lib().xnq_argmax_advance(_p(logits), rows, n, _p(tokens), _p(pos), _stream_ptr(logits.device)))
+
+
 def rope_kv_store(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor,
                   v_cache: torch.Tensor, heads: int, kv_heads: int) -> None:
     """One token per sequence: rotate q and k at ``pos`` (int64 device scalar), write q to ``q_out [B, heads, hd]``

@@ -254,7 +254,7 @@ class QLlama:
         """One token per sequence (self.tokens at position self.pos) -> logits [B, vocab], fused operators."""
         c = self.cfg
         self._gather_idx = 0
-        self._x.copy_(self.embed.index_select(0, self.tokens))
+        ops.embed_rows(self.embed, self.tokens, self._x)   # one plain launch: the step's barrier against the step before
         delta = None
         xi, hi = self._xn_img, self._h_img
         # one row: every linear's kernel is told which weight comes next, and asks for it to be brought into L2 as it finishes
@@ -313,8 +313,11 @@ class QLlama:
     @torch.no_grad()
     def _decode_step(self) -> None:
         logits = self._forward_decode() if self.fused_decode else self._forward(self.tokens.view(-1, 1), self.pos)
-        self.tokens.copy_(logits.argmax(-1))
-        self.pos.add_(1)
+        if self.fused_decode and logits.dtype is torch.float32 and logits.is_contiguous():
+            ops.argmax_advance(logits, self.tokens, self.pos)   # greedy choice and position advance in one launch
+        else:
+            self.tokens.copy_(logits.argmax(-1))
+            self.pos.add_(1)
         self.last_logits = logits
 
     @torch.no_grad()
