@@ -119,6 +119,15 @@ int xnq_weight_canonical_bytes(const xnq_weight *w, void *host_dst, size_t nbyte
  * quantizer produces, so results are identical. act_dtype is XNQ_Q8_0 for Q4_0 / Q8_0 weights and XNQ_Q8K
  * for Q4_K / Q6_K weights. The image must be 256-byte aligned. */
 #define XNQ_ACT_IMAGE 100
+/* A second form for batches of 2..64 rows on Q4_K weights: the rows quantized to Q8_K (the same codes, scales and sums) in the
+ * layout the integer tensor-core kernel reads, so that xnq_matmul_t(.., x_dtype = XNQ_ACT_OPERAND, ..) is ONE kernel (with
+ * float rows or an XNQ_ACT_IMAGE it launches a kernel of its own first that quantizes / re-lays the activations). Written by
+ * xnq_add_rmsnorm and xnq_swiglu with act_dtype = XNQ_ACT_OPERAND. xnq_act_operand_bytes(m, k): size (k a multiple of 256,
+ * m <= 64; 0 otherwise). The buffer is 256-byte aligned, belongs to one (m, k), and must be zeroed once after allocation
+ * (rows m.. of the padded batch and the ticket words are never written by a producer). Results are bit for bit those of the
+ * other input forms. One matmul at a time may read an image (its ticket words are in the image). */
+#define XNQ_ACT_OPERAND 101
+size_t xnq_act_operand_bytes(int64_t m, int64_t k);
 size_t xnq_act_image_bytes(int act_dtype, int64_t m, int64_t k);
 int xnq_quantize_act_image(int act_dtype, const void *x, int x_dtype, int64_t m, int64_t k, int64_t ldx,
                            void *image, void *stream);

@@ -174,6 +174,36 @@ def test_attention_workspace_reuse_and_position_range():
     assert st.value == 0
 
 
+@pytest.mark.parametrize("m", [2, 7, 16, 17, 32, 33, 64])
+def test_operand_images_give_the_bits_of_the_other_input_forms(m):
+    """add_rmsnorm / swiglu writing the integer tensor-core kernel's operand layout (XNQ_ACT_OPERAND): the matmul on it, one
+    kernel, must equal bit for bit the matmul on float rows; an image may feed several matmuls in turn (the ticket words of
+    split tiles are put back by the kernel that used them)."""
+    from xn_b200 import decoder_ops as ops, quantized as Q, synth
+    from xn_b200.dtypes import GgmlDType as D
+    Q.init(DEV)
+    torch.manual_seed(31 + m)
+    for n, k in [(300, 256), (6144, 4096), (520, 11008)]:
+        w = Q.QCudaTensor.from_qtensor(Q.QTensor(synth.make_weight(D.Q4K, n, k, seed=90), (n, k), D.Q4K), DEV)
+        w2 = Q.QCudaTensor.from_qtensor(Q.QTensor(synth.make_weight(D.Q4K, 130, k, seed=91), (130, k), D.Q4K), DEV)
+        x = torch.randn(m, k, device=DEV) * 2; g = torch.rand(k, device=DEV) + 0.5
+        x[0, :40] = 0.0
+        xn = torch.empty(m, k, device=DEV)
+        img = ops.OperandImage(m, k, DEV)
+        ops.add_rmsnorm(x.clone(), None, g, 1e-5, xn, img)
+        want = w.matmul_t(xn)
+        for rep in range(2):   # the second use finds the tickets as the first one left them
+            got = w.matmul_t(img)
+            assert torch.equal(got, want), ("norm", m, n, k, rep, float((got - want).abs().max()))
+        assert torch.equal(w2.matmul_t(img), w2.matmul_t(xn)), ("norm, second weight", m, k)
+        gu = torch.randn(m, 2 * k, device=DEV) * 2
+        h = torch.empty(m, k, device=DEV)
+        ops.swiglu(gu, h, img)   # the same image object, rewritten
+        want = w.matmul_t(h)
+        got = w.matmul_t(img)
+        assert torch.equal(got, want), ("swiglu", m, n, k, float((got - want).abs().max()))
+
+
 def test_activation_images_equal_the_in_call_quantizer():
     """An image written by the stand-alone quantizer, by add_rmsnorm or by swiglu holds the bytes the matmul's own
     quantizer would produce from the same f32 rows, so matmul results through an image are bit-identical."""

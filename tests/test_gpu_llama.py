@@ -98,6 +98,24 @@ def test_norm_in_the_matvec_prologue_is_bit_identical_to_the_separate_kernels():
     assert torch.equal(outs[0][1], outs[1][1])
 
 
+def test_operand_images_in_the_batched_decoder_are_bit_identical(monkeypatch):
+    """Batches above one on Q4_K linears: the norm and the SwiGLU write the integer kernel's operand layout and each linear is
+    one kernel; tokens and logits equal those of the planar images."""
+    from xn_b200.llama import LlamaConfig, QLlama
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device="cpu"); g.manual_seed(14)
+    prompt = torch.randint(0, 512, (4, 9), generator=g).to(dev)
+    outs = []
+    for flag in ("1", "0"):
+        monkeypatch.setenv("XN_OPERAND_IMAGES", flag)
+        m = QLlama(LlamaConfig.tiny(), dev, batch=4, max_seq=64, max_prefill_rows=64)
+        m.prefill(prompt)
+        toks = m.decode(10)
+        outs.append((toks.clone(), m.last_logits.clone()))
+    assert torch.equal(outs[0][0], outs[1][0])
+    assert torch.equal(outs[0][1], outs[1][1])
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

@@ -9,6 +9,7 @@ LIB_PATH = os.path.join(HERE, os.environ.get("XNQ_LIB_NAME", "libxnq.so"))
 
 XNQ_OK = 0
 XNQ_ACT_IMAGE = 100  # x_dtype of an activation image (activations quantized ahead of the matmul)
+XNQ_ACT_OPERAND = 101  # the same, in the integer tensor-core kernel's operand layout (2..64 rows, Q8_K activations)
 STATUS_NAMES = {0: "XNQ_OK", -1: "XNQ_ERR_NULL", -2: "XNQ_ERR_DTYPE", -3: "XNQ_ERR_SHAPE", -4: "XNQ_ERR_ALIGN",
                 -5: "XNQ_ERR_SIZE", -6: "XNQ_ERR_CUDA", -7: "XNQ_ERR_COMM", -8: "XNQ_ERR_UNSUPPORTED"}
 
@@ -72,6 +73,8 @@ def lib() -> ctypes.CDLL:
     L.xnq_comm_free.argtypes = [vp]
     fp = ctypes.c_float
     L.xnq_add_rmsnorm.argtypes = [vp, vp, ci, vp, fp, vp, vp, ci, i64, i64, vp]
+    L.xnq_act_operand_bytes.argtypes = [i64, i64]
+    L.xnq_act_operand_bytes.restype = sz
     L.xnq_swiglu.argtypes = [vp, vp, vp, ci, i64, i64, vp]
     L.xnq_embed_rows.argtypes = [vp, vp, vp, i64, i64, i64, vp]
     L.xnq_argmax_advance.argtypes = [vp, i64, i64, vp, vp, vp]

@@ -119,6 +119,24 @@ using namespace xnq;
 
 // xnq_matmul_t on activations that were quantized ahead of the call (x_dtype == XNQ_ACT_IMAGE): the decode
 // kernels read the image directly; nothing is quantized and no scratch is used.
+// activations in the integer tensor-core kernel's own layout (XNQ_ACT_OPERAND): one kernel
+static int matmul_from_operand(const xnq_weight *w, const void *image, int64_t m, void *y, int y_dtype, int64_t ldy, void *workspace, size_t ws_bytes,
+                               cudaStream_t s) {
+  const int64_t k = w->v.k, n = w->v.n;
+  if (!is_float_dtype(y_dtype)) return fail(XNQ_ERR_DTYPE, "matmul_t: output dtype %d is not f32/f16/bf16", y_dtype);
+  if (ldy < n) return fail(XNQ_ERR_SHAPE, "matmul_t: ldy = %lld is smaller than n = %lld", (long long)ldy, (long long)n);
+  if (m == 0 || n == 0) return XNQ_OK;
+  if (!image || !y) return fail(XNQ_ERR_NULL, "matmul_t: image or y is NULL");
+  if (!aligned(image, 256)) return fail(XNQ_ERR_ALIGN, "matmul_t: the operand image must be 256-byte aligned");
+  if (!aligned(y, type_size(y_dtype))) return fail(XNQ_ERR_ALIGN, "matmul_t: y is not aligned to its element size");
+  if (act_dtype_for(w->v.dtype) != XNQ_Q8K || !is_fast_dtype(w->v.dtype) || !use_imma(w, m))
+    return fail(XNQ_ERR_UNSUPPORTED, "matmul_t: an operand image serves 2..%lld rows on weights of the integer tensor-core kernel with Q8_K activations (dtype %d, m = %lld)",
+                (long long)IMMA_MAX_M, w->v.dtype, (long long)m);
+  if (!workspace || !aligned(workspace, 256) || ws_bytes < imma_workspace_bytes(m, k, n))
+    return fail(XNQ_ERR_SIZE, "matmul_t: the workspace (256-byte aligned, %zu bytes) is needed for the partial sums", imma_workspace_bytes(m, k, n));
+  return launch_imma(w->v, image, XNQ_ACT_OPERAND, m, k, y, y_dtype, ldy, workspace, s);
+}
+
 static int matmul_from_image(const xnq_weight *w, const void *image, int64_t m, void *y, int y_dtype, int64_t ldy, void *workspace, size_t ws_bytes,
                              cudaStream_t s) {
   const int64_t k = w->v.k, n = w->v.n;
@@ -464,6 +482,11 @@ int xnq_quantize_act(int act_dtype, const void *x, int x_dtype, int64_t m, int64
   return launch_quantize_act_blocks(act_dtype, x, x_dtype, m, k, ldx, dst, static_cast<cudaStream_t>(stream));
 }
 
+size_t xnq_act_operand_bytes(int64_t m, int64_t k) {
+  if (m <= 0 || m > IMMA_MAX_M || k <= 0 || k % 256) return 0;
+  return operand_image_bytes(m, k);
+}
+
 size_t xnq_act_image_bytes(int act_dtype, int64_t m, int64_t k) {
   if ((act_dtype != XNQ_Q8_0 && act_dtype != XNQ_Q8K) || m <= 0 || k <= 0) return 0;
   return act_workspace_bytes(m, k, act_dtype);
@@ -543,6 +566,7 @@ int xnq_matmul_t(const xnq_weight *w, const void *x, int x_dtype, int64_t m, int
   if (!w) return fail(XNQ_ERR_NULL, "matmul_t: weight is NULL");
   const int64_t k = w->v.k, n = w->v.n;
   if (x_dtype == XNQ_ACT_IMAGE && is_generic_dtype(w->v.dtype)) return fail(XNQ_ERR_UNSUPPORTED, "matmul_t: dtype %d takes float activations only (no activation image)", w->v.dtype);
+  if (x_dtype == XNQ_ACT_OPERAND) return matmul_from_operand(w, x, m, y, y_dtype, ldy, workspace, ws_bytes, static_cast<cudaStream_t>(stream));
   if (x_dtype == XNQ_ACT_IMAGE) return matmul_from_image(w, x, m, y, y_dtype, ldy, workspace, ws_bytes, static_cast<cudaStream_t>(stream));
   int rc = check_activations("matmul_t", x, x_dtype, m, k, ldx);
   if (rc != XNQ_OK) return rc;

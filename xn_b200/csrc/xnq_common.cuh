@@ -329,6 +329,16 @@ void imma_set_fold(int mode); // Q4_K kernel with the sub-block scales folded in
 int imma_status(unsigned int *bits);
 int decoder_ops_init();
 int decoder_status(unsigned int *bits); // 1 rope/store, 2 attention: a position outside [0, max_seq)
+// Activation OPERAND image (XNQ_ACT_OPERAND): up to 64 rows quantized to Q8_K and laid out as the integer tensor-core kernel reads them,
+// so that a producer (add+RMSNorm, SwiGLU) can write them directly and the matmul needs no activation kernel of its own:
+//   [4096 bytes]              1024 ticket words of split tiles (zero between matmuls: the kernel puts each word back)
+//   [k/256][2][NP x 128]      codes of each 128-k half step, rows 128 bytes apart, 16-byte chunks swizzled with the row (NP = 16 / 32 / 64)
+//   [k/256][NP][32]           per step and row: the eight 32-sums as low-7-bit and high bytes (16 bytes), the f32 block scale, 12 bytes of zero
+constexpr size_t OPERAND_TICKET_BYTES = 4096;
+constexpr int OPERAND_MAX_TILES = 1024;
+__host__ __device__ inline int operand_np(int64_t m) { return m <= 16 ? 16 : (m <= 32 ? 32 : 64); }
+__host__ __device__ inline size_t operand_bimg_bytes(int np, int64_t k) { return (size_t)(k / 256) * np * 256; }
+__host__ __device__ inline size_t operand_image_bytes(int64_t m, int64_t k) { return OPERAND_TICKET_BYTES + (size_t)(k / 256) * operand_np(m) * 288; }
 constexpr int64_t IMMA_MAX_M = 64; // batches up to here take the integer tensor-core kernel; larger ones the fp16 one
 
 // xnq_prefill.cu  (m > 64, and Q6_K above 16 rows: tcgen05 / TMEM contraction on fp16 operands)

@@ -53,6 +53,46 @@ __device__ __forceinline__ void quantize_store8(const float (&v)[8], bool valid,
   if ((lane & 1) == 0) img.bsum[c8 / 2] = (int16_t)q.sum16;
 }
 
+// The same 8 values into an OPERAND image (the integer tensor-core kernel's layout, xnq_common.cuh): k8 = index of the lane's first
+// element in the row (a warp holds one 256-element block, lane = (k8 / 8) % 32).
+constexpr int ACT_OPERAND = XNQ_ACT_OPERAND;
+__device__ __forceinline__ void quantize_store8_operand(const float (&v)[8], bool valid, void *image, int64_t rows, int64_t k, int64_t row, int64_t k8, int lane) {
+  const Quant8 q = quantize8_q8k(v, lane);
+  const int sum16 = q.sum16;
+  const int s32 = sum16 + __shfl_xor_sync(0xffffffffu, sum16, 2); // lanes 4 s .. 4 s + 3 hold sub-block s; sum16 is a lane pair's sum on both lanes
+  const int sub = lane >> 2;
+  uint32_t lo_b = (lane & 3) == 0 ? ((uint32_t)(s32 & 127) << (8 * (sub & 3))) : 0u;
+  uint32_t hi_b = (lane & 3) == 0 ? ((uint32_t)((s32 >> 7) & 0xff) << (8 * (sub & 3))) : 0u;
+#pragma unroll
+  for (int off = 4; off <= 8; off <<= 1) {
+    lo_b |= __shfl_xor_sync(0xffffffffu, lo_b, off);
+    hi_b |= __shfl_xor_sync(0xffffffffu, hi_b, off);
+  }
+  if (!valid) return;
+  const int NP = operand_np(rows);
+  uint8_t *bimg = static_cast<uint8_t *>(image) + OPERAND_TICKET_BYTES;
+  uint8_t *meta = bimg + operand_bimg_bytes(NP, k);
+  const int64_t hs = k8 >> 7;
+  const int chunk = (int)((k8 & 127) >> 4);
+  uint8_t *dst = bimg + (size_t)hs * (NP * 128) + (size_t)(row >> 3) * 1024 + (size_t)(row & 7) * 128 + (size_t)((chunk ^ (int)(row & 7)) << 4) + (k8 & 8);
+  *reinterpret_cast<uint2 *>(dst) = make_uint2(q.lo, q.hi);
+  uint32_t *rec = reinterpret_cast<uint32_t *>(meta + ((size_t)(k8 >> 8) * NP + row) * 32);
+  if (lane == 0 || lane == 16) {
+    rec[(lane >> 4) * 2] = lo_b;
+    rec[(lane >> 4) * 2 + 1] = hi_b;
+  }
+  if (lane == 0) {
+    rec[4] = __float_as_uint(q.d);
+    rec[5] = rec[6] = rec[7] = 0u;
+  }
+}
+// the ticket words of an OPERAND image are put back to zero by the kernel that used them; a producer zeroes them as well, so that a
+// matmul that gave up half way cannot spoil the next one
+__device__ __forceinline__ void operand_clear_tickets(void *image) {
+  unsigned int *t = static_cast<unsigned int *>(image);
+  for (int i = threadIdx.x; i < OPERAND_MAX_TILES; i += blockDim.x) t[i] = 0u;
+}
+
 // x[row] += sum_p delta[row][p] (if delta), out[row] = x[row] * rsqrt(mean(x^2) + eps) * w, and optionally the
 // quantized image of out[row]. One CTA of 256 threads per row, 8 consecutive elements per thread per pass.
 template <int ACT>
@@ -117,7 +157,8 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(float *x, const float 
   for (int i = 0; i < min(np, MAXP); i++) tot += part[i];
   const float r = rms_scale(tot, d, eps);
   RowImage img{};
-  if (ACT != 0) img = row_image(image, rows, d, ACT == XNQ_Q8_0 ? QK : QK_K, row);
+  if (ACT != 0 && ACT != ACT_OPERAND) img = row_image(image, rows, d, ACT == XNQ_Q8_0 ? QK : QK_K, row);
+  if (ACT == ACT_OPERAND && row == 0) operand_clear_tickets(image);
   auto second_pass = [&](int base, float (&v)[8], const float (&g)[8], bool loaded) { // whole warps stay together for the quantizer's shuffles
     const int i = base + threadIdx.x * 8;
     const bool valid = i < d;
@@ -137,7 +178,8 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(float *x, const float 
 #pragma unroll
       for (int e = 0; e < 8; e++) v[e] = 0.f;
     }
-    if (ACT != 0) quantize_store8<ACT>(v, valid, img, i / 8, lane);
+    if (ACT == ACT_OPERAND) quantize_store8_operand(v, valid, image, rows, d, row, i, lane);
+    else if (ACT != 0) quantize_store8<ACT == ACT_OPERAND ? XNQ_Q8K : ACT>(v, valid, img, i / 8, lane);
   };
 #pragma unroll
   for (int p = 0; p < KEEP; p++)
@@ -174,7 +216,12 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const float *gu, float *out
 #pragma unroll
     for (int e = 0; e < 8; e++) v[e] = 0.f;
   }
-  if (ACT != 0) quantize_store8<ACT>(v, valid, row_image(image, rows, f, ACT == XNQ_Q8_0 ? QK : QK_K, r), c8, threadIdx.x & 31);
+  if (ACT == ACT_OPERAND) {
+    if (blockIdx.x == 0) operand_clear_tickets(image);
+    quantize_store8_operand(v, valid, image, rows, f, r, c8 * 8, threadIdx.x & 31);
+  } else if (ACT != 0) {
+    quantize_store8<ACT == ACT_OPERAND ? XNQ_Q8K : ACT>(v, valid, row_image(image, rows, f, ACT == XNQ_Q8_0 ? QK : QK_K, r), c8, threadIdx.x & 31);
+  }
 }
 
 // x[row, :] = table[tokens[row], :] widened to f32 (bf16 table). One CTA per row, 8 elements per thread and pass. A token outside
@@ -490,7 +537,8 @@ extern "C" {
 
 static int check_image(const char *who, const void *image, int act_dtype, int64_t k) {
   if (!image) return XNQ_OK;
-  if (act_dtype != XNQ_Q8_0 && act_dtype != XNQ_Q8K) return fail(XNQ_ERR_DTYPE, "%s: %d is not an activation block format (Q8_0=8, Q8K=15)", who, act_dtype);
+  if (act_dtype != XNQ_Q8_0 && act_dtype != XNQ_Q8K && act_dtype != XNQ_ACT_OPERAND)
+    return fail(XNQ_ERR_DTYPE, "%s: %d is not an activation block format (Q8_0=8, Q8K=15) nor XNQ_ACT_OPERAND", who, act_dtype);
   const int blk = act_dtype == XNQ_Q8_0 ? QK : QK_K;
   if (k % blk) return fail(XNQ_ERR_SHAPE, "%s: row length %lld is not a multiple of the %d-value block", who, (long long)k, blk);
   if (reinterpret_cast<uintptr_t>(image) & 255) return fail(XNQ_ERR_ALIGN, "%s: the activation image must be 256-byte aligned", who);
@@ -510,7 +558,10 @@ int xnq_add_rmsnorm(float *x, const float *delta, int delta_parts, const float *
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const dim3 grid((unsigned)rows), block(256);
   if (!act_image) XNQ_CUDA(launch_pdl(add_rmsnorm_kernel<0>, grid, block, 0, s, x, delta, delta_parts, weight, eps, out, nullptr, rows, (int)d));
-  else if (act_dtype == XNQ_Q8_0) XNQ_CUDA(launch_pdl(add_rmsnorm_kernel<XNQ_Q8_0>, grid, block, 0, s, x, delta, delta_parts, weight, eps, out, act_image, rows, (int)d));
+  else if (act_dtype == XNQ_ACT_OPERAND) {
+    if (rows > IMMA_MAX_M) return fail(XNQ_ERR_SIZE, "add_rmsnorm: an operand image holds at most %lld rows", (long long)IMMA_MAX_M);
+    XNQ_CUDA(launch_pdl(add_rmsnorm_kernel<ACT_OPERAND>, grid, block, 0, s, x, delta, delta_parts, weight, eps, out, act_image, rows, (int)d));
+  } else if (act_dtype == XNQ_Q8_0) XNQ_CUDA(launch_pdl(add_rmsnorm_kernel<XNQ_Q8_0>, grid, block, 0, s, x, delta, delta_parts, weight, eps, out, act_image, rows, (int)d));
   else XNQ_CUDA(launch_pdl(add_rmsnorm_kernel<XNQ_Q8K>, grid, block, 0, s, x, delta, delta_parts, weight, eps, out, act_image, rows, (int)d));
   count_launch();
   return XNQ_OK;
@@ -528,7 +579,10 @@ int xnq_swiglu(const float *gate_up, float *out, void *act_image, int act_dtype,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const unsigned grid = (unsigned)((rows * f / 8 + 255) / 256);
   if (!act_image) XNQ_CUDA(launch_pdl(swiglu_kernel<0>, dim3(grid), dim3(256), 0, s, gate_up, out, nullptr, rows, (int)f));
-  else if (act_dtype == XNQ_Q8_0) XNQ_CUDA(launch_pdl(swiglu_kernel<XNQ_Q8_0>, dim3(grid), dim3(256), 0, s, gate_up, out, act_image, rows, (int)f));
+  else if (act_dtype == XNQ_ACT_OPERAND) {
+    if (rows > IMMA_MAX_M) return fail(XNQ_ERR_SIZE, "swiglu: an operand image holds at most %lld rows", (long long)IMMA_MAX_M);
+    XNQ_CUDA(launch_pdl(swiglu_kernel<ACT_OPERAND>, dim3(grid), dim3(256), 0, s, gate_up, out, act_image, rows, (int)f));
+  } else if (act_dtype == XNQ_Q8_0) XNQ_CUDA(launch_pdl(swiglu_kernel<XNQ_Q8_0>, dim3(grid), dim3(256), 0, s, gate_up, out, act_image, rows, (int)f));
   else XNQ_CUDA(launch_pdl(swiglu_kernel<XNQ_Q8K>, dim3(grid), dim3(256), 0, s, gate_up, out, act_image, rows, (int)f));
   count_launch();
   return XNQ_OK;

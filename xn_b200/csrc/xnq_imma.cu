@@ -698,6 +698,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) imma_kernel(const __grid_constant
           asm volatile("bar.sync 1, %0;" ::"n"(2 * DWG * 32) : "memory"); // s_ticket may be rewritten from here on
           const int t_u0 = tile * KT, t_u1 = t_u0 + KT;
           const int c_first = cta_of(t_u0, p.units_q, p.units_r), c_last = cta_of(t_u1 - 1, p.units_q, p.units_r);
+          if (et == 0 && (int)ticket == c_last - c_first) p.tile_cnt[tile] = 0u; // every part has its ticket: the word is zero again for the next call
           if (h == 0 && (int)ticket == c_last - c_first) { // the last part to arrive adds all parts in k order
             __threadfence();
             float (&sum)[NPT] = acc; // the segment's own sums are in its scratch slot by now
@@ -1067,6 +1068,7 @@ __global__ void __launch_bounds__(F_NTHREADS, 1) imma_q4k_fold_kernel(const __gr
           asm volatile("bar.sync 1, %0;" ::"n"(F_DRAIN_WARPS * 32) : "memory");
           const int t_u0 = tile * KT, t_u1 = t_u0 + KT;
           const int c_first = cta_of(t_u0, p.units_q, p.units_r), c_last = cta_of(t_u1 - 1, p.units_q, p.units_r);
+          if (et == 0 && (int)ticket == c_last - c_first) p.tile_cnt[tile] = 0u; // every part has its ticket: the word is zero again for the next call
           if (dg == 0 && (int)ticket == c_last - c_first) { // the last part to arrive adds all parts in k order
             __threadfence();
 #pragma unroll
@@ -1255,8 +1257,10 @@ int launch_imma(const WeightView &w, const void *x, int x_dtype, int64_t m, int6
   // Q4_K: sub-block scales folded into the weight operand. Measured on the 14336 x 4096 weight: as fast as the per-block
   // kernel up to 16 rows, 8 % faster for 17..32, slower beyond (it runs in passes of 32 rows), so by default it takes 17..32.
   const int fold_opt = g_fold.load(std::memory_order_relaxed);
-  const bool fold = w.dtype == XNQ_Q4K && (fold_opt == 2 || (fold_opt == 1 && m > 16 && m <= 32));
+  const bool fold = w.dtype == XNQ_Q4K && (fold_opt == 2 || (fold_opt == 1 && m > 16 && m <= 32)) && !(x_dtype == XNQ_ACT_OPERAND && m > 32); // an operand image is one pass
   const int64_t pass_rows = fold ? 32 : MAX_NP;
+  const bool operand = x_dtype == XNQ_ACT_OPERAND; // the activations arrive in the kernel's own layout, with their ticket words: no activation kernel
+  if (operand && (act != XNQ_Q8K || k % 256 || m > pass_rows)) return fail(XNQ_ERR_UNSUPPORTED, "imma: an operand image serves Q8_K activations of one pass (m = %lld)", (long long)m);
   for (int64_t r0 = 0; r0 < m; r0 += pass_rows) { // passes of at most 64 (32) activation rows
     const int64_t rows = std::min<int64_t>(pass_rows, m - r0);
     const Plan pl = plan_for(rows, k, w.n);
@@ -1264,7 +1268,14 @@ int launch_imma(const WeightView &w, const void *x, int x_dtype, int64_t m, int6
     uint8_t *bimg = ws;
     uint8_t *meta = bimg + pl.bimg_bytes;
     unsigned int *cnt = reinterpret_cast<unsigned int *>(meta + pl.meta_bytes);
-    float *partials = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(cnt) + pl.cnt_bytes);
+    float *partials = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(cnt) + pl.cnt_bytes); // always in the caller's workspace
+    if (operand) {
+      if (pl.tiles > OPERAND_MAX_TILES) return fail(XNQ_ERR_SIZE, "imma: an operand image has ticket words for %d tiles of 128 rows, the weight has %d", OPERAND_MAX_TILES, pl.tiles);
+      uint8_t *img = static_cast<uint8_t *>(const_cast<void *>(x));
+      cnt = reinterpret_cast<unsigned int *>(img);
+      bimg = img + OPERAND_TICKET_BYTES;
+      meta = bimg + operand_bimg_bytes(pl.NP, k);
+    }
     // ---- activations ----
     const int8_t *iq = nullptr;
     const float *id = nullptr;
@@ -1277,7 +1288,9 @@ int launch_imma(const WeightView &w, const void *x, int x_dtype, int64_t m, int6
 #define XNQ_IMMA_PREP(ACT, XT)                                                                                                          \
   XNQ_CUDA(launch_pdl(imma_prepare<ACT, XT>, dim3((unsigned)pl.NP, (unsigned)std::min<int64_t>(16, (k + 2047) / 2048)), dim3(256), 0, s,     \
                       iq ? nullptr : static_cast<const XT *>(x) + r0 * ldx, iq, id, ib, rows, k, ldx, pl.NP, pl.nsteps, bimg, meta, cnt, pl.tiles))
-    if (act == XNQ_Q8_0) {
+    if (operand) {
+      // nothing to prepare
+    } else if (act == XNQ_Q8_0) {
       if (x_dtype == XNQ_F16) XNQ_IMMA_PREP(XNQ_Q8_0, __half);
       else if (x_dtype == XNQ_BF16) XNQ_IMMA_PREP(XNQ_Q8_0, __nv_bfloat16);
       else XNQ_IMMA_PREP(XNQ_Q8_0, float);
@@ -1287,7 +1300,7 @@ int launch_imma(const WeightView &w, const void *x, int x_dtype, int64_t m, int6
       else XNQ_IMMA_PREP(XNQ_Q8K, float);
     }
 #undef XNQ_IMMA_PREP
-    count_launch();
+    if (!operand) count_launch();
 
     ImmaArgs a{};
     a.w = w;

@@ -33,6 +33,24 @@ class ActImage:
         return self.buf.data_ptr()
 
 
+class OperandImage:
+    """Up to 64 activation rows quantized to Q8_K in the layout the integer tensor-core kernel reads (``XNQ_ACT_OPERAND``), with
+    the ticket words of its split tiles: written by ``add_rmsnorm`` / ``swiglu``, read by ``QCudaTensor.matmul_t`` on Q4_K weights,
+    which then is one kernel. Zeroed at creation (the padded rows and the tickets are never written by a producer); belongs to one
+    ``(m, k)``; one matmul at a time may read it."""
+    operand = True
+
+    def __init__(self, m: int, k: int, device: torch.device):
+        self.act_dtype, self.m, self.k, self.device = GgmlDType.Q8K, m, k, device
+        nbytes = int(_lib.lib().xnq_act_operand_bytes(m, k))
+        if nbytes == 0:
+            raise ValueError(f"no operand image for [{m}, {k}] (1..64 rows, k a multiple of 256)")
+        self.buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+
+    def data_ptr(self) -> int:
+        return self.buf.data_ptr()
+
+
 def quantize_act_image(x: torch.Tensor, image: ActImage) -> ActImage:
     """Quantize ``x [m, k]`` (f32 / f16 / bf16, contiguous rows) into ``image``."""
     from .quantized import _TORCH_TO_XNQ
@@ -50,7 +68,7 @@ def _img(image: Optional[ActImage], rows: int, k: int):
         return None, 0
     if (image.m, image.k) != (rows, k):
         raise ValueError(f"image is [{image.m}, {image.k}], rows are [{rows}, {k}]")
-    return ctypes.c_void_p(image.data_ptr()), int(image.act_dtype)
+    return ctypes.c_void_p(image.data_ptr()), (_lib.XNQ_ACT_OPERAND if getattr(image, "operand", False) else int(image.act_dtype))
 
 
 def _p(t: Optional[torch.Tensor]):

@@ -156,9 +156,20 @@ class QLlama:
         # its prologue, hidden behind its weight prefetch, and is better left alone.
         def wants_image(k):
             return batch <= 16 and k % 256 == 0 and (batch > 1 or k > 4096)
-        self._xn_img = ops.ActImage.for_weight(c.linear_dtype, batch, c.d_model, device) if wants_image(c.d_model) else None
-        self._h_img = ops.ActImage.for_weight(c.linear_dtype, batch, c.ffn // G, device) if wants_image(c.ffn // G) else None
-        self._head_img = self._xn_img if c.head_dtype.vec_dot_type == c.linear_dtype.vec_dot_type else None
+        # Batches of 2..64 rows on Q4_K linears: the images are written in the integer tensor-core kernel's own layout, and each such
+        # linear is one kernel instead of two (XN_OPERAND_IMAGES=0/1 for measurements).
+        env = os.environ.get("XN_OPERAND_IMAGES")
+        operand = (env == "1" if env in ("0", "1") else True) and 2 <= batch <= 64 and c.linear_dtype == GgmlDType.Q4K and world == 1
+        def image(k):
+            if operand and k % 256 == 0:
+                return ops.OperandImage(batch, k, device)
+            return ops.ActImage.for_weight(c.linear_dtype, batch, k, device) if wants_image(k) else None
+        self._xn_img = image(c.d_model)
+        self._h_img = image(c.ffn // G)
+        if isinstance(self._xn_img, ops.OperandImage):   # the LM head is not an integer tensor-core weight: it keeps a planar image, or float rows
+            self._head_img = ops.ActImage.for_weight(c.head_dtype, batch, c.d_model, device) if wants_image(c.d_model) else None
+        else:
+            self._head_img = self._xn_img if c.head_dtype.vec_dot_type == c.linear_dtype.vec_dot_type else None
 
         for L in self.layers:   # scratch is sized once, before any capture
             for w in (L.wqkv, L.wo, L.wgu, L.wdown):

@@ -236,7 +236,8 @@ class QCudaTensor:
             y = out.view(-1, self.n)
             ws = self.workspace(lhs.m) if lhs.m > 1 else None   # batches go to the tensor-core kernel, which re-lays the image out in scratch
             with torch.cuda.device(self.device):
-                check(_lib.lib().xnq_matmul_t(self._h, ctypes.c_void_p(lhs.data_ptr()), _lib.XNQ_ACT_IMAGE, lhs.m, 0, ctypes.c_void_p(y.data_ptr()),
+                check(_lib.lib().xnq_matmul_t(self._h, ctypes.c_void_p(lhs.data_ptr()), _lib.XNQ_ACT_OPERAND if getattr(lhs, "operand", False) else _lib.XNQ_ACT_IMAGE,
+                                              lhs.m, 0, ctypes.c_void_p(y.data_ptr()),
                                               int(_TORCH_TO_XNQ[y.dtype]), y.stride(0) if lhs.m > 1 else self.n,
                                               ctypes.c_void_p(ws.data_ptr()) if ws is not None else None, ws.numel() if ws is not None else 0,
                                               _stream_ptr(self.device)))
