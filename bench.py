@@ -258,8 +258,8 @@ def _graph_us(torch, dev, fn, calls: int, reps: int) -> float:
 EXTRA_MATMULS = [
     ("C1_q4_0_4096x4096", D.Q4_0, 4096, 4096, (1,)),
     ("C2_q8_0_11008x4096", D.Q8_0, 11008, 4096, (1, 16, 128, 512)),
-    ("C3_q4k_14336x4096", D.Q4K, 14336, 4096, (4, 16, 64, 512)),
-    ("C4_q6k_128256x4096", D.Q6K, 128256, 4096, (1, 32)),
+    ("C3_q4k_14336x4096", D.Q4K, 14336, 4096, (4, 16, 32, 64, 512)),   # 32: the folded-scale variant of the integer kernel
+    ("C4_q6k_128256x4096", D.Q6K, 128256, 4096, (1, 16, 32)),          # 16: the dp4a small-batch kernel
 ]
 
 
