@@ -46,6 +46,17 @@ def _upload(dtype, buf, nbytes, n, k, rank=0, count=1):
     return rc, _lib.lib().xnq_last_error().decode()
 
 
+def test_operand_image_geometry():
+    """XNQ_ACT_OPERAND images: 4096 bytes of ticket words, then per 256-k step NP rows of 256 code bytes and NP records of
+    32 bytes, NP = 16 / 32 / 64 for up to 16 / 32 / 64 rows; nothing for shapes the integer kernel does not serve."""
+    L = _lib.lib()
+    for m, np_ in [(1, 16), (2, 16), (16, 16), (17, 32), (32, 32), (33, 64), (64, 64)]:
+        for k in (256, 4096, 11008, 14336):
+            assert L.xnq_act_operand_bytes(m, k) == 4096 + (k // 256) * np_ * 288, (m, k)
+    for m, k in [(0, 4096), (65, 4096), (16, 4100), (16, 0), (-1, 256)]:
+        assert L.xnq_act_operand_bytes(m, k) == 0, (m, k)
+
+
 def test_upload_validation_happens_before_cuda():
     buf = np.zeros(4 * 18, np.uint8)
     p = ctypes.c_void_p(buf.ctypes.data)
